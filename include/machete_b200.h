@@ -1,0 +1,268 @@
+/*
+ * machete_b200 — C ABI of the B200 (sm_100a) decode megakernel library.
+ *
+ * The library is the native replacement for the device side of the
+ * reference's `Megakernel` runtime (src/machete/megakernel/megakernel.py:285
+ * `class Megakernel`, `.compile()` :1594, `.run()` :2183) and of the CuTe-DSL
+ * op bodies it JIT-compiles.  Host code (Python via ctypes, or any C caller)
+ * describes a decode step as a *program*: a table of op records, a per-CTA
+ * instruction list, dependency-counter wait tables and op-entry events.  One
+ * persistent kernel (one CTA per SM) executes the whole program per launch.
+ *
+ * Ownership: the caller owns every buffer.  `mk_create` copies the program
+ * tables into a caller-provided device workspace; no entry point allocates or
+ * frees device memory.
+ *
+ * Error model: every function returns 0 on success, a negative value for a
+ * host-side error (bad argument, unsupported shape, CUDA error) with a
+ * message available from `mk_last_error()`, and `mk_status` reports
+ * device-side conditions (bounded waits that expired) after the caller has
+ * synchronised the stream.
+ */
+#ifndef MACHETE_B200_H_
+#define MACHETE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_ABI_VERSION 3
+
+/* ---- opcodes ------------------------------------------------------------ */
+enum {
+  MK_OP_NOP = 0,
+  /* y = epilogue(W · prologue(x)); replaces GemmOp (kernels/gemm/gemm.py:290)
+   * at S<=32 rows and the decode matvec family
+   * (kernels/decode_matvec/sm100.py:224-654, sm120.py NVFP4 variants). */
+  MK_OP_MATVEC = 1,
+  /* split-KV decode attention; replaces FlashDecodingSplitBSHDOp
+   * (kernels/attention/flash_decoding.py:1175). */
+  MK_OP_ATTN_SPLIT = 2,
+  /* log-sum-exp combine; replaces FlashDecodingCombineBSHDOp (:1858). */
+  MK_OP_ATTN_COMBINE = 3,
+  /* RMSNormOp forward (kernels/rms_norm/rms_norm.py:162). */
+  MK_OP_RMSNORM = 4,
+  /* RopeOp forward (kernels/rope/rope.py:41). */
+  MK_OP_ROPE = 5,
+  /* QKNormRopeOp forward (kernels/qknorm_rope/qknorm_rope.py:47). */
+  MK_OP_QKNORM_ROPE = 6,
+  /* GLUOp / DirectGLUOp forward (kernels/glu/glu.py:316, :567). */
+  MK_OP_GLU = 7,
+  /* AddOp / ResidualAddSm100Op (kernels/activation/add.py:11,
+   * kernels/decode_matvec/sm100.py:441). */
+  MK_OP_ADD = 8,
+  /* top-1 finalise: unpack per-row (max, argmax) keys; replaces
+   * Llama1BReduceTop1PartialsSm120Op (kernels/llama1b/sm120.py:3464). */
+  MK_OP_TOP1_FINAL = 9,
+  /* one-shot all-reduce over peer-mapped inboxes (tensor parallel); replaces
+   * GemmRowParallelOp's peer reduce-store (kernels/gemm/gemm.py:1290). */
+  MK_OP_ALLREDUCE = 10,
+  MK_OP__COUNT
+};
+
+/* matvec row-mapping modes (mk_op_t.i[MK_MV_MODE]) */
+enum { MK_MV_PLAIN = 0, MK_MV_PAIR = 1, MK_MV_ROPE = 2 };
+/* matvec prologues */
+enum { MK_PRO_NONE = 0, MK_PRO_RMS = 1, MK_PRO_ADD_RMS = 2 };
+/* matvec epilogues */
+enum { MK_EPI_STORE = 0, MK_EPI_RESIDUAL = 1, MK_EPI_TOP1 = 2 };
+/* matvec transforms applied to the accumulators before the epilogue */
+enum { MK_TR_NONE = 0, MK_TR_ROPE = 1, MK_TR_SILU_MUL = 2, MK_TR_RELU = 3, MK_TR_SILU = 4 };
+/* weight formats */
+enum {
+  MK_W_BF16 = 0,
+  MK_W_FP16 = 1,
+  /* e2m1 pairs per byte (low nibble first) + fp16 scale per 32 values:
+   * the reference's format (quantization/nvfp4.py:3-9). */
+  MK_W_NVFP4_F16S32 = 2,
+  /* e2m1 + e4m3 scale per 16 values + one fp32 global scale. */
+  MK_W_NVFP4_E4M3S16 = 3
+};
+/* element types of activations / outputs */
+enum { MK_T_BF16 = 0, MK_T_FP16 = 1, MK_T_FP32 = 2 };
+
+/* Indices into mk_op_t.i / .f / .p / .s for MK_OP_MATVEC. */
+enum {
+  MK_MV_O = 0, MK_MV_K, MK_MV_M, MK_MV_S, MK_MV_MODE, MK_MV_PRO, MK_MV_EPI,
+  MK_MV_TR, MK_MV_HD, MK_MV_D2, MK_MV_POS, MK_MV_WFMT, MK_MV_KC, MK_MV_OUT_T,
+  MK_MV_X_T, MK_MV_ROWS_PER_UNIT
+};
+enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1 };
+enum {
+  MK_MV_P_W0 = 0, MK_MV_P_W1, MK_MV_P_X, MK_MV_P_RES_IN, MK_MV_P_NORM_W,
+  MK_MV_P_RES_OUT, MK_MV_P_OUT, MK_MV_P_EPI_RES, MK_MV_P_COS, MK_MV_P_SIN,
+  MK_MV_P_SC0, MK_MV_P_SC1
+};
+enum {
+  MK_MV_S_WROW = 0,   /* weight row stride, bytes                         */
+  MK_MV_S_X_B, MK_MV_S_X_S,           /* x strides, elements              */
+  MK_MV_S_RI_B, MK_MV_S_RI_S,         /* residual_in (prologue)           */
+  MK_MV_S_RO_B, MK_MV_S_RO_S,         /* residual_out (prologue)          */
+  MK_MV_S_O_B, MK_MV_S_O_S, MK_MV_S_O_H, /* output (b, s, head) strides   */
+  MK_MV_S_ER_B, MK_MV_S_ER_S,         /* epilogue residual                */
+  MK_MV_S_COS,                        /* cos/sin row stride               */
+  MK_MV_S_SCROW                       /* scale row stride, bytes          */
+};
+
+/* MK_OP_ATTN_SPLIT / MK_OP_ATTN_COMBINE */
+enum {
+  MK_AT_B = 0, MK_AT_M, MK_AT_H, MK_AT_HKV, MK_AT_D, MK_AT_N, MK_AT_SPLITS,
+  MK_AT_CAUSAL, MK_AT_MT, MK_AT_TS /* tokens per split */, MK_AT_O_T
+};
+enum { MK_AT_F_SCALE = 0 };
+enum { MK_AT_P_Q = 0, MK_AT_P_K, MK_AT_P_V, MK_AT_P_OPART, MK_AT_P_LSEPART, MK_AT_P_O, MK_AT_P_LSE };
+enum {
+  MK_AT_S_Q_B = 0, MK_AT_S_Q_M, MK_AT_S_Q_H,
+  MK_AT_S_K_B, MK_AT_S_K_N, MK_AT_S_K_H,
+  MK_AT_S_V_B, MK_AT_S_V_N, MK_AT_S_V_H,
+  MK_AT_S_O_B, MK_AT_S_O_M, MK_AT_S_O_H
+};
+
+/* elementwise ops (RMSNORM, ROPE, QKNORM_ROPE, GLU, ADD): generic slots */
+enum {
+  MK_EW_ROWS = 0, MK_EW_D, MK_EW_S, MK_EW_H, MK_EW_D2, MK_EW_FLAGS, MK_EW_ACT,
+  MK_EW_T, MK_EW_ROWS_PER_UNIT
+};
+enum { MK_EW_F_EPS = 0 };
+enum { MK_EW_P_X = 0, MK_EW_P_Y, MK_EW_P_W, MK_EW_P_RES_IN, MK_EW_P_RES_OUT, MK_EW_P_GATE, MK_EW_P_COS, MK_EW_P_SIN };
+enum { MK_EW_S_X = 0, MK_EW_S_Y, MK_EW_S_W, MK_EW_S_RI, MK_EW_S_RO, MK_EW_S_G, MK_EW_S_COS, MK_EW_S_X_H };
+/* MK_EW_FLAGS bits */
+enum { MK_EWF_RESIDUAL = 1, MK_EWF_GEMMA = 2, MK_EWF_FUSED_ADD = 4, MK_EWF_GATED = 8, MK_EWF_ROW_WEIGHT = 16 };
+
+/* A device-visible op record.  Field meaning depends on `opcode`; see the
+ * index enums above.  The layout is fixed: 16 + 96 + 16 + 128 + 128 bytes. */
+typedef struct mk_op {
+  int32_t opcode;
+  int32_t n_units;        /* work units (one warp processes one unit)        */
+  int32_t act_key;        /* ops with equal non-zero key share staged input  */
+  int32_t reserved;
+  int32_t i[24];
+  float f[4];
+  uint64_t p[16];
+  int64_t s[16];
+} mk_op_t;
+
+/* One work unit assigned to one CTA (executed by one consumer warp). */
+typedef struct mk_instr {
+  int32_t op;             /* index into the op table                         */
+  int32_t unit;           /* unit index within the op                        */
+  int32_t signal;         /* counter incremented on completion, -1 = none    */
+  int32_t n_waits;        /* consumer-side waits (pairs in the wait table)   */
+  int32_t wait_off;
+  int32_t n_lwaits;       /* loader-side waits (before the unit's loads)     */
+  int32_t lwait_off;
+  int32_t n_pages;        /* ring pages the unit consumes                    */
+} mk_instr_t;
+
+/* Op-entry event: before a CTA executes instruction `pos` of its list, all
+ * of its consumer warps meet, wait for the listed counters and stage the
+ * op's activations into shared memory. */
+typedef struct mk_event {
+  int32_t pos;
+  int32_t op;
+  int32_t n_waits;
+  int32_t wait_off;
+  int32_t flags;          /* MK_EVF_* */
+  int32_t reserved[3];
+} mk_event_t;
+
+/* mk_event_t.flags: this CTA materialises residual_out = x + residual_in of
+ * the op's prologue in global memory (exactly one CTA per op does). */
+enum { MK_EVF_WRITE_RES_OUT = 1 };
+
+typedef struct mk_wait {
+  int32_t counter;
+  int32_t expected;       /* wait until counter >= expected                  */
+} mk_wait_t;
+
+/* Host-side program description handed to mk_create (all arrays in HOST
+ * memory; mk_create copies them into the device workspace). */
+typedef struct mk_program {
+  int32_t n_ops;
+  int32_t n_instrs;
+  int32_t n_events;
+  int32_t n_waits;
+  int32_t n_counters;
+  int32_t n_ctas;           /* persistent grid size                          */
+  int32_t page_bytes;       /* shared-memory page stride                     */
+  int32_t n_pages;          /* ring depth                                    */
+  int32_t act_bytes;        /* staged-activation buffer size                 */
+  int32_t timeout_ms;       /* bound of every device-side wait               */
+  int32_t device;           /* CUDA device ordinal                           */
+  int32_t flags;
+  const mk_op_t* ops;
+  const mk_instr_t* instrs;       /* grouped per CTA                         */
+  const int32_t* cta_instr_begin; /* n_ctas + 1 offsets into instrs          */
+  const mk_event_t* events;       /* grouped per CTA                         */
+  const int32_t* cta_event_begin; /* n_ctas + 1 offsets into events          */
+  const mk_wait_t* waits;
+  void* workspace;                /* DEVICE memory, >= mk_workspace_bytes()  */
+  uint64_t workspace_bytes;
+} mk_program_t;
+
+typedef struct mk_handle_s* mk_handle_t;
+
+/* ABI version of the loaded library (MK_ABI_VERSION). */
+int mk_abi_version(void);
+/* Thread-local message describing the last host-side error. */
+const char* mk_last_error(void);
+/* Multiprocessor count and opt-in shared memory per block of `device`;
+ * replaces the torch.cuda.get_device_properties queries in
+ * megakernel/megakernel.py:523-569. */
+int mk_device_info(int device, int32_t* num_sms, int32_t* smem_optin, int32_t* cc_major, int32_t* cc_minor);
+/* Device workspace needed for `prog` (tables + counters + status block). */
+uint64_t mk_workspace_bytes(const mk_program_t* prog);
+/* Validate `prog`, upload its tables into prog->workspace, return a handle.
+ * Replaces Megakernel.compile()'s metadata upload
+ * (megakernel/megakernel.py:709-962); there is no JIT. */
+int mk_create(const mk_program_t* prog, mk_handle_t* out);
+/* Launch the persistent kernel on `cuda_stream` (a cudaStream_t; NULL = the
+ * legacy default stream).  Asynchronous.  Counters are reset by the kernel
+ * itself, so back-to-back launches and CUDA-graph replay are legal.
+ * Replaces Megakernel.run() / launch_prepared (megakernel.py:2163-2204). */
+int mk_run(mk_handle_t h, void* cuda_stream);
+/* Copy the 16-word device status block to `out` (synchronises the device).
+ * out[0] == 0 means no device-side error. */
+int mk_status(mk_handle_t h, int32_t out[16]);
+/* Clear counters and status after a device-side error. */
+int mk_reset(mk_handle_t h, void* cuda_stream);
+/* Overwrite op record `op_index` (e.g. new cache position or pointers). */
+int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_stream);
+/* Read back the dependency counters (n_counters words) — after a completed
+ * run they are all zero; used by the tests' invariant checks. */
+int mk_read_counters(mk_handle_t h, int32_t* out, int32_t n);
+int mk_destroy(mk_handle_t h);
+
+/* ---- standalone single-op entry points ----------------------------------
+ * Each builds a one-op program in `workspace` (device memory, at least
+ * mk_standalone_workspace_bytes() bytes) and launches it on `cuda_stream`.
+ * They exist for profiling and for C callers that do not need a schedule. */
+uint64_t mk_standalone_workspace_bytes(void);
+
+/* y[M,O] = x[M,K] · W[O,K]^T, bf16 in/out, fp32 accumulate, M <= 32.
+ * Replaces MatvecSm100Op (kernels/decode_matvec/sm100.py:386) and GemmOp at
+ * decode sizes (kernels/gemm/gemm.py:290). */
+int mk_matvec_bf16(const void* w, const void* x, void* y, int32_t M, int32_t O, int32_t K,
+                   void* workspace, uint64_t workspace_bytes, void* cuda_stream);
+/* Same with NVFP4 weights: `packed` [O,K/2] bytes, `scales` [O,K/group],
+ * wfmt = MK_W_NVFP4_F16S32 or MK_W_NVFP4_E4M3S16.  Replaces
+ * MatvecNvfp4Sm120Op (kernels/decode_matvec/sm120.py:1058). */
+int mk_matvec_nvfp4(const void* packed, const void* scales, float global_scale, int32_t wfmt,
+                    const void* x, void* y, int32_t M, int32_t O, int32_t K,
+                    void* workspace, uint64_t workspace_bytes, void* cuda_stream);
+/* Split-KV flash decoding + combine on contiguous BSHD tensors
+ * q,o [B,M,H,D], k,v [B,N,Hkv,D] bf16; o_partial [B,H,splits,M,D] and
+ * lse_partial [B,H,splits,M] fp32 scratch, lse [B,H,M] fp32.  Replaces
+ * flash_decoding_schedule + run (kernels/attention/flash_decoding.py:1958). */
+int mk_flash_decode(const void* q, const void* k, const void* v, void* o, void* lse,
+                    void* o_partial, void* lse_partial,
+                    int32_t B, int32_t M, int32_t H, int32_t Hkv, int32_t D, int32_t N,
+                    int32_t splits, int32_t causal, float scale,
+                    void* workspace, uint64_t workspace_bytes, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MACHETE_B200_H_ */

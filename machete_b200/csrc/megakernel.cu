@@ -1,0 +1,581 @@
+// The persistent decode megakernel and its C ABI.
+//
+// One CTA per SM.  Warp 0 is the loader: it walks the CTA's instruction list
+// and streams every unit's pages (weights by untiled TMA, K/V rows by
+// cp.async) into a shared-memory ring, running as far ahead of the consumers
+// as the ring allows — weights carry no data dependency, so the HBM stream
+// continues across op boundaries while consumers wait on dependency counters.
+// Warps 1..8 are consumers: instruction j of the CTA belongs to consumer
+// j mod 8, which waits for its pages, computes and signals the unit's counter.
+// Op-entry events make all consumers of the CTA meet, wait for the op's
+// producers and stage its activations (RMSNorm fused) into shared memory.
+//
+// Counterpart of the reference's ring loop (megakernel/replay_loops.py:27-824)
+// and launch path (megakernel/megakernel.py:2163-2204).
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "op_attn.cuh"
+#include "op_elementwise.cuh"
+#include "op_matvec.cuh"
+
+namespace mk {
+
+// ---------------------------------------------------------------- device side
+__device__ __forceinline__ mk_instr_t bcast_instr(const mk_instr_t& mine, int src) {
+  mk_instr_t r;
+  r.op = __shfl_sync(0xffffffffu, mine.op, src);
+  r.unit = __shfl_sync(0xffffffffu, mine.unit, src);
+  r.signal = __shfl_sync(0xffffffffu, mine.signal, src);
+  r.n_waits = __shfl_sync(0xffffffffu, mine.n_waits, src);
+  r.wait_off = __shfl_sync(0xffffffffu, mine.wait_off, src);
+  r.n_lwaits = __shfl_sync(0xffffffffu, mine.n_lwaits, src);
+  r.lwait_off = __shfl_sync(0xffffffffu, mine.lwait_off, src);
+  r.n_pages = __shfl_sync(0xffffffffu, mine.n_pages, src);
+  return r;
+}
+
+__device__ __forceinline__ mk_instr_t load_instr(const mk_instr_t* p) {
+  const int4* q = reinterpret_cast<const int4*>(p);
+  const int4 a = q[0], b = q[1];
+  mk_instr_t r;
+  r.op = a.x; r.unit = a.y; r.signal = a.z; r.n_waits = a.w;
+  r.wait_off = b.x; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
+  return r;
+}
+
+__device__ void loader_loop(Ctx& c, int ibeg, int iend) {
+  const ProgramView& pv = *c.pv;
+  const int NP = pv.n_pages;
+  uint32_t seq = 0;
+  for (int base = ibeg; base < iend && !c.dead; base += 32) {
+    const int n = min(32, iend - base);
+    mk_instr_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (c.lane < n) mine = load_instr(pv.instrs + base + c.lane);
+    for (int i = 0; i < n && !c.dead; ++i) {
+      const mk_instr_t ins = bcast_instr(mine, i);
+      c.instr_idx = base + i;
+      if (ins.n_pages == 0) continue;
+      if (ins.n_lwaits > 0 && !wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
+      const mk_op_t* op = pv.ops + ins.op;
+      const int opcode = op->opcode;
+      for (int p = 0; p < ins.n_pages; ++p) {
+        const uint32_t slot = seq % NP;
+        const uint32_t par = ((seq / NP) & 1u) ^ 1u;
+        if (!wait_mbar(c, empty_bar(c, slot), par, MK_ST_TIMEOUT_PAGE_EMPTY, (int)seq)) break;
+        const uint32_t page = c.pages_u32 + slot * (uint32_t)pv.page_bytes;
+        const uint32_t bar = full_bar(c, slot);
+        if (opcode == MK_OP_MATVEC) {
+          mv_load_page(op, ins.unit, p, page, bar, c.lane);
+        } else if (opcode == MK_OP_ATTN_SPLIT) {
+          at_load_page(op, ins.unit, p, page, bar, c.lane, pv.page_bytes);
+        } else {
+          mbar_arrive(bar);  // an op without loads: hand over an empty page
+        }
+        ++seq;
+      }
+    }
+  }
+  // Every copy this warp issued must have landed before the CTA may exit.
+  // On the normal path the consumers already observed all of them; after an
+  // abandoned wait they may not have, so drain with a bounded wait.
+  if (c.dead) {
+    const uint32_t first = seq > (uint32_t)NP ? seq - NP : 0u;
+    for (uint32_t s = first; s < seq; ++s) {
+      const uint32_t bar = full_bar(c, s % NP);
+      const uint32_t par = (s / NP) & 1u;
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(bar, par)) {
+        if (globaltimer_ns() - t0 > pv.timeout_ns) break;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+  switch (op->opcode) {
+    case MK_OP_MATVEC: mv_dispatch(c, op, ins, seq); break;
+    case MK_OP_ATTN_SPLIT: at_dispatch(c, op, ins, seq); break;
+    case MK_OP_ATTN_COMBINE: at_combine_unit(c, op, ins); break;
+    case MK_OP_RMSNORM: ew_rmsnorm(c, op, ins.unit); break;
+    case MK_OP_ROPE: ew_rope(c, op, ins.unit); break;
+    case MK_OP_QKNORM_ROPE: ew_qknorm_rope(c, op, ins.unit); break;
+    case MK_OP_GLU: ew_glu(c, op, ins.unit); break;
+    case MK_OP_ADD: ew_add(c, op, ins.unit); break;
+    case MK_OP_TOP1_FINAL: ew_top1_final(c, op, ins.unit); break;
+    case MK_OP_NOP: break;
+    default:
+      if (c.lane == 0) report(c, MK_ST_BAD_OP, op->opcode, ins.op);
+      c.dead = true;
+      break;
+  }
+}
+
+__device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
+  const ProgramView& pv = *c.pv;
+  const int w = c.warp - 1;
+  constexpr int T = kConsumerWarps * 32;
+  uint32_t seq = 0;
+  int staged_key = 0;
+  int ev = ebeg;
+  mk_event_t cur;
+  cur.pos = 0x7fffffff;
+  if (ev < eend) cur = pv.events[ev];
+
+  auto do_event = [&]() {
+    // Every consumer warp runs this, dead or not: the barriers must balance.
+    named_bar_sync(kConsumerBarrier, T);
+    if (w == 0) wait_counters(c, cur.n_waits, cur.wait_off);
+    named_bar_sync(kConsumerBarrier, T);
+    const mk_op_t* op = pv.ops + cur.op;
+    if (op->opcode == MK_OP_MATVEC) {
+      const bool need = (op->act_key == 0) || (op->act_key != staged_key);
+      mv_stage(c, op, need, (cur.flags & MK_EVF_WRITE_RES_OUT) != 0);
+      staged_key = op->act_key;
+    }
+    named_bar_sync(kConsumerBarrier, T);
+    ++ev;
+    cur.pos = 0x7fffffff;
+    if (ev < eend) cur = pv.events[ev];
+  };
+
+  for (int base = ibeg; base < iend; base += 32) {
+    const int n = min(32, iend - base);
+    mk_instr_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (c.lane < n) mine = load_instr(pv.instrs + base + c.lane);
+    for (int i = 0; i < n; ++i) {
+      const int local = base + i - ibeg;
+      while (cur.pos <= local) do_event();
+      const mk_instr_t ins = bcast_instr(mine, i);
+      if ((local % kConsumerWarps) == w && !c.dead) {
+        c.instr_idx = base + i;
+        if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
+          run_unit(c, pv.ops + ins.op, ins, seq);
+          if (!c.dead) signal_unit(c, ins.signal);
+        }
+      }
+      seq += (uint32_t)ins.n_pages;
+    }
+  }
+  while (ev < eend) do_event();
+}
+
+__global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid_constant__ ProgramView pv) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Ctx c;
+  c.pv = &pv;
+  c.ctrl = reinterpret_cast<Ctrl*>(smem);
+  c.act = smem + kCtrlBytes;
+  c.pages = smem + kCtrlBytes + pv.act_bytes;
+  c.act_u32 = smem_u32(c.act);
+  c.pages_u32 = smem_u32(c.pages);
+  c.warp = threadIdx.x >> 5;
+  c.lane = threadIdx.x & 31;
+  c.instr_idx = -1;
+  c.dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < pv.n_pages; ++i) {
+      mbar_init(smem_u32(&c.ctrl->full[i]), 32);
+      mbar_init(smem_u32(&c.ctrl->empty[i]), 1);
+    }
+    c.ctrl->abort_flag = 0;
+    c.ctrl->is_last = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int ibeg = pv.cta_instr_begin[blockIdx.x], iend = pv.cta_instr_begin[blockIdx.x + 1];
+  const int ebeg = pv.cta_event_begin[blockIdx.x], eend = pv.cta_event_begin[blockIdx.x + 1];
+  if (c.warp == 0)
+    loader_loop(c, ibeg, iend);
+  else
+    consumer_loop(c, ibeg, iend, ebeg, eend);
+  __syncthreads();
+
+  // The last CTA to finish clears the dependency counters, so the next launch
+  // (or graph replay) starts from zero without a host-side memset.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(&pv.state->done_ctas, 1);
+    c.ctrl->is_last = (prev == (int)gridDim.x - 1) ? 1 : 0;
+    __threadfence();
+  }
+  __syncthreads();
+  if (c.ctrl->is_last) {
+    const bool ok = *reinterpret_cast<volatile int32_t*>(&pv.state->abort_flag) == 0;
+    if (ok)
+      for (int i = threadIdx.x; i < pv.n_counters; i += blockDim.x) pv.counters[i] = 0;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      pv.state->done_ctas = 0;
+      pv.state->launches += 1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static thread_local std::string g_err;
+
+static int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                       \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess) return fail(-(int)e_ - 1000, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+static inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+struct Layout {
+  uint64_t state, counters, ops, instrs, ibegin, events, ebegin, waits, total;
+};
+
+static Layout layout_of(const mk_program_t* p) {
+  Layout l;
+  uint64_t o = 0;
+  l.state = o;
+  o = align_up(o + sizeof(DeviceState), 256);
+  l.counters = o;
+  o = align_up(o + (uint64_t)(p->n_counters > 0 ? p->n_counters : 1) * 4, 256);
+  l.ops = o;
+  o = align_up(o + (uint64_t)p->n_ops * sizeof(mk_op_t), 256);
+  l.instrs = o;
+  o = align_up(o + (uint64_t)(p->n_instrs > 0 ? p->n_instrs : 1) * sizeof(mk_instr_t), 256);
+  l.ibegin = o;
+  o = align_up(o + (uint64_t)(p->n_ctas + 1) * 4, 256);
+  l.events = o;
+  o = align_up(o + (uint64_t)(p->n_events > 0 ? p->n_events : 1) * sizeof(mk_event_t), 256);
+  l.ebegin = o;
+  o = align_up(o + (uint64_t)(p->n_ctas + 1) * 4, 256);
+  l.waits = o;
+  o = align_up(o + (uint64_t)(p->n_waits > 0 ? p->n_waits : 1) * sizeof(mk_wait_t), 256);
+  l.total = o;
+  return l;
+}
+
+static bool aligned16(uint64_t p) { return (p & 15ull) == 0; }
+
+static int matvec_pages(const mk_op_t& op) {
+  const int K = op.i[MK_MV_K], Kc = op.i[MK_MV_KC];
+  return (K + Kc - 1) / Kc;
+}
+static int attn_pages(const mk_op_t& op, int unit, int page_bytes) {
+  const int S = op.i[MK_AT_SPLITS];
+  const int sp = unit % S;
+  const int ts = op.i[MK_AT_TS], N = op.i[MK_AT_N];
+  const int tb = std::min(N, sp * ts), te = std::min(N, tb + ts);
+  const int tn = at_page_tokens(op.i[MK_AT_D], page_bytes);
+  return (te - tb + tn - 1) / tn;
+}
+
+static int validate_op(const mk_program_t* p, int idx) {
+  const mk_op_t& op = p->ops[idx];
+  if (op.opcode < 0 || op.opcode >= MK_OP__COUNT) return fail(-2, "op %d: unknown opcode %d", idx, op.opcode);
+  if (op.n_units < 0) return fail(-2, "op %d: negative unit count", idx);
+  if (op.opcode == MK_OP_MATVEC) {
+    const int O = op.i[MK_MV_O], K = op.i[MK_MV_K], M = op.i[MK_MV_M], Kc = op.i[MK_MV_KC];
+    const int wf = op.i[MK_MV_WFMT], mode = op.i[MK_MV_MODE];
+    const bool fp4 = wf >= MK_W_NVFP4_F16S32;
+    if (O <= 0 || K <= 0 || M <= 0 || op.i[MK_MV_S] <= 0) return fail(-2, "op %d: bad matvec dims", idx);
+    if (M > 32) return fail(-2, "op %d: matvec supports at most 32 activation rows, got %d", idx, M);
+    if (wf < 0 || wf > MK_W_NVFP4_E4M3S16) return fail(-2, "op %d: bad weight format", idx);
+    if (fp4 ? (K % 256 != 0 || Kc % 256 != 0) : (K % 32 != 0 || Kc % 32 != 0))
+      return fail(-2, "op %d: K=%d / Kc=%d must be multiples of %d", idx, K, Kc, fp4 ? 256 : 32);
+    const uint64_t need = fp4 ? 16ull * (Kc / 2 + 64) + 16ull * (Kc / 16 + 16) : 16ull * (Kc * 2 + 64);
+    if (need > (uint64_t)p->page_bytes) return fail(-2, "op %d: K slice %d does not fit a %d-byte page", idx, Kc, p->page_bytes);
+    if ((uint64_t)M * ((uint64_t)K * 2 + 64) > (uint64_t)p->act_bytes)
+      return fail(-2, "op %d: %d x %d activations exceed the %d-byte staging buffer", idx, M, K, p->act_bytes);
+    if (!aligned16(op.p[MK_MV_P_W0]) || !op.p[MK_MV_P_W0] || (op.s[MK_MV_S_WROW] & 15))
+      return fail(-2, "op %d: weight pointer / row stride must be 16-byte aligned", idx);
+    if (mode == MK_MV_PAIR && (!aligned16(op.p[MK_MV_P_W1]) || !op.p[MK_MV_P_W1]))
+      return fail(-2, "op %d: second weight pointer missing or unaligned", idx);
+    if (fp4) {
+      if (!aligned16(op.p[MK_MV_P_SC0]) || !op.p[MK_MV_P_SC0] || (op.s[MK_MV_S_SCROW] & 15))
+        return fail(-2, "op %d: scale pointer / row stride must be 16-byte aligned", idx);
+      if (mode == MK_MV_PAIR && (!aligned16(op.p[MK_MV_P_SC1]) || !op.p[MK_MV_P_SC1]))
+        return fail(-2, "op %d: second scale pointer missing or unaligned", idx);
+    }
+    if (!aligned16(op.p[MK_MV_P_X]) || !op.p[MK_MV_P_X] || (op.s[MK_MV_S_X_B] & 7) || (op.s[MK_MV_S_X_S] & 7))
+      return fail(-2, "op %d: activation pointer / strides must be 16-byte aligned", idx);
+    if (op.i[MK_MV_PRO] != MK_PRO_NONE && (!op.p[MK_MV_P_NORM_W] || !aligned16(op.p[MK_MV_P_NORM_W])))
+      return fail(-2, "op %d: norm weight missing or unaligned", idx);
+    if (op.i[MK_MV_PRO] == MK_PRO_ADD_RMS && op.p[MK_MV_P_RES_IN] &&
+        (!aligned16(op.p[MK_MV_P_RES_IN]) || (op.s[MK_MV_S_RI_B] & 7) || (op.s[MK_MV_S_RI_S] & 7) ||
+         (op.p[MK_MV_P_RES_OUT] && (!aligned16(op.p[MK_MV_P_RES_OUT]) || (op.s[MK_MV_S_RO_B] & 7) || (op.s[MK_MV_S_RO_S] & 7)))))
+      return fail(-2, "op %d: residual pointers / strides must be 16-byte aligned", idx);
+    if (!op.p[MK_MV_P_OUT]) return fail(-2, "op %d: output pointer missing", idx);
+    if (op.i[MK_MV_HD] <= 0) return fail(-2, "op %d: head dim must be positive", idx);
+    int units;
+    if (mode == MK_MV_PLAIN) {
+      units = (O + 15) / 16;
+    } else if (mode == MK_MV_PAIR) {
+      units = (O + 7) / 8;
+    } else if (mode == MK_MV_ROPE) {
+      const int hd = op.i[MK_MV_HD], d2 = op.i[MK_MV_D2];
+      if (d2 <= 0 || d2 % 8 != 0 || hd != 2 * d2 || O % hd != 0)
+        return fail(-2, "op %d: rope mode needs head_dim == 2*D2, D2 %% 8 == 0, O %% head_dim == 0", idx);
+      if (!op.p[MK_MV_P_COS] || !op.p[MK_MV_P_SIN]) return fail(-2, "op %d: cos/sin missing", idx);
+      units = (O / hd) * (d2 / 8);
+    } else {
+      return fail(-2, "op %d: bad matvec mode", idx);
+    }
+    if (op.i[MK_MV_TR] == MK_TR_ROPE && mode != MK_MV_ROPE) return fail(-2, "op %d: rope transform needs rope mode", idx);
+    if (op.i[MK_MV_TR] == MK_TR_SILU_MUL && mode != MK_MV_PAIR) return fail(-2, "op %d: silu-mul needs pair mode", idx);
+    if (op.i[MK_MV_EPI] == MK_EPI_RESIDUAL && !op.p[MK_MV_P_EPI_RES]) return fail(-2, "op %d: epilogue residual missing", idx);
+    if (op.n_units != units) return fail(-2, "op %d: expected %d units, got %d", idx, units, op.n_units);
+  } else if (op.opcode == MK_OP_ATTN_SPLIT || op.opcode == MK_OP_ATTN_COMBINE) {
+    const int D = op.i[MK_AT_D], H = op.i[MK_AT_H], HKV = op.i[MK_AT_HKV], M = op.i[MK_AT_M];
+    if (D != 64 && D != 128) return fail(-2, "op %d: head dim %d unsupported (64 or 128)", idx, D);
+    if (H <= 0 || HKV <= 0 || H % HKV != 0 || M <= 0 || op.i[MK_AT_B] <= 0 || op.i[MK_AT_SPLITS] <= 0 || op.i[MK_AT_N] < 0)
+      return fail(-2, "op %d: bad attention dims", idx);
+    if (!op.p[MK_AT_P_OPART] || !op.p[MK_AT_P_LSEPART] || (op.p[MK_AT_P_OPART] & 7))
+      return fail(-2, "op %d: partial buffers missing", idx);
+    if (op.opcode == MK_OP_ATTN_SPLIT) {
+      const int G = H / HKV;
+      if (op.i[MK_AT_MT] != (M * G + 15) / 16) return fail(-2, "op %d: bad query tile count", idx);
+      if (op.i[MK_AT_TS] <= 0) return fail(-2, "op %d: tokens per split must be positive", idx);
+      if ((int64_t)op.i[MK_AT_TS] * op.i[MK_AT_SPLITS] < op.i[MK_AT_N]) return fail(-2, "op %d: splits do not cover N", idx);
+      if (at_page_tokens(D, p->page_bytes) <= 0) return fail(-2, "op %d: page too small for attention", idx);
+      for (int k = MK_AT_P_Q; k <= MK_AT_P_V; ++k)
+        if (!op.p[k] || !aligned16(op.p[k])) return fail(-2, "op %d: q/k/v pointer missing or unaligned", idx);
+      for (int k = MK_AT_S_Q_B; k <= MK_AT_S_V_H; ++k)
+        if (op.s[k] & 7) return fail(-2, "op %d: q/k/v strides must be multiples of 8 elements", idx);
+      if (op.n_units != op.i[MK_AT_B] * HKV * op.i[MK_AT_MT] * op.i[MK_AT_SPLITS])
+        return fail(-2, "op %d: bad unit count", idx);
+    } else {
+      if (!op.p[MK_AT_P_O] || (op.p[MK_AT_P_O] & 3)) return fail(-2, "op %d: output pointer missing or unaligned", idx);
+      for (int k = MK_AT_S_O_B; k <= MK_AT_S_O_H; ++k)
+        if (op.s[k] & 1) return fail(-2, "op %d: output strides must be even", idx);
+      if (op.n_units != op.i[MK_AT_B] * H) return fail(-2, "op %d: bad unit count", idx);
+    }
+  } else if (op.opcode >= MK_OP_RMSNORM && op.opcode <= MK_OP_ADD) {
+    if (!op.p[MK_EW_P_X]) return fail(-2, "op %d: input pointer missing", idx);
+    if (op.i[MK_EW_T] < 0 || op.i[MK_EW_T] > MK_T_FP32) return fail(-2, "op %d: bad element type", idx);
+  } else if (op.opcode == MK_OP_TOP1_FINAL) {
+    if (!op.p[MK_EW_P_X] || !op.p[MK_EW_P_W] || (op.p[MK_EW_P_X] & 7)) return fail(-2, "op %d: top-1 buffers missing", idx);
+  } else if (op.opcode == MK_OP_ALLREDUCE) {
+    return fail(-2, "op %d: all-reduce op is not available in this build", idx);
+  }
+  return 0;
+}
+
+static int validate_program(const mk_program_t* p, int smem_optin, int* smem_bytes) {
+  if (!p) return fail(-1, "null program");
+  if (p->n_ops <= 0 || !p->ops) return fail(-1, "program has no ops");
+  if (p->n_ctas <= 0 || p->n_ctas > 4096) return fail(-1, "bad grid size %d", p->n_ctas);
+  if (p->n_pages < 2 || p->n_pages > kMaxPages) return fail(-1, "ring depth must be in [2, %d]", kMaxPages);
+  if (p->page_bytes <= 0 || (p->page_bytes & 1023)) return fail(-1, "page size must be a positive multiple of 1024");
+  if (p->act_bytes < 0 || (p->act_bytes & 1023)) return fail(-1, "activation buffer must be a multiple of 1024 bytes");
+  if (!p->cta_instr_begin || !p->cta_event_begin) return fail(-1, "missing per-CTA offsets");
+  if (p->n_instrs > 0 && !p->instrs) return fail(-1, "missing instruction table");
+  if (p->n_events > 0 && !p->events) return fail(-1, "missing event table");
+  if (p->n_waits > 0 && !p->waits) return fail(-1, "missing wait table");
+  const int64_t smem = (int64_t)kCtrlBytes + p->act_bytes + (int64_t)p->n_pages * p->page_bytes;
+  if (smem > smem_optin) return fail(-1, "program needs %lld bytes of shared memory, device offers %d", (long long)smem, smem_optin);
+  *smem_bytes = (int)smem;
+  for (int i = 0; i < p->n_ops; ++i) {
+    const int rc = validate_op(p, i);
+    if (rc) return rc;
+  }
+  for (int i = 0; i < p->n_waits; ++i)
+    if (p->waits[i].counter < 0 || p->waits[i].counter >= p->n_counters)
+      return fail(-3, "wait %d: counter %d out of range", i, p->waits[i].counter);
+  if (p->cta_instr_begin[0] != 0 || p->cta_instr_begin[p->n_ctas] != p->n_instrs)
+    return fail(-3, "per-CTA instruction offsets do not span the table");
+  if (p->cta_event_begin[0] != 0 || p->cta_event_begin[p->n_ctas] != p->n_events)
+    return fail(-3, "per-CTA event offsets do not span the table");
+  for (int cta = 0; cta < p->n_ctas; ++cta) {
+    const int ib = p->cta_instr_begin[cta], ie = p->cta_instr_begin[cta + 1];
+    const int eb = p->cta_event_begin[cta], ee = p->cta_event_begin[cta + 1];
+    if (ie < ib || ee < eb) return fail(-3, "per-CTA offsets not monotonic at CTA %d", cta);
+    for (int j = ib; j < ie; ++j) {
+      const mk_instr_t& in = p->instrs[j];
+      if (in.op < 0 || in.op >= p->n_ops) return fail(-3, "instr %d: op out of range", j);
+      const mk_op_t& op = p->ops[in.op];
+      if (in.unit < 0 || in.unit >= op.n_units) return fail(-3, "instr %d: unit %d out of range (op %d has %d)", j, in.unit, in.op, op.n_units);
+      if (in.signal >= p->n_counters) return fail(-3, "instr %d: signal counter out of range", j);
+      if (in.n_waits < 0 || in.wait_off < 0 || in.wait_off + in.n_waits > p->n_waits) return fail(-3, "instr %d: wait list out of range", j);
+      if (in.n_lwaits < 0 || in.lwait_off < 0 || in.lwait_off + in.n_lwaits > p->n_waits) return fail(-3, "instr %d: loader wait list out of range", j);
+      int pages = 0;
+      if (op.opcode == MK_OP_MATVEC) pages = matvec_pages(op);
+      else if (op.opcode == MK_OP_ATTN_SPLIT) pages = attn_pages(op, in.unit, p->page_bytes);
+      if (in.n_pages != pages) return fail(-3, "instr %d: expected %d pages, got %d", j, pages, in.n_pages);
+    }
+    int last = -1;
+    for (int e = eb; e < ee; ++e) {
+      const mk_event_t& ev = p->events[e];
+      if (ev.op < 0 || ev.op >= p->n_ops) return fail(-3, "event %d: op out of range", e);
+      if (ev.pos < last || ev.pos < 0 || ev.pos > ie - ib) return fail(-3, "event %d: position out of order", e);
+      if (ev.n_waits < 0 || ev.wait_off < 0 || ev.wait_off + ev.n_waits > p->n_waits) return fail(-3, "event %d: wait list out of range", e);
+      last = ev.pos;
+    }
+  }
+  return 0;
+}
+
+}  // namespace mk
+
+struct mk_handle_s {
+  mk::ProgramView pv;
+  int n_ctas;
+  int smem_bytes;
+  int device;
+  int n_ops;
+  uint8_t* ws;
+  mk::Layout layout;
+};
+
+extern "C" {
+
+int mk_abi_version(void) { return MK_ABI_VERSION; }
+
+const char* mk_last_error(void) { return mk::g_err.c_str(); }
+
+int mk_device_info(int device, int32_t* num_sms, int32_t* smem_optin, int32_t* cc_major, int32_t* cc_minor) {
+  using namespace mk;
+  int v = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+  if (num_sms) *num_sms = v;
+  CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  if (smem_optin) *smem_optin = v;
+  CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, device));
+  if (cc_major) *cc_major = v;
+  CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMinor, device));
+  if (cc_minor) *cc_minor = v;
+  return 0;
+}
+
+uint64_t mk_workspace_bytes(const mk_program_t* prog) {
+  if (!prog) return 0;
+  return mk::layout_of(prog).total;
+}
+
+int mk_create(const mk_program_t* prog, mk_handle_t* out) {
+  using namespace mk;
+  if (!out) return fail(-1, "null output handle");
+  *out = nullptr;
+  if (!prog) return fail(-1, "null program");
+  int prev_dev = 0;
+  CUDA_TRY(cudaGetDevice(&prev_dev));
+  CUDA_TRY(cudaSetDevice(prog->device));
+  int smem_optin = 0, cc = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, prog->device));
+  CUDA_TRY(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, prog->device));
+  if (cc != 10) {
+    cudaSetDevice(prev_dev);
+    return fail(-4, "device %d has compute capability %d.x; this library is built for sm_100a only", prog->device, cc);
+  }
+  int smem_bytes = 0;
+  int rc = validate_program(prog, smem_optin, &smem_bytes);
+  if (rc) {
+    cudaSetDevice(prev_dev);
+    return rc;
+  }
+  const Layout l = layout_of(prog);
+  if (!prog->workspace || prog->workspace_bytes < l.total || ((uint64_t)prog->workspace & 255)) {
+    cudaSetDevice(prev_dev);
+    return fail(-1, "workspace must be 256-byte aligned device memory of at least %llu bytes", (unsigned long long)l.total);
+  }
+  uint8_t* ws = reinterpret_cast<uint8_t*>(prog->workspace);
+  CUDA_TRY(cudaMemset(ws + l.state, 0, l.ops - l.state));
+  CUDA_TRY(cudaMemcpy(ws + l.ops, prog->ops, (size_t)prog->n_ops * sizeof(mk_op_t), cudaMemcpyHostToDevice));
+  if (prog->n_instrs)
+    CUDA_TRY(cudaMemcpy(ws + l.instrs, prog->instrs, (size_t)prog->n_instrs * sizeof(mk_instr_t), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(ws + l.ibegin, prog->cta_instr_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
+  if (prog->n_events)
+    CUDA_TRY(cudaMemcpy(ws + l.events, prog->events, (size_t)prog->n_events * sizeof(mk_event_t), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMemcpy(ws + l.ebegin, prog->cta_event_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
+  if (prog->n_waits)
+    CUDA_TRY(cudaMemcpy(ws + l.waits, prog->waits, (size_t)prog->n_waits * sizeof(mk_wait_t), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaFuncSetAttribute(mk_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+
+  mk_handle_s* h = new mk_handle_s();
+  h->pv.ops = reinterpret_cast<const mk_op_t*>(ws + l.ops);
+  h->pv.instrs = reinterpret_cast<const mk_instr_t*>(ws + l.instrs);
+  h->pv.cta_instr_begin = reinterpret_cast<const int32_t*>(ws + l.ibegin);
+  h->pv.events = reinterpret_cast<const mk_event_t*>(ws + l.events);
+  h->pv.cta_event_begin = reinterpret_cast<const int32_t*>(ws + l.ebegin);
+  h->pv.waits = reinterpret_cast<const mk_wait_t*>(ws + l.waits);
+  h->pv.counters = reinterpret_cast<int32_t*>(ws + l.counters);
+  h->pv.state = reinterpret_cast<DeviceState*>(ws + l.state);
+  h->pv.n_counters = prog->n_counters;
+  h->pv.n_pages = prog->n_pages;
+  h->pv.page_bytes = prog->page_bytes;
+  h->pv.act_bytes = prog->act_bytes;
+  h->pv.timeout_ns = (uint64_t)(prog->timeout_ms > 0 ? prog->timeout_ms : 1000) * 1000000ull;
+  h->n_ctas = prog->n_ctas;
+  h->smem_bytes = smem_bytes;
+  h->device = prog->device;
+  h->n_ops = prog->n_ops;
+  h->ws = ws;
+  h->layout = l;
+  *out = h;
+  cudaSetDevice(prev_dev);
+  return 0;
+}
+
+int mk_run(mk_handle_t h, void* cuda_stream) {
+  using namespace mk;
+  if (!h) return fail(-1, "null handle");
+  mk_persistent_kernel<<<h->n_ctas, kThreads, h->smem_bytes, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(h->pv);
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mk_status(mk_handle_t h, int32_t out[16]) {
+  using namespace mk;
+  if (!h || !out) return fail(-1, "null argument");
+  CUDA_TRY(cudaMemcpy(out, h->ws + h->layout.state, 16 * sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+int mk_reset(mk_handle_t h, void* cuda_stream) {
+  using namespace mk;
+  if (!h) return fail(-1, "null handle");
+  CUDA_TRY(cudaMemsetAsync(h->ws + h->layout.state, 0, h->layout.ops - h->layout.state,
+                           reinterpret_cast<cudaStream_t>(cuda_stream)));
+  return 0;
+}
+
+int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_stream) {
+  using namespace mk;
+  if (!h || !op) return fail(-1, "null argument");
+  if (op_index < 0 || op_index >= h->n_ops) return fail(-1, "op index %d out of range", op_index);
+  CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.ops + (size_t)op_index * sizeof(mk_op_t), op, sizeof(mk_op_t),
+                           cudaMemcpyHostToDevice, reinterpret_cast<cudaStream_t>(cuda_stream)));
+  return 0;
+}
+
+int mk_read_counters(mk_handle_t h, int32_t* out, int32_t n) {
+  using namespace mk;
+  if (!h || !out) return fail(-1, "null argument");
+  if (n > h->pv.n_counters) n = h->pv.n_counters;
+  if (n > 0) CUDA_TRY(cudaMemcpy(out, h->ws + h->layout.counters, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+int mk_destroy(mk_handle_t h) {
+  delete h;
+  return 0;
+}
+
+}  // extern "C"
+
+#include "standalone.inc"

@@ -1,0 +1,299 @@
+// Split-KV flash decoding for one KV head per unit, and the log-sum-exp combine.
+//
+// A unit is (batch b, kv head, 16-row query tile, split).  The 16 rows of the
+// tile enumerate (query position m, query head within the GQA group), so at
+// decode (M = 1) one unit serves every query head that shares the KV head and
+// each K/V byte is fetched once — the reference tiles per *query* head and
+// re-reads each KV head `group` times (attention/flash_decoding.py:1192, 1324).
+//
+// K and V token rows are gathered into a ring page by 16-byte cp.async with an
+// XOR-8 chunk swizzle so that ldmatrix is bank-conflict free; scores and P·V
+// run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with an exp2 online
+// softmax.  Partials follow the reference's contract: normalised fp32
+// o_partial[B,H,SPLIT,M,D] and lse_partial[B,H,SPLIT,M] = max*scale + ln(sum)
+// (attention/flash_decoding.py:1139-1172); the combine implements
+// o = sum_s e^{lse_s-max} o_s / sum_s e^{lse_s-max} (:1858-1950).
+#pragma once
+#include "shell.cuh"
+
+namespace mk {
+
+struct AtUnit {
+  int b, kvh, mt, sp;
+  int t_begin, t_end;  // token range of the split
+};
+
+__device__ __forceinline__ AtUnit at_decode(const mk_op_t* op, int unit) {
+  AtUnit u;
+  const int S = op->i[MK_AT_SPLITS], MT = op->i[MK_AT_MT], HKV = op->i[MK_AT_HKV];
+  u.sp = unit % S;
+  int r = unit / S;
+  u.mt = r % MT;
+  r /= MT;
+  u.kvh = r % HKV;
+  u.b = r / HKV;
+  const int ts = op->i[MK_AT_TS], N = op->i[MK_AT_N];
+  u.t_begin = min(N, u.sp * ts);
+  u.t_end = min(N, u.t_begin + ts);
+  return u;
+}
+
+// Tokens per page for head dim D and a given page size: a K block and a V
+// block of `tn` rows each; tn is a multiple of the consumer's inner block
+// (64 tokens for D = 64, 32 for D = 128) and at most 128.
+__device__ __host__ __forceinline__ int at_page_tokens(int D, int page_bytes) {
+  const int blk = (D == 64) ? 64 : 32;
+  int tn = page_bytes / (4 * D);
+  tn = (tn / blk) * blk;
+  return tn > 128 ? 128 : tn;
+}
+
+// ---- loader -----------------------------------------------------------------------
+__device__ __forceinline__ void at_load_page(const mk_op_t* op, int unit, int p, uint32_t page, uint32_t bar,
+                                             int lane, int page_bytes) {
+  const AtUnit u = at_decode(op, unit);
+  const int D = op->i[MK_AT_D];
+  const int tn = at_page_tokens(D, page_bytes);
+  const int t0 = u.t_begin + p * tn;
+  const int ch = D >> 3;  // 16-byte chunks per row
+  const uint32_t rowb = (uint32_t)D * 2u;
+  const uint16_t* kb = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_K]) + u.b * op->s[MK_AT_S_K_B] +
+                       u.kvh * op->s[MK_AT_S_K_H];
+  const uint16_t* vb = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_V]) + u.b * op->s[MK_AT_S_V_B] +
+                       u.kvh * op->s[MK_AT_S_V_H];
+  const int64_t kn = op->s[MK_AT_S_K_N], vn = op->s[MK_AT_S_V_N];
+  const int total = tn * ch;
+  const uint32_t vbase = page + (uint32_t)tn * rowb;
+  for (int idx = lane; idx < total; idx += 32) {
+    const int tok = idx / ch, cc = idx - tok * ch;
+    const int tg = t0 + tok;
+    const bool valid = tg < u.t_end;
+    const uint32_t dsto = (uint32_t)tok * rowb + (uint32_t)((cc ^ (tok & 7)) << 4);
+    const uint16_t* ks = valid ? kb + (int64_t)tg * kn + cc * 8 : kb;
+    const uint16_t* vs = valid ? vb + (int64_t)tg * vn + cc * 8 : vb;
+    cp_async16(page + dsto, ks, valid ? 16u : 0u);
+    cp_async16(vbase + dsto, vs, valid ? 16u : 0u);
+  }
+  cp_async_mbar_arrive_noinc(bar);
+}
+
+// ---- consumer ---------------------------------------------------------------------
+template <int D>
+__device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+  constexpr int KS = D / 16;   // k-steps of Q·K^T
+  constexpr int ND = D / 8;    // n-tiles of the output
+  constexpr int TN = (D == 64) ? 64 : 32;  // tokens processed per inner block
+  constexpr int NS = TN / 8;   // score n-tiles per block
+  const AtUnit u = at_decode(op, ins.unit);
+  const int g = c.lane >> 2, t = c.lane & 3;
+  const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], N = op->i[MK_AT_N];
+  const int G = H / HKV;
+  const int S = op->i[MK_AT_SPLITS];
+  const bool causal = op->i[MK_AT_CAUSAL] != 0;
+  const float sc = op->f[MK_AT_F_SCALE];
+  const float c2 = sc * 1.4426950408889634f;
+  const int tn = at_page_tokens(D, c.pv->page_bytes);
+  const uint32_t rowb = (uint32_t)D * 2u;
+
+  // rows of this thread: r0 = mt*16 + g, r1 = r0 + 8 -> (m, head)
+  int rm[2], rh[2];
+  bool rv[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int r = u.mt * 16 + g + 8 * e;
+    rv[e] = r < M * G;
+    rm[e] = rv[e] ? r / G : 0;
+    rh[e] = u.kvh * G + (rv[e] ? r % G : 0);
+  }
+  // Q fragments (A operand), loaded straight from global.
+  uint32_t qf[KS][4];
+  {
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_Q]) + u.b * op->s[MK_AT_S_Q_B];
+    const uint16_t* q0 = q + rm[0] * op->s[MK_AT_S_Q_M] + rh[0] * op->s[MK_AT_S_Q_H];
+    const uint16_t* q1 = q + rm[1] * op->s[MK_AT_S_Q_M] + rh[1] * op->s[MK_AT_S_Q_H];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int col = ks * 16 + 2 * t;
+      qf[ks][0] = rv[0] ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+      qf[ks][1] = rv[1] ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+      qf[ks][2] = rv[0] ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+      qf[ks][3] = rv[1] ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+    }
+  }
+  // causal limit per row: token index <= N - M + m
+  int lim[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) lim[e] = causal ? (N - M + rm[e]) : (N - 1);
+
+  float o[ND][4];
+#pragma unroll
+  for (int i = 0; i < ND; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY};
+  float lrow[2] = {0.f, 0.f};
+
+  const int np = ins.n_pages;
+  for (int p = 0; p < np; ++p) {
+    uint32_t page;
+    if (!page_acquire(c, seq + p, page)) return;
+    const uint32_t kpage = page, vpage = page + (uint32_t)tn * rowb;
+    const int tp0 = u.t_begin + p * tn;
+    for (int blk = 0; blk * TN < tn; ++blk) {
+      const int tb0 = tp0 + blk * TN;       // global token of column 0 of the block
+      if (tb0 >= u.t_end) break;
+      const int lt0 = blk * TN;             // token row inside the page
+      float s[NS][4];
+#pragma unroll
+      for (int i = 0; i < NS; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+      // S = Q K^T
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int pr = 0; pr < NS / 2; ++pr) {
+          const int mat = c.lane >> 3, r = c.lane & 7;
+          const int tok = lt0 + pr * 16 + (mat >> 1) * 8 + r;
+          const int chunk = 2 * ks + (mat & 1);
+          const uint32_t addr = kpage + (uint32_t)tok * rowb + (uint32_t)((chunk ^ (tok & 7)) << 4);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(addr, b0, b1, b2, b3);
+          mma_bf16(s[2 * pr], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+          mma_bf16(s[2 * pr + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+        }
+      }
+      // mask + row max
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < NS; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tb0 + i * 8 + 2 * t + (e & 1);
+          const int row = e >> 1;
+          if (tok >= u.t_end || tok > lim[row]) s[i][e] = -INFINITY;
+          mx[row] = fmaxf(mx[row], s[i][e]);
+        }
+      }
+      float corr[2], muse[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+        mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+        const float mnew = fmaxf(mrow[e], mx[e]);
+        muse[e] = (mnew == -INFINITY) ? 0.f : mnew;
+        corr[e] = fast_exp2((mrow[e] - muse[e]) * c2);
+        mrow[e] = mnew;
+        lrow[e] *= corr[e];
+      }
+#pragma unroll
+      for (int i = 0; i < ND; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      // P = exp2(S*c2 - m*c2), packed as bf16 A fragments
+      uint32_t pf[NS / 2][4];
+#pragma unroll
+      for (int i = 0; i < NS; ++i) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = e >> 1;
+          pv[e] = fast_exp2(s[i][e] * c2 - muse[row] * c2);
+          lrow[row] += pv[e];
+        }
+        pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+      }
+      // O += P V
+#pragma unroll
+      for (int kk = 0; kk < NS / 2; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < ND / 2; ++dp) {
+          const int mat = c.lane >> 3, r = c.lane & 7;
+          const int tok = lt0 + kk * 16 + (mat & 1) * 8 + r;
+          const int chunk = 2 * dp + (mat >> 1);
+          const uint32_t addr = vpage + (uint32_t)tok * rowb + (uint32_t)((chunk ^ (tok & 7)) << 4);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+          mma_bf16(o[2 * dp], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
+          mma_bf16(o[2 * dp + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
+        }
+      }
+    }
+    page_release(c, seq + p);
+  }
+  // finalise: normalised partial + lse
+  float* op_ = reinterpret_cast<float*>(op->p[MK_AT_P_OPART]);
+  float* lp_ = reinterpret_cast<float*>(op->p[MK_AT_P_LSEPART]);
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float l = lrow[e];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (!rv[e]) continue;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float lse = l > 0.f ? mrow[e] * sc + __logf(l) : -INFINITY;
+    const int64_t base = ((((int64_t)u.b * H + rh[e]) * S + u.sp) * M + rm[e]);
+    float* dst = op_ + base * D;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      float2 v = make_float2(o[i][2 * e] * inv, o[i][2 * e + 1] * inv);
+      *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = v;
+    }
+    if (t == 0) lp_[base] = lse;
+  }
+}
+
+__device__ __forceinline__ void at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+  if (op->i[MK_AT_D] == 64)
+    at_unit<64>(c, op, ins, seq);
+  else
+    at_unit<128>(c, op, ins, seq);
+}
+
+// Combine: one unit per (b, query head); all M rows.
+__device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins) {
+  const int H = op->i[MK_AT_H], M = op->i[MK_AT_M], D = op->i[MK_AT_D], S = op->i[MK_AT_SPLITS];
+  const int b = ins.unit / H, h = ins.unit - b * H;
+  const float* opart = reinterpret_cast<const float*>(op->p[MK_AT_P_OPART]);
+  const float* lpart = reinterpret_cast<const float*>(op->p[MK_AT_P_LSEPART]);
+  float* lse_out = reinterpret_cast<float*>(op->p[MK_AT_P_LSE]);
+  const int ot = op->i[MK_AT_O_T];
+  for (int m = 0; m < M; ++m) {
+    const int64_t base = ((int64_t)b * H + h) * S;
+    float mx = -INFINITY;
+    for (int s = c.lane; s < S; s += 32) mx = fmaxf(mx, lpart[(base + s) * M + m]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    if (mx != -INFINITY)
+      for (int s = c.lane; s < S; s += 32) sum += __expf(lpart[(base + s) * M + m] - mx);
+    sum = warp_sum(sum);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    const int64_t ooff = b * op->s[MK_AT_S_O_B] + m * op->s[MK_AT_S_O_M] + h * op->s[MK_AT_S_O_H];
+    for (int d = c.lane * 2; d < D; d += 64) {
+      float a0 = 0.f, a1 = 0.f;
+      if (sum > 0.f) {
+        for (int s = 0; s < S; ++s) {
+          const float w = __expf(lpart[(base + s) * M + m] - mx) * inv;
+          const float2 v = *reinterpret_cast<const float2*>(opart + ((base + s) * M + m) * D + d);
+          a0 += w * v.x;
+          a1 += w * v.y;
+        }
+      }
+      if (ot == MK_T_FP32) {
+        float* o = reinterpret_cast<float*>(op->p[MK_AT_P_O]) + ooff + d;
+        o[0] = a0;
+        o[1] = a1;
+      } else {
+        uint32_t* o = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(op->p[MK_AT_P_O]) + ooff + d);
+        *o = (ot == MK_T_BF16) ? pack_bf16(a0, a1) : pack_f16(a0, a1);
+      }
+    }
+    if (c.lane == 0 && lse_out) lse_out[((int64_t)b * H + h) * M + m] = (sum > 0.f) ? mx + __logf(sum) : -INFINITY;
+  }
+}
+
+}  // namespace mk

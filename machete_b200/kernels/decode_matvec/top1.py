@@ -1,0 +1,147 @@
+"""Greedy-token LM head: fused final add + RMSNorm + vocabulary matvec + arg-max.
+
+The reference's B200 path writes full bf16 logits (``FinalRmsLmHeadSm100Op``,
+src/machete/kernels/decode_matvec/sm100.py:574) and only its sm120 path has a
+top-1 head, as a partial/reduce pair (``Llama1BFinalAddRmsTop1PartialLmHead
+KStreamSm120Op`` / ``Llama1BReduceTop1PartialsSm120Op``,
+src/machete/kernels/llama1b/sm120.py:3151, 3464).  Here every vocabulary unit
+folds its 16 rows into one 64-bit key per activation row with ``atomicMax``
+(order-preserving float bits in the high word, ``~index`` in the low word, so
+ties resolve to the lowest index exactly like ``argmax``), and a one-unit
+finalise op unpacks the keys and clears them for the next launch.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ... import _native as N
+from ...megakernel.lowering import NativeOp, Region, meta_of
+from ...megakernel.ops import DEFAULT_PAGE_SIZE, Float32, Int32, Int64, Op
+from .._matvec import Weight, dense_weight, lower_matvec, nvfp4_weight
+
+
+class FinalAddRmsTop1LmHeadSm100Op(Op):
+    """keys[b, s] = max over vocab of (logit, index); logits = rms(x + residual_in) * w @ W^T."""
+
+    reads = {
+        "x": (None, ("B", "S", "K")),
+        "residual_in": (None, ("B", "S", "K")),
+        "norm_weight": (None, ("K",)),
+        "weight": (None, ("V", "K")),
+    }
+    writes = {"top_keys": (Int64, ("B", "S"))}
+    tile = ("B", "S", "V")
+    dynamic_dims = ("B",)
+
+    @classmethod
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, **tensors):
+        tile_sizes = dict(tile_sizes or {})
+        tile_sizes.setdefault("B", 1)
+        tile_sizes.setdefault("S", 16)
+        tile_sizes.setdefault("V", 16)
+        keys = tensors["top_keys"]
+        if keys.dtype != torch.int64 or not keys.is_contiguous():
+            raise ValueError("top_keys must be a contiguous int64 (B, S) tensor, zero-initialised")
+        op = cls._schedule_single(tile_sizes=tile_sizes, **tensors)
+        op.static_dims["page_size"] = page_size
+        op.static_dims["eps"] = eps
+        return [op]
+
+    @classmethod
+    def _weight(cls, sop) -> Weight:
+        return dense_weight(sop.tensor_refs["weight"])
+
+    @classmethod
+    def lower(cls, sop, ctx):
+        t = sop.tensor_refs
+        has_res = "residual_in" in t and t["residual_in"] is not None
+        return [lower_matvec(cls.__name__, ctx, w0=cls._weight(sop), x=t["x"], out=t["top_keys"],
+                             out_strides=(0, 0, 0), pro=N.PRO_ADD_RMS if has_res else N.PRO_RMS,
+                             norm_weight=t["norm_weight"], residual_in=t.get("residual_in"), epi=N.EPI_TOP1,
+                             eps=float(sop.static_dims.get("eps", 1e-5)), kind="lm_head_top1")]
+
+
+class FinalAddRmsTop1LmHeadNvfp4Sm100Op(FinalAddRmsTop1LmHeadSm100Op):
+    """NVFP4-weight variant (``weight_packed``, ``weight_scales``)."""
+
+    uses_nvfp4 = True
+    reads = {
+        "x": (None, ("B", "S", "K")),
+        "residual_in": (None, ("B", "S", "K")),
+        "norm_weight": (None, ("K",)),
+        "weight_packed": (None, ("V", "K2")),
+        "weight_scales": (None, ("V", "G")),
+    }
+    writes = {"top_keys": (Int64, ("B", "S"))}
+    tile = ("B", "S", "V")
+    dynamic_dims = ("B",)
+
+    @classmethod
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, group_size=32, global_scale=1.0,
+                 **tensors):
+        ops = super().schedule(tile_sizes=tile_sizes, page_size=page_size, eps=eps, **tensors)
+        ops[0].static_dims["group_size"] = group_size
+        ops[0].params["global_scale"] = float(global_scale)
+        return ops
+
+    @classmethod
+    def _weight(cls, sop) -> Weight:
+        t = sop.tensor_refs
+        return nvfp4_weight(t["weight_packed"], t["weight_scales"], int(sop.static_dims["group_size"]),
+                            sop.params.get("global_scale", 1.0))
+
+
+class ReduceTop1Sm100Op(Op):
+    """Unpack ``top_keys`` into ``top_values (B, S) f32`` / ``top_indices (B, S) i32`` and clear the keys."""
+
+    reads = {"top_keys": (Int64, ("B", "S"))}
+    writes = {"top_values": (Float32, ("B", "S")), "top_indices": (Int32, ("B", "S"))}
+    tile = ("B",)
+    dynamic_dims = ("B", "S")
+
+    @classmethod
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, **tensors):
+        for name, dt in (("top_values", torch.float32), ("top_indices", torch.int32)):
+            if tensors[name].dtype != dt or not tensors[name].is_contiguous():
+                raise ValueError(f"{name} must be a contiguous {dt} (B, S) tensor")
+        op = cls._schedule_single(tile_sizes={}, **tensors)
+        op.static_dims["page_size"] = page_size
+        return [op]
+
+    @classmethod
+    def lower(cls, sop, ctx):
+        t = sop.tensor_refs
+        keys, vals, idxs = t["top_keys"], t["top_values"], t["top_indices"]
+        op = NativeOp(name=cls.__name__, opcode=N.OP_TOP1_FINAL, n_units=1, kind="top1_final")
+        op.i = {N.EW_ROWS: keys.numel()}
+        op.p = {N.EW_P_X: keys.data_ptr(), N.EW_P_Y: vals.data_ptr(), N.EW_P_W: idxs.data_ptr()}
+        op.reads = [Region(meta_of(keys, "top_keys"))]
+        op.writes = [Region(meta_of(keys, "top_keys")), Region(meta_of(vals, "top_values")),
+                     Region(meta_of(idxs, "top_indices"))]
+        op.keep = [keys, vals, idxs]
+        return [op]
+
+
+def schedule_final_top1_sm100(*, x, residual_in, final_norm, lm_head, top_values, top_indices, seq_len,
+                              page_size=DEFAULT_PAGE_SIZE, eps=1e-5, lm_head_scales=None, group_size=32,
+                              global_scale=1.0):
+    """Final add + RMSNorm + LM head + greedy token, without materialising logits."""
+    keys = torch.zeros(top_values.shape, dtype=torch.int64, device=top_values.device)
+    tiles = {"S": seq_len, "V": 16}
+    if lm_head_scales is None:
+        ops = FinalAddRmsTop1LmHeadSm100Op.schedule(x=x, residual_in=residual_in, norm_weight=final_norm,
+                                                    weight=lm_head, top_keys=keys, tile_sizes=tiles,
+                                                    page_size=page_size, eps=eps)
+    else:
+        ops = FinalAddRmsTop1LmHeadNvfp4Sm100Op.schedule(
+            x=x, residual_in=residual_in, norm_weight=final_norm, weight_packed=lm_head,
+            weight_scales=lm_head_scales, top_keys=keys, tile_sizes=tiles, page_size=page_size, eps=eps,
+            group_size=group_size, global_scale=global_scale)
+    ops += ReduceTop1Sm100Op.schedule(top_keys=keys, top_values=top_values, top_indices=top_indices,
+                                      page_size=page_size)
+    return ops
+
+
+__all__ = ["FinalAddRmsTop1LmHeadSm100Op", "FinalAddRmsTop1LmHeadNvfp4Sm100Op", "ReduceTop1Sm100Op",
+           "schedule_final_top1_sm100"]

@@ -1,0 +1,110 @@
+"""Llama-3.2-1B-shape decode: aliases, constants and the whole-model schedule.
+
+The aliases and constants follow the reference's package
+(src/machete/kernels/llama1b/sm100.py:3-29).  ``schedule_decode_model_sm100``
+is this build's counterpart of ``schedule_decode_model_sm120``
+(src/machete/kernels/llama1b/sm120.py:4679-4762) for B200: ``num_layers``
+decoder layers with ping-pong activation buffers, then the final norm and
+either bf16 logits or the fused greedy-token head.
+"""
+
+from __future__ import annotations
+
+from ...megakernel.ops import DEFAULT_PAGE_SIZE
+from ..decode_matvec.sm100 import DecodeLayerSchedule as Llama1BLayerSchedule
+from ..decode_matvec.sm100 import FinalRmsLmHeadSm100Op as Llama1BFinalRmsLmHeadSm100Op
+from ..decode_matvec.sm100 import MatvecResidualSm100Op as Llama1BMatvecResidualSm100Op
+from ..decode_matvec.sm100 import MatvecSm100Op as Llama1BDownMatvecSm100Op
+from ..decode_matvec.sm100 import ResidualAddSm100Op as Llama1BResidualAddSm100Op
+from ..decode_matvec.sm100 import RmsGateUpSiluSm100Op as Llama1BRmsGateUpSiluSm100Op
+from ..decode_matvec.sm100 import RmsKMatvecRopeCacheSm100Op as Llama1BRmsKCacheSm100Op
+from ..decode_matvec.sm100 import RmsQMatvecRopeSm100Op as Llama1BRmsQSm100Op
+from ..decode_matvec.sm100 import RmsVMatvecCacheSm100Op as Llama1BRmsVCacheSm100Op
+from ..decode_matvec.sm100 import schedule_decode_layer_sm100, schedule_final_sm100
+from ..decode_matvec.top1 import schedule_final_top1_sm100
+
+LLAMA1B_HIDDEN = 2048
+LLAMA1B_HEAD_DIM = 64
+LLAMA1B_ROTARY_D2 = 32
+LLAMA1B_Q_DIM = 2048
+LLAMA1B_KV_DIM = 512
+LLAMA1B_INTERMEDIATE = 8192
+LLAMA1B_VOCAB = 128256
+LLAMA1B_MATVEC_BLOCK = 16
+LLAMA1B_REDUCTION_DIM_PER_WARP = 512
+LLAMA1B_CONSUMER_WARPS = 4
+LLAMA1B_NUM_LAYERS = 16
+
+
+def schedule_decode_model_sm100(
+    *,
+    batch,
+    cache_pos,
+    weights,
+    k_cache,
+    v_cache,
+    x_buffers,
+    residual_buffers,
+    q_buf,
+    attn_out_buf,
+    mlp_h_buf,
+    final_norm=None,
+    lm_head=None,
+    logits=None,
+    top_values=None,
+    top_indices=None,
+    num_layers=LLAMA1B_NUM_LAYERS,
+    seq_len=1,
+    page_size=DEFAULT_PAGE_SIZE,
+    eps=1e-5,
+    fa_num_splits=0,
+    hidden_size=LLAMA1B_HIDDEN,
+    intermediate_size=LLAMA1B_INTERMEDIATE,
+    num_q_heads=LLAMA1B_Q_DIM // LLAMA1B_HEAD_DIM,
+    num_kv_heads=LLAMA1B_KV_DIM // LLAMA1B_HEAD_DIM,
+    head_dim=LLAMA1B_HEAD_DIM,
+):
+    """Schedule a full decode step: ``(ops, keep_alive)``.
+
+    ``k_cache`` / ``v_cache`` are per-layer lists of ``(B, T, H_kv, head_dim)``
+    tensors; ``x_buffers`` / ``residual_buffers`` hold two ``(B, S, hidden)``
+    ping-pong buffers each: layer ``i`` reads pair ``i % 2`` and writes the
+    other.  The layer input is the pair (MLP delta ``x``, residual stream).
+    """
+    if len(x_buffers) < 2 or len(residual_buffers) < 2:
+        raise ValueError("x_buffers and residual_buffers must each contain two ping-pong buffers")
+    ops, keep = [], []
+    cur = 0
+    for layer_idx in range(num_layers):
+        nxt = 1 - cur
+        layer = schedule_decode_layer_sm100(
+            layer_idx=layer_idx, batch=batch, seq_len=seq_len, cache_pos=cache_pos, weights=weights,
+            k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=x_buffers[cur],
+            residual_in=residual_buffers[cur], x_out=x_buffers[nxt], residual_out=residual_buffers[nxt],
+            q_buf=q_buf, attn_out_buf=attn_out_buf, mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps,
+            fa_num_splits=fa_num_splits, hidden_size=hidden_size, intermediate_size=intermediate_size,
+            num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+            kv_group_size=num_q_heads // num_kv_heads,
+        )
+        ops += layer.ops
+        keep += layer.keep_alive
+        cur = nxt
+    if final_norm is not None and lm_head is not None:
+        if logits is not None and (top_values is not None or top_indices is not None):
+            raise ValueError("Provide either logits or top_values/top_indices, not both")
+        if logits is not None:
+            ops += schedule_final_sm100(x=x_buffers[cur], residual_in=residual_buffers[cur],
+                                        residual_out=residual_buffers[1 - cur], final_norm=final_norm,
+                                        lm_head=lm_head, logits=logits, seq_len=seq_len, page_size=page_size,
+                                        eps=eps)
+        elif top_values is not None and top_indices is not None:
+            ops += schedule_final_top1_sm100(x=x_buffers[cur], residual_in=residual_buffers[cur],
+                                             final_norm=final_norm, lm_head=lm_head, top_values=top_values,
+                                             top_indices=top_indices, seq_len=seq_len, page_size=page_size,
+                                             eps=eps)
+        else:
+            raise ValueError("logits or both top_values/top_indices must be provided when lm_head is scheduled")
+    return ops, keep
+
+
+__all__ = [n for n in dir() if n.startswith(("LLAMA1B_", "Llama1B", "schedule_"))]

@@ -1,0 +1,84 @@
+"""Program lowering with peephole fusion.
+
+``lower_program`` turns the scheduled ops into native op records.  With
+``ctx.fuse`` it also rewrites one pattern the reference's layer schedule
+produces: the down projection issued as ``intermediate / hidden`` K-blocks —
+``MatvecSm100Op`` on ``W[:, 0:h]`` followed by ``MatvecResidualSm100Op`` on
+``W[:, h:2h] ...`` accumulating in place (src/machete/kernels/decode_matvec/
+sm100.py:794-817).  The blocks are slices of one weight and one activation
+buffer, so they collapse into a single full-K matvec: one dependency stage
+instead of four, fp32 accumulation across the whole K instead of a bf16
+round trip per block.
+"""
+
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import _native as N
+from .lowering import LowerCtx, NativeOp
+from .ops import ScheduledOp, last_dim_slice_region
+
+
+def _kblock_chain(ops: List[ScheduledOp], start: int):
+    """Length of a fusable down-projection K-block chain starting at ``start`` (0 if none)."""
+    first = ops[start]
+    if first.op_cls.__name__ not in ("MatvecSm100Op", "MatvecSm120Op"):
+        return 0, None
+    a0, w0, y = first.tensor_refs["a"], first.tensor_refs["weight"], first.tensor_refs["y"]
+    if a0.storage_offset() != 0 and a0.stride(-1) != 1:
+        return 0, None
+    k = int(a0.shape[-1])
+    n = 1
+    while start + n < len(ops):
+        nxt = ops[start + n]
+        if nxt.op_cls.__name__ not in ("MatvecResidualSm100Op", "MatvecResidualSm120Op"):
+            break
+        t = nxt.tensor_refs
+        a, w = t["a"], t["weight"]
+        same_out = t["residual_in"].data_ptr() == y.data_ptr() and t["residual_out"].data_ptr() == y.data_ptr()
+        if not same_out or a.shape != a0.shape or w.shape != w0.shape:
+            break
+        if a.stride() != a0.stride() or w.stride() != w0.stride():
+            break
+        esz = a.element_size()
+        if a.data_ptr() != a0.data_ptr() + n * k * esz or w.data_ptr() != w0.data_ptr() + n * k * esz:
+            break
+        if a.untyped_storage().data_ptr() != a0.untyped_storage().data_ptr():
+            break
+        if w.untyped_storage().data_ptr() != w0.untyped_storage().data_ptr():
+            break
+        n += 1
+    if n < 2:
+        return 0, None
+    # the slices must tile one contiguous row range of the parents
+    if a0.stride(-2) < n * k or w0.stride(0) < n * k:
+        return 0, None
+    a_full = torch.as_strided(a0, (a0.shape[0], a0.shape[1], n * k), a0.stride())
+    w_full = torch.as_strided(w0, (w0.shape[0], n * k), w0.stride())
+    return n, (a_full, w_full, y)
+
+
+def lower_program(ops: List[ScheduledOp], ctx: LowerCtx) -> List[NativeOp]:
+    from ..kernels._matvec import dense_weight, flat_out_strides, lower_matvec
+
+    out: List[NativeOp] = []
+    i = 0
+    while i < len(ops):
+        sop = ops[i]
+        if ctx.fuse:
+            n, fused = _kblock_chain(ops, i)
+            if n:
+                a_full, w_full, y = fused
+                nop = lower_matvec("FusedDownProj", ctx, w0=dense_weight(w_full), x=a_full, out=y,
+                                   out_strides=flat_out_strides(y), kind="matvec")
+                nop.keep += [a_full, w_full]
+                out.append(nop)
+                i += n
+                continue
+        lowered = sop.op_cls.lower(sop, ctx)
+        out.extend(lowered)
+        i += 1
+    return out

@@ -1,0 +1,323 @@
+"""``Megakernel``: turns scheduled ops into a native program and launches it.
+
+Host runtime behind the reference's public entry point
+(src/machete/megakernel/megakernel.py: ``MegakernelConfig`` :174-221,
+``Megakernel.__init__`` :490, ``compile`` :1594, ``run`` :2183,
+``bench_spec`` :2206, ``create_megakernel`` :2293).  The constructor lowers
+every ``ScheduledOp`` through its op class, infers dependencies and builds the
+tables; ``compile()`` uploads them through the C ABI (``mk_create``);
+``run()`` is one kernel launch (``mk_run``) with no per-launch host work: the
+kernel resets its own counters, so launches can be queued back to back or
+captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import warnings
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import _native as N
+from .lowering import LowerCtx, NativeOp
+from .ops import ScheduledOp
+from .scheduling import BackwardScheduler, BuiltProgram, InstructionStreamBuilder, TileScheduler
+
+CTRL_BYTES = 4096
+MAX_PAGES = 32
+NUM_DMA_WARPS = 1
+NUM_CONSUMER_WARPS = 8
+
+# Used when no CUDA device is present (table building and CPU tests): B200.
+_DEFAULT_SMS = 148
+_DEFAULT_SMEM_OPTIN = 232448
+
+
+@dataclass
+class MegakernelConfig:
+    """Launch configuration.
+
+    Field-compatible with the reference dataclass; fields that steer its JIT
+    or warp-role split (``threads_per_block``, ``dma_reg_count``,
+    ``mma_reg_count``, ``opt_level``, ``loader_idle_sleep_ns``,
+    ``relaxed_global_barriers``, ``global_barrier_sleep_ns``) are accepted and
+    ignored: the precompiled kernel always runs 1 loader + 8 consumer warps.
+    ``page_size`` is likewise accepted for parity with ``schedule(page_size=)``;
+    the native ring page is sized from the ops (``native_kc``).
+    """
+
+    threads_per_block: int = 256
+    num_sms: Optional[int] = None
+    page_size: int = 49152
+    num_pages: Optional[int] = None
+    tracing: bool = False
+    dma_reg_count: int = 40
+    mma_reg_count: int = 232
+    loader_idle_sleep_ns: int = 100
+    relaxed_global_barriers: bool = True
+    global_barrier_sleep_ns: int = 8
+    opt_level: int = 2
+    peer_buffers: Optional[Dict[str, List[Any]]] = None
+    peer_barriers: Optional[Any] = None
+    device_idx: int = 0
+    num_devices: int = 1
+    # native extensions
+    native_kc: Optional[int] = None      # K columns per bf16 weight page (default 512)
+    native_kc_fp4: Optional[int] = None  # K columns per NVFP4 weight page (default 2048)
+    timeout_ms: int = 1000               # bound of every device-side wait
+    fuse: bool = True                    # allow peephole fusion of op chains
+
+
+def _device_index(device) -> int:
+    if isinstance(device, int):
+        return device
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise ValueError(f"Megakernel runs on CUDA devices only, got {device!r}")
+    return dev.index if dev.index is not None else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
+
+
+class Megakernel:
+    """A decode-step program for the persistent sm_100a kernel.
+
+    Args:
+        ops: list of ``ScheduledOp`` in program order.
+        config: ``MegakernelConfig`` (optional).
+        device: CUDA device of the tensors.
+        scheduler: unit-placement policy (``BackwardScheduler`` by default).
+    """
+
+    def __init__(self, ops: Sequence[ScheduledOp], config: Optional[MegakernelConfig] = None,
+                 device="cuda", scheduler: Optional[TileScheduler] = None):
+        ops = list(ops)
+        if not ops:
+            raise ValueError("Megakernel needs at least one scheduled op")
+        self.ops = ops
+        self.config = config or MegakernelConfig()
+        self.scheduler = scheduler or BackwardScheduler()
+        self._device = device
+        self._handle = C.c_void_p()
+        self._workspace = None
+        self._arrays = None
+
+        cfg = self.config
+        if cfg.num_sms is not None and cfg.num_sms < 1:
+            raise ValueError("num_sms must be positive")
+        sms, smem = _DEFAULT_SMS, _DEFAULT_SMEM_OPTIN
+        if torch.cuda.is_available():
+            info = N.device_info(_device_index(device))
+            sms, smem = info["num_sms"], info["smem_optin"]
+        self._smem_optin = smem
+        self.num_sms = cfg.num_sms if cfg.num_sms is not None else sms
+
+        kc = cfg.native_kc or 512
+        kc4 = cfg.native_kc_fp4 or 2048
+        ctx = LowerCtx(num_sms=self.num_sms, page_bytes=0, smem_optin=smem, kc_bf16=kc, kc_fp4=kc4, fuse=cfg.fuse)
+        # page size: the largest need of any op, rounded to 1 KB
+        self._page_bytes = self._plan_page_bytes(ops, ctx)
+        ctx.page_bytes = self._page_bytes
+
+        from .fusion import lower_program
+
+        self.native_ops: List[NativeOp] = lower_program(ops, ctx)
+        builder = InstructionStreamBuilder(self.num_sms)
+        for nop in self.native_ops:
+            builder.add_op(nop)
+        self.program: BuiltProgram = builder.build(self.scheduler)
+
+        self._act_bytes = -(-self.program.act_bytes // 1024) * 1024
+        avail = smem - CTRL_BYTES - self._act_bytes
+        n_pages = min(MAX_PAGES, avail // self._page_bytes)
+        if cfg.num_pages is not None:
+            n_pages = min(n_pages, int(cfg.num_pages))
+        if n_pages < 2:
+            raise ValueError(
+                f"shared memory too small: {self._act_bytes} B of staged activations leave room for "
+                f"{n_pages} pages of {self._page_bytes} B (need >= 2); reduce batch x K"
+            )
+        self._n_pages = int(n_pages)
+
+    # -- planning ---------------------------------------------------------------------------
+    @staticmethod
+    def _plan_page_bytes(ops, ctx: LowerCtx) -> int:
+        need = 16384  # attention pages: 4 * D * block tokens
+        from .lowering import bf16_page_need, fp4_page_need
+
+        uses_fp4 = any(getattr(op.op_cls, "uses_nvfp4", False) for op in ops)
+        need = max(need, bf16_page_need(ctx.kc_bf16))
+        if uses_fp4:
+            need = max(need, fp4_page_need(ctx.kc_fp4))
+        return -(-need // 1024) * 1024
+
+    # -- properties mirrored from the reference -------------------------------------------------
+    @property
+    def total_tiles(self) -> int:
+        return int(self.program.cta_instr_begin[-1])
+
+    @property
+    def num_barriers(self) -> int:
+        return int(self.program.n_counters)
+
+    @property
+    def smem_size(self) -> int:
+        return CTRL_BYTES + self._act_bytes + self._n_pages * self._page_bytes
+
+    @property
+    def grid(self):
+        return (self.program.num_ctas, 1, 1)
+
+    @property
+    def block(self):
+        return ((NUM_CONSUMER_WARPS + NUM_DMA_WARPS) * 32, 1, 1)
+
+    @property
+    def num_pages(self) -> int:
+        return self._n_pages
+
+    @property
+    def page_bytes(self) -> int:
+        return self._page_bytes
+
+    @property
+    def algorithmic_bytes(self) -> int:
+        """HBM bytes the program streams once per launch (weights, scales, KV)."""
+        return self.program.total_bytes
+
+    # -- compile / run ------------------------------------------------------------------------
+    def compile(self) -> "Megakernel":
+        """Upload the program tables to the device (idempotent)."""
+        if self._handle:
+            return self
+        lib = N.lib()
+        dev = _device_index(self._device)
+        p = self.program
+        arrays = {
+            "ops": np.ascontiguousarray(p.ops), "instrs": np.ascontiguousarray(p.instrs),
+            "ib": np.ascontiguousarray(p.cta_instr_begin), "events": np.ascontiguousarray(p.events),
+            "eb": np.ascontiguousarray(p.cta_event_begin), "waits": np.ascontiguousarray(p.waits),
+        }
+        prog = N.Program()
+        prog.n_ops = len(p.ops)
+        prog.n_instrs = int(p.cta_instr_begin[-1])
+        prog.n_events = int(p.cta_event_begin[-1])
+        prog.n_waits = len(p.waits)
+        prog.n_counters = p.n_counters
+        prog.n_ctas = p.num_ctas
+        prog.page_bytes = self._page_bytes
+        prog.n_pages = self._n_pages
+        prog.act_bytes = self._act_bytes
+        prog.timeout_ms = int(self.config.timeout_ms)
+        prog.device = dev
+        prog.ops = arrays["ops"].ctypes.data
+        prog.instrs = arrays["instrs"].ctypes.data
+        prog.cta_instr_begin = arrays["ib"].ctypes.data
+        prog.events = arrays["events"].ctypes.data
+        prog.cta_event_begin = arrays["eb"].ctypes.data
+        prog.waits = arrays["waits"].ctypes.data
+        nbytes = int(lib.mk_workspace_bytes(C.byref(prog)))
+        self._workspace = torch.empty(nbytes + 256, dtype=torch.uint8, device=torch.device("cuda", dev))
+        base = self._workspace.data_ptr()
+        aligned = (base + 255) // 256 * 256
+        prog.workspace = aligned
+        prog.workspace_bytes = nbytes
+        handle = C.c_void_p()
+        N.check(lib.mk_create(C.byref(prog), C.byref(handle)), "mk_create")
+        self._handle = handle
+        self._arrays = arrays
+        self._dev = dev
+        return self
+
+    def run(self, stream=None, sync: bool = True, validate: bool = True) -> None:
+        """Launch one pass of the program.
+
+        ``stream``: a ``torch.cuda.Stream`` / raw handle, default = torch's
+        current stream.  ``sync=True`` waits for completion and raises
+        ``RuntimeError`` if a device-side wait expired.  ``validate=True``
+        checks that the scheduled tensors were not reallocated.
+        """
+        if validate:
+            self._validate_tensors()
+        self.compile()
+        if stream is None:
+            handle = torch.cuda.current_stream(self._dev).cuda_stream
+        elif hasattr(stream, "cuda_stream"):
+            handle = stream.cuda_stream
+        else:
+            handle = int(stream)
+        N.check(N.lib().mk_run(self._handle, C.c_void_p(handle)), "mk_run")
+        if sync:
+            self.wait()
+
+    def wait(self) -> None:
+        """Drain the device and surface device-side errors."""
+        torch.cuda.synchronize(self._dev)
+        st = self.status()
+        if st[0] != 0:
+            N.lib().mk_reset(self._handle, None)
+            torch.cuda.synchronize(self._dev)
+            raise RuntimeError(
+                f"megakernel aborted: {N.STATUS_NAMES.get(int(st[0]), st[0])} "
+                f"(cta={st[1]}, instr={st[2]}, aux={st[3]}, aux2={st[4]}, warp={st[5]})"
+            )
+
+    def status(self) -> np.ndarray:
+        out = (C.c_int32 * 16)()
+        N.check(N.lib().mk_status(self._handle, out), "mk_status")
+        return np.frombuffer(out, dtype=np.int32).copy()
+
+    def read_counters(self) -> np.ndarray:
+        n = self.program.n_counters
+        out = (C.c_int32 * max(1, n))()
+        N.check(N.lib().mk_read_counters(self._handle, out, n), "mk_read_counters")
+        return np.frombuffer(out, dtype=np.int32)[:n].copy()
+
+    def update_op(self, index: int, native_op: NativeOp, stream=None) -> None:
+        """Replace op record ``index`` on the device (e.g. a new cache position)."""
+        self.compile()
+        rec = np.zeros(1, dtype=N.OP_DTYPE)
+        rec[0] = native_op.record(int(self.program.ops[index]["act_key"]))
+        handle = None if stream is None else C.c_void_p(getattr(stream, "cuda_stream", stream))
+        N.check(N.lib().mk_update_op(self._handle, index, rec.ctypes.data, handle), "mk_update_op")
+        self.native_ops[index] = native_op
+
+    def bench_spec(self, setup_fn=None, keep_alive=None) -> dict:
+        """A launch closure plus byte accounting for benchmark harnesses."""
+        self.compile()
+
+        def launch():
+            self.run(sync=False, validate=False)
+
+        return {"launch": launch, "setup": setup_fn, "bytes": self.algorithmic_bytes, "keep_alive": keep_alive}
+
+    def _validate_tensors(self) -> None:
+        for op in self.ops:
+            for name, ptr in op.tensor_ptrs.items():
+                ref = op.tensor_refs.get(name)
+                if ref is not None and ref.data_ptr() != ptr:
+                    raise RuntimeError(
+                        f"{op.op_cls.__name__}: tensor '{name}' was reallocated after schedule(); "
+                        f"tensors are captured by pointer"
+                    )
+
+    def __del__(self):
+        try:
+            if self._handle:
+                N.lib().mk_destroy(self._handle)
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
+def create_megakernel(ops, num_sms=None, **cfg) -> Megakernel:
+    """Convenience constructor (reference megakernel.py:2293)."""
+    known = {f for f in MegakernelConfig.__dataclass_fields__}
+    unknown = set(cfg) - known
+    if unknown:
+        warnings.warn(f"create_megakernel: ignoring unknown config fields {sorted(unknown)}", stacklevel=2)
+    config = MegakernelConfig(num_sms=num_sms, **{k: v for k, v in cfg.items() if k in known})
+    return Megakernel(ops, config=config)
+
+
+__all__ = ["Megakernel", "MegakernelConfig", "create_megakernel", "NUM_DMA_WARPS"]

@@ -1,0 +1,52 @@
+"""The C-ABI library: it loads, exports every declared symbol, and the struct layouts agree."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from machete_b200 import _native as N
+
+HEADER = Path(__file__).resolve().parents[1] / "include" / "machete_b200.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(mk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_functions_are_exported():
+    lib = N.lib()
+    names = declared_functions()
+    assert set(N.EXPORTS) == set(names)
+    for name in names:
+        assert hasattr(lib, name), name
+    assert lib.mk_abi_version() == N.ABI_VERSION
+
+
+def test_struct_layouts_match_header():
+    assert N.OP_DTYPE.itemsize == 384
+    assert N.OP_DTYPE.fields["i"][1] == 16 and N.OP_DTYPE.fields["f"][1] == 112
+    assert N.OP_DTYPE.fields["p"][1] == 128 and N.OP_DTYPE.fields["s"][1] == 256
+    assert N.INSTR_DTYPE.itemsize == 32 and N.EVENT_DTYPE.itemsize == 32 and N.WAIT_DTYPE.itemsize == 8
+    assert ctypes.sizeof(N.Program) == 12 * 4 + 8 * 8
+
+
+def test_enum_values_match_header():
+    text = HEADER.read_text()
+    for name, value in (("MK_OP_MATVEC", N.OP_MATVEC), ("MK_OP_ATTN_SPLIT", N.OP_ATTN_SPLIT),
+                        ("MK_OP_TOP1_FINAL", N.OP_TOP1_FINAL)):
+        assert re.search(rf"{name} = {value}\b", text), name
+    assert f"#define MK_ABI_VERSION {N.ABI_VERSION}" in text
+
+
+def test_host_errors_without_a_gpu():
+    lib = N.lib()
+    assert lib.mk_workspace_bytes(None) == 0
+    assert lib.mk_standalone_workspace_bytes() >= 1 << 20
+    handle = ctypes.c_void_p()
+    rc = lib.mk_create(None, ctypes.byref(handle))
+    assert rc != 0 and b"null program" in lib.mk_last_error()
+    assert lib.mk_run(None, None) != 0

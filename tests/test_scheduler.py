@@ -1,0 +1,180 @@
+"""Host scheduler: dependency inference, fusion, placement, table invariants, deadlock freedom."""
+
+import numpy as np
+import pytest
+import torch
+
+from machete_b200.kernels.attention import flash_decoding_schedule
+from machete_b200.kernels.decode_matvec import (MatvecResidualSm100Op, MatvecSm100Op, schedule_decode_layer_sm100,
+                                                schedule_final_sm100)
+from machete_b200.kernels.gemm import GemmOp
+from machete_b200.kernels.glu import GLUOp
+from machete_b200.kernels.llama1b import schedule_decode_model_sm100
+from machete_b200.kernels.rms_norm import RMSNormOp
+from machete_b200.megakernel import (BackwardScheduler, Megakernel, MegakernelConfig, OverlapTileScheduler,
+                                     simulate)
+from tests.util import llama_weights
+
+BF = torch.bfloat16
+
+
+def small_model(num_layers=2, B=1, T=256, hidden=256, inter=512, nq=4, nkv=2, hd=64, vocab=512):
+    w = llama_weights(num_layers, hidden, inter, nq * hd, nkv * hd, hd // 2, T)
+    kc = [torch.zeros(B, T, nkv, hd, dtype=BF) for _ in range(num_layers)]
+    vc = [torch.zeros(B, T, nkv, hd, dtype=BF) for _ in range(num_layers)]
+    xb = [torch.zeros(B, 1, hidden, dtype=BF) for _ in range(2)]
+    rb = [torch.zeros(B, 1, hidden, dtype=BF) for _ in range(2)]
+    bufs = dict(q_buf=torch.zeros(B, 1, nq * hd, dtype=BF), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF),
+                mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF))
+    return w, kc, vc, xb, rb, bufs, dict(hidden_size=hidden, intermediate_size=inter, num_q_heads=nq,
+                                         num_kv_heads=nkv, head_dim=hd)
+
+
+def test_chain_dependencies_and_counters():
+    x = torch.zeros(1, 4, 256, dtype=BF)
+    y = torch.zeros_like(x)
+    h = torch.zeros(1, 4, 1024, dtype=BF)
+    g = torch.zeros(1, 4, 512, dtype=BF)
+    out = torch.zeros(1, 4, 256, dtype=BF)
+    ops = RMSNormOp.schedule(x=x, weight=torch.ones(256, dtype=BF), y=y)
+    ops += GemmOp.schedule(a=y, b=torch.zeros(1024, 256, dtype=BF), c=h)
+    ops += GLUOp.schedule(x=h, y=g)
+    ops += GemmOp.schedule(a=g, b=torch.zeros(256, 512, dtype=BF), c=out)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8))
+    deps = mk.program.deps
+    assert [d.coarse for d in deps] == [[], [0], [1], [2]]
+    assert mk.num_barriers == 4
+    final = simulate(mk.program)
+    assert (final == mk.program.counter_expected[:len(final)]).all()
+    assert mk.total_tiles == sum(op.n_units for op in mk.native_ops)
+
+
+def test_war_and_in_place_edges():
+    a = torch.zeros(1, 1, 256, dtype=BF)
+    b = torch.zeros(1, 1, 256, dtype=BF)
+    w = torch.zeros(256, 256, dtype=BF)
+    ops = MatvecSm100Op.schedule(a=a, weight=w, y=b)                       # 0: writes b
+    ops += MatvecSm100Op.schedule(a=b, weight=w, y=torch.zeros_like(a))    # 1: reads b
+    ops += MatvecSm100Op.schedule(a=a, weight=w, y=b)                      # 2: overwrites b -> WAR on 1
+    ops += MatvecResidualSm100Op.schedule(a=a, weight=w, residual_in=b, residual_out=b)   # 3: in place on b
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=4, fuse=False))
+    deps = [d.coarse for d in mk.program.deps]
+    assert deps[1] == [0]
+    assert deps[2] == [1]          # WAW on op 0 is implied by op 1
+    assert deps[3] == [2]
+    simulate(mk.program)
+
+
+def test_layer_schedule_dependencies_and_fusion():
+    w, kc, vc, xb, rb, bufs, dims = small_model(num_layers=1)
+    layer = schedule_decode_layer_sm100(layer_idx=0, batch=1, seq_len=1, cache_pos=200, weights=w, k_cache=kc[0],
+                                        v_cache=vc[0], x_in=xb[0], residual_in=rb[0], x_out=xb[1],
+                                        residual_out=rb[1], kv_group_size=2, **bufs, **dims)
+    names = [op.op_cls.__name__ for op in layer.ops]
+    assert names[:3] == ["RmsQMatvecRopeSm100Op", "RmsKMatvecRopeCacheSm100Op", "RmsVMatvecCacheSm100Op"]
+    assert names[3:5] == ["FlashDecodingSplitBSHDOp", "FlashDecodingCombineBSHDOp"]
+    assert names[5:] == ["MatvecResidualSm100Op", "RmsGateUpSiluSm100Op", "MatvecSm100Op", "MatvecResidualSm100Op"]
+    fused = Megakernel(layer.ops, config=MegakernelConfig(num_sms=16))
+    plain = Megakernel(layer.ops, config=MegakernelConfig(num_sms=16, fuse=False))
+    assert [o.name for o in fused.native_ops][-1] == "FusedDownProj" and len(fused.native_ops) == 8
+    assert len(plain.native_ops) == 9
+    d = fused.program.deps
+    assert d[0].coarse == [] and d[1].coarse == [] and d[2].coarse == []
+    assert d[3].coarse == [0, 1, 2] and d[3].loader == [1, 2]           # split waits for q, k, v; loader for k, v
+    assert d[4].coarse == [] and list(d[4].fine) == [3]                 # combine waits per KV head
+    assert d[5].coarse == [4] and d[6].coarse == [5] and d[7].coarse == [6]
+    # q/k/v share one staged activation; o-proj, gate/up and down each stage their own
+    keys = [int(k) for k in fused.program.ops["act_key"]]
+    assert keys[0] == keys[1] == keys[2] != 0
+    assert len({keys[0], keys[5], keys[6], keys[7]}) == 4
+    # only the split units that cover the appended token row carry loader waits
+    ins = fused.program.instrs
+    split = ins[ins["op"] == 3]
+    n_splits = fused.native_ops[3].i[6]
+    with_lw = split[split["n_lwaits"] > 0]["unit"]
+    assert len(with_lw) == 2 and all(u % n_splits == n_splits - 1 for u in with_lw)
+    for prog in (fused.program, plain.program):
+        final = simulate(prog)
+        assert (final == prog.counter_expected[:len(final)]).all()
+
+
+def test_act_keys_change_across_layers_and_residual_out_written_once():
+    w, kc, vc, xb, rb, bufs, dims = small_model(num_layers=3)
+    tv, ti = torch.zeros(1, 1), torch.zeros(1, 1, dtype=torch.int32)
+    ops, _ = schedule_decode_model_sm100(batch=1, cache_pos=100, weights=w, k_cache=kc, v_cache=vc, x_buffers=xb,
+                                         residual_buffers=rb, final_norm=torch.ones(256, dtype=BF),
+                                         lm_head=torch.zeros(512, 256, dtype=BF), top_values=tv, top_indices=ti,
+                                         num_layers=3, **bufs, **dims)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=32), scheduler=OverlapTileScheduler())
+    keys = [int(k) for k in mk.program.ops["act_key"]]
+    q_ops = [i for i, o in enumerate(mk.native_ops) if o.name == "RmsQMatvecRopeSm100Op"]
+    assert len({keys[i] for i in q_ops}) == 3          # layers 0 and 2 reuse buffers but not keys
+    ev = mk.program.events
+    for i in q_ops:
+        flagged = ev[(ev["op"] == i) & (ev["flags"] == 1)]
+        assert len(flagged) == 1
+    final = simulate(mk.program)
+    assert (final == mk.program.counter_expected[:len(final)]).all()
+    # every CTA list is a subsequence of program order
+    p = mk.program
+    for c in range(p.num_ctas):
+        rows = p.instrs[p.cta_instr_begin[c]:p.cta_instr_begin[c + 1]]
+        assert (np.diff(rows["op"]) >= 0).all()
+
+
+def test_placements_cover_every_unit_once():
+    w, kc, vc, xb, rb, bufs, dims = small_model(num_layers=1)
+    layer = schedule_decode_layer_sm100(layer_idx=0, batch=1, seq_len=1, cache_pos=10, weights=w, k_cache=kc[0],
+                                        v_cache=vc[0], x_in=xb[0], residual_in=rb[0], x_out=xb[1],
+                                        residual_out=rb[1], kv_group_size=2, **bufs, **dims)
+    for sched in (BackwardScheduler(), OverlapTileScheduler()):
+        mk = Megakernel(layer.ops, config=MegakernelConfig(num_sms=7), scheduler=sched)
+        ins = mk.program.instrs
+        for j, op in enumerate(mk.native_ops):
+            units = np.sort(ins[ins["op"] == j]["unit"])
+            assert (units == np.arange(op.n_units)).all()
+        spread = mk.program.bytes_per_cta
+        if isinstance(sched, OverlapTileScheduler):
+            assert spread.max() - spread.min() <= max(o.bytes_of(0) for o in mk.native_ops)
+
+
+def test_simulator_detects_a_lost_signal():
+    x = torch.zeros(1, 1, 256, dtype=BF)
+    ops = MatvecSm100Op.schedule(a=x, weight=torch.zeros(256, 256, dtype=BF), y=torch.zeros_like(x))
+    ops += MatvecSm100Op.schedule(a=ops[0].tensor_refs["y"], weight=torch.zeros(256, 256, dtype=BF), y=torch.zeros_like(x))
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=4))
+    mk.program.waits["expected"][:] += 1          # nobody will ever signal that often
+    with pytest.raises(RuntimeError, match="deadlock"):
+        simulate(mk.program)
+
+
+def test_flash_decoding_schedule_shapes_and_splits():
+    q = torch.zeros(2, 1, 8, 64, dtype=BF)
+    k = torch.zeros(2, 1000, 2, 64, dtype=BF)
+    o = torch.zeros_like(q)
+    ops, cfg = flash_decoding_schedule(q, k, k.clone(), o, num_splits=5, kv_group_size=4)
+    split, comb = ops
+    assert split.tensor_refs["o_partial"].shape == (2, 8, 5, 1, 64)
+    assert split.tensor_refs["lse_partial"].shape == (2, 8, 5, 1)
+    assert split.static_dims["num_splits"] == 5 and comb.tensor_refs["lse"].shape == (2, 8, 1)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8))
+    sp = mk.native_ops[0]
+    assert sp.n_units == 2 * 2 * 1 * 5 and sp.n_groups == 4
+    ts = sp.i[9]
+    assert ts % 16 == 0 and ts * 5 >= 1000
+    assert int(np.sum(sp.unit_bytes)) == 2 * 2 * 1000 * 64 * 2 * 2     # K and V read exactly once
+    with pytest.raises(ValueError):
+        flash_decoding_schedule(q, k[..., :32], k[..., :32], o)
+
+
+def test_final_schedule_and_too_many_rows():
+    x = torch.zeros(1, 1, 256, dtype=BF)
+    ops = schedule_final_sm100(x=x, residual_in=x.clone(), residual_out=x.clone(), final_norm=torch.ones(256, dtype=BF),
+                               lm_head=torch.zeros(1000, 256, dtype=BF), logits=torch.zeros(1, 1, 1000, dtype=BF),
+                               seq_len=1)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=4))
+    assert [o.n_units for o in mk.native_ops] == [1, 63]
+    big = torch.zeros(1, 64, 256, dtype=BF)
+    with pytest.raises(ValueError, match="at most 32"):
+        Megakernel(MatvecSm100Op.schedule(a=big, weight=torch.zeros(256, 256, dtype=BF), y=torch.zeros_like(big)),
+                   config=MegakernelConfig(num_sms=4))
