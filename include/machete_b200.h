@@ -226,6 +226,9 @@ int mk_run(mk_handle_t h, void* cuda_stream);
 /* Copy the 16-word device status block to `out` (synchronises the device).
  * out[0] == 0 means no device-side error. */
 int mk_status(mk_handle_t h, int32_t out[16]);
+/* The same status block read straight from a workspace (it sits at offset
+ * 0): for the standalone entry points, which hand out no handle. */
+int mk_workspace_status(const void* workspace, int32_t out[16]);
 /* Clear counters and status after a device-side error. */
 int mk_reset(mk_handle_t h, void* cuda_stream);
 /* Overwrite op record `op_index` (e.g. new cache position or pointers). */

@@ -55,7 +55,15 @@ STATUS_NAMES = {
     2: "page-full wait timed out",
     3: "page-empty wait timed out",
     4: "unknown opcode",
+    5: "ring-slot turn wait timed out",
 }
+
+
+def workspace_status(workspace_ptr: int):
+    """Status block of a standalone call's workspace (synchronises the device)."""
+    out = (C.c_int32 * 16)()
+    check(lib().mk_workspace_status(C.c_void_p(workspace_ptr), out), "mk_workspace_status")
+    return list(out)
 
 # numpy record layouts of the C structs
 OP_DTYPE = np.dtype([
@@ -88,7 +96,7 @@ class Program(C.Structure):
 
 EXPORTS = [
     "mk_abi_version", "mk_last_error", "mk_device_info", "mk_workspace_bytes", "mk_create", "mk_run",
-    "mk_status", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
+    "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
 ]
 
@@ -139,6 +147,7 @@ def _declare(h: C.CDLL) -> None:
     h.mk_create.argtypes = [C.POINTER(Program), C.POINTER(vp)]
     h.mk_run.argtypes = [vp, vp]
     h.mk_status.argtypes = [vp, C.POINTER(i32)]
+    h.mk_workspace_status.argtypes = [vp, C.POINTER(i32)]
     h.mk_reset.argtypes = [vp, vp]
     h.mk_update_op.argtypes = [vp, i32, vp, vp]
     h.mk_read_counters.argtypes = [vp, C.POINTER(i32), i32]
@@ -148,7 +157,7 @@ def _declare(h: C.CDLL) -> None:
     h.mk_matvec_nvfp4.argtypes = [vp, vp, f32, i32, vp, vp, i32, i32, i32, vp, u64, vp]
     h.mk_flash_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32,
                                   vp, u64, vp]
-    for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_reset", "mk_update_op",
+    for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op",
                  "mk_read_counters", "mk_destroy", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode"):
         getattr(h, name).restype = C.c_int
 

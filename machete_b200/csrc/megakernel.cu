@@ -186,6 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
       mbar_init(smem_u32(&c.ctrl->full[i]), 32);
       mbar_init(smem_u32(&c.ctrl->empty[i]), 1);
     }
+    for (int i = 0; i < kMaxPages; ++i) c.ctrl->released[i] = 0;
     c.ctrl->abort_flag = 0;
     c.ctrl->is_last = 0;
     fence_mbar_init();
@@ -543,6 +544,13 @@ int mk_status(mk_handle_t h, int32_t out[16]) {
   using namespace mk;
   if (!h || !out) return fail(-1, "null argument");
   CUDA_TRY(cudaMemcpy(out, h->ws + h->layout.state, 16 * sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+int mk_workspace_status(const void* workspace, int32_t out[16]) {
+  using namespace mk;
+  if (!workspace || !out) return fail(-1, "null argument");
+  CUDA_TRY(cudaMemcpy(out, workspace, 16 * sizeof(int32_t), cudaMemcpyDeviceToHost));
   return 0;
 }
 

@@ -22,7 +22,8 @@ enum {
   MK_ST_TIMEOUT_COUNTER = 1,  // dependency counter never reached `expected`
   MK_ST_TIMEOUT_PAGE_FULL = 2,
   MK_ST_TIMEOUT_PAGE_EMPTY = 3,
-  MK_ST_BAD_OP = 4
+  MK_ST_BAD_OP = 4,
+  MK_ST_TIMEOUT_PAGE_TURN = 5  // earlier fills of a ring slot were never handed back
 };
 
 // Device memory block owned by a handle (lives in the caller's workspace).
@@ -57,6 +58,8 @@ struct Ctrl {
   int32_t abort_flag;
   int32_t is_last;
   int32_t pad[14];
+  // released[slot] = number of fills of the slot that consumers have handed back
+  uint32_t released[kMaxPages];
   float red[kConsumerWarps * 32];  // block-reduction scratch (per row, per warp)
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
@@ -173,18 +176,58 @@ __device__ __forceinline__ bool wait_counters(Ctx& c, int n, int off) {
 __device__ __forceinline__ uint32_t full_bar(Ctx& c, int slot) { return smem_u32(&c.ctrl->full[slot]); }
 __device__ __forceinline__ uint32_t empty_bar(Ctx& c, int slot) { return smem_u32(&c.ctrl->empty[slot]); }
 
+// Consumer warps run independently of one another, so a warp may ask for fill
+// k of a slot while the slot is still two or more fills behind; an mbarrier
+// only tells odd from even phases.  Waiting first until the k previous fills
+// have been handed back pins the full-barrier to phase k (pending) or k + 1
+// (complete), where the parity test is unambiguous.
+__device__ __forceinline__ bool wait_released(Ctx& c, uint32_t slot, uint32_t k, int aux) {
+  if (c.dead) return false;
+  volatile uint32_t* r = &c.ctrl->released[slot];
+  if (__all_sync(0xffffffffu, *r >= k)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (__all_sync(0xffffffffu, *r >= k)) return true;
+      nanosleep(20);
+    }
+    int give_up = 0;
+    if (c.lane == 0) {
+      if (aborted(c)) {
+        give_up = 1;
+      } else if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
+        report(c, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)k);
+        give_up = 1;
+      }
+    }
+    give_up = __shfl_sync(0xffffffffu, give_up, 0);
+    if (give_up) {
+      c.dead = true;
+      return false;
+    }
+  }
+}
+
 // Consumer side: wait until ring entry `seq` holds data; returns its address.
 __device__ __forceinline__ bool page_acquire(Ctx& c, uint32_t seq, uint32_t& page_addr) {
   const int np = c.pv->n_pages;
   const uint32_t slot = seq % np;
-  const uint32_t par = (seq / np) & 1u;
+  const uint32_t k = seq / np;
   page_addr = c.pages_u32 + slot * (uint32_t)c.pv->page_bytes;
-  return wait_mbar(c, full_bar(c, slot), par, MK_ST_TIMEOUT_PAGE_FULL, (int)seq);
+  if (k > 0 && !wait_released(c, slot, k, (int)seq)) return false;
+  return wait_mbar(c, full_bar(c, slot), k & 1u, MK_ST_TIMEOUT_PAGE_FULL, (int)seq);
 }
 // Consumer side: hand ring entry `seq` back to the loader.
 __device__ __forceinline__ void page_release(Ctx& c, uint32_t seq) {
   __syncwarp();
-  if (c.lane == 0) mbar_arrive(empty_bar(c, seq % c.pv->n_pages));
+  if (c.lane == 0) {
+    const int np = c.pv->n_pages;
+    const uint32_t slot = seq % np;
+    mbar_arrive(empty_bar(c, slot));
+    __threadfence_block();
+    *reinterpret_cast<volatile uint32_t*>(&c.ctrl->released[slot]) = seq / np + 1u;
+  }
 }
 
 // Signal completion of a work unit: all lanes' global writes are ordered

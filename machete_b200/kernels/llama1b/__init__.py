@@ -63,6 +63,8 @@ def schedule_decode_model_sm100(
     num_q_heads=LLAMA1B_Q_DIM // LLAMA1B_HEAD_DIM,
     num_kv_heads=LLAMA1B_KV_DIM // LLAMA1B_HEAD_DIM,
     head_dim=LLAMA1B_HEAD_DIM,
+    x_in=None,
+    residual_in=None,
 ):
     """Schedule a full decode step: ``(ops, keep_alive)``.
 
@@ -70,17 +72,25 @@ def schedule_decode_model_sm100(
     tensors; ``x_buffers`` / ``residual_buffers`` hold two ``(B, S, hidden)``
     ping-pong buffers each: layer ``i`` reads pair ``i % 2`` and writes the
     other.  The layer input is the pair (MLP delta ``x``, residual stream).
+    With ``x_in`` / ``residual_in`` the first layer reads those tensors instead
+    of pair 0, so the step never overwrites its own inputs and can be
+    re-launched unchanged.
     """
     if len(x_buffers) < 2 or len(residual_buffers) < 2:
         raise ValueError("x_buffers and residual_buffers must each contain two ping-pong buffers")
+    if (x_in is None) != (residual_in is None):
+        raise ValueError("x_in and residual_in must be given together")
     ops, keep = [], []
     cur = 0
+    cur_x, cur_r = x_buffers[0], residual_buffers[0]
+    if x_in is not None:
+        cur, cur_x, cur_r = 1, x_in, residual_in      # layer 0 writes pair 0
     for layer_idx in range(num_layers):
         nxt = 1 - cur
         layer = schedule_decode_layer_sm100(
             layer_idx=layer_idx, batch=batch, seq_len=seq_len, cache_pos=cache_pos, weights=weights,
-            k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=x_buffers[cur],
-            residual_in=residual_buffers[cur], x_out=x_buffers[nxt], residual_out=residual_buffers[nxt],
+            k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=cur_x,
+            residual_in=cur_r, x_out=x_buffers[nxt], residual_out=residual_buffers[nxt],
             q_buf=q_buf, attn_out_buf=attn_out_buf, mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps,
             fa_num_splits=fa_num_splits, hidden_size=hidden_size, intermediate_size=intermediate_size,
             num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
@@ -89,6 +99,7 @@ def schedule_decode_model_sm100(
         ops += layer.ops
         keep += layer.keep_alive
         cur = nxt
+        cur_x, cur_r = x_buffers[cur], residual_buffers[cur]
     if final_norm is not None and lm_head is not None:
         if logits is not None and (top_values is not None or top_indices is not None):
             raise ValueError("Provide either logits or top_values/top_indices, not both")
