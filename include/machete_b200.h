@@ -93,7 +93,10 @@ enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1 };
 enum {
   MK_MV_P_W0 = 0, MK_MV_P_W1, MK_MV_P_X, MK_MV_P_RES_IN, MK_MV_P_NORM_W,
   MK_MV_P_RES_OUT, MK_MV_P_OUT, MK_MV_P_EPI_RES, MK_MV_P_COS, MK_MV_P_SIN,
-  MK_MV_P_SC0, MK_MV_P_SC1
+  MK_MV_P_SC0, MK_MV_P_SC1,
+  /* device addresses of the CUtensorMap descriptors of the weights / scales;
+   * filled in by mk_create and mk_update_op, callers leave them zero */
+  MK_MV_P_TM_W0, MK_MV_P_TM_W1, MK_MV_P_TM_SC0, MK_MV_P_TM_SC1
 };
 enum {
   MK_MV_S_WROW = 0,   /* weight row stride, bytes                         */
@@ -154,7 +157,18 @@ typedef struct mk_instr {
   int32_t n_lwaits;       /* loader-side waits (before the unit's loads)     */
   int32_t lwait_off;
   int32_t n_pages;        /* ring pages the unit consumes                    */
+  /* Loader fast path, filled in by mk_create (callers leave these zero): all
+   * the loader warp needs to issue the unit's pages, so that it never reads
+   * the op table on its critical path. */
+  uint64_t ld_maps;       /* device address of the op's 4 tensor maps        */
+  int32_t ld_row_a;       /* first weight row of virtual rows 0-7            */
+  int32_t ld_row_b;       /* first weight row of virtual rows 8-15           */
+  int32_t ld_tiles;       /* 128-byte K-tiles per page                       */
+  int32_t ld_flags;       /* MK_LDF_*                                        */
+  int32_t reserved[2];
 } mk_instr_t;
+
+enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2 };
 
 /* Op-entry event: before a CTA executes instruction `pos` of its list, all
  * of its consumer warps meet, wait for the listed counters and stage the
@@ -229,6 +243,13 @@ int mk_status(mk_handle_t h, int32_t out[16]);
 /* The same status block read straight from a workspace (it sits at offset
  * 0): for the standalone entry points, which hand out no handle. */
 int mk_workspace_status(const void* workspace, int32_t out[16]);
+/* Attach (or, with buffer == NULL, detach) a device buffer that the kernel
+ * fills with 16-byte {globaltimer ns, code, arg} records, `records_per_warp`
+ * per warp of every CTA (9 warps: loader first), followed by one int32 record
+ * count per warp.  Needs n_ctas * 9 * (records_per_warp * 16 + 4) bytes.
+ * Takes the place of the reference's cutedsl-trace lanes
+ * (megakernel/tracing.py:51-153). */
+int mk_set_trace(mk_handle_t h, void* buffer, uint64_t bytes, int32_t records_per_warp);
 /* Clear counters and status after a device-side error. */
 int mk_reset(mk_handle_t h, void* cuda_stream);
 /* Overwrite op record `op_index` (e.g. new cache position or pointers). */

@@ -73,6 +73,9 @@ OP_DTYPE = np.dtype([
 INSTR_DTYPE = np.dtype([
     ("op", "<i4"), ("unit", "<i4"), ("signal", "<i4"), ("n_waits", "<i4"), ("wait_off", "<i4"),
     ("n_lwaits", "<i4"), ("lwait_off", "<i4"), ("n_pages", "<i4"),
+    # loader fast path: left zero here, filled in by mk_create
+    ("ld_maps", "<u8"), ("ld_row_a", "<i4"), ("ld_row_b", "<i4"), ("ld_tiles", "<i4"), ("ld_flags", "<i4"),
+    ("ld_reserved", "<i4", (2,)),
 ])
 EVENT_DTYPE = np.dtype([
     ("pos", "<i4"), ("op", "<i4"), ("n_waits", "<i4"), ("wait_off", "<i4"), ("flags", "<i4"),
@@ -80,7 +83,7 @@ EVENT_DTYPE = np.dtype([
 ])
 WAIT_DTYPE = np.dtype([("counter", "<i4"), ("expected", "<i4")])
 assert OP_DTYPE.itemsize == 16 + 96 + 16 + 128 + 128
-assert INSTR_DTYPE.itemsize == 32 and EVENT_DTYPE.itemsize == 32 and WAIT_DTYPE.itemsize == 8
+assert INSTR_DTYPE.itemsize == 64 and EVENT_DTYPE.itemsize == 32 and WAIT_DTYPE.itemsize == 8
 
 
 class Program(C.Structure):
@@ -96,7 +99,7 @@ class Program(C.Structure):
 
 EXPORTS = [
     "mk_abi_version", "mk_last_error", "mk_device_info", "mk_workspace_bytes", "mk_create", "mk_run",
-    "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
+    "mk_status", "mk_workspace_status", "mk_set_trace", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
 ]
 
@@ -148,6 +151,8 @@ def _declare(h: C.CDLL) -> None:
     h.mk_run.argtypes = [vp, vp]
     h.mk_status.argtypes = [vp, C.POINTER(i32)]
     h.mk_workspace_status.argtypes = [vp, C.POINTER(i32)]
+    h.mk_set_trace.argtypes = [vp, vp, u64, i32]
+    h.mk_set_trace.restype = C.c_int
     h.mk_reset.argtypes = [vp, vp]
     h.mk_update_op.argtypes = [vp, i32, vp, vp]
     h.mk_read_counters.argtypes = [vp, C.POINTER(i32), i32]

@@ -12,6 +12,7 @@
 //
 // Counterpart of the reference's ring loop (megakernel/replay_loops.py:27-824)
 // and launch path (megakernel/megakernel.py:2163-2204).
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -40,12 +41,45 @@ __device__ __forceinline__ mk_instr_t bcast_instr(const mk_instr_t& mine, int sr
   return r;
 }
 
+// Consumers need only the first half of an instruction record.
 __device__ __forceinline__ mk_instr_t load_instr(const mk_instr_t* p) {
   const int4* q = reinterpret_cast<const int4*>(p);
   const int4 a = q[0], b = q[1];
   mk_instr_t r;
   r.op = a.x; r.unit = a.y; r.signal = a.z; r.n_waits = a.w;
   r.wait_off = b.x; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
+  r.ld_maps = 0; r.ld_row_a = 0; r.ld_row_b = 0; r.ld_tiles = 0; r.ld_flags = 0;
+  return r;
+}
+
+// The loader's view: the second half carries everything needed to issue the
+// unit's tiled-TMA pages (tensor-map address, first rows, tiles per page).
+struct LoaderInstr {
+  int op, unit, n_lwaits, lwait_off, n_pages;
+  uint64_t maps;
+  int row_a, row_b, tiles, flags;
+};
+__device__ __forceinline__ LoaderInstr load_loader_instr(const mk_instr_t* p) {
+  const int4* q = reinterpret_cast<const int4*>(p);
+  const int4 a = q[0], b = q[1], c2 = q[2], d = q[3];
+  LoaderInstr r;
+  r.op = a.x; r.unit = a.y; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
+  r.maps = (uint64_t)(uint32_t)c2.x | ((uint64_t)(uint32_t)c2.y << 32);
+  r.row_a = c2.z; r.row_b = c2.w; r.tiles = d.x; r.flags = d.y;
+  return r;
+}
+__device__ __forceinline__ LoaderInstr bcast_loader_instr(const LoaderInstr& m, int src) {
+  LoaderInstr r;
+  r.op = __shfl_sync(0xffffffffu, m.op, src);
+  r.unit = __shfl_sync(0xffffffffu, m.unit, src);
+  r.n_lwaits = __shfl_sync(0xffffffffu, m.n_lwaits, src);
+  r.lwait_off = __shfl_sync(0xffffffffu, m.lwait_off, src);
+  r.n_pages = __shfl_sync(0xffffffffu, m.n_pages, src);
+  r.maps = __shfl_sync(0xffffffffu, m.maps, src);
+  r.row_a = __shfl_sync(0xffffffffu, m.row_a, src);
+  r.row_b = __shfl_sync(0xffffffffu, m.row_b, src);
+  r.tiles = __shfl_sync(0xffffffffu, m.tiles, src);
+  r.flags = __shfl_sync(0xffffffffu, m.flags, src);
   return r;
 }
 
@@ -53,32 +87,72 @@ __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
   const ProgramView& pv = *c.pv;
   const int NP = pv.n_pages;
   uint32_t seq = 0;
+  RingPos rp;
+  rp.slot = 0;
+  rp.k = 0;
   for (int base = ibeg; base < iend && !c.dead; base += 32) {
     const int n = min(32, iend - base);
-    mk_instr_t mine;
+    LoaderInstr mine;
     memset(&mine, 0, sizeof(mine));
-    if (c.lane < n) mine = load_instr(pv.instrs + base + c.lane);
+    if (c.lane < n) mine = load_loader_instr(pv.instrs + base + c.lane);
     for (int i = 0; i < n && !c.dead; ++i) {
-      const mk_instr_t ins = bcast_instr(mine, i);
+      const LoaderInstr ins = bcast_loader_instr(mine, i);
       c.instr_idx = base + i;
       if (ins.n_pages == 0) continue;
-      if (ins.n_lwaits > 0 && !wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
-      const mk_op_t* op = pv.ops + ins.op;
-      const int opcode = op->opcode;
-      for (int p = 0; p < ins.n_pages; ++p) {
-        const uint32_t slot = seq % NP;
-        const uint32_t par = ((seq / NP) & 1u) ^ 1u;
-        if (!wait_mbar(c, empty_bar(c, slot), par, MK_ST_TIMEOUT_PAGE_EMPTY, (int)seq)) break;
-        const uint32_t page = c.pages_u32 + slot * (uint32_t)pv.page_bytes;
-        const uint32_t bar = full_bar(c, slot);
-        if (opcode == MK_OP_MATVEC) {
-          mv_load_page(op, ins.unit, p, page, bar, c.lane);
-        } else if (opcode == MK_OP_ATTN_SPLIT) {
-          at_load_page(op, ins.unit, p, page, bar, c.lane, pv.page_bytes);
-        } else {
-          mbar_arrive(bar);  // an op without loads: hand over an empty page
+      if (ins.n_lwaits > 0) {
+        if (!wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
+        trace(c, TRC_LWAIT_DONE, base + i);
+      }
+      if (ins.maps != 0) {
+        // A matvec unit: tiled-TMA pages, issued by lane 0 alone in a tight
+        // loop from the fields of the instruction record (no op-table read on
+        // this path; a one-thread wait needs no vote).  Fill k of a slot needs
+        // fill k-1 handed back: empty-barrier phase k-1.
+        int issued = 0;
+        if (c.lane == 0) {
+          MvLoad ml;
+          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
+          const bool pair = (ins.flags & MK_LDF_PAIR) != 0;
+          ml.fp4 = (ins.flags & MK_LDF_FP4) != 0;
+          ml.tm_a = maps;
+          ml.tm_b = maps + (pair ? 128 : 0);
+          ml.ts_a = maps + 256;
+          ml.ts_b = maps + (pair ? 384 : 256);
+          ml.rowA0 = ins.row_a;
+          ml.rowB0 = ins.row_b;
+          ml.tiles_per_page = ins.tiles;
+          ml.half = (uint32_t)ins.tiles * 1024u;
+          RingPos q = rp;
+          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
+            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
+                               (int)(seq + issued)))
+              break;
+            trace(c, TRC_LOAD_BEGIN, seq + issued);
+            mv_load_issue(ml, issued, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes, full_bar(c, q.slot));
+            trace(c, TRC_LOAD_ISSUED, seq + issued);
+          }
         }
-        ++seq;
+        issued = __shfl_sync(0xffffffffu, issued, 0);
+        if (issued < ins.n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
+        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
+        seq += (uint32_t)issued;
+      } else {
+        const mk_op_t* op = pv.ops + ins.op;
+        const int opcode = op->opcode;
+        for (int p = 0; p < ins.n_pages; ++p) {
+          if (!wait_mbar(c, empty_bar(c, rp.slot), (rp.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY, (int)seq)) break;
+          trace(c, TRC_LOAD_BEGIN, seq);
+          const uint32_t page = c.pages_u32 + rp.slot * (uint32_t)pv.page_bytes;
+          const uint32_t bar = full_bar(c, rp.slot);
+          if (opcode == MK_OP_ATTN_SPLIT) {
+            at_load_page(op, ins.unit, p, page, bar, c.lane, pv.page_bytes);
+          } else {
+            mbar_arrive(bar);  // an op without loads: hand over an empty page
+          }
+          trace(c, TRC_LOAD_ISSUED, seq);
+          ++seq;
+          ring_next(rp, NP);
+        }
       }
     }
   }
@@ -130,9 +204,11 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
 
   auto do_event = [&]() {
     // Every consumer warp runs this, dead or not: the barriers must balance.
+    trace(c, TRC_EVENT_BEGIN, cur.op);
     named_bar_sync(kConsumerBarrier, T);
     if (w == 0) wait_counters(c, cur.n_waits, cur.wait_off);
     named_bar_sync(kConsumerBarrier, T);
+    trace(c, TRC_EVENT_DEPS, cur.op);
     const mk_op_t* op = pv.ops + cur.op;
     if (op->opcode == MK_OP_MATVEC) {
       const bool need = (op->act_key == 0) || (op->act_key != staged_key);
@@ -140,6 +216,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
       staged_key = op->act_key;
     }
     named_bar_sync(kConsumerBarrier, T);
+    trace(c, TRC_EVENT_END, cur.op);
     ++ev;
     cur.pos = 0x7fffffff;
     if (ev < eend) cur = pv.events[ev];
@@ -157,8 +234,10 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
       if ((local % kConsumerWarps) == w && !c.dead) {
         c.instr_idx = base + i;
         if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
+          trace(c, TRC_UNIT_BEGIN, base + i);
           run_unit(c, pv.ops + ins.op, ins, seq);
           if (!c.dead) signal_unit(c, ins.signal);
+          trace(c, TRC_UNIT_END, base + i);
         }
       }
       seq += (uint32_t)ins.n_pages;
@@ -180,6 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
   c.lane = threadIdx.x & 31;
   c.instr_idx = -1;
   c.dead = false;
+  trace_init(c);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < pv.n_pages; ++i) {
@@ -199,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
     loader_loop(c, ibeg, iend);
   else
     consumer_loop(c, ibeg, iend, ebeg, eend);
+  trace_flush(c);
   __syncthreads();
 
   // The last CTA to finish clears the dependency counters, so the next launch
@@ -244,8 +325,10 @@ static int fail(int code, const char* fmt, ...) {
 
 static inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
+constexpr int kMapsPerOp = 4;  // W0, W1, scales0, scales1
+
 struct Layout {
-  uint64_t state, counters, ops, instrs, ibegin, events, ebegin, waits, total;
+  uint64_t state, counters, ops, instrs, ibegin, events, ebegin, waits, tmaps, total;
 };
 
 static Layout layout_of(const mk_program_t* p) {
@@ -267,11 +350,93 @@ static Layout layout_of(const mk_program_t* p) {
   o = align_up(o + (uint64_t)(p->n_ctas + 1) * 4, 256);
   l.waits = o;
   o = align_up(o + (uint64_t)(p->n_waits > 0 ? p->n_waits : 1) * sizeof(mk_wait_t), 256);
+  l.tmaps = o;
+  o = align_up(o + (uint64_t)p->n_ops * kMapsPerOp * sizeof(CUtensorMap), 256);
   l.total = o;
   return l;
 }
 
 static bool aligned16(uint64_t p) { return (p & 15ull) == 0; }
+
+// ---- tensor maps -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+// A byte matrix of `rows` rows of `row_bytes` valid bytes (row stride `stride`)
+// seen as 128-byte tiles: dims (128 bytes, rows, tiles); one box = 128 bytes x
+// 8 rows x `box_tiles` tiles, written to shared memory tile after tile with
+// the 128-byte swizzle.  Out-of-range rows and bytes read as zero.
+static int encode_tile_map(CUtensorMap* out, uint64_t base, uint64_t rows, uint64_t row_bytes, uint64_t stride,
+                           uint32_t box_tiles) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(-5, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((base & 15) || (stride & 15) || (row_bytes & 15) || rows == 0 || row_bytes == 0)
+    return fail(-2, "tensor map: base, row stride and row length must be 16-byte multiples");
+  const uint64_t tiles = (row_bytes + 127) / 128;
+  // When a row is shorter than one tile the inner extent is the row itself;
+  // otherwise rows are tiled in 128-byte steps and a ragged last tile is
+  // covered by declaring the inner extent 128 (the excess bytes belong to the
+  // same allocation only if row_bytes is a multiple of 128, which callers check).
+  const cuuint64_t inner = row_bytes < 128 ? row_bytes : 128;
+  cuuint64_t dims[3] = {inner, rows, tiles};
+  cuuint64_t strides[2] = {stride, 128};
+  cuuint32_t box[3] = {128, 8, box_tiles};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, reinterpret_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+static uint32_t mv_page_need(int wfmt, int Kc) {
+  return wfmt >= MK_W_NVFP4_F16S32 ? 2u * (uint32_t)(Kc / 256) * 1024u + 2048u : 2u * (uint32_t)(Kc / 64) * 1024u;
+}
+
+// Build the descriptors of matvec op `op` into `maps` (host copies) and point
+// the op record at their device addresses.
+static int build_op_maps(mk_op_t& op, CUtensorMap* maps, uint64_t dev_maps) {
+  if (op.opcode != MK_OP_MATVEC) return 0;
+  const int wf = op.i[MK_MV_WFMT], K = op.i[MK_MV_K], Kc = op.i[MK_MV_KC];
+  const bool fp4 = wf >= MK_W_NVFP4_F16S32;
+  const bool pair = op.i[MK_MV_MODE] == MK_MV_PAIR;
+  const uint64_t rows = (uint64_t)op.i[MK_MV_O];
+  const uint64_t row_bytes = fp4 ? (uint64_t)K / 2 : (uint64_t)K * 2;
+  const uint32_t box_tiles = fp4 ? (uint32_t)(Kc / 256) : (uint32_t)(Kc / 64);
+  int rc = encode_tile_map(&maps[0], op.p[MK_MV_P_W0], rows, row_bytes, (uint64_t)op.s[MK_MV_S_WROW], box_tiles);
+  if (rc) return rc;
+  op.p[MK_MV_P_TM_W0] = dev_maps;
+  if (pair) {
+    rc = encode_tile_map(&maps[1], op.p[MK_MV_P_W1], rows, row_bytes, (uint64_t)op.s[MK_MV_S_WROW], box_tiles);
+    if (rc) return rc;
+    op.p[MK_MV_P_TM_W1] = dev_maps + sizeof(CUtensorMap);
+  }
+  if (fp4) {
+    const uint64_t srow_bytes = (uint64_t)K / 16;
+    rc = encode_tile_map(&maps[2], op.p[MK_MV_P_SC0], rows, srow_bytes, (uint64_t)op.s[MK_MV_S_SCROW], 1);
+    if (rc) return rc;
+    op.p[MK_MV_P_TM_SC0] = dev_maps + 2 * sizeof(CUtensorMap);
+    if (pair) {
+      rc = encode_tile_map(&maps[3], op.p[MK_MV_P_SC1], rows, srow_bytes, (uint64_t)op.s[MK_MV_S_SCROW], 1);
+      if (rc) return rc;
+      op.p[MK_MV_P_TM_SC1] = dev_maps + 3 * sizeof(CUtensorMap);
+    }
+  }
+  return 0;
+}
 
 static int matvec_pages(const mk_op_t& op) {
   const int K = op.i[MK_MV_K], Kc = op.i[MK_MV_KC];
@@ -297,9 +462,15 @@ static int validate_op(const mk_program_t* p, int idx) {
     if (O <= 0 || K <= 0 || M <= 0 || op.i[MK_MV_S] <= 0) return fail(-2, "op %d: bad matvec dims", idx);
     if (M > 32) return fail(-2, "op %d: matvec supports at most 32 activation rows, got %d", idx, M);
     if (wf < 0 || wf > MK_W_NVFP4_E4M3S16) return fail(-2, "op %d: bad weight format", idx);
-    if (fp4 ? (K % 256 != 0 || Kc % 256 != 0) : (K % 32 != 0 || Kc % 32 != 0))
-      return fail(-2, "op %d: K=%d / Kc=%d must be multiples of %d", idx, K, Kc, fp4 ? 256 : 32);
-    const uint64_t need = fp4 ? 16ull * (Kc / 2 + 64) + 16ull * (Kc / 16 + 16) : 16ull * (Kc * 2 + 64);
+    if (fp4 ? (K % 256 != 0 || Kc % 256 != 0) : (K % 64 != 0 || Kc % 64 != 0))
+      return fail(-2, "op %d: K=%d / Kc=%d must be multiples of %d", idx, K, Kc, fp4 ? 256 : 64);
+    if (Kc <= 0 || (fp4 ? Kc > 2048 : Kc > 64 * 256))
+      return fail(-2, "op %d: K slice %d out of range", idx, Kc);
+    if (fp4 && Kc != (K < 2048 ? K : 2048))
+      return fail(-2, "op %d: NVFP4 K slice must be min(K, 2048), got %d", idx, Kc);
+    if (fp4 && K > 2048 && K % 2048 != 0)
+      return fail(-2, "op %d: NVFP4 matvec needs K < 2048 or K %% 2048 == 0, got %d", idx, K);
+    const uint64_t need = mv_page_need(wf, Kc);
     if (need > (uint64_t)p->page_bytes) return fail(-2, "op %d: K slice %d does not fit a %d-byte page", idx, Kc, p->page_bytes);
     if ((uint64_t)M * ((uint64_t)K * 2 + 64) > (uint64_t)p->act_bytes)
       return fail(-2, "op %d: %d x %d activations exceed the %d-byte staging buffer", idx, M, K, p->act_bytes);
@@ -496,9 +667,49 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
   }
   uint8_t* ws = reinterpret_cast<uint8_t*>(prog->workspace);
   CUDA_TRY(cudaMemset(ws + l.state, 0, l.ops - l.state));
-  CUDA_TRY(cudaMemcpy(ws + l.ops, prog->ops, (size_t)prog->n_ops * sizeof(mk_op_t), cudaMemcpyHostToDevice));
-  if (prog->n_instrs)
-    CUDA_TRY(cudaMemcpy(ws + l.instrs, prog->instrs, (size_t)prog->n_instrs * sizeof(mk_instr_t), cudaMemcpyHostToDevice));
+  {
+    // tensor maps of the weight matrices, and op records that point at them
+    std::vector<mk_op_t> ops(prog->ops, prog->ops + prog->n_ops);
+    std::vector<CUtensorMap> maps((size_t)prog->n_ops * kMapsPerOp);
+    memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
+    for (int i = 0; i < prog->n_ops; ++i) {
+      rc = build_op_maps(ops[i], &maps[(size_t)i * kMapsPerOp],
+                         (uint64_t)(ws + l.tmaps) + (uint64_t)i * kMapsPerOp * sizeof(CUtensorMap));
+      if (rc) {
+        cudaSetDevice(prev_dev);
+        return rc;
+      }
+    }
+    CUDA_TRY(cudaMemcpy(ws + l.tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMemcpy(ws + l.ops, ops.data(), ops.size() * sizeof(mk_op_t), cudaMemcpyHostToDevice));
+  }
+  if (prog->n_instrs) {
+    // fill the loader fast path of every matvec unit
+    std::vector<mk_instr_t> instrs(prog->instrs, prog->instrs + prog->n_instrs);
+    for (auto& in : instrs) {
+      in.ld_maps = 0;
+      in.ld_row_a = in.ld_row_b = in.ld_tiles = in.ld_flags = 0;
+      const mk_op_t& op = prog->ops[in.op];
+      if (op.opcode != MK_OP_MATVEC) continue;
+      const bool fp4 = op.i[MK_MV_WFMT] >= MK_W_NVFP4_F16S32;
+      const int mode = op.i[MK_MV_MODE];
+      in.ld_maps = (uint64_t)(ws + l.tmaps) + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
+      in.ld_tiles = fp4 ? op.i[MK_MV_KC] / 256 : op.i[MK_MV_KC] / 64;
+      in.ld_flags = (fp4 ? MK_LDF_FP4 : 0) | (mode == MK_MV_PAIR ? MK_LDF_PAIR : 0);
+      if (mode == MK_MV_PLAIN) {
+        in.ld_row_a = in.unit * 16;
+        in.ld_row_b = in.unit * 16 + 8;
+      } else if (mode == MK_MV_PAIR) {
+        in.ld_row_a = in.ld_row_b = in.unit * 8;
+      } else {
+        const int hd = op.i[MK_MV_HD], d2 = op.i[MK_MV_D2], upb = d2 / 8;
+        const int h = in.unit / upb, j = (in.unit - h * upb) * 8;
+        in.ld_row_a = h * hd + j;
+        in.ld_row_b = in.ld_row_a + d2;
+      }
+    }
+    CUDA_TRY(cudaMemcpy(ws + l.instrs, instrs.data(), instrs.size() * sizeof(mk_instr_t), cudaMemcpyHostToDevice));
+  }
   CUDA_TRY(cudaMemcpy(ws + l.ibegin, prog->cta_instr_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
   if (prog->n_events)
     CUDA_TRY(cudaMemcpy(ws + l.events, prog->events, (size_t)prog->n_events * sizeof(mk_event_t), cudaMemcpyHostToDevice));
@@ -521,6 +732,9 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
   h->pv.page_bytes = prog->page_bytes;
   h->pv.act_bytes = prog->act_bytes;
   h->pv.timeout_ns = (uint64_t)(prog->timeout_ms > 0 ? prog->timeout_ms : 1000) * 1000000ull;
+  h->pv.trace = nullptr;
+  h->pv.trace_cap = 0;
+  h->pv.pad = 0;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
   h->device = prog->device;
@@ -547,6 +761,22 @@ int mk_status(mk_handle_t h, int32_t out[16]) {
   return 0;
 }
 
+int mk_set_trace(mk_handle_t h, void* buffer, uint64_t bytes, int32_t records_per_warp) {
+  using namespace mk;
+  if (!h) return fail(-1, "null handle");
+  if (!buffer || records_per_warp <= 0) {
+    h->pv.trace = nullptr;
+    h->pv.trace_cap = 0;
+    return 0;
+  }
+  const uint64_t warps = (uint64_t)h->n_ctas * (kConsumerWarps + 1);
+  const uint64_t need = warps * records_per_warp * sizeof(TraceRec) + warps * sizeof(int32_t);
+  if (bytes < need || ((uint64_t)buffer & 15)) return fail(-1, "trace buffer needs %llu bytes, 16-byte aligned", (unsigned long long)need);
+  h->pv.trace = reinterpret_cast<TraceRec*>(buffer);
+  h->pv.trace_cap = records_per_warp;
+  return 0;
+}
+
 int mk_workspace_status(const void* workspace, int32_t out[16]) {
   using namespace mk;
   if (!workspace || !out) return fail(-1, "null argument");
@@ -566,8 +796,17 @@ int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_
   using namespace mk;
   if (!h || !op) return fail(-1, "null argument");
   if (op_index < 0 || op_index >= h->n_ops) return fail(-1, "op index %d out of range", op_index);
-  CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.ops + (size_t)op_index * sizeof(mk_op_t), op, sizeof(mk_op_t),
-                           cudaMemcpyHostToDevice, reinterpret_cast<cudaStream_t>(cuda_stream)));
+  // The record may carry new weight pointers: re-encode its tensor maps.
+  mk_op_t rec = *op;
+  CUtensorMap maps[kMapsPerOp];
+  memset(maps, 0, sizeof(maps));
+  uint8_t* dev_maps = h->ws + h->layout.tmaps + (size_t)op_index * kMapsPerOp * sizeof(CUtensorMap);
+  const int rc = build_op_maps(rec, maps, (uint64_t)dev_maps);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  CUDA_TRY(cudaMemcpyAsync(dev_maps, maps, sizeof(maps), cudaMemcpyHostToDevice, st));
+  CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.ops + (size_t)op_index * sizeof(mk_op_t), &rec, sizeof(mk_op_t),
+                           cudaMemcpyHostToDevice, st));
   return 0;
 }
 

@@ -134,9 +134,10 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   float lrow[2] = {0.f, 0.f};
 
   const int np = ins.n_pages;
-  for (int p = 0; p < np; ++p) {
+  RingPos rp = ring_at(seq, c.pv->n_pages);
+  for (int p = 0; p < np; ++p, ring_next(rp, c.pv->n_pages)) {
     uint32_t page;
-    if (!page_acquire(c, seq + p, page)) return;
+    if (!page_acquire(c, rp, page)) return;
     const uint32_t kpage = page, vpage = page + (uint32_t)tn * rowb;
     const int tp0 = u.t_begin + p * tn;
     for (int blk = 0; blk * TN < tn; ++blk) {
@@ -223,7 +224,7 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
         }
       }
     }
-    page_release(c, seq + p);
+    page_release(c, rp);
   }
   // finalise: normalised partial + lse
   float* op_ = reinterpret_cast<float*>(op->p[MK_AT_P_OPART]);
@@ -247,11 +248,23 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   }
 }
 
+template <int D>
+__device__ __noinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq) {
+  at_unit<D>(c, op, ins, seq);
+  UnitResult r;
+  r.dead = c.dead;
+  r.trace_n = c.trace_n;
+  return r;
+}
+
 __device__ __forceinline__ void at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+  UnitResult r;
   if (op->i[MK_AT_D] == 64)
-    at_unit<64>(c, op, ins, seq);
+    r = at_unit_call<64>(c, op, ins, seq);
   else
-    at_unit<128>(c, op, ins, seq);
+    r = at_unit_call<128>(c, op, ins, seq);
+  c.dead = r.dead;
+  c.trace_n = r.trace_n;
 }
 
 // Combine: one unit per (b, query head); all M rows.

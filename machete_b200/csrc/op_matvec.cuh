@@ -18,6 +18,9 @@
 #pragma once
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
+
+#include <type_traits>
+
 #include "shell.cuh"
 
 namespace mk {
@@ -66,53 +69,66 @@ __device__ __forceinline__ MvRows mv_rows(const mk_op_t* op, int unit) {
 __device__ __forceinline__ bool mv_is_fp4(int wfmt) { return wfmt >= MK_W_NVFP4_F16S32; }
 
 // ---- loader ------------------------------------------------------------------
-// Issue the copies of K-slice `p` of `unit` into the page at `page` (shared
-// address).  All 32 loader lanes call this; every lane arrives on `bar` once.
-__device__ __forceinline__ void mv_load_page(const mk_op_t* op, int unit, int p, uint32_t page, uint32_t bar,
-                                             int lane) {
+// Page layout (bf16 / fp16 weights), Kt = Kc / 64 K-tiles per page:
+//   [half A: Kt tiles of 8 rows x 128 B][half B: Kt tiles of 8 rows x 128 B]
+// Half A holds virtual rows 0-7, half B virtual rows 8-15.  Every tile is one
+// 128-byte-swizzled box row group of a 3-D tensor map over the weight matrix
+// (dims: 64 K-values, rows, K-tiles), so a whole half is ONE tiled TMA copy.
+// NVFP4: the same with 256 packed values per 128-byte tile row (Kt4 = Kc / 256
+// tiles), followed by two 1 KB scale tiles (8 rows x 128 B, one per half).
+// Rows past the end of the matrix and K-tiles past K are zero-filled by TMA.
+__device__ __forceinline__ uint32_t mv_half_bytes(int wfmt, int Kc) {
+  return mv_is_fp4(wfmt) ? (uint32_t)(Kc / 256) * 1024u : (uint32_t)(Kc / 64) * 1024u;
+}
+
+// What the loader needs to issue the pages of one unit, gathered once per unit.
+struct MvLoad {
+  const void* tm_a;
+  const void* tm_b;
+  const void* ts_a;
+  const void* ts_b;
+  int rowA0, rowB0;
+  int tiles_per_page;   // K-tiles (weights) per page
+  uint32_t half;
+  bool fp4;
+};
+
+__device__ __forceinline__ MvLoad mv_load_setup(const mk_op_t* op, int unit) {
+  MvLoad l;
   const MvRows r = mv_rows(op, unit);
-  const int K = op->i[MK_MV_K], Kc = op->i[MK_MV_KC];
+  const int Kc = op->i[MK_MV_KC];
   const int wfmt = op->i[MK_MV_WFMT];
-  const int k0 = p * Kc;
-  const int kc = min(Kc, K - k0);
-  const int64_t wrow = op->s[MK_MV_S_WROW];
-  const int nrows = r.nA + r.nB;
-  if (!mv_is_fp4(wfmt)) {
-    const uint32_t seg = (uint32_t)kc * 2u;
-    const uint32_t rs = (uint32_t)Kc * 2u + 64u;
-    if (lane == 0) mbar_arrive_expect_tx(bar, seg * (uint32_t)nrows);
-    __syncwarp();
-    if (lane < 16) {
-      const int g = lane & 7;
-      const bool hi = lane >= 8;
-      const bool valid = g < (hi ? r.nB : r.nA);
-      if (valid) {
-        const uint8_t* src = (hi ? r.wb : r.wa) + (int64_t)((hi ? r.rowB0 : r.rowA0) + g) * wrow + (int64_t)k0 * 2;
-        bulk_g2s(page + (uint32_t)lane * rs, src, seg, bar);
-      }
-    }
+  const bool pair = op->i[MK_MV_MODE] == MK_MV_PAIR;
+  l.fp4 = mv_is_fp4(wfmt);
+  l.tm_a = reinterpret_cast<const void*>(op->p[MK_MV_P_TM_W0]);
+  l.tm_b = reinterpret_cast<const void*>(op->p[pair ? MK_MV_P_TM_W1 : MK_MV_P_TM_W0]);
+  l.ts_a = reinterpret_cast<const void*>(op->p[MK_MV_P_TM_SC0]);
+  l.ts_b = reinterpret_cast<const void*>(op->p[pair ? MK_MV_P_TM_SC1 : MK_MV_P_TM_SC0]);
+  l.rowA0 = r.rowA0;
+  l.rowB0 = r.rowB0;
+  l.tiles_per_page = l.fp4 ? Kc / 256 : Kc / 64;
+  l.half = mv_half_bytes(wfmt, Kc);
+  return l;
+}
+
+// Issue the copies of K-slice `p` into the page at `page` (shared address):
+// two tiled TMA copies (four with NVFP4 scales) and one arrival for the whole
+// loader warp.  Called by loader lane 0 only.
+__device__ __forceinline__ void mv_load_issue(const MvLoad& l, int p, uint32_t page, uint32_t bar) {
+  const int kt0 = p * l.tiles_per_page;
+  if (!l.fp4) {
+    mbar_expect_tx(bar, 2u * l.half);
+    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar);
+    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar);
   } else {
-    const uint32_t pseg = (uint32_t)kc / 2u, sseg = (uint32_t)kc / 16u;
-    const uint32_t ps = (uint32_t)Kc / 2u + 64u, ss = (uint32_t)Kc / 16u + 16u;
-    const int64_t srow = op->s[MK_MV_S_SCROW];
-    if (lane == 0) mbar_arrive_expect_tx(bar, (pseg + sseg) * (uint32_t)nrows);
-    __syncwarp();
-    const int v = lane & 15;
-    const int g = v & 7;
-    const bool hi = v >= 8;
-    const bool valid = g < (hi ? r.nB : r.nA);
-    if (valid) {
-      const int row = (hi ? r.rowB0 : r.rowA0) + g;
-      if (lane < 16) {
-        const uint8_t* src = (hi ? r.wb : r.wa) + (int64_t)row * wrow + k0 / 2;
-        bulk_g2s(page + (uint32_t)v * ps, src, pseg, bar);
-      } else {
-        const uint8_t* src = (hi ? r.sb : r.sa) + (int64_t)row * srow + k0 / 16;
-        bulk_g2s(page + 16u * ps + (uint32_t)v * ss, src, sseg, bar);
-      }
-    }
+    // a scale tile row holds the 128 scale bytes of 2048 K-values = one page
+    mbar_expect_tx(bar, 2u * l.half + 2048u);
+    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar);
+    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar);
+    tma_load_3d(page + 2u * l.half, l.ts_a, 0, l.rowA0, p, bar);
+    tma_load_3d(page + 2u * l.half + 1024u, l.ts_b, 0, l.rowB0, p, bar);
   }
-  if (lane != 0) mbar_arrive(bar);
+  mbar_arrive_n(bar, 32);
 }
 
 // ---- activation staging -----------------------------------------------------------
@@ -333,18 +349,28 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   return d;
 }
 
-template <int NT>
+// Swizzled address of 16-byte chunk `c` of row `r` (0-7) inside a 1 KB tile.
+__device__ __forceinline__ uint32_t tile_chunk(uint32_t tile, int r, int c) {
+  return tile + (uint32_t)r * 128u + (uint32_t)((c ^ r) << 4);
+}
+
+// NT = n-tiles of 8 activation rows; NA = independent accumulator sets (the
+// mma chain on one accumulator is latency-bound, so K-steps rotate over NA).
+template <int NT, int NA>
 __device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
   const int unit = ins.unit;
   const int g = c.lane >> 2, t = c.lane & 3;
   const int K = op->i[MK_MV_K], Kc = op->i[MK_MV_KC], M = op->i[MK_MV_M];
   const int wfmt = op->i[MK_MV_WFMT];
   const uint32_t xs = (uint32_t)K * 2u + 64u;
-  float acc[NT][4];
+  const uint32_t half = mv_half_bytes(wfmt, Kc);
+  float acc[NA][NT][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+  for (int a = 0; a < NA; ++a)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[a][nt][e] = 0.f;
 
   uint32_t xrow[NT];
   bool xok[NT];
@@ -355,98 +381,193 @@ __device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     xrow[nt] = c.act_u32 + (uint32_t)(xok[nt] ? m : 0) * xs;
   }
 
-  const int np = ins.n_pages;  // pages of this unit
-  for (int p = 0; p < np; ++p) {
+  const int np = ins.n_pages;
+  RingPos rp = ring_at(seq, c.pv->n_pages);
+  for (int p = 0; p < np; ++p, ring_next(rp, c.pv->n_pages)) {
     uint32_t page;
-    if (!page_acquire(c, seq + p, page)) return;
+    if (!page_acquire(c, rp, page)) return;
+    trace(c, TRC_PAGE_READY, seq + p);
+    const long long cyc0 = clock64();
     const int k0 = p * Kc;
     const int kc = min(Kc, K - k0);
-    if (wfmt == MK_W_BF16 || wfmt == MK_W_FP16) {
-      const uint32_t rs = (uint32_t)Kc * 2u + 64u;
-      const uint32_t arow_lo = page + (uint32_t)g * rs + (uint32_t)t * 16u;
-      const uint32_t arow_hi = arow_lo + 8u * rs;
-      const uint32_t xoff = (uint32_t)(k0 + t * 8) * 2u;
-      const int steps = kc >> 5;
-#pragma unroll 4
-      for (int ks = 0; ks < steps; ++ks) {
-        const uint4 alo = lds128(arow_lo + (uint32_t)ks * 64u);
-        const uint4 ahi = lds128(arow_hi + (uint32_t)ks * 64u);
+    if (op->reserved & 1) {
+      // diagnostic: consume the page without computing (pipeline cost only)
+    } else if (wfmt == MK_W_BF16 || wfmt == MK_W_FP16) {
+      // One K-tile = 64 K-values = 8 chunks of 16 B per row; this thread takes
+      // chunks 2t and 2t+1 of rows g (half A) and g (half B): with the 128-byte
+      // swizzle the 8 lanes of a shared-memory phase then hit 8 distinct chunks.
+      // The mma wrappers are asm volatile, which the compiler does not move
+      // loads across, so the software pipeline is written out by hand: tiles
+      // are handled two at a time and (for one activation n-tile) the
+      // fragments of the next pair are requested before the mma's of the
+      // current pair are issued.
+      const int tiles = kc >> 6;
+      const uint32_t off0 = (uint32_t)g * 128u + (uint32_t)(((2 * t) ^ g) << 4);      // chunk 2t of row g
+      const uint32_t off1 = (uint32_t)g * 128u + (uint32_t)(((2 * t + 1) ^ g) << 4);  // chunk 2t+1
+      const uint32_t xo0 = (uint32_t)(k0 + 2 * t * 8) * 2u;                           // x offset of chunk 2t
+      struct Frag {
+        uint4 wa[2][2], wb[2][2], x[NT][2][2];   // [tile of the pair][chunk j]
+      };
+      auto load_pair = [&](Frag& f, int kt) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          uint4 xb = make_uint4(0, 0, 0, 0);
-          if (xok[nt]) xb = lds128(xrow[nt] + xoff + (uint32_t)ks * 64u);
-          if (wfmt == MK_W_BF16) {
-            mma_bf16(acc[nt], alo.x, ahi.x, alo.y, ahi.y, xb.x, xb.y);
-            mma_bf16(acc[nt], alo.z, ahi.z, alo.w, ahi.w, xb.z, xb.w);
-          } else {
-            mma_f16(acc[nt], alo.x, ahi.x, alo.y, ahi.y, xb.x, xb.y);
-            mma_f16(acc[nt], alo.z, ahi.z, alo.w, ahi.w, xb.z, xb.w);
-          }
-        }
-      }
-    } else {
-      // NVFP4: per step each thread owns 32 consecutive K values of rows g and
-      // g+8 (16 packed bytes each) and their block scales; values are scaled
-      // in f16 (exact for e2m1 x e4m3) and fed to the f16 tensor-core path.
-      const uint32_t ps = (uint32_t)Kc / 2u + 64u, ss = (uint32_t)Kc / 16u + 16u;
-      const uint32_t prow_lo = page + (uint32_t)g * ps + (uint32_t)t * 16u;
-      const uint32_t prow_hi = prow_lo + 8u * ps;
-      const uint32_t srow_lo = page + 16u * ps + (uint32_t)g * ss + (uint32_t)t * 2u;
-      const uint32_t srow_hi = srow_lo + 8u * ss;
-      const uint32_t xoff = (uint32_t)(k0 + t * 32) * 2u;
-      const int steps = kc >> 7;
-#pragma unroll 1
-      for (int ks = 0; ks < steps; ++ks) {
-        const uint4 plo = lds128(prow_lo + (uint32_t)ks * 64u);
-        const uint4 phi = lds128(prow_hi + (uint32_t)ks * 64u);
-        const uint32_t slo_raw = lds16(srow_lo + (uint32_t)ks * 8u);
-        const uint32_t shi_raw = lds16(srow_hi + (uint32_t)ks * 8u);
-        uint32_t slo[2], shi[2];  // f16x2 broadcast scale for values [0,16) and [16,32)
-        if (wfmt == MK_W_NVFP4_F16S32) {
-          slo[0] = slo[1] = slo_raw | (slo_raw << 16);
-          shi[0] = shi[1] = shi_raw | (shi_raw << 16);
-        } else {
-          __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)slo_raw, __NV_E4M3);
-          __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)shi_raw, __NV_E4M3);
-          slo[0] = (uint32_t)a.x | ((uint32_t)a.x << 16);
-          slo[1] = (uint32_t)a.y | ((uint32_t)a.y << 16);
-          shi[0] = (uint32_t)b.x | ((uint32_t)b.x << 16);
-          shi[1] = (uint32_t)b.y | ((uint32_t)b.y << 16);
-        }
-        const uint32_t pl[4] = {plo.x, plo.y, plo.z, plo.w};
-        const uint32_t ph[4] = {phi.x, phi.y, phi.z, phi.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {  // 8 values (4 bytes) of each row -> two mma k-slots
-          uint32_t al[4], ah[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            al[j] = hmul2(e2m1x2_to_f16x2((pl[q] >> (8 * j)) & 0xffu), slo[q >> 1]);
-            ah[j] = hmul2(e2m1x2_to_f16x2((ph[q] >> (8 * j)) & 0xffu), shi[q >> 1]);
-          }
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t ta = page + (uint32_t)(kt + u) * 1024u, tb = ta + half;
+          f.wa[u][0] = lds128(ta + off0);
+          f.wa[u][1] = lds128(ta + off1);
+          f.wb[u][0] = lds128(tb + off0);
+          f.wb[u][1] = lds128(tb + off1);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            uint4 xb = make_uint4(0, 0, 0, 0);
-            if (xok[nt]) xb = lds128(xrow[nt] + xoff + (uint32_t)ks * 256u + (uint32_t)q * 16u);
-            mma_f16(acc[nt], al[0], ah[0], al[1], ah[1], xb.x, xb.y);
-            mma_f16(acc[nt], al[2], ah[2], al[3], ah[3], xb.z, xb.w);
+            // always load (rows past M read row 0 and are zeroed): no branch in the hot loop
+            const uint4 x0 = lds128(xrow[nt] + xo0 + (uint32_t)(kt + u) * 128u);
+            const uint4 x1 = lds128(xrow[nt] + xo0 + (uint32_t)(kt + u) * 128u + 16u);
+            const uint32_t keep = xok[nt] ? 0xffffffffu : 0u;
+            f.x[nt][u][0] = make_uint4(x0.x & keep, x0.y & keep, x0.z & keep, x0.w & keep);
+            f.x[nt][u][1] = make_uint4(x1.x & keep, x1.y & keep, x1.z & keep, x1.w & keep);
+          }
+        }
+      };
+      auto mma_pair = [&](const Frag& f, int valid, auto is_bf16) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u < valid) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              constexpr int kSets = NA;
+              const int a = (u * 2 + j) % kSets;
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                if constexpr (decltype(is_bf16)::value) {
+                  mma_bf16(acc[a][nt], f.wa[u][j].x, f.wb[u][j].x, f.wa[u][j].y, f.wb[u][j].y, f.x[nt][u][j].x, f.x[nt][u][j].y);
+                  mma_bf16(acc[a][nt], f.wa[u][j].z, f.wb[u][j].z, f.wa[u][j].w, f.wb[u][j].w, f.x[nt][u][j].z, f.x[nt][u][j].w);
+                } else {
+                  mma_f16(acc[a][nt], f.wa[u][j].x, f.wb[u][j].x, f.wa[u][j].y, f.wb[u][j].y, f.x[nt][u][j].x, f.x[nt][u][j].y);
+                  mma_f16(acc[a][nt], f.wa[u][j].z, f.wb[u][j].z, f.wa[u][j].w, f.wb[u][j].w, f.x[nt][u][j].z, f.x[nt][u][j].w);
+                }
+              }
+            }
+          }
+        }
+      };
+      // A page always holds whole tiles up to its capacity (TMA zero-fills past
+      // K), so reading the second tile of the last pair is safe even when odd.
+      auto run_page = [&](auto is_bf16) {
+        if constexpr (NT == 1) {
+          Frag f0, f1;
+          load_pair(f0, 0);
+#pragma unroll 1
+          for (int kt = 0; kt < tiles; kt += 4) {
+            if (kt + 2 < tiles) load_pair(f1, kt + 2);
+            mma_pair(f0, min(2, tiles - kt), is_bf16);
+            if (kt + 2 < tiles) {
+              if (kt + 4 < tiles) load_pair(f0, kt + 4);
+              mma_pair(f1, min(2, tiles - kt - 2), is_bf16);
+            }
+          }
+        } else {
+          Frag f;
+#pragma unroll 1
+          for (int kt = 0; kt < tiles; kt += 2) {
+            load_pair(f, kt);
+            mma_pair(f, min(2, tiles - kt), is_bf16);
+          }
+        }
+      };
+      if (wfmt == MK_W_BF16)
+        run_page(std::true_type{});
+      else
+        run_page(std::false_type{});
+    } else {
+      // NVFP4: one tile row = 256 packed values; chunk ch = 32 consecutive K
+      // values of a row with their block scales.  Values are scaled in f16
+      // (exact for e2m1 x e4m3) and fed to the f16 tensor-core path.
+      const int tiles = kc >> 8;
+      const uint32_t sa = page + 2u * half, sb = sa + 1024u;
+#pragma unroll 1
+      for (int kt = 0; kt < tiles; ++kt) {
+        const uint32_t ta = page + (uint32_t)kt * 1024u, tb = ta + half;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int ch = 2 * t + j;
+          const uint4 plo = lds128(tile_chunk(ta, g, ch));
+          const uint4 phi = lds128(tile_chunk(tb, g, ch));
+          // scale bytes of this chunk: row g, byte kt*16 + ch*2 of the 128-byte scale row
+          const uint32_t soff = (uint32_t)g * 128u + (uint32_t)((kt ^ g) << 4) + (uint32_t)ch * 2u;
+          const uint32_t slo_raw = lds16(sa + soff);
+          const uint32_t shi_raw = lds16(sb + soff);
+          uint32_t slo[2], shi[2];  // f16x2 broadcast scale for values [0,16) and [16,32)
+          if (wfmt == MK_W_NVFP4_F16S32) {
+            slo[0] = slo[1] = slo_raw | (slo_raw << 16);
+            shi[0] = shi[1] = shi_raw | (shi_raw << 16);
+          } else {
+            __half2_raw a2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)slo_raw, __NV_E4M3);
+            __half2_raw b2 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)shi_raw, __NV_E4M3);
+            slo[0] = (uint32_t)a2.x | ((uint32_t)a2.x << 16);
+            slo[1] = (uint32_t)a2.y | ((uint32_t)a2.y << 16);
+            shi[0] = (uint32_t)b2.x | ((uint32_t)b2.x << 16);
+            shi[1] = (uint32_t)b2.y | ((uint32_t)b2.y << 16);
+          }
+          const uint32_t pl[4] = {plo.x, plo.y, plo.z, plo.w};
+          const uint32_t ph[4] = {phi.x, phi.y, phi.z, phi.w};
+          const uint32_t xoff = (uint32_t)(k0 + kt * 256 + ch * 32) * 2u;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // 8 values (4 bytes) of each row -> two mma k-slots
+            uint32_t al[4], ah[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              al[b] = hmul2(e2m1x2_to_f16x2((pl[q] >> (8 * b)) & 0xffu), slo[q >> 1]);
+              ah[b] = hmul2(e2m1x2_to_f16x2((ph[q] >> (8 * b)) & 0xffu), shi[q >> 1]);
+            }
+            const int a = q % NA;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              uint4 xb = make_uint4(0, 0, 0, 0);
+              if (xok[nt]) xb = lds128(xrow[nt] + xoff + (uint32_t)q * 16u);
+              mma_f16(acc[a][nt], al[0], ah[0], al[1], ah[1], xb.x, xb.y);
+              mma_f16(acc[a][nt], al[2], ah[2], al[3], ah[3], xb.z, xb.w);
+            }
           }
         }
       }
     }
-    page_release(c, seq + p);
+    const long long cyc1 = clock64();
+    page_release(c, rp);
+    trace(c, TRC_PAGE_DONE, seq + p);
+    trace(c, TRC_PAGE_CYCLES, (uint32_t)(cyc1 - cyc0));
   }
+#pragma unroll
+  for (int a = 1; a < NA; ++a)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[0][nt][e] += acc[a][nt][e];
   const MvRows r = mv_rows(op, unit);
-  mv_epilogue<NT>(c, op, r, unit, acc);
+  mv_epilogue<NT>(c, op, r, unit, acc[0]);
+}
+
+// Each variant is a real function (not inlined into the shell) so that it gets
+// its own register allocation; the context travels by value and the two
+// fields a unit can change come back in the result.
+template <int NT, int NA>
+__device__ __noinline__ UnitResult mv_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq) {
+  mv_unit<NT, NA>(c, op, ins, seq);
+  UnitResult r;
+  r.dead = c.dead;
+  r.trace_n = c.trace_n;
+  return r;
 }
 
 __device__ __forceinline__ void mv_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
   const int M = op->i[MK_MV_M];
+  UnitResult r;
   if (M <= 8)
-    mv_unit<1>(c, op, ins, seq);
+    r = mv_unit_call<1, 4>(c, op, ins, seq);
   else if (M <= 16)
-    mv_unit<2>(c, op, ins, seq);
+    r = mv_unit_call<2, 2>(c, op, ins, seq);
   else
-    mv_unit<4>(c, op, ins, seq);
+    r = mv_unit_call<4, 1>(c, op, ins, seq);
+  c.dead = r.dead;
+  c.trace_n = r.trace_n;
 }
 
 }  // namespace mk

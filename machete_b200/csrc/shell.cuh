@@ -10,7 +10,10 @@
 
 namespace mk {
 
-constexpr int kConsumerWarps = 8;
+// 1 loader + 7 consumers = 8 warps, two per SM sub-partition: each thread may
+// then use up to 255 registers (9 warps would put 3 on one sub-partition and
+// cap the whole kernel at 168, which spilled).
+constexpr int kConsumerWarps = 7;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxPages = 32;
 constexpr int kCtrlBytes = 4096;  // mbarriers + flags + reduction scratch
@@ -49,6 +52,31 @@ struct ProgramView {
   int32_t page_bytes;
   int32_t act_bytes;
   uint64_t timeout_ns;
+  // optional event trace: per (CTA, warp) a ring of trace_cap records, then
+  // one record count per (CTA, warp) after all rings; null = tracing off
+  struct TraceRec* trace;
+  int32_t trace_cap;
+  int32_t pad;
+};
+
+// One trace event: a globaltimer stamp, an event code and an argument.
+struct TraceRec {
+  uint64_t t;
+  uint32_t code;
+  uint32_t arg;
+};
+enum {
+  TRC_LOAD_BEGIN = 1,   // loader: ring slot free, about to issue (arg = ring seq)
+  TRC_LOAD_ISSUED = 2,  // loader: copies issued (arg = ring seq)
+  TRC_PAGE_READY = 3,   // consumer: page data visible (arg = ring seq)
+  TRC_PAGE_DONE = 4,    // consumer: page handed back (arg = ring seq)
+  TRC_UNIT_BEGIN = 5,   // consumer: unit starts (arg = instruction index)
+  TRC_UNIT_END = 6,     // consumer: unit signalled (arg = instruction index)
+  TRC_EVENT_BEGIN = 7,  // consumers meet at an op-entry event (arg = op)
+  TRC_EVENT_DEPS = 8,   // event: producers complete (arg = op)
+  TRC_EVENT_END = 9,    // event: activations staged (arg = op)
+  TRC_LWAIT_DONE = 10,  // loader: loader-side wait satisfied (arg = instruction index)
+  TRC_PAGE_CYCLES = 11  // consumer: SM cycles spent computing on the page just handed back (arg = cycles)
 };
 
 // Shared-memory control block (first kCtrlBytes of dynamic smem).
@@ -76,7 +104,44 @@ struct Ctx {
   int lane;
   int instr_idx;      // global index of the instruction being executed
   bool dead;          // a wait expired somewhere: skip work, keep barriers
+  int trace_n;        // records this warp has written
+  int trace_cap;
+  TraceRec* trace_base;  // this warp's trace ring (lane 0 only), null = off
 };
+
+// What a non-inlined unit handler hands back to the shell.
+struct UnitResult {
+  bool dead;
+  int trace_n;
+};
+
+// The per-warp ring base is resolved once at kernel start (null = tracing
+// off), so a disabled trace point costs one predicated branch.
+__device__ __forceinline__ void trace_init(Ctx& c) {
+  c.trace_n = 0;
+  c.trace_cap = 0;
+  c.trace_base = nullptr;
+  TraceRec* base = c.pv->trace;
+  if (base != nullptr && c.lane == 0) {
+    c.trace_cap = c.pv->trace_cap;
+    c.trace_base = base + ((size_t)blockIdx.x * (kConsumerWarps + 1) + c.warp) * c.trace_cap;
+  }
+}
+__device__ __forceinline__ void trace(Ctx& c, uint32_t code, uint32_t arg) {
+  if (c.trace_base == nullptr) return;
+  if (c.trace_n < c.trace_cap) {
+    TraceRec* r = c.trace_base + c.trace_n;
+    r->t = globaltimer_ns();
+    r->code = code;
+    r->arg = arg;
+  }
+  ++c.trace_n;
+}
+__device__ __forceinline__ void trace_flush(Ctx& c) {
+  if (c.trace_base == nullptr) return;
+  int32_t* counts = reinterpret_cast<int32_t*>(c.pv->trace + (size_t)gridDim.x * (kConsumerWarps + 1) * c.trace_cap);
+  counts[blockIdx.x * (kConsumerWarps + 1) + c.warp] = c.trace_n;
+}
 
 __device__ __forceinline__ void report(Ctx& c, int code, int aux, int aux2) {
   DeviceState* st = c.pv->state;
@@ -101,33 +166,54 @@ __device__ __forceinline__ bool aborted(Ctx& c) {
   return false;
 }
 
+// Slow path shared by the bounded waits: lane 0 decides whether to give up
+// (abort seen, or the time budget spent) and the decision is broadcast.
+__device__ __forceinline__ bool give_up_check(Ctx& c, uint64_t t0, int code, int aux, int aux2) {
+  int give_up = 0;
+  if (c.lane == 0) {
+    if (aborted(c)) {
+      give_up = 1;
+    } else if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
+      report(c, code, aux, aux2);
+      give_up = 1;
+    }
+  }
+  return __shfl_sync(0xffffffffu, give_up, 0) != 0;
+}
+
 // Wait until the mbarrier phase with `parity` has completed.  All lanes of
-// the warp call this together.  Returns false (and marks the context dead)
-// when the wait is abandoned.
+// the warp call this together and all observe the phase themselves.  The
+// fast path is one try_wait plus one vote; the outcome is warp-uniform.
+// Returns false (and marks the context dead) when the wait is abandoned.
 __device__ __forceinline__ bool wait_mbar(Ctx& c, uint32_t bar, uint32_t parity, int code, int aux) {
   if (c.dead) return false;
-  // The outcome must be warp-uniform (callers shuffle and __syncwarp right
-  // after), so success needs every lane to have observed the phase and the
-  // give-up decision is taken by lane 0 alone and broadcast.
   if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < 64; ++i) {
       if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
     }
-    int give_up = 0;
-    if (c.lane == 0) {
-      if (aborted(c)) {
-        give_up = 1;
-      } else if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
-        report(c, code, aux, (int)parity);
-        give_up = 1;
-      }
-    }
-    give_up = __shfl_sync(0xffffffffu, give_up, 0);
-    if (give_up) {
+    if (give_up_check(c, t0, code, aux, (int)parity)) {
       c.dead = true;
+      return false;
+    }
+  }
+}
+
+// The same wait for a single thread (the loader's lane 0).  On give-up the
+// abort flag is raised; the caller's warp learns of it at its next __syncwarp.
+__device__ __forceinline__ bool wait_mbar_one(Ctx& c, uint32_t bar, uint32_t parity, int code, int aux) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (aborted(c)) return false;
+    if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
+      report(c, code, aux, (int)parity);
       return false;
     }
   }
@@ -188,45 +274,48 @@ __device__ __forceinline__ bool wait_released(Ctx& c, uint32_t slot, uint32_t k,
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < 64; ++i) {
       if (__all_sync(0xffffffffu, *r >= k)) return true;
-      nanosleep(20);
+      nanosleep(40);
     }
-    int give_up = 0;
-    if (c.lane == 0) {
-      if (aborted(c)) {
-        give_up = 1;
-      } else if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
-        report(c, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)k);
-        give_up = 1;
-      }
-    }
-    give_up = __shfl_sync(0xffffffffu, give_up, 0);
-    if (give_up) {
+    if (give_up_check(c, t0, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)k)) {
       c.dead = true;
       return false;
     }
   }
 }
 
-// Consumer side: wait until ring entry `seq` holds data; returns its address.
-__device__ __forceinline__ bool page_acquire(Ctx& c, uint32_t seq, uint32_t& page_addr) {
-  const int np = c.pv->n_pages;
-  const uint32_t slot = seq % np;
-  const uint32_t k = seq / np;
-  page_addr = c.pages_u32 + slot * (uint32_t)c.pv->page_bytes;
-  if (k > 0 && !wait_released(c, slot, k, (int)seq)) return false;
-  return wait_mbar(c, full_bar(c, slot), k & 1u, MK_ST_TIMEOUT_PAGE_FULL, (int)seq);
+// Position of a ring entry: slot index and how many times the slot was filled
+// before (seq = k * n_pages + slot).  Kept incrementally: one division per
+// unit instead of two per page.
+struct RingPos {
+  uint32_t slot, k;
+};
+__device__ __forceinline__ RingPos ring_at(uint32_t seq, int np) {
+  RingPos r;
+  r.k = seq / (uint32_t)np;
+  r.slot = seq - r.k * (uint32_t)np;
+  return r;
 }
-// Consumer side: hand ring entry `seq` back to the loader.
-__device__ __forceinline__ void page_release(Ctx& c, uint32_t seq) {
+__device__ __forceinline__ void ring_next(RingPos& r, int np) {
+  if (++r.slot == (uint32_t)np) {
+    r.slot = 0;
+    ++r.k;
+  }
+}
+
+// Consumer side: wait until the ring entry holds data; returns its address.
+__device__ __forceinline__ bool page_acquire(Ctx& c, const RingPos& r, uint32_t& page_addr) {
+  page_addr = c.pages_u32 + r.slot * (uint32_t)c.pv->page_bytes;
+  if (r.k > 0 && !wait_released(c, r.slot, r.k, (int)r.slot)) return false;
+  return wait_mbar(c, full_bar(c, r.slot), r.k & 1u, MK_ST_TIMEOUT_PAGE_FULL, (int)r.slot);
+}
+// Consumer side: hand the ring entry back to the loader.
+__device__ __forceinline__ void page_release(Ctx& c, const RingPos& r) {
   __syncwarp();
   if (c.lane == 0) {
-    const int np = c.pv->n_pages;
-    const uint32_t slot = seq % np;
-    mbar_arrive(empty_bar(c, slot));
-    __threadfence_block();
-    *reinterpret_cast<volatile uint32_t*>(&c.ctrl->released[slot]) = seq / np + 1u;
+    mbar_arrive(empty_bar(c, r.slot));
+    *reinterpret_cast<volatile uint32_t*>(&c.ctrl->released[r.slot]) = r.k + 1u;
   }
 }
 

@@ -107,13 +107,13 @@ def lower_matvec(
         raise ValueError(f"{name}: paired weights must share format and shape")
     kc = min(ctx.kc_fp4 if fp4 else ctx.kc_bf16, K)
     if fp4:
-        if K % 256:
-            raise ValueError(f"{name}: NVFP4 matvec needs K % 256 == 0, got {K}")
-        kc = max(256, kc // 256 * 256)
+        if K % 256 or (K > 2048 and K % 2048):
+            raise ValueError(f"{name}: NVFP4 matvec needs K % 256 == 0 and, above 2048, K % 2048 == 0; got {K}")
+        kc = min(K, 2048)     # one 128-byte scale tile row covers 2048 K-values
     else:
-        if K % 32:
-            raise ValueError(f"{name}: matvec needs K % 32 == 0, got {K}")
-        kc = max(32, kc // 32 * 32)
+        if K % 64:
+            raise ValueError(f"{name}: matvec needs K % 64 == 0, got {K}")
+        kc = max(64, kc // 64 * 64)
     xt = elem_type(x, f"{name}: x")
     if w0.fmt == N.W_BF16 and xt != N.T_BF16:
         raise ValueError(f"{name}: bf16 weights need bf16 activations")

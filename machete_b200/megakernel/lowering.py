@@ -14,6 +14,7 @@ choose their own unit shapes, independent of the API-level tile sizes.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -95,6 +96,7 @@ class NativeOp:
         rec["opcode"] = self.opcode
         rec["n_units"] = self.n_units
         rec["act_key"] = act_key
+        rec["reserved"] = int(os.environ.get("MK_DIAG_FLAGS", "0"))   # diagnostic bits, 0 in production
         for k, v in self.i.items():
             rec["i"][k] = int(v)
         for k, v in self.f.items():
@@ -134,11 +136,13 @@ class LowerCtx:
 
 # ---- helpers shared by the matvec-family lowerings ---------------------------------------
 def bf16_page_need(kc: int) -> int:
-    return 16 * (kc * 2 + 64)
+    """Two halves of kc/64 swizzled 1 KB tiles (8 rows x 128 B) each."""
+    return 2 * (kc // 64) * 1024
 
 
 def fp4_page_need(kc: int) -> int:
-    return 16 * (kc // 2 + 64) + 16 * (kc // 16 + 16)
+    """Two halves of kc/256 packed tiles plus two 1 KB scale tiles."""
+    return 2 * (kc // 256) * 1024 + 2048
 
 
 def attn_page_tokens(D: int, page_bytes: int) -> int:

@@ -29,7 +29,7 @@ from .scheduling import BackwardScheduler, BuiltProgram, InstructionStreamBuilde
 CTRL_BYTES = 4096
 MAX_PAGES = 32
 NUM_DMA_WARPS = 1
-NUM_CONSUMER_WARPS = 8
+NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
 
 # Used when no CUDA device is present (table building and CPU tests): B200.
 _DEFAULT_SMS = 148
@@ -282,6 +282,68 @@ class Megakernel:
         handle = None if stream is None else C.c_void_p(getattr(stream, "cuda_stream", stream))
         N.check(N.lib().mk_update_op(self._handle, index, rec.ctypes.data, handle), "mk_update_op")
         self.native_ops[index] = native_op
+
+    # -- tracing --------------------------------------------------------------------------------
+    TRACE_DTYPE = np.dtype([("t", "<u8"), ("code", "<u4"), ("arg", "<u4")])
+    TRACE_CODES = {1: "load_begin", 2: "load_issued", 3: "page_ready", 4: "page_done", 5: "unit_begin",
+                   6: "unit_end", 7: "event_begin", 8: "event_deps", 9: "event_end", 10: "lwait_done"}
+
+    def enable_trace(self, records_per_warp: int = 4096) -> None:
+        """Record globaltimer-stamped events of every warp on the next launches.
+
+        The counterpart of ``MegakernelConfig.tracing`` in the reference
+        (megakernel/tracing.py:51-153); costs a few global stores per page, so
+        timings taken with tracing on are for analysis only.
+        """
+        self.compile()
+        warps = self.program.num_ctas * (NUM_CONSUMER_WARPS + NUM_DMA_WARPS)
+        nbytes = warps * (records_per_warp * 16 + 4)
+        self._trace_buf = torch.zeros(nbytes + 16, dtype=torch.uint8, device=torch.device("cuda", self._dev))
+        self._trace_cap = records_per_warp
+        N.check(N.lib().mk_set_trace(self._handle, C.c_void_p(self._trace_buf.data_ptr()), nbytes,
+                                     records_per_warp), "mk_set_trace")
+
+    def disable_trace(self) -> None:
+        if self._handle:
+            N.check(N.lib().mk_set_trace(self._handle, None, 0, 0), "mk_set_trace")
+
+    def read_trace(self):
+        """Return ``{(cta, warp): structured array of (t, code, arg)}`` of the last launch."""
+        torch.cuda.synchronize(self._dev)
+        raw = self._trace_buf.cpu().numpy()
+        warps_per_cta = NUM_CONSUMER_WARPS + NUM_DMA_WARPS
+        warps = self.program.num_ctas * warps_per_cta
+        cap = self._trace_cap
+        recs = raw[:warps * cap * 16].view(self.TRACE_DTYPE).reshape(warps, cap)
+        counts = raw[warps * cap * 16: warps * cap * 16 + warps * 4].view(np.int32)
+        out = {}
+        for wi in range(warps):
+            n = min(int(counts[wi]), cap)
+            out[(wi // warps_per_cta, wi % warps_per_cta)] = recs[wi, :n].copy()
+        return out
+
+    def export_chrome_trace(self, path: str, ctas=(0,)) -> None:
+        """Write the begin/end pairs of the chosen CTAs as a Chrome / Perfetto trace."""
+        import json
+
+        tr = self.read_trace()
+        t0 = min((int(a["t"][0]) for a in tr.values() if len(a)), default=0)
+        pairs = {1: (2, "load"), 3: (4, "page"), 5: (6, "unit"), 7: (9, "event")}
+        events = []
+        for (cta, warp), arr in tr.items():
+            if cta not in ctas:
+                continue
+            open_at = {}
+            for r in arr:
+                code, arg, t = int(r["code"]), int(r["arg"]), (int(r["t"]) - t0) / 1e3
+                if code in pairs:
+                    open_at[(pairs[code][0], arg)] = (t, pairs[code][1])
+                elif (code, arg) in open_at:
+                    tb, name = open_at.pop((code, arg))
+                    events.append({"name": f"{name} {arg}", "ph": "X", "ts": tb, "dur": t - tb, "pid": cta,
+                                   "tid": warp})
+        with open(path, "w") as fh:
+            json.dump({"traceEvents": events}, fh)
 
     def bench_spec(self, setup_fn=None, keep_alive=None) -> dict:
         """A launch closure plus byte accounting for benchmark harnesses."""
