@@ -179,12 +179,17 @@ typedef struct mk_event {
   int32_t n_waits;
   int32_t wait_off;
   int32_t flags;          /* MK_EVF_* */
-  int32_t reserved[3];
+  int32_t bulk_units;     /* with MK_EVF_BULK_SIGNAL: units of `op` on this CTA */
+  int32_t reserved[2];
 } mk_event_t;
 
-/* mk_event_t.flags: this CTA materialises residual_out = x + residual_in of
- * the op's prologue in global memory (exactly one CTA per op does). */
-enum { MK_EVF_WRITE_RES_OUT = 1 };
+/* mk_event_t.flags
+ * WRITE_RES_OUT: this CTA materialises residual_out = x + residual_in of the
+ *   op's prologue in global memory (exactly one CTA per op does).
+ * BULK_SIGNAL: the op's units on this CTA all signal the same counter; the CTA
+ *   adds `bulk_units` to it once, after its last unit, instead of one
+ *   device-scope release per unit. */
+enum { MK_EVF_WRITE_RES_OUT = 1, MK_EVF_BULK_SIGNAL = 2 };
 
 typedef struct mk_wait {
   int32_t counter;

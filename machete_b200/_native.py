@@ -46,7 +46,7 @@ EW_F_EPS = 0
 (EW_P_X, EW_P_Y, EW_P_W, EW_P_RES_IN, EW_P_RES_OUT, EW_P_GATE, EW_P_COS, EW_P_SIN) = range(8)
 (EW_S_X, EW_S_Y, EW_S_W, EW_S_RI, EW_S_RO, EW_S_G, EW_S_COS, EW_S_X_H) = range(8)
 EWF_RESIDUAL, EWF_GEMMA, EWF_FUSED_ADD, EWF_GATED, EWF_ROW_WEIGHT = 1, 2, 4, 8, 16
-EVF_WRITE_RES_OUT = 1
+EVF_WRITE_RES_OUT, EVF_BULK_SIGNAL = 1, 2
 
 # Device status codes (csrc/shell.cuh).
 STATUS_NAMES = {
@@ -79,7 +79,7 @@ INSTR_DTYPE = np.dtype([
 ])
 EVENT_DTYPE = np.dtype([
     ("pos", "<i4"), ("op", "<i4"), ("n_waits", "<i4"), ("wait_off", "<i4"), ("flags", "<i4"),
-    ("reserved", "<i4", (3,)),
+    ("bulk_units", "<i4"), ("reserved", "<i4", (2,)),
 ])
 WAIT_DTYPE = np.dtype([("counter", "<i4"), ("expected", "<i4")])
 assert OP_DTYPE.itemsize == 16 + 96 + 16 + 128 + 128

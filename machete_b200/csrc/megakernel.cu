@@ -38,17 +38,21 @@ __device__ __forceinline__ mk_instr_t bcast_instr(const mk_instr_t& mine, int sr
   r.n_lwaits = __shfl_sync(0xffffffffu, mine.n_lwaits, src);
   r.lwait_off = __shfl_sync(0xffffffffu, mine.lwait_off, src);
   r.n_pages = __shfl_sync(0xffffffffu, mine.n_pages, src);
+  r.ld_flags = __shfl_sync(0xffffffffu, mine.ld_flags, src);
   return r;
 }
 
-// Consumers need only the first half of an instruction record.
+// Consumers need the first half of an instruction record, and whether it is a
+// matvec unit (ld_flags is reused in registers for that: bit 31).
+constexpr int kInsMatvec = (int)0x80000000;
 __device__ __forceinline__ mk_instr_t load_instr(const mk_instr_t* p) {
   const int4* q = reinterpret_cast<const int4*>(p);
-  const int4 a = q[0], b = q[1];
+  const int4 a = q[0], b = q[1], c2 = q[2];
   mk_instr_t r;
   r.op = a.x; r.unit = a.y; r.signal = a.z; r.n_waits = a.w;
   r.wait_off = b.x; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
-  r.ld_maps = 0; r.ld_row_a = 0; r.ld_row_b = 0; r.ld_tiles = 0; r.ld_flags = 0;
+  r.ld_maps = 0; r.ld_row_a = 0; r.ld_row_b = 0; r.ld_tiles = 0;
+  r.ld_flags = (c2.x | c2.y) != 0 ? kInsMatvec : 0;
   return r;
 }
 
@@ -172,9 +176,11 @@ __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
   }
 }
 
-__device__ __forceinline__ void run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+// Returns whether this warp completed the unit (and therefore signals it).
+template <int NTC, int WFC>
+__device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t mv_ord) {
   switch (op->opcode) {
-    case MK_OP_MATVEC: mv_dispatch(c, op, ins, seq); break;
+    case MK_OP_MATVEC: return mv_dispatch<NTC, WFC>(c, op, ins, seq, mv_ord);
     case MK_OP_ATTN_SPLIT: at_dispatch(c, op, ins, seq); break;
     case MK_OP_ATTN_COMBINE: at_combine_unit(c, op, ins); break;
     case MK_OP_RMSNORM: ew_rmsnorm(c, op, ins.unit); break;
@@ -189,14 +195,19 @@ __device__ __forceinline__ void run_unit(Ctx& c, const mk_op_t* op, const mk_ins
       c.dead = true;
       break;
   }
+  return true;
 }
 
+template <int NTC, int WFC>
 __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
   const ProgramView& pv = *c.pv;
   const int w = c.warp - 1;
   constexpr int T = kConsumerWarps * 32;
   uint32_t seq = 0;
+  uint32_t mv_ord = 0;  // multi-page matvec units of this CTA so far (selects the split-K slot set)
   int staged_key = 0;
+  int cached_op = -1;   // op whose record sits in the shared-memory copy
+  int bulk_units = 0;   // > 0: units of cached_op are signalled in bulk
   int ev = ebeg;
   mk_event_t cur;
   cur.pos = 0x7fffffff;
@@ -204,12 +215,23 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
 
   auto do_event = [&]() {
     // Every consumer warp runs this, dead or not: the barriers must balance.
+    // All units before the event are complete after the first barrier, so the
+    // shared copy of the op record can be replaced: unit handlers then read
+    // their parameters from shared memory instead of the op table.
     trace(c, TRC_EVENT_BEGIN, cur.op);
     named_bar_sync(kConsumerBarrier, T);
-    if (w == 0) wait_counters(c, cur.n_waits, cur.wait_off);
+    const mk_op_t* op = pv.ops + cur.op;
+    if (w == 0) {
+      wait_counters(c, cur.n_waits, cur.wait_off);
+    } else if (w == 1 && c.lane < (int)(sizeof(mk_op_t) / 16)) {
+      reinterpret_cast<uint4*>(&c.ctrl->op_cache)[c.lane] = reinterpret_cast<const uint4*>(op)[c.lane];
+      if (c.lane == 0) c.ctrl->bulk_done = 0;
+    }
+    bulk_units = (cur.flags & MK_EVF_BULK_SIGNAL) ? cur.bulk_units : 0;
     named_bar_sync(kConsumerBarrier, T);
     trace(c, TRC_EVENT_DEPS, cur.op);
-    const mk_op_t* op = pv.ops + cur.op;
+    op = &c.ctrl->op_cache;
+    cached_op = cur.op;
     if (op->opcode == MK_OP_MATVEC) {
       const bool need = (op->act_key == 0) || (op->act_key != staged_key);
       mv_stage(c, op, need, (cur.flags & MK_EVF_WRITE_RES_OUT) != 0);
@@ -230,22 +252,37 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     for (int i = 0; i < n; ++i) {
       const int local = base + i - ibeg;
       while (cur.pos <= local) do_event();
-      const mk_instr_t ins = bcast_instr(mine, i);
-      if ((local % kConsumerWarps) == w && !c.dead) {
+      // A matvec unit is shared: consumer (seq + p) mod kConsumerWarps takes
+      // page p.  Every other unit belongs to one consumer, round-robin.  Only
+      // a consumer that takes part fetches the rest of the record.
+      const int n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i);
+      const bool is_mv = (__shfl_sync(0xffffffffu, mine.ld_flags, i) & kInsMatvec) != 0;
+      const bool take = is_mv ? mv_first_page(w, seq) < n_pages : (local % kConsumerWarps) == w;
+      if (take && !c.dead) {
+        const mk_instr_t ins = bcast_instr(mine, i);
         c.instr_idx = base + i;
         if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
           trace(c, TRC_UNIT_BEGIN, base + i);
-          run_unit(c, pv.ops + ins.op, ins, seq);
-          if (!c.dead) signal_unit(c, ins.signal);
+          const mk_op_t* op = ins.op == cached_op ? &c.ctrl->op_cache : pv.ops + ins.op;
+          const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord);
+          if (!c.dead && finished) {
+            if (bulk_units > 0 && ins.op == cached_op)
+              signal_unit_bulk(c, ins.signal, bulk_units);
+            else
+              signal_unit(c, ins.signal);
+          }
           trace(c, TRC_UNIT_END, base + i);
         }
       }
-      seq += (uint32_t)ins.n_pages;
+      if (is_mv && n_pages > 1) ++mv_ord;
+      seq += (uint32_t)n_pages;
     }
   }
   while (ev < eend) do_event();
 }
 
+// NTC / WFC specialise the matvec path (see mv_dispatch); <0, -1> handles any program.
+template <int NTC, int WFC>
 __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid_constant__ ProgramView pv) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Ctx c;
@@ -267,6 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
       mbar_init(smem_u32(&c.ctrl->empty[i]), 1);
     }
     for (int i = 0; i < kMaxPages; ++i) c.ctrl->released[i] = 0;
+    for (int i = 0; i < 4; ++i) c.ctrl->mv_arrive[i] = c.ctrl->mv_done[i] = 0;
     c.ctrl->abort_flag = 0;
     c.ctrl->is_last = 0;
     fence_mbar_init();
@@ -278,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
   if (c.warp == 0)
     loader_loop(c, ibeg, iend);
   else
-    consumer_loop(c, ibeg, iend, ebeg, eend);
+    consumer_loop<NTC, WFC>(c, ibeg, iend, ebeg, eend);
   trace_flush(c);
   __syncthreads();
 
@@ -604,8 +642,25 @@ static int validate_program(const mk_program_t* p, int smem_optin, int* smem_byt
 
 }  // namespace mk
 
+// The kernel variants: <NT class, weight family>; the first entry handles any
+// program, the others carry the matvec code of one combination only (smaller
+// code, fewer instruction-cache misses on the hot path).
+typedef void (*mk_kernel_fn)(const mk::ProgramView);
+struct mk_variant {
+  int ntc, wfc;
+  mk_kernel_fn fn;
+};
+static const mk_variant g_variants[] = {
+    {0, -1, mk::mk_persistent_kernel<0, -1>}, {1, 0, mk::mk_persistent_kernel<1, 0>},
+    {2, 0, mk::mk_persistent_kernel<2, 0>},   {4, 0, mk::mk_persistent_kernel<4, 0>},
+    {1, 2, mk::mk_persistent_kernel<1, 2>},   {2, 2, mk::mk_persistent_kernel<2, 2>},
+    {4, 2, mk::mk_persistent_kernel<4, 2>},
+};
+
 struct mk_handle_s {
   mk::ProgramView pv;
+  mk_kernel_fn kernel;
+  std::vector<int> op_ntc, op_wfc;   // per op: NT class and weight family (0 = not a matvec)
   int n_ctas;
   int smem_bytes;
   int device;
@@ -613,6 +668,41 @@ struct mk_handle_s {
   uint8_t* ws;
   mk::Layout layout;
 };
+
+static void classify_op(const mk_op_t& op, int* ntc, int* wfc) {
+  *ntc = 0;
+  *wfc = -1;
+  if (op.opcode != MK_OP_MATVEC) return;
+  const int m = op.i[MK_MV_M], wf = op.i[MK_MV_WFMT];
+  *ntc = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+  *wfc = wf == MK_W_BF16 ? 0 : (wf >= MK_W_NVFP4_F16S32 ? 2 : 1);
+}
+
+// Pick the most specific kernel that covers every matvec op of the program.
+static int select_kernel(mk_handle_s* h) {
+  int ntc = -1, wfc = -2;
+  bool mixed = false;
+  for (size_t i = 0; i < h->op_ntc.size(); ++i) {
+    if (h->op_ntc[i] == 0) continue;
+    if (ntc == -1) {
+      ntc = h->op_ntc[i];
+      wfc = h->op_wfc[i];
+    } else if (ntc != h->op_ntc[i] || wfc != h->op_wfc[i]) {
+      mixed = true;
+    }
+  }
+  h->kernel = g_variants[0].fn;
+  if (!mixed && ntc > 0)
+    for (const mk_variant& v : g_variants)
+      if (v.ntc == ntc && v.wfc == wfc) h->kernel = v.fn;
+  h->pv.mv_sets = 4;
+  for (int n : h->op_ntc)
+    if (n > 0) h->pv.mv_sets = std::min(h->pv.mv_sets, n == 1 ? 4 : (n == 2 ? 2 : 1));
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_bytes);
+  if (e != cudaSuccess) return mk::fail(-(int)e - 1000, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  return 0;
+}
 
 extern "C" {
 
@@ -716,7 +806,6 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
   CUDA_TRY(cudaMemcpy(ws + l.ebegin, prog->cta_event_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
   if (prog->n_waits)
     CUDA_TRY(cudaMemcpy(ws + l.waits, prog->waits, (size_t)prog->n_waits * sizeof(mk_wait_t), cudaMemcpyHostToDevice));
-  CUDA_TRY(cudaFuncSetAttribute(mk_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
 
   mk_handle_s* h = new mk_handle_s();
   h->pv.ops = reinterpret_cast<const mk_op_t*>(ws + l.ops);
@@ -734,9 +823,17 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
   h->pv.timeout_ns = (uint64_t)(prog->timeout_ms > 0 ? prog->timeout_ms : 1000) * 1000000ull;
   h->pv.trace = nullptr;
   h->pv.trace_cap = 0;
-  h->pv.pad = 0;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
+  h->op_ntc.resize(prog->n_ops);
+  h->op_wfc.resize(prog->n_ops);
+  for (int i = 0; i < prog->n_ops; ++i) classify_op(prog->ops[i], &h->op_ntc[i], &h->op_wfc[i]);
+  rc = select_kernel(h);
+  if (rc) {
+    delete h;
+    cudaSetDevice(prev_dev);
+    return rc;
+  }
   h->device = prog->device;
   h->n_ops = prog->n_ops;
   h->ws = ws;
@@ -749,8 +846,9 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
 int mk_run(mk_handle_t h, void* cuda_stream) {
   using namespace mk;
   if (!h) return fail(-1, "null handle");
-  mk_persistent_kernel<<<h->n_ctas, kThreads, h->smem_bytes, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(h->pv);
-  CUDA_TRY(cudaGetLastError());
+  void* args[] = {&h->pv};
+  CUDA_TRY(cudaLaunchKernel(reinterpret_cast<const void*>(h->kernel), dim3(h->n_ctas), dim3(kThreads), args,
+                            (size_t)h->smem_bytes, reinterpret_cast<cudaStream_t>(cuda_stream)));
   return 0;
 }
 
@@ -807,7 +905,9 @@ int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_
   CUDA_TRY(cudaMemcpyAsync(dev_maps, maps, sizeof(maps), cudaMemcpyHostToDevice, st));
   CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.ops + (size_t)op_index * sizeof(mk_op_t), &rec, sizeof(mk_op_t),
                            cudaMemcpyHostToDevice, st));
-  return 0;
+  // a changed batch size or weight format may need another kernel variant
+  classify_op(rec, &h->op_ntc[op_index], &h->op_wfc[op_index]);
+  return select_kernel(h);
 }
 
 int mk_read_counters(mk_handle_t h, int32_t* out, int32_t n) {

@@ -354,14 +354,53 @@ __device__ __forceinline__ uint32_t tile_chunk(uint32_t tile, int r, int c) {
   return tile + (uint32_t)r * 128u + (uint32_t)((c ^ r) << 4);
 }
 
+// First page (K-slice) of a unit that consumer `w` takes when the unit's pages
+// start at ring entry `seq`: consumers take ring entries round-robin, so all
+// of them stream at once whatever the shape of the op.
+__device__ __forceinline__ int mv_first_page(int w, uint32_t seq) {
+  const int s = (int)(seq % (uint32_t)kConsumerWarps);
+  return w >= s ? w - s : w + kConsumerWarps - s;
+}
+
+// Bounded wait until a shared-memory word reaches `want`.
+__device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, uint32_t want, int aux) {
+  if (c.dead) return false;
+  if (__all_sync(0xffffffffu, *word >= want)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (__all_sync(0xffffffffu, *word >= want)) return true;
+      nanosleep(20);
+    }
+    if (give_up_check(c, t0, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)want)) {
+      c.dead = true;
+      return false;
+    }
+  }
+}
+
 // NT = n-tiles of 8 activation rows; NA = independent accumulator sets (the
 // mma chain on one accumulator is latency-bound, so K-steps rotate over NA).
-template <int NT, int NA>
-__device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+//
+// All consumers that own a page of the unit call this.  Each accumulates its
+// K-slices; with more than one participant the partial sums meet in a
+// shared-memory slot set, and the last one to arrive adds them up in warp
+// order (so the result does not depend on timing), runs the epilogue and
+// returns true: it is the one that signals the unit.
+//
+// WFC fixes the weight-format family at compile time so that a kernel built
+// for one family carries only that code: 0 = bf16, 2 = NVFP4 (either scale
+// layout), -1 = decided per op at run time.
+template <int NT, int NA, int WFC>
+__device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ord) {
   const int unit = ins.unit;
+  const int w = c.warp - 1;
+  const int p0 = mv_first_page(w, seq);
   const int g = c.lane >> 2, t = c.lane & 3;
   const int K = op->i[MK_MV_K], Kc = op->i[MK_MV_KC], M = op->i[MK_MV_M];
-  const int wfmt = op->i[MK_MV_WFMT];
+  const int wfmt = WFC == 0 ? (int)MK_W_BF16 : op->i[MK_MV_WFMT];
+  const bool dense = WFC == 0 ? true : (WFC == 2 ? false : (wfmt == MK_W_BF16 || wfmt == MK_W_FP16));
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const uint32_t half = mv_half_bytes(wfmt, Kc);
   float acc[NA][NT][4];
@@ -382,17 +421,17 @@ __device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
   }
 
   const int np = ins.n_pages;
-  RingPos rp = ring_at(seq, c.pv->n_pages);
-  for (int p = 0; p < np; ++p, ring_next(rp, c.pv->n_pages)) {
+  RingPos rp = ring_at(seq + (uint32_t)p0, c.pv->n_pages);
+  for (int p = p0; p < np; p += kConsumerWarps, ring_advance(rp, kConsumerWarps, c.pv->n_pages)) {
     uint32_t page;
-    if (!page_acquire(c, rp, page)) return;
+    if (!page_acquire(c, rp, page)) return false;
     trace(c, TRC_PAGE_READY, seq + p);
     const long long cyc0 = clock64();
     const int k0 = p * Kc;
     const int kc = min(Kc, K - k0);
     if (op->reserved & 1) {
       // diagnostic: consume the page without computing (pipeline cost only)
-    } else if (wfmt == MK_W_BF16 || wfmt == MK_W_FP16) {
+    } else if (dense) {
       // One K-tile = 64 K-values = 8 chunks of 16 B per row; this thread takes
       // chunks 2t and 2t+1 of rows g (half A) and g (half B): with the 128-byte
       // swizzle the 8 lanes of a shared-memory phase then hit 8 distinct chunks.
@@ -473,7 +512,7 @@ __device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
           }
         }
       };
-      if (wfmt == MK_W_BF16)
+      if (WFC == 0 || wfmt == MK_W_BF16)
         run_page(std::true_type{});
       else
         run_page(std::false_type{});
@@ -541,33 +580,76 @@ __device__ __forceinline__ void mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[0][nt][e] += acc[a][nt][e];
+
+  // Split-K reduction across the participating consumers.
+  const int parts = min(np, kConsumerWarps);
+  // mv_sets (1, 2 or 4) slot sets share kPartialBytes; the host picks the
+  // count so that the widest matvec op of the program fits a slot.
+  const uint32_t sets = (uint32_t)c.pv->mv_sets;
+  const int kSlotFloats = kPartialBytes / 4 / kConsumerWarps / (int)sets;
+  const uint32_t set = ord % sets, gen = ord / sets;
+  float* slots = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.ctrl) + kCtrlStructBytes) +
+                 (size_t)set * kConsumerWarps * kSlotFloats;
+  if (parts > 1) {
+    // the set's previous users (units ord - kSets, ...) must have been reduced
+    if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
+    float* mine = slots + (size_t)w * kSlotFloats;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mine[(nt * 4 + e) * 32 + c.lane] = acc[0][nt][e];
+    __syncwarp();
+    int last = 0;
+    if (c.lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&c.ctrl->mv_arrive[set], 1u) == (uint32_t)(parts - 1);
+      __threadfence_block();
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    trace(c, TRC_MV_ARRIVED, ord);
+    if (!last) return false;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[0][nt][e] = 0.f;
+    for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
+      if (mv_first_page(w2, seq) >= np) continue;
+      const float* src = slots + (size_t)w2 * kSlotFloats;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][nt][e] += src[(nt * 4 + e) * 32 + c.lane];
+    }
+    __syncwarp();
+    if (c.lane == 0) {
+      c.ctrl->mv_arrive[set] = 0;
+      __threadfence_block();
+      *reinterpret_cast<volatile uint32_t*>(&c.ctrl->mv_done[set]) = gen + 1u;
+    }
+  }
+  trace(c, TRC_MV_REDUCED, ord);
   const MvRows r = mv_rows(op, unit);
   mv_epilogue<NT>(c, op, r, unit, acc[0]);
+  trace(c, TRC_MV_EPILOGUE, ord);
+  return true;
 }
 
-// Each variant is a real function (not inlined into the shell) so that it gets
-// its own register allocation; the context travels by value and the two
-// fields a unit can change come back in the result.
-template <int NT, int NA>
-__device__ __noinline__ UnitResult mv_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq) {
-  mv_unit<NT, NA>(c, op, ins, seq);
-  UnitResult r;
-  r.dead = c.dead;
-  r.trace_n = c.trace_n;
-  return r;
-}
-
-__device__ __forceinline__ void mv_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
-  const int M = op->i[MK_MV_M];
-  UnitResult r;
-  if (M <= 8)
-    r = mv_unit_call<1, 4>(c, op, ins, seq);
-  else if (M <= 16)
-    r = mv_unit_call<2, 2>(c, op, ins, seq);
-  else
-    r = mv_unit_call<4, 1>(c, op, ins, seq);
-  c.dead = r.dead;
-  c.trace_n = r.trace_n;
+// NTC / WFC: the activation-tile count (1, 2, 4) and weight family the kernel
+// was built for, or 0 / -1 to decide per op.
+template <int NTC, int WFC>
+__device__ __forceinline__ bool mv_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ord) {
+  if constexpr (NTC == 1) {
+    return mv_unit<1, 4, WFC>(c, op, ins, seq, ord);
+  } else if constexpr (NTC == 2) {
+    return mv_unit<2, 2, WFC>(c, op, ins, seq, ord);
+  } else if constexpr (NTC == 4) {
+    return mv_unit<4, 1, WFC>(c, op, ins, seq, ord);
+  } else {
+    const int M = op->i[MK_MV_M];
+    if (M <= 8) return mv_unit<1, 4, WFC>(c, op, ins, seq, ord);
+    if (M <= 16) return mv_unit<2, 2, WFC>(c, op, ins, seq, ord);
+    return mv_unit<4, 1, WFC>(c, op, ins, seq, ord);
+  }
 }
 
 }  // namespace mk

@@ -16,7 +16,11 @@ namespace mk {
 constexpr int kConsumerWarps = 7;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxPages = 32;
-constexpr int kCtrlBytes = 4096;  // mbarriers + flags + reduction scratch
+constexpr int kCtrlStructBytes = 4096;  // mbarriers + flags + reduction scratch
+// Split-K partial accumulators of the matvec units: one slot per consumer warp
+// (32 lanes x 4 floats per activation n-tile), kPartialBytes in all.
+constexpr int kPartialBytes = kConsumerWarps * 2048;
+constexpr int kCtrlBytes = kCtrlStructBytes + kPartialBytes;
 constexpr uint32_t kConsumerBarrier = 1;
 
 // Device status codes (status[0]).
@@ -56,7 +60,7 @@ struct ProgramView {
   // one record count per (CTA, warp) after all rings; null = tracing off
   struct TraceRec* trace;
   int32_t trace_cap;
-  int32_t pad;
+  int32_t mv_sets;  // split-K slot sets in use: 4 (every matvec has M <= 8), 2 (M <= 16) or 1
 };
 
 // One trace event: a globaltimer stamp, an event code and an argument.
@@ -76,7 +80,10 @@ enum {
   TRC_EVENT_DEPS = 8,   // event: producers complete (arg = op)
   TRC_EVENT_END = 9,    // event: activations staged (arg = op)
   TRC_LWAIT_DONE = 10,  // loader: loader-side wait satisfied (arg = instruction index)
-  TRC_PAGE_CYCLES = 11  // consumer: SM cycles spent computing on the page just handed back (arg = cycles)
+  TRC_PAGE_CYCLES = 11, // consumer: SM cycles spent computing on the page just handed back (arg = cycles)
+  TRC_MV_ARRIVED = 12,  // consumer: split-K partial handed in (arg = slot-set ordinal)
+  TRC_MV_REDUCED = 13,  // consumer: partials of the unit summed, epilogue starts (arg = ordinal)
+  TRC_MV_EPILOGUE = 14  // consumer: epilogue stores issued (arg = ordinal)
 };
 
 // Shared-memory control block (first kCtrlBytes of dynamic smem).
@@ -85,12 +92,19 @@ struct Ctrl {
   uint64_t empty[kMaxPages];
   int32_t abort_flag;
   int32_t is_last;
-  int32_t pad[14];
+  // Split-K slot sets: arrivals of the current user, and how many users of
+  // the set have finished their epilogue.
+  uint32_t mv_arrive[4];
+  uint32_t mv_done[4];
+  uint32_t bulk_done;  // units of the current op finished on this CTA (bulk signalling)
+  int32_t pad[5];
   // released[slot] = number of fills of the slot that consumers have handed back
   uint32_t released[kMaxPages];
   float red[kConsumerWarps * 32];  // block-reduction scratch (per row, per warp)
+  // copy of the record of the op the CTA is working on (refreshed by its op-entry event)
+  __align__(16) mk_op_t op_cache;
 };
-static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+static_assert(sizeof(Ctrl) <= kCtrlStructBytes, "control block too large");
 
 // Per-thread execution context.
 struct Ctx {
@@ -112,6 +126,7 @@ struct Ctx {
 // What a non-inlined unit handler hands back to the shell.
 struct UnitResult {
   bool dead;
+  bool signal;  // this warp finished the unit: it signals the unit's counter
   int trace_n;
 };
 
@@ -297,6 +312,14 @@ __device__ __forceinline__ RingPos ring_at(uint32_t seq, int np) {
   r.slot = seq - r.k * (uint32_t)np;
   return r;
 }
+// Step `stride` entries ahead.
+__device__ __forceinline__ void ring_advance(RingPos& r, int stride, int np) {
+  r.slot += (uint32_t)stride;
+  while (r.slot >= (uint32_t)np) {
+    r.slot -= (uint32_t)np;
+    ++r.k;
+  }
+}
 __device__ __forceinline__ void ring_next(RingPos& r, int np) {
   if (++r.slot == (uint32_t)np) {
     r.slot = 0;
@@ -324,8 +347,25 @@ __device__ __forceinline__ void page_release(Ctx& c, const RingPos& r) {
 __device__ __forceinline__ void signal_unit(Ctx& c, int counter) {
   __syncwarp();
   if (c.lane == 0 && counter >= 0) {
-    __threadfence();
+    // release at gpu scope is cumulative: it also publishes the other lanes'
+    // writes that the __syncwarp above ordered before this point
     red_release_gpu_add(c.pv->counters + counter, 1);
+  }
+}
+
+// Bulk variant: the unit's finisher counts it in shared memory; whoever counts
+// the CTA's last unit of the op publishes all of them with one device-scope
+// release (the earlier finishers' writes reach it through the cta-scope
+// fences around the shared-memory counter).
+__device__ __forceinline__ void signal_unit_bulk(Ctx& c, int counter, int units) {
+  __syncwarp();
+  if (c.lane == 0 && counter >= 0) {
+    __threadfence_block();
+    const uint32_t old = atomicAdd(&c.ctrl->bulk_done, 1u);
+    if (old == (uint32_t)(units - 1)) {
+      __threadfence();
+      red_release_gpu_add(c.pv->counters + counter, units);
+    }
   }
 }
 

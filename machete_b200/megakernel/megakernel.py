@@ -26,10 +26,10 @@ from .lowering import LowerCtx, NativeOp
 from .ops import ScheduledOp
 from .scheduling import BackwardScheduler, BuiltProgram, InstructionStreamBuilder, TileScheduler
 
-CTRL_BYTES = 4096
 MAX_PAGES = 32
 NUM_DMA_WARPS = 1
 NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
+CTRL_BYTES = 4096 + NUM_CONSUMER_WARPS * 2048   # control block + split-K partial slots (csrc/shell.cuh)
 
 # Used when no CUDA device is present (table building and CPU tests): B200.
 _DEFAULT_SMS = 148

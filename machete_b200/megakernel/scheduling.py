@@ -255,6 +255,9 @@ class InstructionStreamBuilder:
             seen_cta = set()
             res_out_cta = int(where[0]) if (op.writes_res_out and op.n_units > 0) else -1
             loader_pairs_all = [p for i in d.loader for p in all_groups(i)]
+            # one counter for the whole op: each CTA signals its units in bulk
+            per_cta = np.bincount(np.asarray(where[:op.n_units], dtype=np.int64), minlength=num_ctas)
+            bulk = op.n_groups == 1
             for u in range(op.n_units):
                 cta = int(where[u])
                 if cta not in seen_cta:
@@ -263,7 +266,9 @@ class InstructionStreamBuilder:
                     pairs = [p for i in need for p in all_groups(i)]
                     nw, off = wait_list(pairs)
                     flags = N.EVF_WRITE_RES_OUT if cta == res_out_cta else 0
-                    cta_events[cta].append((len(cta_instrs[cta]), j, nw, off, flags))
+                    if bulk:
+                        flags |= N.EVF_BULK_SIGNAL
+                    cta_events[cta].append((len(cta_instrs[cta]), j, nw, off, flags, int(per_cta[cta]) if bulk else 0))
                     for i in d.coarse:
                         cta_known[cta] |= closure[i] | (1 << i)
                 # fine-grained consumer waits
@@ -302,9 +307,10 @@ class InstructionStreamBuilder:
                     blk[name] = arr[:, k]
             io += len(rows)
             ibegin[c + 1] = io
-            for (pos, opi, nw, off, flags) in cta_events[c]:
+            for (pos, opi, nw, off, flags, bulk_units) in cta_events[c]:
                 ev = events[eo]
                 ev["pos"], ev["op"], ev["n_waits"], ev["wait_off"], ev["flags"] = pos, opi, nw, off, flags
+                ev["bulk_units"] = bulk_units
                 eo += 1
             ebegin[c + 1] = eo
         events = events[:max(1, n_events)]

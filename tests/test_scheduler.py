@@ -111,8 +111,12 @@ def test_act_keys_change_across_layers_and_residual_out_written_once():
     assert len({keys[i] for i in q_ops}) == 3          # layers 0 and 2 reuse buffers but not keys
     ev = mk.program.events
     for i in q_ops:
-        flagged = ev[(ev["op"] == i) & (ev["flags"] == 1)]
+        mine = ev[ev["op"] == i]
+        flagged = mine[(mine["flags"] & 1) == 1]              # residual_out is written by one CTA
         assert len(flagged) == 1
+        # one counter per op: every CTA signals its units in bulk, and the bulk sizes add up
+        assert ((mine["flags"] & 2) == 2).all()
+        assert int(mine["bulk_units"].sum()) == mk.native_ops[i].n_units
     final = simulate(mk.program)
     assert (final == mk.program.counter_expected[:len(final)]).all()
     # every CTA list is a subsequence of program order
