@@ -87,7 +87,12 @@ enum { MK_T_BF16 = 0, MK_T_FP16 = 1, MK_T_FP32 = 2 };
 enum {
   MK_MV_O = 0, MK_MV_K, MK_MV_M, MK_MV_S, MK_MV_MODE, MK_MV_PRO, MK_MV_EPI,
   MK_MV_TR, MK_MV_HD, MK_MV_D2, MK_MV_POS, MK_MV_WFMT, MK_MV_KC, MK_MV_OUT_T,
-  MK_MV_X_T, MK_MV_ROWS_PER_UNIT
+  MK_MV_X_T, MK_MV_ROWS_PER_UNIT,
+  /* consumer warps that share one unit: its K-slices (pages) are dealt to them
+   * round-robin and the partial sums meet in shared memory.
+   * 1 suits ops with many units per CTA, more suits ops with few.
+   * 0 = one warp per page, up to all consumer warps. */
+  MK_MV_SPLIT
 };
 enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1 };
 enum {
@@ -168,7 +173,8 @@ typedef struct mk_instr {
   int32_t reserved[2];
 } mk_instr_t;
 
-enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2 };
+/* bits 8-11 of ld_flags: consumer warps sharing the unit (from MK_MV_SPLIT) */
+enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15 };
 
 /* Op-entry event: before a CTA executes instruction `pos` of its list, all
  * of its consumer warps meet, wait for the listed counters and stage the

@@ -16,6 +16,7 @@ import numpy as np
 from . import build as _build
 
 ABI_VERSION = 3
+NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
 
 # ---- enums (keep in sync with include/machete_b200.h) ------------------------
 OP_NOP, OP_MATVEC, OP_ATTN_SPLIT, OP_ATTN_COMBINE, OP_RMSNORM, OP_ROPE, OP_QKNORM_ROPE, OP_GLU, OP_ADD, \
@@ -28,7 +29,7 @@ W_BF16, W_FP16, W_NVFP4_F16S32, W_NVFP4_E4M3S16 = range(4)
 T_BF16, T_FP16, T_FP32 = range(3)
 
 (MV_O, MV_K, MV_M, MV_S, MV_MODE, MV_PRO, MV_EPI, MV_TR, MV_HD, MV_D2, MV_POS, MV_WFMT, MV_KC, MV_OUT_T,
- MV_X_T, MV_ROWS_PER_UNIT) = range(16)
+ MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT) = range(17)
 MV_F_EPS, MV_F_GSCALE = range(2)
 (MV_P_W0, MV_P_W1, MV_P_X, MV_P_RES_IN, MV_P_NORM_W, MV_P_RES_OUT, MV_P_OUT, MV_P_EPI_RES, MV_P_COS,
  MV_P_SIN, MV_P_SC0, MV_P_SC1) = range(12)

@@ -47,12 +47,12 @@ __device__ __forceinline__ mk_instr_t bcast_instr(const mk_instr_t& mine, int sr
 constexpr int kInsMatvec = (int)0x80000000;
 __device__ __forceinline__ mk_instr_t load_instr(const mk_instr_t* p) {
   const int4* q = reinterpret_cast<const int4*>(p);
-  const int4 a = q[0], b = q[1], c2 = q[2];
+  const int4 a = q[0], b = q[1], c2 = q[2], d = q[3];
   mk_instr_t r;
   r.op = a.x; r.unit = a.y; r.signal = a.z; r.n_waits = a.w;
   r.wait_off = b.x; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
   r.ld_maps = 0; r.ld_row_a = 0; r.ld_row_b = 0; r.ld_tiles = 0;
-  r.ld_flags = (c2.x | c2.y) != 0 ? kInsMatvec : 0;
+  r.ld_flags = (c2.x | c2.y) != 0 ? (d.y | kInsMatvec) : 0;
   return r;
 }
 
@@ -204,7 +204,8 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
   const int w = c.warp - 1;
   constexpr int T = kConsumerWarps * 32;
   uint32_t seq = 0;
-  uint32_t mv_ord = 0;  // multi-page matvec units of this CTA so far (selects the split-K slot set)
+  uint32_t mv_ord = 0;  // shared matvec units of this CTA so far (selects the split-K slot set)
+  uint32_t pseq = 0;    // consumer slots handed out to matvec units so far (round-robin over warps)
   int staged_key = 0;
   int cached_op = -1;   // op whose record sits in the shared-memory copy
   int bulk_units = 0;   // > 0: units of cached_op are signalled in bulk
@@ -252,19 +253,23 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     for (int i = 0; i < n; ++i) {
       const int local = base + i - ibeg;
       while (cur.pos <= local) do_event();
-      // A matvec unit is shared: consumer (seq + p) mod kConsumerWarps takes
-      // page p.  Every other unit belongs to one consumer, round-robin.  Only
-      // a consumer that takes part fetches the rest of the record.
+      // A matvec unit is shared by `split` consumers, taken round-robin:
+      // consumer (pseq + j) mod kConsumerWarps is participant j and gets
+      // pages j, j + split, ... of the unit.  Every other unit belongs to one
+      // consumer.  Only a consumer that takes part fetches the whole record.
       const int n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i);
-      const bool is_mv = (__shfl_sync(0xffffffffu, mine.ld_flags, i) & kInsMatvec) != 0;
-      const bool take = is_mv ? mv_first_page(w, seq) < n_pages : (local % kConsumerWarps) == w;
+      const int lflags = __shfl_sync(0xffffffffu, mine.ld_flags, i);
+      const bool is_mv = (lflags & kInsMatvec) != 0;
+      const int split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+      const int part = mv_first_page(w, pseq);
+      const bool take = is_mv ? part < split : (local % kConsumerWarps) == w;
       if (take && !c.dead) {
         const mk_instr_t ins = bcast_instr(mine, i);
         c.instr_idx = base + i;
         if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
           trace(c, TRC_UNIT_BEGIN, base + i);
           const mk_op_t* op = ins.op == cached_op ? &c.ctrl->op_cache : pv.ops + ins.op;
-          const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord);
+          const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord | ((uint32_t)part << 28));
           if (!c.dead && finished) {
             if (bulk_units > 0 && ins.op == cached_op)
               signal_unit_bulk(c, ins.signal, bulk_units);
@@ -274,7 +279,10 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
           trace(c, TRC_UNIT_END, base + i);
         }
       }
-      if (is_mv && n_pages > 1) ++mv_ord;
+      if (is_mv) {
+        pseq += (uint32_t)split;
+        if (split > 1) ++mv_ord;
+      }
       seq += (uint32_t)n_pages;
     }
   }
@@ -785,7 +793,12 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
       const int mode = op.i[MK_MV_MODE];
       in.ld_maps = (uint64_t)(ws + l.tmaps) + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
       in.ld_tiles = fp4 ? op.i[MK_MV_KC] / 256 : op.i[MK_MV_KC] / 64;
-      in.ld_flags = (fp4 ? MK_LDF_FP4 : 0) | (mode == MK_MV_PAIR ? MK_LDF_PAIR : 0);
+      // consumers per unit: participant j takes pages j, j + split, ...; none idle
+      int split = op.i[MK_MV_SPLIT];
+      if (split <= 0 || split > kConsumerWarps) split = kConsumerWarps;
+      split = std::min(split, std::max(1, in.n_pages));
+      in.ld_flags = (fp4 ? MK_LDF_FP4 : 0) | (mode == MK_MV_PAIR ? MK_LDF_PAIR : 0) |
+                    (std::max(1, split) << MK_LDF_SPLIT_SHIFT);
       if (mode == MK_MV_PLAIN) {
         in.ld_row_a = in.unit * 16;
         in.ld_row_b = in.unit * 16 + 8;

@@ -275,6 +275,9 @@ __device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, const
   const float* lpart = reinterpret_cast<const float*>(op->p[MK_AT_P_LSEPART]);
   float* lse_out = reinterpret_cast<float*>(op->p[MK_AT_P_LSE]);
   const int ot = op->i[MK_AT_O_T];
+  // Lane j of a chunk holds the weight of split c0 + j; the partial rows of
+  // several splits are requested together so that their latencies overlap.
+  constexpr int UN = 6;
   for (int m = 0; m < M; ++m) {
     const int64_t base = ((int64_t)b * H + h) * S;
     float mx = -INFINITY;
@@ -286,16 +289,30 @@ __device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, const
     sum = warp_sum(sum);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
     const int64_t ooff = b * op->s[MK_AT_S_O_B] + m * op->s[MK_AT_S_O_M] + h * op->s[MK_AT_S_O_H];
-    for (int d = c.lane * 2; d < D; d += 64) {
+    for (int d0 = 0; d0 < D; d0 += 64) {
+      const int d = d0 + c.lane * 2;
+      const bool dv = d < D;
       float a0 = 0.f, a1 = 0.f;
-      if (sum > 0.f) {
-        for (int s = 0; s < S; ++s) {
-          const float w = __expf(lpart[(base + s) * M + m] - mx) * inv;
-          const float2 v = *reinterpret_cast<const float2*>(opart + ((base + s) * M + m) * D + d);
-          a0 += w * v.x;
-          a1 += w * v.y;
+      for (int c0 = 0; c0 < S && sum > 0.f; c0 += 32) {
+        const int cnt = min(32, S - c0);
+        const float wl = (c.lane < cnt) ? __expf(lpart[(base + c0 + c.lane) * M + m] - mx) * inv : 0.f;
+        for (int j0 = 0; j0 < cnt; j0 += UN) {
+          float2 v[UN];
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            v[u] = make_float2(0.f, 0.f);
+            if (dv && j0 + u < cnt)
+              v[u] = *reinterpret_cast<const float2*>(opart + ((base + c0 + j0 + u) * M + m) * D + d);
+          }
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const float w = __shfl_sync(0xffffffffu, wl, (j0 + u) & 31);
+            a0 += w * v[u].x;
+            a1 += w * v[u].y;
+          }
         }
       }
+      if (!dv) continue;
       if (ot == MK_T_FP32) {
         float* o = reinterpret_cast<float*>(op->p[MK_AT_P_O]) + ooff + d;
         o[0] = a0;

@@ -394,9 +394,12 @@ __device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, ui
 // layout), -1 = decided per op at run time.
 template <int NT, int NA, int WFC>
 __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ord) {
+  // ord: bits 0-27 = slot-set ordinal, bits 28-31 = this consumer's participant index
   const int unit = ins.unit;
-  const int w = c.warp - 1;
-  const int p0 = mv_first_page(w, seq);
+  const int part = (int)(ord >> 28);
+  ord &= 0x0fffffffu;
+  const int parts = (ins.ld_flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+  const int p0 = part;   // participant j takes pages j, j + parts, j + 2 parts, ...
   const int g = c.lane >> 2, t = c.lane & 3;
   const int K = op->i[MK_MV_K], Kc = op->i[MK_MV_KC], M = op->i[MK_MV_M];
   const int wfmt = WFC == 0 ? (int)MK_W_BF16 : op->i[MK_MV_WFMT];
@@ -422,7 +425,7 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
 
   const int np = ins.n_pages;
   RingPos rp = ring_at(seq + (uint32_t)p0, c.pv->n_pages);
-  for (int p = p0; p < np; p += kConsumerWarps, ring_advance(rp, kConsumerWarps, c.pv->n_pages)) {
+  for (int p = p0; p < np; p += parts, ring_advance(rp, parts, c.pv->n_pages)) {
     uint32_t page;
     if (!page_acquire(c, rp, page)) return false;
     trace(c, TRC_PAGE_READY, seq + p);
@@ -582,7 +585,6 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
       for (int e = 0; e < 4; ++e) acc[0][nt][e] += acc[a][nt][e];
 
   // Split-K reduction across the participating consumers.
-  const int parts = min(np, kConsumerWarps);
   // mv_sets (1, 2 or 4) slot sets share kPartialBytes; the host picks the
   // count so that the widest matvec op of the program fits a slot.
   const uint32_t sets = (uint32_t)c.pv->mv_sets;
@@ -593,7 +595,7 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
   if (parts > 1) {
     // the set's previous users (units ord - kSets, ...) must have been reduced
     if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
-    float* mine = slots + (size_t)w * kSlotFloats;
+    float* mine = slots + (size_t)part * kSlotFloats;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -612,9 +614,8 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[0][nt][e] = 0.f;
-    for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
-      if (mv_first_page(w2, seq) >= np) continue;
-      const float* src = slots + (size_t)w2 * kSlotFloats;
+    for (int j = 0; j < parts; ++j) {
+      const float* src = slots + (size_t)j * kSlotFloats;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll

@@ -134,6 +134,12 @@ def lower_matvec(
         n_units = (O // hd) * (d2 // 8)
         rows_per_unit = 16
 
+    # Consumer warps per unit: an op with few units per CTA spreads each unit's
+    # K-slices over several warps, an op with many keeps one warp per unit.
+    n_pages = -(-K // kc)
+    units_per_cta = -(-n_units // max(1, ctx.num_sms))
+    split = 1 if units_per_cta >= 2 * N.NUM_CONSUMER_WARPS else min(N.NUM_CONSUMER_WARPS, n_pages)
+
     wrow = int(w0.data.stride(0)) * w0.data.element_size()
     bytes_per_row = K // 2 + (K // 16) if fp4 else K * 2
     op = NativeOp(name=name, opcode=N.OP_MATVEC, n_units=n_units, kind=kind)
@@ -141,7 +147,7 @@ def lower_matvec(
         N.MV_O: O, N.MV_K: K, N.MV_M: M, N.MV_S: S, N.MV_MODE: mode, N.MV_PRO: pro, N.MV_EPI: epi,
         N.MV_TR: tr, N.MV_HD: hd, N.MV_D2: int(cos.shape[1]) if cos is not None else 0, N.MV_POS: int(pos),
         N.MV_WFMT: w0.fmt, N.MV_KC: kc, N.MV_OUT_T: elem_type(out, f"{name}: out") if epi != N.EPI_TOP1 else 0,
-        N.MV_X_T: xt, N.MV_ROWS_PER_UNIT: rows_per_unit,
+        N.MV_X_T: xt, N.MV_ROWS_PER_UNIT: rows_per_unit, N.MV_SPLIT: split,
     }
     op.f = {N.MV_F_EPS: eps, N.MV_F_GSCALE: w0.global_scale}
     op.p = {N.MV_P_W0: w0.data.data_ptr(), N.MV_P_W1: (w1 or w0).data.data_ptr(), N.MV_P_X: x.data_ptr(),

@@ -28,7 +28,7 @@ from .scheduling import BackwardScheduler, BuiltProgram, InstructionStreamBuilde
 
 MAX_PAGES = 32
 NUM_DMA_WARPS = 1
-NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
+NUM_CONSUMER_WARPS = N.NUM_CONSUMER_WARPS
 CTRL_BYTES = 4096 + NUM_CONSUMER_WARPS * 2048   # control block + split-K partial slots (csrc/shell.cuh)
 
 # Used when no CUDA device is present (table building and CPU tests): B200.
