@@ -174,7 +174,10 @@ typedef struct mk_instr {
 } mk_instr_t;
 
 /* bits 8-11 of ld_flags: consumer warps sharing the unit (from MK_MV_SPLIT) */
-enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15 };
+/* MK_LDF_ATTN marks a split-KV attention unit: ld_maps holds the K and V cache
+ * maps, ld_row_a the first token, ld_row_b = kv head | batch << 16, ld_tiles
+ * the tokens per page; MK_LDF_D128 = head dim 128 (two 64-wide sub-tiles). */
+enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_ATTN = 4, MK_LDF_D128 = 8, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15 };
 
 /* Op-entry event: before a CTA executes instruction `pos` of its list, all
  * of its consumer warps meet, wait for the listed counters and stage the

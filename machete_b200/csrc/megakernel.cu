@@ -90,6 +90,7 @@ __device__ __forceinline__ LoaderInstr bcast_loader_instr(const LoaderInstr& m, 
 __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
   const ProgramView& pv = *c.pv;
   const int NP = pv.n_pages;
+  const uint64_t policy = l2_evict_first_policy();
   uint32_t seq = 0;
   RingPos rp;
   rp.slot = 0;
@@ -107,7 +108,30 @@ __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
         if (!wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
         trace(c, TRC_LWAIT_DONE, base + i);
       }
-      if (ins.maps != 0) {
+      if (ins.maps != 0 && (ins.flags & MK_LDF_ATTN)) {
+        // A split-KV attention unit: one K box and one V box per page (two each
+        // for head dim 128), issued by lane 0 from the instruction record.
+        if (ins.n_lwaits > 0) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
+        int issued = 0;
+        if (c.lane == 0) {
+          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
+          RingPos q = rp;
+          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
+            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
+                               (int)(seq + issued)))
+              break;
+            trace(c, TRC_LOAD_BEGIN, seq + issued);
+            at_load_issue(maps, maps + 128, (ins.flags & MK_LDF_D128) != 0, ins.tiles, ins.row_a + issued * ins.tiles,
+                          ins.row_b & 0xffff, ins.row_b >> 16, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes,
+                          full_bar(c, q.slot), policy);
+            trace(c, TRC_LOAD_ISSUED, seq + issued);
+          }
+        }
+        issued = __shfl_sync(0xffffffffu, issued, 0);
+        if (issued < ins.n_pages) c.dead = true;
+        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
+        seq += (uint32_t)issued;
+      } else if (ins.maps != 0) {
         // A matvec unit: tiled-TMA pages, issued by lane 0 alone in a tight
         // loop from the fields of the instruction record (no op-table read on
         // this path; a one-thread wait needs no vote).  Fill k of a slot needs
@@ -132,7 +156,7 @@ __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
                                (int)(seq + issued)))
               break;
             trace(c, TRC_LOAD_BEGIN, seq + issued);
-            mv_load_issue(ml, issued, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes, full_bar(c, q.slot));
+            mv_load_issue(ml, issued, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes, full_bar(c, q.slot), policy);
             trace(c, TRC_LOAD_ISSUED, seq + issued);
           }
         }
@@ -148,11 +172,9 @@ __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
           trace(c, TRC_LOAD_BEGIN, seq);
           const uint32_t page = c.pages_u32 + rp.slot * (uint32_t)pv.page_bytes;
           const uint32_t bar = full_bar(c, rp.slot);
-          if (opcode == MK_OP_ATTN_SPLIT) {
-            at_load_page(op, ins.unit, p, page, bar, c.lane, pv.page_bytes);
-          } else {
-            mbar_arrive(bar);  // an op without loads: hand over an empty page
-          }
+          (void)opcode;
+          (void)page;
+          mbar_arrive(bar);  // an op without loads: hand over an empty page
           trace(c, TRC_LOAD_ISSUED, seq);
           ++seq;
           ring_next(rp, NP);
@@ -181,7 +203,7 @@ template <int NTC, int WFC>
 __device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t mv_ord) {
   switch (op->opcode) {
     case MK_OP_MATVEC: return mv_dispatch<NTC, WFC>(c, op, ins, seq, mv_ord);
-    case MK_OP_ATTN_SPLIT: at_dispatch(c, op, ins, seq); break;
+    case MK_OP_ATTN_SPLIT: return at_dispatch(c, op, ins, seq, mv_ord);
     case MK_OP_ATTN_COMBINE: at_combine_unit(c, op, ins); break;
     case MK_OP_RMSNORM: ew_rmsnorm(c, op, ins.unit); break;
     case MK_OP_ROPE: ew_rope(c, op, ins.unit); break;
@@ -454,7 +476,37 @@ static uint32_t mv_page_need(int wfmt, int Kc) {
 
 // Build the descriptors of matvec op `op` into `maps` (host copies) and point
 // the op record at their device addresses.
-static int build_op_maps(mk_op_t& op, CUtensorMap* maps, uint64_t dev_maps) {
+// K or V cache [B, N, HKV, D] (any strides with a contiguous head dim) as a
+// 4-D map: box = 64 head-dim values x 1 head x tn tokens x 1 batch, swizzled.
+static int encode_kv_map(CUtensorMap* out, uint64_t base, int D, int HKV, int N, int B, int64_t s_h, int64_t s_n,
+                         int64_t s_b, uint32_t tn) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(-5, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((base & 15) || ((s_h * 2) & 15) || ((s_n * 2) & 15) || (B > 1 && ((s_b * 2) & 15)))
+    return fail(-2, "attention: K/V base and head/token/batch strides must be 16-byte multiples");
+  if (s_h <= 0 || s_n <= 0) return fail(-2, "attention: K/V strides must be positive");
+  const uint64_t sb = (B > 1 && s_b > 0) ? (uint64_t)s_b * 2 : (uint64_t)s_n * 2 * (uint64_t)N;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)HKV, (cuuint64_t)N, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)s_h * 2, (cuuint64_t)s_n * 2, (cuuint64_t)((sb + 15) / 16 * 16)};
+  cuuint32_t box[4] = {64, 1, tn, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, reinterpret_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled (K/V cache) failed with CUresult %d", (int)r);
+  return 0;
+}
+
+static int build_op_maps(mk_op_t& op, CUtensorMap* maps, uint64_t dev_maps, int page_bytes) {
+  if (op.opcode == MK_OP_ATTN_SPLIT) {
+    const int D = op.i[MK_AT_D];
+    const uint32_t tn = (uint32_t)at_page_tokens(D, page_bytes);
+    int rc = encode_kv_map(&maps[0], op.p[MK_AT_P_K], D, op.i[MK_AT_HKV], op.i[MK_AT_N], op.i[MK_AT_B],
+                           op.s[MK_AT_S_K_H], op.s[MK_AT_S_K_N], op.s[MK_AT_S_K_B], tn);
+    if (rc) return rc;
+    return encode_kv_map(&maps[1], op.p[MK_AT_P_V], D, op.i[MK_AT_HKV], op.i[MK_AT_N], op.i[MK_AT_B],
+                         op.s[MK_AT_S_V_H], op.s[MK_AT_S_V_N], op.s[MK_AT_S_V_B], tn);
+  }
   if (op.opcode != MK_OP_MATVEC) return 0;
   const int wf = op.i[MK_MV_WFMT], K = op.i[MK_MV_K], Kc = op.i[MK_MV_KC];
   const bool fp4 = wf >= MK_W_NVFP4_F16S32;
@@ -772,7 +824,7 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
     memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
     for (int i = 0; i < prog->n_ops; ++i) {
       rc = build_op_maps(ops[i], &maps[(size_t)i * kMapsPerOp],
-                         (uint64_t)(ws + l.tmaps) + (uint64_t)i * kMapsPerOp * sizeof(CUtensorMap));
+                         (uint64_t)(ws + l.tmaps) + (uint64_t)i * kMapsPerOp * sizeof(CUtensorMap), prog->page_bytes);
       if (rc) {
         cudaSetDevice(prev_dev);
         return rc;
@@ -788,6 +840,20 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
       in.ld_maps = 0;
       in.ld_row_a = in.ld_row_b = in.ld_tiles = in.ld_flags = 0;
       const mk_op_t& op = prog->ops[in.op];
+      if (op.opcode == MK_OP_ATTN_SPLIT) {
+        // unit -> (batch, kv head, query tile, split), as at_decode does on the device
+        const int S = op.i[MK_AT_SPLITS], MT = op.i[MK_AT_MT], HKV = op.i[MK_AT_HKV];
+        const int sp = in.unit % S, kvh = (in.unit / S / MT) % HKV, b = in.unit / S / MT / HKV;
+        const int t_begin = std::min(op.i[MK_AT_N], sp * op.i[MK_AT_TS]);
+        in.ld_maps = (uint64_t)(ws + l.tmaps) + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
+        in.ld_row_a = t_begin;
+        in.ld_row_b = kvh | (b << 16);
+        in.ld_tiles = at_page_tokens(op.i[MK_AT_D], prog->page_bytes);
+        const int split = std::max(1, std::min((int)kConsumerWarps, in.n_pages));
+        in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT);
+        if (in.n_pages == 0) in.ld_maps = 0;   // an empty split: nothing to load, one consumer writes the empty partial
+        continue;
+      }
       if (op.opcode != MK_OP_MATVEC) continue;
       const bool fp4 = op.i[MK_MV_WFMT] >= MK_W_NVFP4_F16S32;
       const int mode = op.i[MK_MV_MODE];
@@ -912,7 +978,7 @@ int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_
   CUtensorMap maps[kMapsPerOp];
   memset(maps, 0, sizeof(maps));
   uint8_t* dev_maps = h->ws + h->layout.tmaps + (size_t)op_index * kMapsPerOp * sizeof(CUtensorMap);
-  const int rc = build_op_maps(rec, maps, (uint64_t)dev_maps);
+  const int rc = build_op_maps(rec, maps, (uint64_t)dev_maps, h->pv.page_bytes);
   if (rc) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   CUDA_TRY(cudaMemcpyAsync(dev_maps, maps, sizeof(maps), cudaMemcpyHostToDevice, st));

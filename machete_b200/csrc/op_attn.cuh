@@ -6,8 +6,8 @@
 // each K/V byte is fetched once — the reference tiles per *query* head and
 // re-reads each KV head `group` times (attention/flash_decoding.py:1192, 1324).
 //
-// K and V token rows are gathered into a ring page by 16-byte cp.async with an
-// XOR-8 chunk swizzle so that ldmatrix is bank-conflict free; scores and P·V
+// K and V token rows arrive in a ring page by tiled TMA with the 128-byte
+// swizzle, which makes ldmatrix bank-conflict free; scores and P·V
 // run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with an exp2 online
 // softmax.  Partials follow the reference's contract: normalised fp32
 // o_partial[B,H,SPLIT,M,D] and lse_partial[B,H,SPLIT,M] = max*scale + ln(sum)
@@ -49,41 +49,48 @@ __device__ __host__ __forceinline__ int at_page_tokens(int D, int page_bytes) {
 }
 
 // ---- loader -----------------------------------------------------------------------
-__device__ __forceinline__ void at_load_page(const mk_op_t* op, int unit, int p, uint32_t page, uint32_t bar,
-                                             int lane, int page_bytes) {
-  const AtUnit u = at_decode(op, unit);
-  const int D = op->i[MK_AT_D];
-  const int tn = at_page_tokens(D, page_bytes);
-  const int t0 = u.t_begin + p * tn;
-  const int ch = D >> 3;  // 16-byte chunks per row
-  const uint32_t rowb = (uint32_t)D * 2u;
-  const uint16_t* kb = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_K]) + u.b * op->s[MK_AT_S_K_B] +
-                       u.kvh * op->s[MK_AT_S_K_H];
-  const uint16_t* vb = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_V]) + u.b * op->s[MK_AT_S_V_B] +
-                       u.kvh * op->s[MK_AT_S_V_H];
-  const int64_t kn = op->s[MK_AT_S_K_N], vn = op->s[MK_AT_S_V_N];
-  const int total = tn * ch;
-  const uint32_t vbase = page + (uint32_t)tn * rowb;
-  for (int idx = lane; idx < total; idx += 32) {
-    const int tok = idx / ch, cc = idx - tok * ch;
-    const int tg = t0 + tok;
-    const bool valid = tg < u.t_end;
-    const uint32_t dsto = (uint32_t)tok * rowb + (uint32_t)((cc ^ (tok & 7)) << 4);
-    const uint16_t* ks = valid ? kb + (int64_t)tg * kn + cc * 8 : kb;
-    const uint16_t* vs = valid ? vb + (int64_t)tg * vn + cc * 8 : vb;
-    cp_async16(page + dsto, ks, valid ? 16u : 0u);
-    cp_async16(vbase + dsto, vs, valid ? 16u : 0u);
-  }
-  cp_async_mbar_arrive_noinc(bar);
+// Page layout: a K tile followed by a V tile.  A tile is D/64 sub-tiles of
+// [tn token rows][128 bytes] (64 head-dim values each), written by tiled TMA
+// with the 128-byte swizzle: 16-byte chunk c of token row r sits at
+// r*128 + ((c ^ (r & 7)) << 4), which is what ldmatrix wants (8 rows of a
+// matrix hit 8 different bank groups).  Tokens past the end of the cache are
+// zero-filled by TMA; tokens past the end of the split are masked by the
+// consumer.  Called by loader lane 0 only.
+__device__ __forceinline__ void at_load_issue(const void* tm_k, const void* tm_v, bool d128, int tn, int tok0, int kvh,
+                                              int b, uint32_t page, uint32_t bar, uint64_t policy) {
+  const uint32_t sub = (uint32_t)tn * 128u;
+  const uint32_t tile = d128 ? 2u * sub : sub;
+  mbar_expect_tx(bar, 2u * tile);
+  tma_load_4d(page, tm_k, 0, kvh, tok0, b, bar, policy);
+  if (d128) tma_load_4d(page + sub, tm_k, 64, kvh, tok0, b, bar, policy);
+  tma_load_4d(page + tile, tm_v, 0, kvh, tok0, b, bar, policy);
+  if (d128) tma_load_4d(page + tile + sub, tm_v, 64, kvh, tok0, b, bar, policy);
+  mbar_arrive_n(bar, 32);
+}
+
+__device__ __forceinline__ uint32_t at_chunk_addr(uint32_t tile, int tn, int tok, int chunk) {
+  return tile + (uint32_t)(chunk >> 3) * (uint32_t)tn * 128u + (uint32_t)tok * 128u +
+         (uint32_t)(((chunk & 7) ^ (tok & 7)) << 4);
 }
 
 // ---- consumer ---------------------------------------------------------------------
+// The unit's pages (blocks of tn tokens) are dealt round-robin to `parts`
+// consumer warps; each keeps its own online-softmax state (row max, row sum,
+// unnormalised output).  A participant parks its state in the last page it
+// consumed instead of handing that page back; the last one to arrive merges
+// the states in participant order, writes the normalised partial and then
+// releases everybody's parked page.  `ordpart`: bits 0-27 slot-set ordinal,
+// bits 28-31 participant index.  Returns true for the warp that finished the
+// unit.
 template <int D>
-__device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+__device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
   constexpr int KS = D / 16;   // k-steps of Q·K^T
   constexpr int ND = D / 8;    // n-tiles of the output
   constexpr int TN = (D == 64) ? 64 : 32;  // tokens processed per inner block
   constexpr int NS = TN / 8;   // score n-tiles per block
+  const int part = (int)(ordpart >> 28);
+  const uint32_t ord = ordpart & 0x0fffffffu;
+  const int parts = (ins.ld_flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
   const AtUnit u = at_decode(op, ins.unit);
   const int g = c.lane >> 2, t = c.lane & 3;
   const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], N = op->i[MK_AT_N];
@@ -93,7 +100,8 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   const float sc = op->f[MK_AT_F_SCALE];
   const float c2 = sc * 1.4426950408889634f;
   const int tn = at_page_tokens(D, c.pv->page_bytes);
-  const uint32_t rowb = (uint32_t)D * 2u;
+  const uint32_t tile_bytes = (uint32_t)tn * (uint32_t)D * 2u;
+  const int NPG = c.pv->n_pages;
 
   // rows of this thread: r0 = mt*16 + g, r1 = r0 + 8 -> (m, head)
   int rm[2], rh[2];
@@ -131,14 +139,16 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
   float mrow[2] = {-INFINITY, -INFINITY};
-  float lrow[2] = {0.f, 0.f};
+  float lrow[2] = {0.f, 0.f};   // per-lane partial row sums (summed over the quad at the end)
 
   const int np = ins.n_pages;
-  RingPos rp = ring_at(seq, c.pv->n_pages);
-  for (int p = 0; p < np; ++p, ring_next(rp, c.pv->n_pages)) {
+  RingPos rp = ring_at(seq + (uint32_t)part, NPG);
+  uint32_t park = 0;            // address of the page this warp keeps for its state
+  for (int p = part; p < np; p += parts, ring_advance(rp, parts, NPG)) {
     uint32_t page;
-    if (!page_acquire(c, rp, page)) return;
-    const uint32_t kpage = page, vpage = page + (uint32_t)tn * rowb;
+    if (!page_acquire(c, rp, page)) return false;
+    trace(c, TRC_PAGE_READY, seq + p);
+    const uint32_t kpage = page, vpage = page + tile_bytes;
     const int tp0 = u.t_begin + p * tn;
     for (int blk = 0; blk * TN < tn; ++blk) {
       const int tb0 = tp0 + blk * TN;       // global token of column 0 of the block
@@ -157,9 +167,8 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
           const int mat = c.lane >> 3, r = c.lane & 7;
           const int tok = lt0 + pr * 16 + (mat >> 1) * 8 + r;
           const int chunk = 2 * ks + (mat & 1);
-          const uint32_t addr = kpage + (uint32_t)tok * rowb + (uint32_t)((chunk ^ (tok & 7)) << 4);
           uint32_t b0, b1, b2, b3;
-          ldmatrix_x4(addr, b0, b1, b2, b3);
+          ldmatrix_x4(at_chunk_addr(kpage, tn, tok, chunk), b0, b1, b2, b3);
           mma_bf16(s[2 * pr], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
           mma_bf16(s[2 * pr + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
         }
@@ -216,17 +225,93 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
           const int mat = c.lane >> 3, r = c.lane & 7;
           const int tok = lt0 + kk * 16 + (mat & 1) * 8 + r;
           const int chunk = 2 * dp + (mat >> 1);
-          const uint32_t addr = vpage + (uint32_t)tok * rowb + (uint32_t)((chunk ^ (tok & 7)) << 4);
           uint32_t b0, b1, b2, b3;
-          ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+          ldmatrix_x4_trans(at_chunk_addr(vpage, tn, tok, chunk), b0, b1, b2, b3);
           mma_bf16(o[2 * dp], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
           mma_bf16(o[2 * dp + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
         }
       }
     }
-    page_release(c, rp);
+    trace(c, TRC_PAGE_DONE, seq + p);
+    if (parts > 1 && p + parts >= np)
+      park = page;              // the last page of this participant: keep it
+    else
+      page_release(c, rp);
   }
+
+  if (parts > 1) {
+    // park (o, m, l) lane-major in the kept page: word (i*32 + lane) of the state
+    const uint32_t set = ord % (uint32_t)c.pv->mv_sets, gen = ord / (uint32_t)c.pv->mv_sets;
+    if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < ND; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sts32(park + (uint32_t)((i * 4 + e) * 32 + c.lane) * 4u, __float_as_uint(o[i][e]));
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      sts32(park + (uint32_t)((ND * 4 + e) * 32 + c.lane) * 4u, __float_as_uint(mrow[e]));
+      sts32(park + (uint32_t)((ND * 4 + 2 + e) * 32 + c.lane) * 4u, __float_as_uint(lrow[e]));
+    }
+    __syncwarp();
+    int last = 0;
+    if (c.lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&c.ctrl->mv_arrive[set], 1u) == (uint32_t)(parts - 1);
+      __threadfence_block();
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    trace(c, TRC_MV_ARRIVED, ord);
+    if (!last) return false;
+    // merge in participant order
+#pragma unroll
+    for (int i = 0; i < ND; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    mrow[0] = mrow[1] = -INFINITY;
+    lrow[0] = lrow[1] = 0.f;
+    for (int j = 0; j < parts; ++j) {
+      const int pl = j + ((np - 1 - j) / parts) * parts;   // last page of participant j
+      const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
+      const uint32_t src = c.pages_u32 + rj.slot * (uint32_t)c.pv->page_bytes;
+      float mj[2], lj[2], wa[2], wb[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        mj[e] = __uint_as_float(lds32(src + (uint32_t)((ND * 4 + e) * 32 + c.lane) * 4u));
+        lj[e] = __uint_as_float(lds32(src + (uint32_t)((ND * 4 + 2 + e) * 32 + c.lane) * 4u));
+        const float mnew = fmaxf(mrow[e], mj[e]);
+        const float muse = (mnew == -INFINITY) ? 0.f : mnew;
+        wa[e] = fast_exp2((mrow[e] - muse) * c2);
+        wb[e] = fast_exp2((mj[e] - muse) * c2);
+        mrow[e] = mnew;
+        lrow[e] = lrow[e] * wa[e] + lj[e] * wb[e];
+      }
+#pragma unroll
+      for (int i = 0; i < ND; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float v = __uint_as_float(lds32(src + (uint32_t)((i * 4 + e) * 32 + c.lane) * 4u));
+          o[i][e] = o[i][e] * wa[e >> 1] + v * wb[e >> 1];
+        }
+    }
+    // hand the parked pages back (generic-proxy writes before the next TMA fill)
+    __syncwarp();
+    if (c.lane == 0) {
+      fence_proxy_async();
+      for (int j = 0; j < parts; ++j) {
+        const int pl = j + ((np - 1 - j) / parts) * parts;
+        const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
+        mbar_arrive(empty_bar(c, rj.slot));
+        *reinterpret_cast<volatile uint32_t*>(&c.ctrl->released[rj.slot]) = rj.k + 1u;
+      }
+      c.ctrl->mv_arrive[set] = 0;
+      __threadfence_block();
+      *reinterpret_cast<volatile uint32_t*>(&c.ctrl->mv_done[set]) = gen + 1u;
+    }
+  }
+
   // finalise: normalised partial + lse
+  trace(c, TRC_MV_REDUCED, ord);
   float* op_ = reinterpret_cast<float*>(op->p[MK_AT_P_OPART]);
   float* lp_ = reinterpret_cast<float*>(op->p[MK_AT_P_LSEPART]);
 #pragma unroll
@@ -246,25 +331,27 @@ __device__ __forceinline__ void at_unit(Ctx& c, const mk_op_t* op, const mk_inst
     }
     if (t == 0) lp_[base] = lse;
   }
+  return true;
 }
 
 template <int D>
-__device__ __noinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq) {
-  at_unit<D>(c, op, ins, seq);
+__device__ __forceinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq, uint32_t ordpart) {
   UnitResult r;
+  r.signal = at_unit<D>(c, op, ins, seq, ordpart);
   r.dead = c.dead;
   r.trace_n = c.trace_n;
   return r;
 }
 
-__device__ __forceinline__ void at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq) {
+__device__ __forceinline__ bool at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
   UnitResult r;
   if (op->i[MK_AT_D] == 64)
-    r = at_unit_call<64>(c, op, ins, seq);
+    r = at_unit_call<64>(c, op, ins, seq, ordpart);
   else
-    r = at_unit_call<128>(c, op, ins, seq);
+    r = at_unit_call<128>(c, op, ins, seq, ordpart);
   c.dead = r.dead;
   c.trace_n = r.trace_n;
+  return r.signal;
 }
 
 // Combine: one unit per (b, query head); all M rows.

@@ -114,19 +114,19 @@ __device__ __forceinline__ MvLoad mv_load_setup(const mk_op_t* op, int unit) {
 // Issue the copies of K-slice `p` into the page at `page` (shared address):
 // two tiled TMA copies (four with NVFP4 scales) and one arrival for the whole
 // loader warp.  Called by loader lane 0 only.
-__device__ __forceinline__ void mv_load_issue(const MvLoad& l, int p, uint32_t page, uint32_t bar) {
+__device__ __forceinline__ void mv_load_issue(const MvLoad& l, int p, uint32_t page, uint32_t bar, uint64_t policy) {
   const int kt0 = p * l.tiles_per_page;
   if (!l.fp4) {
     mbar_expect_tx(bar, 2u * l.half);
-    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar);
-    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar);
+    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar, policy);
+    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar, policy);
   } else {
     // a scale tile row holds the 128 scale bytes of 2048 K-values = one page
     mbar_expect_tx(bar, 2u * l.half + 2048u);
-    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar);
-    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar);
-    tma_load_3d(page + 2u * l.half, l.ts_a, 0, l.rowA0, p, bar);
-    tma_load_3d(page + 2u * l.half + 1024u, l.ts_b, 0, l.rowB0, p, bar);
+    tma_load_3d(page, l.tm_a, 0, l.rowA0, kt0, bar, policy);
+    tma_load_3d(page + l.half, l.tm_b, 0, l.rowB0, kt0, bar, policy);
+    tma_load_3d(page + 2u * l.half, l.ts_a, 0, l.rowA0, p, bar, policy);
+    tma_load_3d(page + 2u * l.half + 1024u, l.ts_b, 0, l.rowB0, p, bar, policy);
   }
   mbar_arrive_n(bar, 32);
 }
@@ -352,32 +352,6 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
 // Swizzled address of 16-byte chunk `c` of row `r` (0-7) inside a 1 KB tile.
 __device__ __forceinline__ uint32_t tile_chunk(uint32_t tile, int r, int c) {
   return tile + (uint32_t)r * 128u + (uint32_t)((c ^ r) << 4);
-}
-
-// First page (K-slice) of a unit that consumer `w` takes when the unit's pages
-// start at ring entry `seq`: consumers take ring entries round-robin, so all
-// of them stream at once whatever the shape of the op.
-__device__ __forceinline__ int mv_first_page(int w, uint32_t seq) {
-  const int s = (int)(seq % (uint32_t)kConsumerWarps);
-  return w >= s ? w - s : w + kConsumerWarps - s;
-}
-
-// Bounded wait until a shared-memory word reaches `want`.
-__device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, uint32_t want, int aux) {
-  if (c.dead) return false;
-  if (__all_sync(0xffffffffu, *word >= want)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (__all_sync(0xffffffffu, *word >= want)) return true;
-      nanosleep(20);
-    }
-    if (give_up_check(c, t0, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)want)) {
-      c.dead = true;
-      return false;
-    }
-  }
 }
 
 // NT = n-tiles of 8 activation rows; NA = independent accumulator sets (the

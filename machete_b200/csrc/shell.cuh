@@ -353,6 +353,32 @@ __device__ __forceinline__ void signal_unit(Ctx& c, int counter) {
   }
 }
 
+// Participant index of consumer `w` in a shared unit whose first participant
+// slot is `seq` (slots are handed to the consumer warps round-robin); the
+// consumer takes part if the result is below the unit's participant count.
+__device__ __forceinline__ int mv_first_page(int w, uint32_t seq) {
+  const int s = (int)(seq % (uint32_t)kConsumerWarps);
+  return w >= s ? w - s : w + kConsumerWarps - s;
+}
+
+// Bounded wait until a shared-memory word reaches `want`.
+__device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, uint32_t want, int aux) {
+  if (c.dead) return false;
+  if (__all_sync(0xffffffffu, *word >= want)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (__all_sync(0xffffffffu, *word >= want)) return true;
+      nanosleep(20);
+    }
+    if (give_up_check(c, t0, MK_ST_TIMEOUT_PAGE_TURN, aux, (int)want)) {
+      c.dead = true;
+      return false;
+    }
+  }
+}
+
 // Bulk variant: the unit's finisher counts it in shared memory; whoever counts
 // the CTA's last unit of the op publishes all of them with one device-scope
 // release (the earlier finishers' writes reach it through the cta-scope
