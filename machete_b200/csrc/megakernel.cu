@@ -226,8 +226,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
   const int w = c.warp - 1;
   constexpr int T = kConsumerWarps * 32;
   uint32_t seq = 0;
-  uint32_t mv_ord = 0;  // shared matvec units of this CTA so far (selects the split-K slot set)
-  uint32_t pseq = 0;    // consumer slots handed out to matvec units so far (round-robin over warps)
+  uint32_t mv_ord = 0;  // shared units before the cursor (selects the split-K slot set)
   int staged_key = 0;
   int cached_op = -1;   // op whose record sits in the shared-memory copy
   int bulk_units = 0;   // > 0: units of cached_op are signalled in bulk
@@ -267,45 +266,63 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     if (ev < eend) cur = pv.events[ev];
   };
 
-  for (int base = ibeg; base < iend; base += 32) {
-    const int n = min(32, iend - base);
-    mk_instr_t mine;
-    memset(&mine, 0, sizeof(mine));
-    if (c.lane < n) mine = load_instr(pv.instrs + base + c.lane);
-    for (int i = 0; i < n; ++i) {
-      const int local = base + i - ibeg;
-      while (cur.pos <= local) do_event();
-      // A matvec unit is shared by `split` consumers, taken round-robin:
-      // consumer (pseq + j) mod kConsumerWarps is participant j and gets
-      // pages j, j + split, ... of the unit.  Every other unit belongs to one
-      // consumer.  Only a consumer that takes part fetches the whole record.
-      const int n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i);
-      const int lflags = __shfl_sync(0xffffffffu, mine.ld_flags, i);
-      const bool is_mv = (lflags & kInsMatvec) != 0;
-      const int split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
-      const int part = mv_first_page(w, pseq);
-      const bool take = is_mv ? part < split : (local % kConsumerWarps) == w;
-      if (take && !c.dead) {
-        const mk_instr_t ins = bcast_instr(mine, i);
-        c.instr_idx = base + i;
-        if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
-          trace(c, TRC_UNIT_BEGIN, base + i);
-          const mk_op_t* op = ins.op == cached_op ? &c.ctrl->op_cache : pv.ops + ins.op;
-          const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord | ((uint32_t)part << 28));
-          if (!c.dead && finished) {
-            if (bulk_units > 0 && ins.op == cached_op)
-              signal_unit_bulk(c, ins.signal, bulk_units);
-            else
-              signal_unit(c, ins.signal);
-          }
-          trace(c, TRC_UNIT_END, base + i);
-        }
+  // Consumer slots are handed out through a ticket counter: a unit owns as
+  // many consecutive tickets as it has participants (one for a unit that is
+  // not shared), and a consumer that becomes free draws the next ticket, so a
+  // warp that is held up (by an epilogue, by a page that is late) never has
+  // a fixed share of later work waiting behind it.  Tickets rise, so each
+  // consumer walks the instruction list forward only; passing an op-entry
+  // event on the way means taking part in it.
+  int i = ibeg;          // instruction under the cursor
+  int base = ibeg - 32;  // `mine` holds the records of [base, base + 32)
+  uint32_t first_slot = 0;  // ticket of the first slot of instruction i
+  mk_instr_t mine;
+  memset(&mine, 0, sizeof(mine));
+  for (;;) {
+    uint32_t ticket = 0;
+    if (c.lane == 0) ticket = atomicAdd(&c.ctrl->ticket, 1u);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    bool found = false;
+    int n_pages = 0, split = 0;
+    bool shared = false;
+    while (i < iend) {
+      if (i - base >= 32) {
+        base = ibeg + ((i - ibeg) & ~31);
+        memset(&mine, 0, sizeof(mine));
+        if (base + c.lane < iend) mine = load_instr(pv.instrs + base + c.lane);
       }
-      if (is_mv) {
-        pseq += (uint32_t)split;
-        if (split > 1) ++mv_ord;
+      while (cur.pos <= i - ibeg) do_event();
+      n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i - base);
+      const int lflags = __shfl_sync(0xffffffffu, mine.ld_flags, i - base);
+      shared = (lflags & kInsMatvec) != 0;
+      split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+      const uint32_t slots = shared ? (uint32_t)split : 1u;
+      if (ticket < first_slot + slots) {
+        found = true;
+        break;
       }
+      first_slot += slots;
       seq += (uint32_t)n_pages;
+      if (shared && split > 1) ++mv_ord;
+      ++i;
+    }
+    if (!found) break;
+    if (!c.dead) {
+      const int part = (int)(ticket - first_slot);
+      const mk_instr_t ins = bcast_instr(mine, i - base);
+      c.instr_idx = i;
+      if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
+        trace(c, TRC_UNIT_BEGIN, i);
+        const mk_op_t* op = ins.op == cached_op ? &c.ctrl->op_cache : pv.ops + ins.op;
+        const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord | ((uint32_t)part << 28));
+        if (!c.dead && finished) {
+          if (bulk_units > 0 && ins.op == cached_op)
+            signal_unit_bulk(c, ins.signal, bulk_units);
+          else
+            signal_unit(c, ins.signal);
+        }
+        trace(c, TRC_UNIT_END, i);
+      }
     }
   }
   while (ev < eend) do_event();
@@ -337,6 +354,8 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
     for (int i = 0; i < 4; ++i) c.ctrl->mv_arrive[i] = c.ctrl->mv_done[i] = 0;
     c.ctrl->abort_flag = 0;
     c.ctrl->is_last = 0;
+    c.ctrl->ticket = 0;
+    c.ctrl->bulk_done = 0;
     fence_mbar_init();
   }
   __syncthreads();

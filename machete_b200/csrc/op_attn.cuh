@@ -240,19 +240,18 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   }
 
   if (parts > 1) {
-    // park (o, m, l) lane-major in the kept page: word (i*32 + lane) of the state
+    // park (o, m, l) in the kept page: 16-byte record (i*32 + lane) holds o[i][0..3], the last one (m, m, l, l)
     const uint32_t set = ord % (uint32_t)c.pv->mv_sets, gen = ord / (uint32_t)c.pv->mv_sets;
     if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < ND; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sts32(park + (uint32_t)((i * 4 + e) * 32 + c.lane) * 4u, __float_as_uint(o[i][e]));
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      sts32(park + (uint32_t)((ND * 4 + e) * 32 + c.lane) * 4u, __float_as_uint(mrow[e]));
-      sts32(park + (uint32_t)((ND * 4 + 2 + e) * 32 + c.lane) * 4u, __float_as_uint(lrow[e]));
-    }
+      sts128(park + (uint32_t)(i * 32 + c.lane) * 16u,
+             make_uint4(__float_as_uint(o[i][0]), __float_as_uint(o[i][1]), __float_as_uint(o[i][2]),
+                        __float_as_uint(o[i][3])));
+    sts128(park + (uint32_t)(ND * 32 + c.lane) * 16u,
+           make_uint4(__float_as_uint(mrow[0]), __float_as_uint(mrow[1]), __float_as_uint(lrow[0]),
+                      __float_as_uint(lrow[1])));
     __syncwarp();
     int last = 0;
     if (c.lane == 0) {
@@ -274,11 +273,12 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       const int pl = j + ((np - 1 - j) / parts) * parts;   // last page of participant j
       const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
       const uint32_t src = c.pages_u32 + rj.slot * (uint32_t)c.pv->page_bytes;
-      float mj[2], lj[2], wa[2], wb[2];
+      float wa[2], wb[2];
+      const uint4 ml = lds128_sync(src + (uint32_t)(ND * 32 + c.lane) * 16u);
+      const float mj[2] = {__uint_as_float(ml.x), __uint_as_float(ml.y)};
+      const float lj[2] = {__uint_as_float(ml.z), __uint_as_float(ml.w)};
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        mj[e] = __uint_as_float(lds32(src + (uint32_t)((ND * 4 + e) * 32 + c.lane) * 4u));
-        lj[e] = __uint_as_float(lds32(src + (uint32_t)((ND * 4 + 2 + e) * 32 + c.lane) * 4u));
         const float mnew = fmaxf(mrow[e], mj[e]);
         const float muse = (mnew == -INFINITY) ? 0.f : mnew;
         wa[e] = fast_exp2((mrow[e] - muse) * c2);
@@ -287,12 +287,13 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
         lrow[e] = lrow[e] * wa[e] + lj[e] * wb[e];
       }
 #pragma unroll
-      for (int i = 0; i < ND; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float v = __uint_as_float(lds32(src + (uint32_t)((i * 4 + e) * 32 + c.lane) * 4u));
-          o[i][e] = o[i][e] * wa[e >> 1] + v * wb[e >> 1];
-        }
+      for (int i = 0; i < ND; ++i) {
+        const uint4 v = lds128_sync(src + (uint32_t)(i * 32 + c.lane) * 16u);
+        o[i][0] = o[i][0] * wa[0] + __uint_as_float(v.x) * wb[0];
+        o[i][1] = o[i][1] * wa[0] + __uint_as_float(v.y) * wb[0];
+        o[i][2] = o[i][2] * wa[1] + __uint_as_float(v.z) * wb[1];
+        o[i][3] = o[i][3] * wa[1] + __uint_as_float(v.w) * wb[1];
+      }
     }
     // hand the parked pages back (generic-proxy writes before the next TMA fill)
     __syncwarp();

@@ -183,6 +183,19 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   write_res = write_res && add && ro != nullptr;
   if (!stage && !write_res) return;
 
+  // The norm weights do not depend on the row sums: request this thread's
+  // first chunks now, so that their latency overlaps the activation loads and
+  // the barrier instead of following them.
+  constexpr int kNwCached = 5;
+  uint4 nwc[kNwCached];
+  if (stage && pro != MK_PRO_NONE) {
+#pragma unroll
+    for (int i = 0; i < kNwCached; ++i) {
+      const int ch = tid + i * T;
+      nwc[i] = ch < chunks ? *reinterpret_cast<const uint4*>(nw + ch * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
+
   for (int m = 0; m < M; ++m) {
     const int b = m / S, s = m - b * S;
     const uint16_t* xr = x + b * op->s[MK_MV_S_X_B] + s * op->s[MK_MV_S_X_S];
@@ -227,7 +240,23 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
       for (int w = 0; w < kConsumerWarps; ++w) tot += c.ctrl->red[m * kConsumerWarps + w];
       rstd = rsqrtf(tot / (float)K + eps);
     }
-    for (int ch = tid; ch < chunks; ch += T) {
+#pragma unroll
+    for (int i = 0; i < kNwCached; ++i) {
+      const int ch = tid + i * T;
+      if (ch >= chunks) break;
+      const uint32_t a = c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u;
+      uint4 v = lds128(a);
+      float f[8];
+      unpack8(v, xt, f);
+      if (pro != MK_PRO_NONE) {
+        float w[8];
+        unpack8(nwc[i], xt, w);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * w[k];
+      }
+      sts128(a, pack8(f, at));
+    }
+    for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
       const uint32_t a = c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u;
       uint4 v = lds128(a);
       float f[8];
@@ -380,6 +409,15 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
   const bool dense = WFC == 0 ? true : (WFC == 2 ? false : (wfmt == MK_W_BF16 || wfmt == MK_W_FP16));
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const uint32_t half = mv_half_bytes(wfmt, Kc);
+  if (op->i[MK_MV_EPI] == MK_EPI_RESIDUAL && c.lane < 2 * M) {
+    // whoever finishes the unit adds this residual: pull its lines into L1 now
+    const MvRows r0 = mv_rows(op, unit);
+    const int m = c.lane >> 1, S_ = op->i[MK_MV_S];
+    const int b = m / S_, s_ = m - b * S_;
+    const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) + b * op->s[MK_MV_S_ER_B] +
+                         s_ * op->s[MK_MV_S_ER_S] + ((c.lane & 1) ? r0.rowB0 : r0.rowA0);
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(er));
+  }
   float acc[NA][NT][4];
 #pragma unroll
   for (int a = 0; a < NA; ++a)

@@ -97,7 +97,8 @@ struct Ctrl {
   uint32_t mv_arrive[4];
   uint32_t mv_done[4];
   uint32_t bulk_done;  // units of the current op finished on this CTA (bulk signalling)
-  int32_t pad[5];
+  uint32_t ticket;     // next consumer slot of the CTA (see consumer_loop)
+  int32_t pad[4];
   // released[slot] = number of fills of the slot that consumers have handed back
   uint32_t released[kMaxPages];
   float red[kConsumerWarps * 32];  // block-reduction scratch (per row, per warp)
@@ -389,8 +390,8 @@ __device__ __forceinline__ void signal_unit_bulk(Ctx& c, int counter, int units)
     __threadfence_block();
     const uint32_t old = atomicAdd(&c.ctrl->bulk_done, 1u);
     if (old == (uint32_t)(units - 1)) {
-      __threadfence();
-      red_release_gpu_add(c.pv->counters + counter, units);
+      __threadfence_block();
+      red_release_gpu_add(c.pv->counters + counter, units);   // the release is the device-scope fence
     }
   }
 }

@@ -64,7 +64,14 @@ class BackwardScheduler(TileScheduler):
 
 
 class OverlapTileScheduler(TileScheduler):
-    """Byte-balanced placement: each unit goes to the CTA that has streamed the least so far.
+    """Level placement: every op is spread evenly, lightest CTAs first.
+
+    Ops of a decode step run one after another (each needs the whole output of
+    its producer), so what bounds the step is, per op, the CTA with the most
+    units of that op.  Each op therefore gives every CTA at most
+    ``ceil(n_units / num_ctas)`` units, dealing them round-robin over the CTAs
+    ordered by the bytes they have streamed so far; the leftovers of one op
+    thus fill the CTAs that the previous ops left lighter.
 
     Accepts the reference's constructor keywords (scheduling.py:486-506) so
     existing call sites keep working; they tune a readiness simulation this
@@ -80,18 +87,14 @@ class OverlapTileScheduler(TileScheduler):
         self.use_controller_waits_for_readiness = use_controller_waits_for_readiness
 
     def place(self, ops, num_ctas):
-        import heapq
-
-        heap = [(0, c) for c in range(num_ctas)]
-        heapq.heapify(heap)
+        load = np.zeros(num_ctas, dtype=np.int64)
         out = []
         for op in ops:
-            a = np.empty(op.n_units, dtype=np.int32)
+            order = np.argsort(load, kind="stable").astype(np.int32)
+            a = order[np.arange(op.n_units) % num_ctas].astype(np.int32)
             for u in range(op.n_units):
-                load, cta = heapq.heappop(heap)
-                a[u] = cta
                 # a unit with no streamed bytes still costs a little time
-                heapq.heappush(heap, (load + max(op.bytes_of(u), 2048), cta))
+                load[a[u]] += max(op.bytes_of(u), 2048)
             out.append(a)
         return out
 
@@ -247,6 +250,7 @@ class InstructionStreamBuilder:
         cta_instrs: List[List[tuple]] = [[] for _ in range(num_ctas)]
         cta_events: List[List[tuple]] = [[] for _ in range(num_ctas)]
         cta_known = [0] * num_ctas       # ops known complete on this CTA (bitset)
+        cta_staged = [0] * num_ctas      # activation key staged in the CTA's shared memory (0 = none)
         bytes_per_cta = np.zeros(num_ctas, dtype=np.int64)
 
         for j, op in enumerate(ops):
@@ -266,9 +270,20 @@ class InstructionStreamBuilder:
                     pairs = [p for i in need for p in all_groups(i)]
                     nw, off = wait_list(pairs)
                     flags = N.EVF_WRITE_RES_OUT if cta == res_out_cta else 0
-                    if bulk:
-                        flags |= N.EVF_BULK_SIGNAL
-                    cta_events[cta].append((len(cta_instrs[cta]), j, nw, off, flags, int(per_cta[cta]) if bulk else 0))
+                    # An op that waits for nothing new and finds its activations already
+                    # staged (same key as the op before it, e.g. K and V after Q) needs no
+                    # event: its units start on whichever consumer warps are free, next to
+                    # the previous op's, read their record from the op table and signal
+                    # one by one.
+                    staged_already = (op.opcode == N.OP_MATVEC and act_keys[j] != 0
+                                      and act_keys[j] == cta_staged[cta])
+                    if not (staged_already and nw == 0 and flags == 0):
+                        if bulk:
+                            flags |= N.EVF_BULK_SIGNAL
+                        cta_events[cta].append(
+                            (len(cta_instrs[cta]), j, nw, off, flags, int(per_cta[cta]) if bulk else 0))
+                        if op.opcode == N.OP_MATVEC:
+                            cta_staged[cta] = act_keys[j]
                     for i in d.coarse:
                         cta_known[cta] |= closure[i] | (1 << i)
                 # fine-grained consumer waits
