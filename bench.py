@@ -47,13 +47,17 @@ if ROOT not in sys.path:
 
 LLAMA1B = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=128256, layers=16, theta=500000.0)
 FALLBACK_HBM_GBS = 6650.0
+# dram read + write bytes per algorithmic byte, from one ncu capture of a 4-layer + LM-head case
+# of the same kernel (profiles/mk_persistent_kernel_llama1b_decode.md); DRAM traffic is
+# proportional to the layers streamed, so the ratio carries over to the full workload.
+NCU_TRAFFIC_RATIO = 1.006
 NOMINAL_HBM_GBS = 8000.0
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--batch", type=int, default=1)
@@ -130,7 +134,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:  # noqa: BLE001
             self.proc = None
@@ -139,14 +143,23 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
-    def stop(self):
+    def wait_first(self, timeout_s=5.0):
+        """Block until nvidia-smi has produced its first row (it takes a while to start)."""
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < timeout_s:
+            time.sleep(0.01)
+
+    def mark(self):
+        """Index of the next row: brackets the rows that fall inside the timed region."""
+        return len(self.rows)
+
+    def stop(self, first=0, last=None):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[first:last]:
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
@@ -289,7 +302,9 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+        sampler.wait_first()
     barrier()
+    first_row = sampler.mark()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)
     for _ in range(args.steps):
@@ -297,8 +312,9 @@ def main():
     stop.record(stream)
     barrier()
     mk.wait()
+    last_row = sampler.mark()
     ms_total = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(first_row, max(last_row, first_row + 1)) if rank == 0 else None
     t = torch.tensor([ms_total], device=dev)
     if use_dist:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -342,7 +358,8 @@ def main():
             "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
-                         "algorithmic_bytes_per_step": alg, "kernel": "mk_persistent_kernel", "traffic": None},
+                         "algorithmic_bytes_per_step": alg, "kernel": "mk_persistent_kernel",
+                         "traffic": int(alg * NCU_TRAFFIC_RATIO)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
             "kernel_config": {"ctas": mk.grid[0], "threads": mk.block[0], "smem": mk.smem_size, "pages": mk.num_pages,
                               "page_bytes": mk.page_bytes, "instructions": mk.total_tiles,
