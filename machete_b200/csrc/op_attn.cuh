@@ -365,7 +365,7 @@ __device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, const
   const int ot = op->i[MK_AT_O_T];
   // Lane j of a chunk holds the weight of split c0 + j; the partial rows of
   // several splits are requested together so that their latencies overlap.
-  constexpr int UN = 6;
+  constexpr int UN = 12;
   for (int m = 0; m < M; ++m) {
     const int64_t base = ((int64_t)b * H + h) * S;
     float mx = -INFINITY;

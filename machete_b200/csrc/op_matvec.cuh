@@ -418,6 +418,13 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
                          s_ * op->s[MK_MV_S_ER_S] + ((c.lane & 1) ? r0.rowB0 : r0.rowA0);
     asm volatile("prefetch.global.L1 [%0];" ::"l"(er));
   }
+  if (op->i[MK_MV_TR] == MK_TR_ROPE && c.lane < M) {
+    // likewise the cos/sin rows of the RoPE epilogue (one row per activation row)
+    const int S_ = op->i[MK_MV_S];
+    const size_t off = (size_t)(c.lane % S_) * (size_t)op->s[MK_MV_S_COS] * 2u;
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_COS]) + off));
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_SIN]) + off));
+  }
   float acc[NA][NT][4];
 #pragma unroll
   for (int a = 0; a < NA; ++a)

@@ -129,7 +129,7 @@ class LowerCtx:
     num_sms: int
     page_bytes: int
     smem_optin: int
-    kc_bf16: int = 512
+    kc_bf16: int = 1024
     kc_fp4: int = 2048
     fuse: bool = True
 

@@ -65,7 +65,7 @@ class MegakernelConfig:
     device_idx: int = 0
     num_devices: int = 1
     # native extensions
-    native_kc: Optional[int] = None      # K columns per bf16 weight page (default 512)
+    native_kc: Optional[int] = None      # K columns per bf16 weight page (default 1024: 32 KB pages)
     native_kc_fp4: Optional[int] = None  # K columns per NVFP4 weight page (default 2048)
     timeout_ms: int = 1000               # bound of every device-side wait
     fuse: bool = True                    # allow peephole fusion of op chains
@@ -113,7 +113,7 @@ class Megakernel:
         self._smem_optin = smem
         self.num_sms = cfg.num_sms if cfg.num_sms is not None else sms
 
-        kc = cfg.native_kc or 512
+        kc = cfg.native_kc or 1024
         kc4 = cfg.native_kc_fp4 or 2048
         ctx = LowerCtx(num_sms=self.num_sms, page_bytes=0, smem_optin=smem, kc_bf16=kc, kc_fp4=kc4, fuse=cfg.fuse)
         # page size: the largest need of any op, rounded to 1 KB
