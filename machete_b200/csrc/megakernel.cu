@@ -241,6 +241,10 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     // shared copy of the op record can be replaced: unit handlers then read
     // their parameters from shared memory instead of the op table.
     trace(c, TRC_EVENT_BEGIN, cur.op);
+    // request the next event record now: its latency hides behind the barriers
+    mk_event_t nxt;
+    nxt.pos = 0x7fffffff;
+    if (ev + 1 < eend) nxt = pv.events[ev + 1];
     named_bar_sync(kConsumerBarrier, T);
     const mk_op_t* op = pv.ops + cur.op;
     if (w == 0) {
@@ -262,8 +266,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     named_bar_sync(kConsumerBarrier, T);
     trace(c, TRC_EVENT_END, cur.op);
     ++ev;
-    cur.pos = 0x7fffffff;
-    if (ev < eend) cur = pv.events[ev];
+    cur = nxt;
   };
 
   // Consumer slots are handed out through a ticket counter: a unit owns as
@@ -868,7 +871,9 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
         in.ld_row_a = t_begin;
         in.ld_row_b = kvh | (b << 16);
         in.ld_tiles = at_page_tokens(op.i[MK_AT_D], prog->page_bytes);
-        const int split = std::max(1, std::min((int)kConsumerWarps, in.n_pages));
+        // every participant keeps one ring page until the unit's states are merged:
+        // leave at least two pages for the stream
+        const int split = std::max(1, std::min(std::min((int)kConsumerWarps, in.n_pages), prog->n_pages - 2));
         in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT);
         if (in.n_pages == 0) in.ld_maps = 0;   // an empty split: nothing to load, one consumer writes the empty partial
         continue;
