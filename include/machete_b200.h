@@ -300,6 +300,25 @@ int mk_flash_decode(const void* q, const void* k, const void* v, void* o, void* 
                     int32_t splits, int32_t causal, float scale,
                     void* workspace, uint64_t workspace_bytes, void* cuda_stream);
 
+/* The same computation for callers that cannot hand over scratch memory (a
+ * plugin slot or custom-op hook that receives only its tensors, a loop that
+ * must not touch the allocator).  No counterpart in the reference, whose
+ * schedule() allocates the partials with torch.  The attention partials and
+ * the program tables live in one fixed array inside the library's device
+ * image (4 MiB + 1 MiB per device), so the call allocates nothing.
+ *   - The first call on a device looks the array's address up (and may make
+ *     the runtime load the module): make it before any stream capture.
+ *   - Limits: B*H*splits*M partial rows must fit 4 MiB ((D+1)*4 bytes each,
+ *     rounded to 256), and the work units (B*Hkv*ceil(M*H/Hkv/16)*splits +
+ *     B*H) must fit the 1 MiB of tables; larger shapes are refused with a
+ *     message, use mk_flash_decode for them.
+ *   - The array is shared by all calls on a device and keeps its last
+ *     contents; the call clears the part that must start at zero itself.
+ *     Calls that overlap in time on one device race: serialise them. */
+int mk_flash_decode_noalloc(const void* q, const void* k, const void* v, void* o, void* lse,
+                            int32_t B, int32_t M, int32_t H, int32_t Hkv, int32_t D, int32_t N,
+                            int32_t splits, int32_t causal, float scale, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

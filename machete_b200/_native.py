@@ -102,6 +102,7 @@ EXPORTS = [
     "mk_abi_version", "mk_last_error", "mk_device_info", "mk_workspace_bytes", "mk_create", "mk_run",
     "mk_status", "mk_workspace_status", "mk_set_trace", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
+    "mk_flash_decode_noalloc",
 ]
 
 _lib = None
@@ -163,6 +164,8 @@ def _declare(h: C.CDLL) -> None:
     h.mk_matvec_nvfp4.argtypes = [vp, vp, f32, i32, vp, vp, i32, i32, i32, vp, u64, vp]
     h.mk_flash_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32,
                                   vp, u64, vp]
+    h.mk_flash_decode_noalloc.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp]
+    h.mk_flash_decode_noalloc.restype = C.c_int
     for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op",
                  "mk_read_counters", "mk_destroy", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode"):
         getattr(h, name).restype = C.c_int

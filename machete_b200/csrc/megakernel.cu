@@ -1029,3 +1029,4 @@ int mk_destroy(mk_handle_t h) {
 }  // extern "C"
 
 #include "standalone.inc"
+#include "noalloc.inc"
