@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--vocab", type=int, default=LLAMA1B["vocab"])
     ap.add_argument("--kc", type=int, default=0, help="K columns per weight page (0 = default)")
     ap.add_argument("--scheduler", default="overlap", choices=["overlap", "roundrobin"])
+    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                    help="N > 1: tensor-parallel decode of ONE stream (in-kernel all-reduce) or N independent replicas")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -236,13 +238,18 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, world):
+def workload_config(args, world, tp=False, note=None):
+    if world == 1:
+        par = "single gpu"
+    elif tp:
+        par = f"tp{world}: Megatron tensor parallel, all-reduce after O-proj and down-proj inside the kernel"
+    else:
+        par = f"{world} independent replicas (one sequence set per GPU)" + (f"; {note}" if note else "")
     return {
         "workload": f"llama-3.2-1b-shape {args.layers}-layer decode step, batch {args.batch}, kv {args.kv_len}, "
                     f"vocab {args.vocab}, bf16, greedy token",
-        "global_batch": args.batch * world, "kv_len": args.kv_len,
-        "parallelism": "single gpu" if world == 1 else f"{world} independent replicas (one sequence set per GPU)",
-        "l2": "inputs (2.6 GB of weights per step) larger than L2; no flush needed",
+        "global_batch": args.batch * (1 if tp else world), "kv_len": args.kv_len, "parallelism": par,
+        "l2": "inputs (2.6 GB of weights per step, divided by the ranks under tp) larger than L2; no flush needed",
     }
 
 
@@ -265,9 +272,30 @@ def main():
     from machete_b200.kernels.llama1b import schedule_decode_model_sm100
     from machete_b200.megakernel import BackwardScheduler, Megakernel, MegakernelConfig, OverlapTileScheduler
 
-    cfg = LLAMA1B
+    cfg = dict(LLAMA1B)
     B, L, bf = args.batch, args.kv_len, torch.bfloat16
-    weights = make_weights(cfg, args.layers, args.vocab, L, dev, seed=rank)
+    # N > 1: one decode stream sharded Megatron-style over the ranks, unless the peer mapping
+    # cannot be set up on this box (then N independent replicas, and the line says so)
+    peers, tp_note, vocab = None, None, args.vocab
+    if use_dist and args.parallel == "tp":
+        ok = 1
+        try:
+            if cfg["nq"] % world or cfg["nkv"] % world or cfg["inter"] % world or args.vocab % (16 * world):
+                raise ValueError(f"heads / intermediate / vocabulary do not divide by {world}")
+            from machete_b200.megakernel.peer import PeerBuffers
+
+            peers = PeerBuffers(PeerBuffers.bytes_for_model(B, cfg["hidden"], args.layers), device=dev)
+        except Exception as exc:  # noqa: BLE001
+            ok, tp_note = 0, f"tp unavailable: {type(exc).__name__}: {exc}"[:200]
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peers, tp_note = None, tp_note or "tp unavailable on another rank"
+        else:
+            cfg.update(nq=cfg["nq"] // world, nkv=cfg["nkv"] // world, inter=cfg["inter"] // world)
+            vocab = args.vocab // world
+    tp = peers is not None
+    weights = make_weights(cfg, args.layers, vocab, L, dev, seed=rank)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     kcs = [torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g, device=dev).to(bf) for _ in range(args.layers)]
     vcs = [torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g, device=dev).to(bf) for _ in range(args.layers)]
@@ -283,7 +311,8 @@ def main():
         attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
         mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), final_norm=weights["final_norm"],
         lm_head=weights["lm_head"], top_values=tv, top_indices=ti, num_layers=args.layers, x_in=x_in,
-        residual_in=r_in)
+        residual_in=r_in, hidden_size=cfg["hidden"], intermediate_size=cfg["inter"], num_q_heads=cfg["nq"],
+        num_kv_heads=cfg["nkv"], head_dim=cfg["hd"], tp_peers=peers)
     sched = OverlapTileScheduler() if args.scheduler == "overlap" else BackwardScheduler()
     mk = Megakernel(ops, config=MegakernelConfig(native_kc=args.kc or None), device=dev, scheduler=sched)
     mk.compile()
@@ -343,19 +372,20 @@ def main():
         if use_dist:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_s = float(te.item())
-        e2e = {"value": B * world / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
+        e2e = {"value": B * (1 if tp else world) / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_tok.numel() * 4, "steps": n_e2e}
         mk.wait()
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        alg = algorithmic_bytes(cfg, B, L, args.layers, args.vocab)
+        alg = algorithmic_bytes(cfg, B, L, args.layers, vocab)      # per GPU (this rank's shard under tp)
         achieved = alg / (ms_step * 1e-3) / 1e9
         line = {
-            "metric": "decode_tokens_per_s", "value": B * world / (ms_step * 1e-3), "unit": "tokens/s",
+            "metric": "decode_tokens_per_s", "value": B * (1 if tp else world) / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
-            "us_per_step": ms_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+            "us_per_step": ms_step * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args, world, tp, tp_note),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
                          "algorithmic_bytes_per_step": alg, "kernel": "mk_persistent_kernel",
@@ -365,7 +395,7 @@ def main():
                               "page_bytes": mk.page_bytes, "instructions": mk.total_tiles,
                               "counters": mk.num_barriers, "scheduler": args.scheduler},
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             wcpu = {k: v.cpu() for k, v in weights.items()}
             secs, sample = cpu_step_seconds(args, cfg, wcpu)
             line["cpu_baseline"] = {"value": B / secs, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",

@@ -57,7 +57,8 @@ enum {
    * Llama1BReduceTop1PartialsSm120Op (kernels/llama1b/sm120.py:3464). */
   MK_OP_TOP1_FINAL = 9,
   /* one-shot all-reduce over peer-mapped inboxes (tensor parallel); replaces
-   * GemmRowParallelOp's peer reduce-store (kernels/gemm/gemm.py:1290). */
+   * GemmRowParallelOp's peer reduce-store and peer barriers
+   * (kernels/gemm/gemm.py:1253-1363). */
   MK_OP_ALLREDUCE = 10,
   MK_OP__COUNT
 };
@@ -92,7 +93,10 @@ enum {
    * round-robin and the partial sums meet in shared memory.
    * 1 suits ops with many units per CTA, more suits ops with few.
    * 0 = one warp per page, up to all consumer warps. */
-  MK_MV_SPLIT
+  MK_MV_SPLIT,
+  /* MK_EPI_TOP1: added to the row index packed into the key (the first
+   * vocabulary row of this rank's shard under tensor parallelism) */
+  MK_MV_IDX0
 };
 enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1 };
 enum {
@@ -138,6 +142,17 @@ enum { MK_EW_P_X = 0, MK_EW_P_Y, MK_EW_P_W, MK_EW_P_RES_IN, MK_EW_P_RES_OUT, MK_
 enum { MK_EW_S_X = 0, MK_EW_S_Y, MK_EW_S_W, MK_EW_S_RI, MK_EW_S_RO, MK_EW_S_G, MK_EW_S_COS, MK_EW_S_X_H };
 /* MK_EW_FLAGS bits */
 enum { MK_EWF_RESIDUAL = 1, MK_EWF_GEMMA = 2, MK_EWF_FUSED_ADD = 4, MK_EWF_GATED = 8, MK_EWF_ROW_WEIGHT = 16 };
+
+/* MK_OP_ALLREDUCE: one-shot all-reduce over peer-mapped inboxes.  Every rank
+ * runs the same op with its own MK_AR_RANK; p[MK_AR_P_PEER0 + r] is rank r's
+ * symmetric buffer as mapped into this process (r = own rank included), and
+ * s[] holds the byte offsets of the op's inbox and flag regions inside it. */
+enum { MK_AR_N = 0 /* elements (sum) or rows (keys) */, MK_AR_P, MK_AR_RANK, MK_AR_MODE, MK_AR_X_T, MK_AR_Y_T,
+       MK_AR_R_T, MK_AR_EPOCH_BASE };
+enum { MK_AR_SUM = 0 /* y = sum_r x_r (+ residual) */, MK_AR_MAX_KEY = 1 /* y = max_r of 64-bit top-1 keys */ };
+enum { MK_AR_P_X = 0, MK_AR_P_RES, MK_AR_P_Y, MK_AR_P_PEER0 /* .. MK_AR_P_PEER0 + 7 */ };
+enum { MK_AR_S_INBOX = 0, MK_AR_S_FLAGS };
+#define MK_AR_MAX_RANKS 8
 
 /* A device-visible op record.  Field meaning depends on `opcode`; see the
  * index enums above.  The layout is fixed: 16 + 96 + 16 + 128 + 128 bytes. */

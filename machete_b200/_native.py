@@ -29,7 +29,7 @@ W_BF16, W_FP16, W_NVFP4_F16S32, W_NVFP4_E4M3S16 = range(4)
 T_BF16, T_FP16, T_FP32 = range(3)
 
 (MV_O, MV_K, MV_M, MV_S, MV_MODE, MV_PRO, MV_EPI, MV_TR, MV_HD, MV_D2, MV_POS, MV_WFMT, MV_KC, MV_OUT_T,
- MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT) = range(17)
+ MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT, MV_IDX0) = range(18)
 MV_F_EPS, MV_F_GSCALE = range(2)
 (MV_P_W0, MV_P_W1, MV_P_X, MV_P_RES_IN, MV_P_NORM_W, MV_P_RES_OUT, MV_P_OUT, MV_P_EPI_RES, MV_P_COS,
  MV_P_SIN, MV_P_SC0, MV_P_SC1) = range(12)
@@ -46,6 +46,11 @@ AT_F_SCALE = 0
 EW_F_EPS = 0
 (EW_P_X, EW_P_Y, EW_P_W, EW_P_RES_IN, EW_P_RES_OUT, EW_P_GATE, EW_P_COS, EW_P_SIN) = range(8)
 (EW_S_X, EW_S_Y, EW_S_W, EW_S_RI, EW_S_RO, EW_S_G, EW_S_COS, EW_S_X_H) = range(8)
+(AR_N, AR_P, AR_RANK, AR_MODE, AR_X_T, AR_Y_T, AR_R_T, AR_EPOCH_BASE) = range(8)
+AR_SUM, AR_MAX_KEY = 0, 1
+(AR_P_X, AR_P_RES, AR_P_Y, AR_P_PEER0) = range(4)
+AR_S_INBOX, AR_S_FLAGS = 0, 1
+AR_MAX_RANKS = 8
 EWF_RESIDUAL, EWF_GEMMA, EWF_FUSED_ADD, EWF_GATED, EWF_ROW_WEIGHT = 1, 2, 4, 8, 16
 EVF_WRITE_RES_OUT, EVF_BULK_SIGNAL = 1, 2
 
@@ -57,6 +62,7 @@ STATUS_NAMES = {
     3: "page-empty wait timed out",
     4: "unknown opcode",
     5: "ring-slot turn wait timed out",
+    6: "a peer rank's all-reduce flag never arrived",
 }
 
 

@@ -21,6 +21,7 @@
 #include <string>
 #include <vector>
 
+#include "op_allreduce.cuh"
 #include "op_attn.cuh"
 #include "op_elementwise.cuh"
 #include "op_matvec.cuh"
@@ -211,6 +212,7 @@ __device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const mk_ins
     case MK_OP_GLU: ew_glu(c, op, ins.unit); break;
     case MK_OP_ADD: ew_add(c, op, ins.unit); break;
     case MK_OP_TOP1_FINAL: ew_top1_final(c, op, ins.unit); break;
+    case MK_OP_ALLREDUCE: ew_allreduce(c, op, ins.unit); break;
     case MK_OP_NOP: break;
     default:
       if (c.lane == 0) report(c, MK_ST_BAD_OP, op->opcode, ins.op);
@@ -663,7 +665,18 @@ static int validate_op(const mk_program_t* p, int idx) {
   } else if (op.opcode == MK_OP_TOP1_FINAL) {
     if (!op.p[MK_EW_P_X] || !op.p[MK_EW_P_W] || (op.p[MK_EW_P_X] & 7)) return fail(-2, "op %d: top-1 buffers missing", idx);
   } else if (op.opcode == MK_OP_ALLREDUCE) {
-    return fail(-2, "op %d: all-reduce op is not available in this build", idx);
+    const int P = op.i[MK_AR_P], rank = op.i[MK_AR_RANK], n = op.i[MK_AR_N];
+    if (P < 2 || P > MK_AR_MAX_RANKS || rank < 0 || rank >= P) return fail(-2, "op %d: bad all-reduce world %d / rank %d", idx, P, rank);
+    if (!op.p[MK_AR_P_X] || !op.p[MK_AR_P_Y]) return fail(-2, "op %d: all-reduce input/output pointer missing", idx);
+    for (int r = 0; r < P; ++r)
+      if (!op.p[MK_AR_P_PEER0 + r] || (op.p[MK_AR_P_PEER0 + r] & 15)) return fail(-2, "op %d: peer buffer %d missing or unaligned", idx, r);
+    if ((op.s[MK_AR_S_INBOX] & 15) || (op.s[MK_AR_S_FLAGS] & 3)) return fail(-2, "op %d: unaligned inbox/flag offsets", idx);
+    if (op.i[MK_AR_MODE] == MK_AR_MAX_KEY) {
+      if (n < 1 || n > 32 || op.n_units != 1) return fail(-2, "op %d: key all-reduce handles 1..32 rows in one unit", idx);
+    } else {
+      if (n < 8 || (n & 7) || op.n_units != (n + 255) / 256) return fail(-2, "op %d: bad all-reduce size %d", idx, n);
+      if ((op.p[MK_AR_P_X] & 15) || (op.p[MK_AR_P_Y] & 15) || (op.p[MK_AR_P_RES] & 15)) return fail(-2, "op %d: all-reduce tensors must be 16-byte aligned", idx);
+    }
   }
   return 0;
 }

@@ -343,9 +343,10 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvR
       }
       if (epi == MK_EPI_TOP1) {
         unsigned long long key = 0ull;
-        if (va) key = top1_key(a, r.rowA0 + g);
+        const int idx0 = op->i[MK_MV_IDX0];
+        if (va) key = top1_key(a, idx0 + r.rowA0 + g);
         if (vb) {
-          const unsigned long long kb = top1_key(b, r.rowB0 + g);
+          const unsigned long long kb = top1_key(b, idx0 + r.rowB0 + g);
           key = kb > key ? kb : key;
         }
 #pragma unroll

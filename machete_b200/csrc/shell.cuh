@@ -30,7 +30,8 @@ enum {
   MK_ST_TIMEOUT_PAGE_FULL = 2,
   MK_ST_TIMEOUT_PAGE_EMPTY = 3,
   MK_ST_BAD_OP = 4,
-  MK_ST_TIMEOUT_PAGE_TURN = 5  // earlier fills of a ring slot were never handed back
+  MK_ST_TIMEOUT_PAGE_TURN = 5,  // earlier fills of a ring slot were never handed back
+  MK_ST_TIMEOUT_PEER = 6        // a peer rank's all-reduce flag never arrived
 };
 
 // Device memory block owned by a handle (lives in the caller's workspace).

@@ -93,6 +93,7 @@ def lower_matvec(
     eps: float = 1e-5,
     out_rows: Optional[int] = None,
     kind: str = "matvec",
+    index_offset: int = 0,
 ) -> NativeOp:
     if x.ndim != 3 or x.stride(-1) != 1:
         raise ValueError(f"{name}: activations must be (B, S, K) with unit innermost stride")
@@ -147,7 +148,7 @@ def lower_matvec(
         N.MV_O: O, N.MV_K: K, N.MV_M: M, N.MV_S: S, N.MV_MODE: mode, N.MV_PRO: pro, N.MV_EPI: epi,
         N.MV_TR: tr, N.MV_HD: hd, N.MV_D2: int(cos.shape[1]) if cos is not None else 0, N.MV_POS: int(pos),
         N.MV_WFMT: w0.fmt, N.MV_KC: kc, N.MV_OUT_T: elem_type(out, f"{name}: out") if epi != N.EPI_TOP1 else 0,
-        N.MV_X_T: xt, N.MV_ROWS_PER_UNIT: rows_per_unit, N.MV_SPLIT: split,
+        N.MV_X_T: xt, N.MV_ROWS_PER_UNIT: rows_per_unit, N.MV_SPLIT: split, N.MV_IDX0: int(index_offset),
     }
     op.f = {N.MV_F_EPS: eps, N.MV_F_GSCALE: w0.global_scale}
     op.p = {N.MV_P_W0: w0.data.data_ptr(), N.MV_P_W1: (w1 or w0).data.data_ptr(), N.MV_P_X: x.data_ptr(),

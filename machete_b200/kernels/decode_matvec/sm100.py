@@ -16,6 +16,8 @@ accumulator fragment instead of a second dot product.
 
 from __future__ import annotations
 
+import torch
+
 from dataclasses import dataclass
 
 from ... import _native as N
@@ -324,6 +326,7 @@ def schedule_decode_layer_sm100(
     head_dim=SM100_DECODE_HEAD_DIM_DEFAULT,
     kv_group_size=SM100_DECODE_KV_GROUP_SIZE_DEFAULT,
     matvec_block=SM100_DECODE_MATVEC_BLOCK,
+    tp_peers=None,
 ):
     """One decoder layer: RMS+Q/RoPE, RMS+K/RoPE/cache, RMS+V/cache, split-KV
     attention + combine, O-proj + residual, RMS+gate/up+SiLU and the down
@@ -331,6 +334,13 @@ def schedule_decode_layer_sm100(
 
     Unlike the reference, attention always goes through flash decoding (its
     short-KV branch uses a prefill attention kernel this build does not have).
+
+    ``tp_peers`` (a ``PeerBuffers``) switches to Megatron-style tensor
+    parallelism: ``weights`` then hold THIS RANK's shards (W_q/W_k/W_v/W_gate/
+    W_up split by output rows, W_o/W_down split by K), ``num_q_heads`` /
+    ``num_kv_heads`` / ``intermediate_size`` are the local counts, and the two
+    K-split projections write fp32 partials that an in-kernel all-reduce adds
+    across ranks (plus the residual for the O-projection).
     """
     from ..attention.flash_decoding import flash_decoding_schedule
 
@@ -357,13 +367,32 @@ def schedule_decode_layer_sm100(
         num_splits=fa_num_splits,
     )
     ops += fa_ops
-    ops += MatvecResidualSm100Op.schedule(a=attn_out_buf, weight=weights[f"{pfx}.W_o"], residual_in=residual_out,
-                                          residual_out=residual_out, tile_sizes=tiles, page_size=page_size)
+    tp_keep = []
+    if tp_peers is not None:
+        from ..allreduce import AllReduceSm100Op
+
+        o_part = torch.empty(residual_out.shape, dtype=torch.float32, device=residual_out.device)
+        x_part = torch.empty(x_out.shape, dtype=torch.float32, device=x_out.device)
+        tp_keep = [o_part, x_part]
+        ops += MatvecSm100Op.schedule(a=attn_out_buf, weight=weights[f"{pfx}.W_o"], y=o_part, tile_sizes=tiles,
+                                      page_size=page_size)
+        ops += AllReduceSm100Op.schedule(peers=tp_peers, x=o_part, residual_in=residual_out, y=residual_out)
+    else:
+        ops += MatvecResidualSm100Op.schedule(a=attn_out_buf, weight=weights[f"{pfx}.W_o"],
+                                              residual_in=residual_out, residual_out=residual_out,
+                                              tile_sizes=tiles, page_size=page_size)
     ops += RmsGateUpSiluSm100Op.schedule(x=residual_out, norm_weight=weights[f"{pfx}.mlp_norm"],
                                          gate_weight=weights[f"{pfx}.W_gate"], up_weight=weights[f"{pfx}.W_up"],
                                          y=mlp_h_buf, tile_sizes={"S": seq_len, "D": matvec_block},
                                          page_size=page_size, eps=eps)
     down_keep = []
+    if tp_peers is not None:
+        # one matvec over this rank's K range, then the exchange
+        ops += MatvecSm100Op.schedule(a=mlp_h_buf, weight=weights[f"{pfx}.W_down"], y=x_part, tile_sizes=tiles,
+                                      page_size=page_size)
+        ops += AllReduceSm100Op.schedule(peers=tp_peers, x=x_part, y=x_out)
+        return DecodeLayerSchedule(ops=ops, attention_config=fa_config,
+                                   keep_alive=[cos, sin, q_4d, k_window, v_window, o_4d, *tp_keep])
     for blk in range(intermediate_size // hidden_size):
         start, stop = blk * hidden_size, (blk + 1) * hidden_size
         a_block = mlp_h_buf[:, :, start:stop]

@@ -35,7 +35,7 @@ class FinalAddRmsTop1LmHeadSm100Op(Op):
     dynamic_dims = ("B",)
 
     @classmethod
-    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, **tensors):
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, index_offset=0, **tensors):
         tile_sizes = dict(tile_sizes or {})
         tile_sizes.setdefault("B", 1)
         tile_sizes.setdefault("S", 16)
@@ -46,6 +46,7 @@ class FinalAddRmsTop1LmHeadSm100Op(Op):
         op = cls._schedule_single(tile_sizes=tile_sizes, **tensors)
         op.static_dims["page_size"] = page_size
         op.static_dims["eps"] = eps
+        op.static_dims["index_offset"] = int(index_offset)   # first vocabulary row of this rank's shard
         return [op]
 
     @classmethod
@@ -59,7 +60,8 @@ class FinalAddRmsTop1LmHeadSm100Op(Op):
         return [lower_matvec(cls.__name__, ctx, w0=cls._weight(sop), x=t["x"], out=t["top_keys"],
                              out_strides=(0, 0, 0), pro=N.PRO_ADD_RMS if has_res else N.PRO_RMS,
                              norm_weight=t["norm_weight"], residual_in=t.get("residual_in"), epi=N.EPI_TOP1,
-                             eps=float(sop.static_dims.get("eps", 1e-5)), kind="lm_head_top1")]
+                             eps=float(sop.static_dims.get("eps", 1e-5)), kind="lm_head_top1",
+                             index_offset=int(sop.static_dims.get("index_offset", 0)))]
 
 
 class FinalAddRmsTop1LmHeadNvfp4Sm100Op(FinalAddRmsTop1LmHeadSm100Op):
@@ -79,8 +81,9 @@ class FinalAddRmsTop1LmHeadNvfp4Sm100Op(FinalAddRmsTop1LmHeadSm100Op):
 
     @classmethod
     def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, group_size=32, global_scale=1.0,
-                 **tensors):
-        ops = super().schedule(tile_sizes=tile_sizes, page_size=page_size, eps=eps, **tensors)
+                 index_offset=0, **tensors):
+        ops = super().schedule(tile_sizes=tile_sizes, page_size=page_size, eps=eps, index_offset=index_offset,
+                               **tensors)
         ops[0].static_dims["group_size"] = group_size
         ops[0].params["global_scale"] = float(global_scale)
         return ops
@@ -125,20 +128,32 @@ class ReduceTop1Sm100Op(Op):
 
 def schedule_final_top1_sm100(*, x, residual_in, final_norm, lm_head, top_values, top_indices, seq_len,
                               page_size=DEFAULT_PAGE_SIZE, eps=1e-5, lm_head_scales=None, group_size=32,
-                              global_scale=1.0):
-    """Final add + RMSNorm + LM head + greedy token, without materialising logits."""
+                              global_scale=1.0, tp_peers=None):
+    """Final add + RMSNorm + LM head + greedy token, without materialising logits.
+
+    With ``tp_peers`` the LM head is this rank's vocabulary shard (rows
+    ``rank * V_local ...``): the ranks exchange their best keys inside the
+    kernel and every rank ends up with the global greedy token.
+    """
     keys = torch.zeros(top_values.shape, dtype=torch.int64, device=top_values.device)
     tiles = {"S": seq_len, "V": 16}
+    idx0 = 0 if tp_peers is None else tp_peers.rank * int(lm_head.shape[0])
     if lm_head_scales is None:
         ops = FinalAddRmsTop1LmHeadSm100Op.schedule(x=x, residual_in=residual_in, norm_weight=final_norm,
                                                     weight=lm_head, top_keys=keys, tile_sizes=tiles,
-                                                    page_size=page_size, eps=eps)
+                                                    page_size=page_size, eps=eps, index_offset=idx0)
     else:
         ops = FinalAddRmsTop1LmHeadNvfp4Sm100Op.schedule(
             x=x, residual_in=residual_in, norm_weight=final_norm, weight_packed=lm_head,
             weight_scales=lm_head_scales, top_keys=keys, tile_sizes=tiles, page_size=page_size, eps=eps,
-            group_size=group_size, global_scale=global_scale)
-    ops += ReduceTop1Sm100Op.schedule(top_keys=keys, top_values=top_values, top_indices=top_indices,
+            group_size=group_size, global_scale=global_scale, index_offset=idx0)
+    final_keys = keys
+    if tp_peers is not None:
+        from ..allreduce import AllReduceTop1KeysSm100Op
+
+        final_keys = torch.zeros_like(keys)
+        ops += AllReduceTop1KeysSm100Op.schedule(peers=tp_peers, top_keys=keys, top_keys_out=final_keys)
+    ops += ReduceTop1Sm100Op.schedule(top_keys=final_keys, top_values=top_values, top_indices=top_indices,
                                       page_size=page_size)
     return ops
 

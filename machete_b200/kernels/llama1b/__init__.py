@@ -65,6 +65,7 @@ def schedule_decode_model_sm100(
     head_dim=LLAMA1B_HEAD_DIM,
     x_in=None,
     residual_in=None,
+    tp_peers=None,
 ):
     """Schedule a full decode step: ``(ops, keep_alive)``.
 
@@ -75,7 +76,15 @@ def schedule_decode_model_sm100(
     With ``x_in`` / ``residual_in`` the first layer reads those tensors instead
     of pair 0, so the step never overwrites its own inputs and can be
     re-launched unchanged.
+
+    ``tp_peers``: tensor parallelism over the ranks of a ``PeerBuffers``;
+    ``weights``, the KV caches, ``q_buf`` / ``attn_out_buf`` / ``mlp_h_buf``, the
+    head counts, ``intermediate_size`` and ``lm_head`` are then this rank's
+    shards (see ``schedule_decode_layer_sm100``); full logits are not
+    supported under tensor parallelism, only the greedy-token head.
     """
+    if tp_peers is not None and logits is not None:
+        raise ValueError("tensor parallelism supports the top-1 head only (logits would need an all-gather)")
     if len(x_buffers) < 2 or len(residual_buffers) < 2:
         raise ValueError("x_buffers and residual_buffers must each contain two ping-pong buffers")
     if (x_in is None) != (residual_in is None):
@@ -94,7 +103,7 @@ def schedule_decode_model_sm100(
             q_buf=q_buf, attn_out_buf=attn_out_buf, mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps,
             fa_num_splits=fa_num_splits, hidden_size=hidden_size, intermediate_size=intermediate_size,
             num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-            kv_group_size=num_q_heads // num_kv_heads,
+            kv_group_size=num_q_heads // num_kv_heads, tp_peers=tp_peers,
         )
         ops += layer.ops
         keep += layer.keep_alive
@@ -112,7 +121,7 @@ def schedule_decode_model_sm100(
             ops += schedule_final_top1_sm100(x=x_buffers[cur], residual_in=residual_buffers[cur],
                                              final_norm=final_norm, lm_head=lm_head, top_values=top_values,
                                              top_indices=top_indices, seq_len=seq_len, page_size=page_size,
-                                             eps=eps)
+                                             eps=eps, tp_peers=tp_peers)
         else:
             raise ValueError("logits or both top_values/top_indices must be provided when lm_head is scheduled")
     return ops, keep

@@ -1,0 +1,140 @@
+"""Tensor-parallel host logic on CPU: two gloo ranks build the sharded decode program.
+
+Covers what needs no GPU: the ranks agree on every inbox / flag offset and
+epoch base without exchanging them, each rank's program is deadlock-free
+(`simulate`), the all-reduce ops carry the right rank / world fields, and the
+sharding itself is sound (K-split partials add up to the unsplit product, the
+vocabulary-split arg-max equals the global one).
+"""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from machete_b200 import _native as N
+from machete_b200.kernels.llama1b import schedule_decode_model_sm100
+from machete_b200.megakernel import Megakernel, MegakernelConfig, OverlapTileScheduler, simulate
+from machete_b200.megakernel.peer import PeerBuffers
+from tests.util import llama_weights
+
+BF = torch.bfloat16
+DIMS = dict(hidden=256, inter=512, nq=4, nkv=2, hd=64, vocab=512, layers=2, T=128)
+
+
+def shard_weights(w, rank, world, d):
+    """Megatron split of a `llama_weights` dict: rows for Q/K/V/gate/up/LM head, K for O/down."""
+    out = {}
+    for k, v in w.items():
+        name = k.split(".")[-1]
+        if name in ("W_q", "W_k", "W_v", "W_gate", "W_up"):
+            out[k] = v.chunk(world, dim=0)[rank].contiguous()
+        elif name in ("W_o", "W_down"):
+            out[k] = v.chunk(world, dim=1)[rank].contiguous()
+        else:
+            out[k] = v
+    return out
+
+
+def build_rank_program(rank, world):
+    d = DIMS
+    torch.manual_seed(0)
+    w = llama_weights(d["layers"], d["hidden"], d["inter"], d["nq"] * d["hd"], d["nkv"] * d["hd"], d["hd"] // 2, d["T"])
+    lm = (torch.randn(d["vocab"], d["hidden"]) * 0.02).to(BF)
+    ws = shard_weights(w, rank, world, d)
+    nq, nkv, inter = d["nq"] // world, d["nkv"] // world, d["inter"] // world
+    kc = [torch.zeros(1, d["T"], nkv, d["hd"], dtype=BF) for _ in range(d["layers"])]
+    vc = [torch.zeros(1, d["T"], nkv, d["hd"], dtype=BF) for _ in range(d["layers"])]
+    xb = [torch.zeros(1, 1, d["hidden"], dtype=BF) for _ in range(2)]
+    rb = [torch.zeros(1, 1, d["hidden"], dtype=BF) for _ in range(2)]
+    peers = PeerBuffers(PeerBuffers.bytes_for_model(1, d["hidden"], d["layers"]), rank=rank, world_size=world)
+    tv, ti = torch.zeros(1, 1), torch.zeros(1, 1, dtype=torch.int32)
+    ops, _ = schedule_decode_model_sm100(
+        batch=1, cache_pos=40, weights=ws, k_cache=kc, v_cache=vc, x_buffers=xb, residual_buffers=rb,
+        q_buf=torch.zeros(1, 1, nq * d["hd"], dtype=BF), attn_out_buf=torch.zeros(1, 1, nq * d["hd"], dtype=BF),
+        mlp_h_buf=torch.zeros(1, 1, inter, dtype=BF), final_norm=torch.ones(d["hidden"], dtype=BF),
+        lm_head=lm.chunk(world, dim=0)[rank].contiguous(), top_values=tv, top_indices=ti, num_layers=d["layers"],
+        hidden_size=d["hidden"], intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=d["hd"],
+        tp_peers=peers)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=16), scheduler=OverlapTileScheduler())
+    return mk, peers
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mk, peers = build_rank_program(rank, world)
+        final = simulate(mk.program)
+        ok_counters = bool((final == mk.program.counter_expected[:len(final)]).all())
+        ar = [(o.name, int(o.i[N.AR_RANK]), int(o.i[N.AR_P]), int(o.i[N.AR_N]), int(o.i[N.AR_MODE]),
+               int(o.s[N.AR_S_INBOX]), int(o.s[N.AR_S_FLAGS]), int(o.i[N.AR_EPOCH_BASE]), int(o.n_units))
+              for o in mk.native_ops if o.opcode == N.OP_ALLREDUCE]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, ar)
+        q.put((rank, ok_counters, gathered, len(mk.native_ops)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_agree_on_the_exchange_layout():
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok_counters, gathered, n_ops in results:
+        assert ok_counters                                   # every counter reaches its expected value: no lost signal
+        a, b = gathered
+        assert len(a) == len(b) == 2 * DIMS["layers"] + 1    # O-proj + down per layer, and the key exchange
+        for ra, rb_ in zip(a, b):
+            assert ra[0] == rb_[0] and ra[2:] == rb_[2:]      # same op, world, size, mode, offsets, epoch base, units
+            assert (ra[1], rb_[1]) == (0, 1)                  # and each carries its own rank
+        offs = [r[5] for r in a] + [r[6] for r in a]
+        assert len(set(offs)) == len(offs)                   # regions are distinct
+        assert a[-1][4] == N.AR_MAX_KEY and all(r[4] == N.AR_SUM for r in a[:-1])
+
+
+def test_sharded_math_adds_up():
+    """K-split partials summed in rank order equal the unsplit matvec; split arg-max equals the global one."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1, 1024, generator=g).to(BF)
+    w = (torch.randn(256, 1024, generator=g) * 0.02).to(BF)
+    full = oracle.matvec(x, w)
+    for world in (2, 4, 8):
+        parts = [oracle.matvec(xs.contiguous(), ws.contiguous())
+                 for xs, ws in zip(x.chunk(world, dim=1), w.chunk(world, dim=1))]
+        acc = torch.zeros_like(parts[0])
+        for p in parts:                                      # the kernel adds inbox slots in rank order
+            acc = acc + p
+        assert float((acc - full).abs().max()) < 1e-3
+        logits = oracle.matvec(x, w).flatten()
+        shard = logits.numel() // world
+        best = max(((float(logits[r * shard:(r + 1) * shard].max()),
+                     -(r * shard + int(logits[r * shard:(r + 1) * shard].argmax()))) for r in range(world)))
+        assert -best[1] == int(logits.argmax())
+
+
+def test_peer_buffers_reject_bad_worlds():
+    with pytest.raises(ValueError):
+        PeerBuffers(1024, rank=0, world_size=1)
+    with pytest.raises(ValueError):
+        PeerBuffers(1024, rank=0, world_size=16)
+    pb = PeerBuffers(1024, rank=1, world_size=2)
+    assert pb.alloc(100) == 0 and pb.alloc(100) == 256
+    with pytest.raises(ValueError):
+        pb.alloc(4096)
+    assert pb.next_epoch_base() != pb.next_epoch_base()
