@@ -14,9 +14,11 @@
 // barriers (kernels/gemm/gemm.py:1253-1363), which run P ranks in one process.
 //
 // Layout of the symmetric buffer (same offsets on every rank):
-//   inbox: [P][n] elements (fp32 for sums, u64 for keys), slot r written by rank r
+//   inbox: two buffers of [P][n] 8-byte words, slot r written by rank r.  For
+//          sums a word is {fp32 value, epoch}: the data carries its own flag.
+//          For keys a word is the 64-bit key, guarded by
 //   flags: [P][units] u32, flag (r, u) = epoch of the last launch whose unit u
-//          of rank r has been delivered
+//          of rank r has been delivered (keys only)
 // A launch uses epoch = epoch_base + launches + 1 and waits for flags >= epoch,
 // so flags never need a reset.  A peer can run at most one launch ahead of
 // this rank at the same op (it needs this rank's next contribution to go
@@ -42,6 +44,14 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
                : "l"(p)
                : "memory");
   return v;
+}
+__device__ __forceinline__ uint2 ld_sys_u2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_u2(uint2* p, uint2 v) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
   unsigned long long v;
@@ -76,7 +86,7 @@ __device__ __forceinline__ void ew_allreduce(Ctx& c, const mk_op_t* op, int unit
   const int n = op->i[MK_AR_N], P = op->i[MK_AR_P], rank = op->i[MK_AR_RANK];
   const int units = op->n_units;
   const uint32_t epoch = (uint32_t)op->i[MK_AR_EPOCH_BASE] + (uint32_t)c.pv->state->launches + 1u;
-  const int64_t elem = op->i[MK_AR_MODE] == MK_AR_MAX_KEY ? 8 : 4;
+  const int64_t elem = 8;   // a 64-bit key, or an fp32 with its epoch
   const int64_t half = ((int64_t)P * n * elem + 15) / 16 * 16;   // one of the two inbox buffers
   const int64_t inbox_off = op->s[MK_AR_S_INBOX] + (int64_t)(epoch & 1u) * half, flags_off = op->s[MK_AR_S_FLAGS];
   uint8_t* self = reinterpret_cast<uint8_t*>(op->p[MK_AR_P_PEER0 + rank]);
@@ -130,38 +140,56 @@ __device__ __forceinline__ void ew_allreduce(Ctx& c, const mk_op_t* op, int unit
         v[2 * i + 1] = op->i[MK_AR_X_T] == MK_T_BF16 ? bf16hi(w[i]) : f16hi(w[i]);
       }
     }
-    // push this rank's partial into every peer's inbox slot `rank`
+    // Push this rank's partial into slot `rank` of every peer's inbox.  Each
+    // fp32 travels as one 8-byte word {value, epoch}: an 8-byte store arrives
+    // whole, so the receiver polls the data itself and no fence or separate
+    // flag (one more NVLink crossing) is needed.
     for (int r = 0; r < P; ++r) {
       if (r == rank) continue;
-      float4* dst = reinterpret_cast<float4*>(
-          reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(op->p[MK_AR_P_PEER0 + r]) + inbox_off) +
-          (size_t)rank * n + idx);
-      dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-      dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+      uint2* dst = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(op->p[MK_AR_P_PEER0 + r]) + inbox_off) +
+                   (size_t)rank * n + idx;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) st_sys_u2(dst + i, make_uint2(__float_as_uint(v[i]), epoch));
     }
   }
-  __threadfence_system();
-  __syncwarp();
-  if (c.lane < P && c.lane != rank)
-    st_release_sys_u32(reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(op->p[MK_AR_P_PEER0 + c.lane]) +
-                                                   flags_off) + (size_t)rank * units + unit, epoch);
-  if (!ar_wait_flags(c, my_flags, P, rank, units, unit, epoch)) return;
-  if (!valid) return;
   // add in rank order: every rank computes the same sum bit for bit
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  const float* in = reinterpret_cast<const float*>(self + inbox_off);
+  const uint2* in = reinterpret_cast<const uint2*>(self + inbox_off);
   for (int r = 0; r < P; ++r) {
     if (r == rank) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += v[i];
-    } else {
-      const float4 a = ld_sys_f4(in + (size_t)r * n + idx), b = ld_sys_f4(in + (size_t)r * n + idx + 4);
-      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      continue;
+    }
+    // wait (bounded) until all 8 words of this lane carry the epoch
+    uint2 w[8];
+    uint64_t t0 = 0;
+    for (int spin = 0;; ++spin) {
+      bool ok = true;
+      if (valid && !c.dead) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          w[i] = ld_sys_u2(in + (size_t)r * n + idx + i);
+          ok = ok && w[i].y == epoch;
+        }
+      }
+      if (__all_sync(0xffffffffu, ok)) break;
+      if ((spin & 15) == 15) {
+        if (t0 == 0) t0 = globaltimer_ns();
+        if (give_up_check(c, t0, MK_ST_TIMEOUT_PEER, unit, r)) {
+          c.dead = true;
+          return;
+        }
+      }
+    }
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += __uint_as_float(w[i].x);
     }
   }
+  if (!valid || c.dead) return;
   const int yt = op->i[MK_AR_Y_T];
   if (op->p[MK_AR_P_RES] != 0) {
     const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AR_P_RES]) + idx);

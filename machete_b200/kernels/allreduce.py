@@ -79,7 +79,7 @@ class AllReduceSm100Op(Op):
             op.keep.append(res)
         op.writes = [Region(meta_of(y, "y"))]
         op.unit_bytes = 0
-        _peer_fields(op, peers, n, 4, units, N.AR_SUM)
+        _peer_fields(op, peers, n, 8, units, N.AR_SUM)
         return [op]
 
 

@@ -88,5 +88,5 @@ class PeerBuffers:
     @staticmethod
     def bytes_for_model(batch_rows: int, hidden: int, num_layers: int) -> int:
         """Enough for two sum all-reduces per layer and the final key exchange."""
-        per_sum = 2 * N.AR_MAX_RANKS * batch_rows * hidden * 4 + N.AR_MAX_RANKS * ((batch_rows * hidden + 255) // 256) * 4
+        per_sum = 2 * N.AR_MAX_RANKS * batch_rows * hidden * 8 + N.AR_MAX_RANKS * ((batch_rows * hidden + 255) // 256) * 4
         return (2 * num_layers + 2) * (per_sum + 1024) + 65536
