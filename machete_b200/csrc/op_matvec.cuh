@@ -81,7 +81,7 @@ __device__ __forceinline__ uint32_t mv_half_bytes(int wfmt, int Kc) {
   return mv_is_fp4(wfmt) ? (uint32_t)(Kc / 256) * 1024u : (uint32_t)(Kc / 64) * 1024u;
 }
 
-// What the loader needs to issue the pages of one unit, gathered once per unit.
+// What the loader needs to issue the pages of one unit (from the instruction record).
 struct MvLoad {
   const void* tm_a;
   const void* tm_b;
@@ -92,24 +92,6 @@ struct MvLoad {
   uint32_t half;
   bool fp4;
 };
-
-__device__ __forceinline__ MvLoad mv_load_setup(const mk_op_t* op, int unit) {
-  MvLoad l;
-  const MvRows r = mv_rows(op, unit);
-  const int Kc = op->i[MK_MV_KC];
-  const int wfmt = op->i[MK_MV_WFMT];
-  const bool pair = op->i[MK_MV_MODE] == MK_MV_PAIR;
-  l.fp4 = mv_is_fp4(wfmt);
-  l.tm_a = reinterpret_cast<const void*>(op->p[MK_MV_P_TM_W0]);
-  l.tm_b = reinterpret_cast<const void*>(op->p[pair ? MK_MV_P_TM_W1 : MK_MV_P_TM_W0]);
-  l.ts_a = reinterpret_cast<const void*>(op->p[MK_MV_P_TM_SC0]);
-  l.ts_b = reinterpret_cast<const void*>(op->p[pair ? MK_MV_P_TM_SC1 : MK_MV_P_TM_SC0]);
-  l.rowA0 = r.rowA0;
-  l.rowB0 = r.rowB0;
-  l.tiles_per_page = l.fp4 ? Kc / 256 : Kc / 64;
-  l.half = mv_half_bytes(wfmt, Kc);
-  return l;
-}
 
 // Issue the copies of K-slice `p` into the page at `page` (shared address):
 // two tiled TMA copies (four with NVFP4 scales) and one arrival for the whole
@@ -452,9 +434,7 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     const long long cyc0 = clock64();
     const int k0 = p * Kc;
     const int kc = min(Kc, K - k0);
-    if (op->reserved & 1) {
-      // diagnostic: consume the page without computing (pipeline cost only)
-    } else if (dense) {
+    if (dense) {
       // One K-tile = 64 K-values = 8 chunks of 16 B per row; this thread takes
       // chunks 2t and 2t+1 of rows g (half A) and g (half B): with the 128-byte
       // swizzle the 8 lanes of a shared-memory phase then hit 8 distinct chunks.

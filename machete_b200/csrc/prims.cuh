@@ -51,15 +51,6 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// ---- copies ----------------------------------------------------------------
-// Untiled TMA: contiguous global -> shared, completion counted in bytes on an
-// mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 // Tiled TMA: one 3-D box of a tensor map -> shared, completion in bytes on an
 // mbarrier.  The innermost coordinate c0 must keep c0 * element size a
 // multiple of 16 bytes (this build always passes 0).
@@ -103,15 +94,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
   asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(count) : "memory");
-}
-// 16-byte async copy; src_bytes == 0 writes zeros without touching global.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
-}
-// This thread's arrival on `bar` fires once all its earlier cp.async landed.
-__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // ---- dependency counters ----------------------------------------------------

@@ -355,13 +355,6 @@ __device__ __forceinline__ void signal_unit(Ctx& c, int counter) {
   }
 }
 
-// Participant index of consumer `w` in a shared unit whose first participant
-// slot is `seq` (slots are handed to the consumer warps round-robin); the
-// consumer takes part if the result is below the unit's participant count.
-__device__ __forceinline__ int mv_first_page(int w, uint32_t seq) {
-  const int s = (int)(seq % (uint32_t)kConsumerWarps);
-  return w >= s ? w - s : w + kConsumerWarps - s;
-}
 
 // Bounded wait until a shared-memory word reaches `want`.
 __device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, uint32_t want, int aux) {

@@ -1,0 +1,115 @@
+"""Decode-layer and whole-model schedules with NVFP4 weights on B200.
+
+Same composition as ``schedule_decode_layer_sm100`` (the reference's bf16
+B200 layer, src/machete/kernels/decode_matvec/sm100.py:666-823) built from the
+NVFP4 op family the reference only has for sm_120
+(src/machete/kernels/decode_matvec/sm120.py:596-2464): RMS + packed Q/K/V
+projections with RoPE and the KV-cache append, split-KV attention, packed
+O-projection with the residual, RMS + packed gate/up with SiLU, packed down
+projection, and the greedy-token head over a packed LM head.
+
+``weights`` holds, per matrix ``layer.{i}.W_x``, the keys ``...W_x.packed``
+(uint8 ``(rows, K/2)``) and ``...W_x.scales`` (fp16 ``(rows, K/32)`` — the
+reference's layout — or float8_e4m3fn ``(rows, K/16)`` with one fp32
+``global_scale`` per matrix under ``...W_x.global_scale``).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ...megakernel.ops import DEFAULT_PAGE_SIZE
+from .nvfp4 import (MatvecNvfp4Sm120Op, MatvecResidualNvfp4Sm120Op, RmsGateUpSiluNvfp4Sm120Op,
+                    RmsKMatvecRopeCacheNvfp4Sm120Op, RmsQMatvecRopeNvfp4Sm120Op, RmsVMatvecCacheNvfp4Sm120Op)
+from .sm100 import DecodeLayerSchedule
+from .top1 import schedule_final_top1_sm100
+
+
+def _w(weights, key):
+    packed, scales = weights[f"{key}.packed"], weights[f"{key}.scales"]
+    group = 16 if scales.element_size() == 1 else 32
+    return dict(packed=packed, scales=scales, group_size=group, global_scale=float(weights.get(f"{key}.global_scale", 1.0)))
+
+
+def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, weights, k_cache, v_cache, x_in,
+                                      residual_in, x_out, residual_out, q_buf, attn_out_buf, mlp_h_buf,
+                                      page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0, num_q_heads=32,
+                                      num_kv_heads=8, head_dim=128):
+    """One decoder layer with packed weights: ``DecodeLayerSchedule`` like the bf16 layer."""
+    from ..attention.flash_decoding import flash_decoding_schedule
+
+    pfx = f"layer.{layer_idx}"
+    cos = weights["cos"][cache_pos: cache_pos + seq_len]
+    sin = weights["sin"][cache_pos: cache_pos + seq_len]
+    q_4d = q_buf.view(batch, seq_len, num_q_heads, head_dim)
+    k_window = k_cache[:, : cache_pos + seq_len]
+    v_window = v_cache[:, : cache_pos + seq_len]
+    o_4d = attn_out_buf.view(batch, seq_len, num_q_heads, head_dim)
+
+    def proj(cls, key, **extra):
+        w = _w(weights, f"{pfx}.{key}")
+        return cls.schedule(x=x_in, residual_in=residual_in, norm_weight=weights[f"{pfx}.attn_norm"], cos=cos, sin=sin,
+                            weight_packed=w["packed"], weight_scales=w["scales"], group_size=w["group_size"],
+                            global_scale=w["global_scale"], tile_sizes={"S": seq_len, "O": 16}, page_size=page_size,
+                            eps=eps, head_dim=head_dim, **extra)
+
+    ops = []
+    ops += proj(RmsQMatvecRopeNvfp4Sm120Op, "W_q", residual_out=residual_out, q=q_buf)
+    ops += proj(RmsKMatvecRopeCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)
+    ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
+    fa_ops, fa_config = flash_decoding_schedule(q=q_4d, k=k_window, v=v_window, o=o_4d,
+                                                kv_group_size=num_q_heads // num_kv_heads, page_size=page_size,
+                                                num_splits=fa_num_splits)
+    ops += fa_ops
+    wo = _w(weights, f"{pfx}.W_o")
+    ops += MatvecResidualNvfp4Sm120Op.schedule(a=attn_out_buf, weight_packed=wo["packed"], weight_scales=wo["scales"],
+                                               residual_in=residual_out, residual_out=residual_out,
+                                               group_size=wo["group_size"], global_scale=wo["global_scale"],
+                                               tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
+    wg, wu = _w(weights, f"{pfx}.W_gate"), _w(weights, f"{pfx}.W_up")
+    ops += RmsGateUpSiluNvfp4Sm120Op.schedule(x=residual_out, norm_weight=weights[f"{pfx}.mlp_norm"],
+                                              gate_packed=wg["packed"], gate_scales=wg["scales"],
+                                              up_packed=wu["packed"], up_scales=wu["scales"], y=mlp_h_buf,
+                                              group_size=wg["group_size"], global_scale=wg["global_scale"],
+                                              tile_sizes={"S": seq_len, "D": 16}, page_size=page_size, eps=eps)
+    wd = _w(weights, f"{pfx}.W_down")
+    ops += MatvecNvfp4Sm120Op.schedule(a=mlp_h_buf, weight_packed=wd["packed"], weight_scales=wd["scales"], y=x_out,
+                                       group_size=wd["group_size"], global_scale=wd["global_scale"],
+                                       tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
+    return DecodeLayerSchedule(ops=ops, attention_config=fa_config, keep_alive=[cos, sin, q_4d, k_window, v_window, o_4d])
+
+
+def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_cache, x_buffers, residual_buffers,
+                                      q_buf, attn_out_buf, mlp_h_buf, top_values, top_indices, num_layers, x_in,
+                                      residual_in, seq_len=1, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0,
+                                      num_q_heads=32, num_kv_heads=8, head_dim=128):
+    """A full greedy decode step with packed weights: ``(ops, keep_alive)``.
+
+    Layer ``i`` reads the pair (``x``, residual) it is given and writes the
+    ping-pong pair ``x_buffers[j]`` / ``residual_buffers[j]``; the first layer
+    reads ``x_in`` / ``residual_in`` so that the step can be re-launched.  The
+    LM head is ``weights['lm_head.packed']`` / ``['lm_head.scales']``.
+    """
+    ops, keep = [], []
+    cur, cur_x, cur_r = 1, x_in, residual_in
+    for layer_idx in range(num_layers):
+        nxt = 1 - cur
+        layer = schedule_decode_layer_nvfp4_sm100(
+            layer_idx=layer_idx, batch=batch, seq_len=seq_len, cache_pos=cache_pos, weights=weights,
+            k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=cur_x, residual_in=cur_r,
+            x_out=x_buffers[nxt], residual_out=residual_buffers[nxt], q_buf=q_buf, attn_out_buf=attn_out_buf,
+            mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps, fa_num_splits=fa_num_splits, num_q_heads=num_q_heads,
+            num_kv_heads=num_kv_heads, head_dim=head_dim)
+        ops += layer.ops
+        keep += layer.keep_alive
+        cur = nxt
+        cur_x, cur_r = x_buffers[cur], residual_buffers[cur]
+    lm = _w(weights, "lm_head")
+    ops += schedule_final_top1_sm100(x=cur_x, residual_in=cur_r, final_norm=weights["final_norm"], lm_head=lm["packed"],
+                                     lm_head_scales=lm["scales"], group_size=lm["group_size"],
+                                     global_scale=lm["global_scale"], top_values=top_values, top_indices=top_indices,
+                                     seq_len=seq_len, page_size=page_size, eps=eps)
+    return ops, keep
+
+
+__all__ = ["schedule_decode_layer_nvfp4_sm100", "schedule_decode_model_nvfp4_sm100"]

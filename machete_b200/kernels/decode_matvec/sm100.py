@@ -40,6 +40,7 @@ SM100_DECODE_KV_GROUP_SIZE_DEFAULT = SM100_DECODE_NUM_Q_HEADS_DEFAULT // SM100_D
 
 
 class _DecodeMatvecSm100Base(Op):
+    uses_dense_weights = True   # bf16/fp16 weight pages (sizes the ring page)
     """Shared schedule/config helpers of the decode matvec ops."""
 
     @classmethod

@@ -22,6 +22,7 @@ from .._matvec import Weight, dense_weight, lower_matvec, nvfp4_weight
 
 
 class FinalAddRmsTop1LmHeadSm100Op(Op):
+    uses_dense_weights = True
     """keys[b, s] = max over vocab of (logit, index); logits = rms(x + residual_in) * w @ W^T."""
 
     reads = {
@@ -68,6 +69,7 @@ class FinalAddRmsTop1LmHeadNvfp4Sm100Op(FinalAddRmsTop1LmHeadSm100Op):
     """NVFP4-weight variant (``weight_packed``, ``weight_scales``)."""
 
     uses_nvfp4 = True
+    uses_dense_weights = False
     reads = {
         "x": (None, ("B", "S", "K")),
         "residual_in": (None, ("B", "S", "K")),

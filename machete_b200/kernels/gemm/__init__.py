@@ -23,6 +23,7 @@ ACT_MAP = {"relu": 1, "silu": 2}
 
 
 class GemmOp(Op):
+    uses_dense_weights = True
     reads = {
         "a": (None, ("B", "S", "K")),
         "a_scale": (None, ("B", "S", "K")),

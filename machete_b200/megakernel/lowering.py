@@ -14,7 +14,6 @@ choose their own unit shapes, independent of the API-level tile sizes.
 
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -96,7 +95,6 @@ class NativeOp:
         rec["opcode"] = self.opcode
         rec["n_units"] = self.n_units
         rec["act_key"] = act_key
-        rec["reserved"] = int(os.environ.get("MK_DIAG_FLAGS", "0"))   # diagnostic bits, 0 in production
         for k, v in self.i.items():
             rec["i"][k] = int(v)
         for k, v in self.f.items():

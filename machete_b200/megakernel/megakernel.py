@@ -147,7 +147,9 @@ class Megakernel:
         from .lowering import bf16_page_need, fp4_page_need
 
         uses_fp4 = any(getattr(op.op_cls, "uses_nvfp4", False) for op in ops)
-        need = max(need, bf16_page_need(ctx.kc_bf16))
+        uses_dense = any(getattr(op.op_cls, "uses_dense_weights", False) for op in ops)
+        if uses_dense or not uses_fp4:
+            need = max(need, bf16_page_need(ctx.kc_bf16))
         if uses_fp4:
             need = max(need, fp4_page_need(ctx.kc_fp4))
         return -(-need // 1024) * 1024
