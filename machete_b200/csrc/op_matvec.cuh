@@ -184,12 +184,10 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     const uint16_t* rr = add ? ri + b * op->s[MK_MV_S_RI_B] + s * op->s[MK_MV_S_RI_S] : nullptr;
     uint16_t* wr = write_res ? ro + b * op->s[MK_MV_S_RO_B] + s * op->s[MK_MV_S_RO_S] : nullptr;
     float sum = 0.f;
-    for (int ch = tid; ch < chunks; ch += T) {
-      uint4 v = *reinterpret_cast<const uint4*>(xr + ch * 8);
+    auto absorb = [&](int ch, uint4 v, uint4 rv) {
       float f[8];
       unpack8(v, xt, f);
       if (add) {
-        uint4 rv = *reinterpret_cast<const uint4*>(rr + ch * 8);
         float r[8];
         unpack8(rv, xt, r);
 #pragma unroll
@@ -204,6 +202,19 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
         // keep the (rounded) input in its own type for now; pass 2 rescales
         sts128(c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u, v);
       }
+    };
+    // two chunks per step, both requested before either is used (the stores to
+    // shared memory keep the compiler from hoisting the second load itself)
+    for (int ch = tid; ch < chunks; ch += 2 * T) {
+      const int ch2 = ch + T;
+      const bool two = ch2 < chunks;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
+      const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
+      const uint4 v2 = two ? *reinterpret_cast<const uint4*>(xr + ch2 * 8) : z;
+      const uint4 r2 = (two && add) ? *reinterpret_cast<const uint4*>(rr + ch2 * 8) : z;
+      absorb(ch, v1, r1);
+      if (two) absorb(ch2, v2, r2);
     }
     if (stage && pro != MK_PRO_NONE) {
       sum = warp_sum(sum);
@@ -469,22 +480,29 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
           }
         }
       };
+      // The two mma's on one 16-byte chunk feed the same accumulator; issuing
+      // the first halves of all chunks before the second halves keeps dependent
+      // mma's several issue slots apart.
       auto mma_pair = [&](const Frag& f, int valid, auto is_bf16) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (u < valid) {
+        for (int half = 0; half < 2; ++half) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              constexpr int kSets = NA;
-              const int a = (u * 2 + j) % kSets;
+          for (int u = 0; u < 2; ++u) {
+            if (u < valid) {
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                if constexpr (decltype(is_bf16)::value) {
-                  mma_bf16(acc[a][nt], f.wa[u][j].x, f.wb[u][j].x, f.wa[u][j].y, f.wb[u][j].y, f.x[nt][u][j].x, f.x[nt][u][j].y);
-                  mma_bf16(acc[a][nt], f.wa[u][j].z, f.wb[u][j].z, f.wa[u][j].w, f.wb[u][j].w, f.x[nt][u][j].z, f.x[nt][u][j].w);
-                } else {
-                  mma_f16(acc[a][nt], f.wa[u][j].x, f.wb[u][j].x, f.wa[u][j].y, f.wb[u][j].y, f.x[nt][u][j].x, f.x[nt][u][j].y);
-                  mma_f16(acc[a][nt], f.wa[u][j].z, f.wb[u][j].z, f.wa[u][j].w, f.wb[u][j].w, f.x[nt][u][j].z, f.x[nt][u][j].w);
+              for (int j = 0; j < 2; ++j) {
+                constexpr int kSets = NA;
+                const int a = (u * 2 + j) % kSets;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                  const uint32_t a0 = half ? f.wa[u][j].z : f.wa[u][j].x, a1 = half ? f.wb[u][j].z : f.wb[u][j].x;
+                  const uint32_t a2 = half ? f.wa[u][j].w : f.wa[u][j].y, a3 = half ? f.wb[u][j].w : f.wb[u][j].y;
+                  const uint32_t b0 = half ? f.x[nt][u][j].z : f.x[nt][u][j].x;
+                  const uint32_t b1 = half ? f.x[nt][u][j].w : f.x[nt][u][j].y;
+                  if constexpr (decltype(is_bf16)::value)
+                    mma_bf16(acc[a][nt], a0, a1, a2, a3, b0, b1);
+                  else
+                    mma_f16(acc[a][nt], a0, a1, a2, a3, b0, b1);
                 }
               }
             }
