@@ -44,7 +44,7 @@ class MegakernelConfig:
     or warp-role split (``threads_per_block``, ``dma_reg_count``,
     ``mma_reg_count``, ``opt_level``, ``loader_idle_sleep_ns``,
     ``relaxed_global_barriers``, ``global_barrier_sleep_ns``) are accepted and
-    ignored: the precompiled kernel always runs 1 loader + 8 consumer warps.
+    ignored: the precompiled kernel always runs 1 loader + 7 consumer warps.
     ``page_size`` is likewise accepted for parity with ``schedule(page_size=)``;
     the native ring page is sized from the ops (``native_kc``).
     """

@@ -8,8 +8,9 @@ scheduling.py:915-1120), work is dealt statically to one persistent CTA per SM,
 and completion is tracked by monotonic counters compared with ``>=``
 (megakernel/interpreter.py:33-77) — but the tables are this build's own:
 
-* an instruction is one *unit* owned by one consumer warp (32 bytes,
-  ``mk_instr_t``), stored per CTA contiguously rather than interleaved;
+* an instruction is one *unit* of one CTA (64 bytes, ``mk_instr_t``; matvec and
+  attention units are shared by several consumer warps of that CTA), stored
+  per CTA contiguously rather than interleaved;
 * every op has an *entry event* on each CTA that holds units of it: all
   consumer warps of the CTA meet there, wait for the op's producers and stage
   its activations, so units themselves carry waits only for finer-grained
