@@ -121,10 +121,18 @@ enum {
 /* MK_OP_ATTN_SPLIT / MK_OP_ATTN_COMBINE */
 enum {
   MK_AT_B = 0, MK_AT_M, MK_AT_H, MK_AT_HKV, MK_AT_D, MK_AT_N, MK_AT_SPLITS,
-  MK_AT_CAUSAL, MK_AT_MT, MK_AT_TS /* tokens per split */, MK_AT_O_T
+  MK_AT_CAUSAL, MK_AT_MT, MK_AT_TS /* tokens per split */, MK_AT_O_T,
+  /* MK_OP_ATTN_SPLIT only: 1 = the unit that completes a (batch, kv head,
+   * query tile) group also combines the group's splits into o / lse, so no
+   * separate MK_OP_ATTN_COMBINE op (and no dependency stage) is needed */
+  MK_AT_FUSE_COMBINE
 };
 enum { MK_AT_F_SCALE = 0 };
-enum { MK_AT_P_Q = 0, MK_AT_P_K, MK_AT_P_V, MK_AT_P_OPART, MK_AT_P_LSEPART, MK_AT_P_O, MK_AT_P_LSE };
+enum {
+  MK_AT_P_Q = 0, MK_AT_P_K, MK_AT_P_V, MK_AT_P_OPART, MK_AT_P_LSEPART, MK_AT_P_O, MK_AT_P_LSE,
+  /* fused combine: int32[B * Hkv * MT] arrival counters, zero before the first launch (the kernel leaves them zero) */
+  MK_AT_P_ARRIVE
+};
 enum {
   MK_AT_S_Q_B = 0, MK_AT_S_Q_M, MK_AT_S_Q_H,
   MK_AT_S_K_B, MK_AT_S_K_N, MK_AT_S_K_H,
@@ -158,7 +166,7 @@ enum { MK_AR_S_INBOX = 0, MK_AR_S_FLAGS };
  * index enums above.  The layout is fixed: 16 + 96 + 16 + 128 + 128 bytes. */
 typedef struct mk_op {
   int32_t opcode;
-  int32_t n_units;        /* work units (one warp processes one unit)        */
+  int32_t n_units;        /* work units                                      */
   int32_t act_key;        /* ops with equal non-zero key share staged input  */
   int32_t reserved;
   int32_t i[24];
@@ -167,7 +175,8 @@ typedef struct mk_op {
   int64_t s[16];
 } mk_op_t;
 
-/* One work unit assigned to one CTA (executed by one consumer warp). */
+/* One work unit assigned to one CTA (executed by one consumer warp, or shared
+ * page by page by several: see MK_LDF_SPLIT_SHIFT). */
 typedef struct mk_instr {
   int32_t op;             /* index into the op table                         */
   int32_t unit;           /* unit index within the op                        */

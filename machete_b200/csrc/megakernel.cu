@@ -1,14 +1,17 @@
 // The persistent decode megakernel and its C ABI.
 //
 // One CTA per SM.  Warp 0 is the loader: it walks the CTA's instruction list
-// and streams every unit's pages (weights by untiled TMA, K/V rows by
-// cp.async) into a shared-memory ring, running as far ahead of the consumers
+// and streams every unit's pages (weight K-slices and K/V token blocks, both by
+// tiled TMA) into a shared-memory ring, running as far ahead of the consumers
 // as the ring allows — weights carry no data dependency, so the HBM stream
 // continues across op boundaries while consumers wait on dependency counters.
-// Warps 1..8 are consumers: instruction j of the CTA belongs to consumer
-// j mod 8, which waits for its pages, computes and signals the unit's counter.
-// Op-entry events make all consumers of the CTA meet, wait for the op's
-// producers and stage its activations (RMSNorm fused) into shared memory.
+// Warps 1..7 are consumers.  A unit owns one consumer slot per participant
+// (matvec and attention units are shared page by page, every other unit has
+// one); a consumer that becomes free draws the next slot from a ticket
+// counter, waits for its pages, computes, and the participant that completes
+// the unit signals its counter.  Op-entry events make all consumers of the
+// CTA meet, wait for the op's producers, copy the op record to shared memory
+// and stage its activations (RMSNorm and residual add fused).
 //
 // Counterpart of the reference's ring loop (megakernel/replay_loops.py:27-824)
 // and launch path (megakernel/megakernel.py:2163-2204).
@@ -658,6 +661,13 @@ static int validate_op(const mk_program_t* p, int idx) {
       for (int k = MK_AT_S_O_B; k <= MK_AT_S_O_H; ++k)
         if (op.s[k] & 1) return fail(-2, "op %d: output strides must be even", idx);
       if (op.n_units != op.i[MK_AT_B] * H) return fail(-2, "op %d: bad unit count", idx);
+    }
+    if (op.opcode == MK_OP_ATTN_SPLIT && op.i[MK_AT_FUSE_COMBINE]) {
+      if (!op.p[MK_AT_P_O] || (op.p[MK_AT_P_O] & 15) || !op.p[MK_AT_P_ARRIVE] || (op.p[MK_AT_P_ARRIVE] & 3))
+        return fail(-2, "op %d: fused combine needs a 16-byte aligned output and the arrival counters", idx);
+      if (op.i[MK_AT_SPLITS] > 128) return fail(-2, "op %d: fused combine handles at most 128 splits", idx);
+      for (int k = MK_AT_S_O_B; k <= MK_AT_S_O_H; ++k)
+        if (op.s[k] & 7) return fail(-2, "op %d: fused combine needs output strides that are multiples of 8", idx);
     }
   } else if (op.opcode >= MK_OP_RMSNORM && op.opcode <= MK_OP_ADD) {
     if (!op.p[MK_EW_P_X]) return fail(-2, "op %d: input pointer missing", idx);

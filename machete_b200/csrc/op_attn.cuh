@@ -40,12 +40,13 @@ __device__ __forceinline__ AtUnit at_decode(const mk_op_t* op, int unit) {
 
 // Tokens per page for head dim D and a given page size: a K block and a V
 // block of `tn` rows each; tn is a multiple of the consumer's inner block
-// (64 tokens for D = 64, 32 for D = 128) and at most 128.
+// (64 tokens for D = 64, 32 for D = 128) and at most 64: a split of a few
+// hundred tokens then spans several pages, which several consumer warps share.
 __device__ __host__ __forceinline__ int at_page_tokens(int D, int page_bytes) {
   const int blk = (D == 64) ? 64 : 32;
   int tn = page_bytes / (4 * D);
   tn = (tn / blk) * blk;
-  return tn > 128 ? 128 : tn;
+  return tn > 64 ? 64 : tn;
 }
 
 // ---- loader -----------------------------------------------------------------------
@@ -71,6 +72,97 @@ __device__ __forceinline__ void at_load_issue(const void* tm_k, const void* tm_v
 __device__ __forceinline__ uint32_t at_chunk_addr(uint32_t tile, int tn, int tok, int chunk) {
   return tile + (uint32_t)(chunk >> 3) * (uint32_t)tn * 128u + (uint32_t)tok * 128u +
          (uint32_t)(((chunk & 7) ^ (tok & 7)) << 4);
+}
+
+// ---- fused combine ----------------------------------------------------------------
+__device__ __forceinline__ float ldcg_f(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float4 ldcg_f4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+// Combine all splits of one (batch, kv head, query tile) group: the same sum
+// as the combine op (weights e^{lse_s - max} / sum, splits added in order), for
+// every query row of the tile at once.  A row is spread over D/8 lanes of 8
+// output values each, so 32/(D/8) rows are in flight together and all of a
+// pass's partial rows are requested in two batches.  The partials were written
+// by other CTAs and fenced before their arrival was counted: they are read
+// past L1.
+template <int D>
+__device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, const AtUnit& u) {
+  constexpr int LPR = D / 8, RPP = 32 / LPR, UN = 9;
+  const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], S = op->i[MK_AT_SPLITS];
+  const int G = H / HKV;
+  const float* opart = reinterpret_cast<const float*>(op->p[MK_AT_P_OPART]);
+  const float* lpart = reinterpret_cast<const float*>(op->p[MK_AT_P_LSEPART]);
+  float* lse_out = reinterpret_cast<float*>(op->p[MK_AT_P_LSE]);
+  const int ot = op->i[MK_AT_O_T];
+  // this warp's 2 KB of the split-K slot area (no matvec unit runs beside an attention op's units)
+  float* scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.ctrl) + kCtrlStructBytes) + (c.warp - 1) * 512;
+  const int rows = min(16, M * G - u.mt * 16);
+  const int row = c.lane / LPR, dch = (c.lane % LPR) * 8;
+  for (int r0 = 0; r0 < rows; r0 += RPP) {
+    const int nr = min(RPP, rows - r0);
+    const bool rv = row < nr;
+    const int r = u.mt * 16 + r0 + (rv ? row : 0);
+    const int m = r / G, h = u.kvh * G + r % G;
+    const float* base = opart + ((((int64_t)u.b * H + h) * S) * M + m) * D + dch;
+    const int64_t sstride = (int64_t)M * D;
+    // request the first batch of partial rows together with the lse values:
+    // neither depends on the other, so they share one round trip
+    float4 a[UN], b2[UN];
+    auto fetch = [&](int s0) {
+#pragma unroll
+      for (int k = 0; k < UN; ++k) {
+        a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        b2[k] = a[k];
+        if (rv && s0 + k < S) {
+          a[k] = ldcg_f4(base + (s0 + k) * sstride);
+          b2[k] = ldcg_f4(base + (s0 + k) * sstride + 4);
+        }
+      }
+    };
+    fetch(0);
+    for (int i = c.lane; i < nr * S; i += 32) {
+      const int rr = i / S, s = i - rr * S, r2 = u.mt * 16 + r0 + rr;
+      const int m2 = r2 / G, h2 = u.kvh * G + r2 % G;
+      scratch[i] = ldcg_f(lpart + (((int64_t)u.b * H + h2) * S + s) * M + m2);
+    }
+    __syncwarp();
+    const float* ls = scratch + (rv ? row : 0) * S;
+    float mx = -INFINITY;
+    for (int s = 0; s < S; ++s) mx = fmaxf(mx, ls[s]);
+    float sum = 0.f;
+    if (mx != -INFINITY)
+      for (int s = 0; s < S; ++s) sum += __expf(ls[s] - mx);
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int s0 = 0; s0 < S; s0 += UN) {
+      if (s0 > 0) fetch(s0);
+#pragma unroll
+      for (int k = 0; k < UN; ++k) {
+        if (s0 + k >= S) break;
+        const float w = sum > 0.f ? __expf(ls[s0 + k] - mx) * inv : 0.f;
+        acc[0] += w * a[k].x; acc[1] += w * a[k].y; acc[2] += w * a[k].z; acc[3] += w * a[k].w;
+        acc[4] += w * b2[k].x; acc[5] += w * b2[k].y; acc[6] += w * b2[k].z; acc[7] += w * b2[k].w;
+      }
+    }
+    if (rv) {
+      const int64_t ooff = u.b * op->s[MK_AT_S_O_B] + m * op->s[MK_AT_S_O_M] + h * op->s[MK_AT_S_O_H] + dch;
+      if (ot == MK_T_FP32) {
+        float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(op->p[MK_AT_P_O]) + ooff);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          w[i] = ot == MK_T_BF16 ? pack_bf16(acc[2 * i], acc[2 * i + 1]) : pack_f16(acc[2 * i], acc[2 * i + 1]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(op->p[MK_AT_P_O]) + ooff) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (dch == 0 && lse_out) lse_out[((int64_t)u.b * H + h) * M + m] = (sum > 0.f) ? mx + __logf(sum) : -INFINITY;
+    }
+    __syncwarp();
+  }
 }
 
 // ---- consumer ---------------------------------------------------------------------
@@ -331,6 +423,23 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = v;
     }
     if (t == 0) lp_[base] = lse;
+  }
+  if (op->i[MK_AT_FUSE_COMBINE]) {
+    // count this split in; whoever completes the group combines it
+    __syncwarp();
+    int last = 0;
+    if (c.lane == 0) {
+      int32_t* arrive = reinterpret_cast<int32_t*>(op->p[MK_AT_P_ARRIVE]) +
+                        ((size_t)u.b * HKV + u.kvh) * op->i[MK_AT_MT] + u.mt;
+      // one acq_rel atomic: releases this unit's partial (all lanes' stores, ordered by the
+      // __syncwarp) and acquires the other splits' partials for the combine
+      int32_t old;
+      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(arrive) : "memory");
+      last = old == S - 1;
+      if (last) *arrive = 0;   // ready for the next launch
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) at_combine_group<D>(c, op, u);
   }
   return true;
 }

@@ -1,11 +1,12 @@
 // Weight-streaming matvec / small-M GEMM unit:  out[m, o] = epi(W[o, :] · pro(x[m, :])).
 //
 // One unit = 16 "virtual rows" of the weight matrix over the full K, streamed
-// through the page ring in K-slices of Kc columns (16 row segments per page,
-// one untiled TMA copy each).  The consumer warp feeds the slices to
-// mma.sync m16n8k16 with the weights as the A operand (M = 16 virtual rows)
-// and the staged activations as the B operand (N = 8 batch rows per n-tile),
-// so batch 1..32 share one code path and accumulate in fp32.
+// through the page ring in K-slices of Kc columns (one page = two tiled TMA
+// copies of 8 rows x Kc columns).  The unit's pages are dealt to one or more
+// consumer warps; each feeds its slices to mma.sync m16n8k16 with the weights
+// as the A operand (M = 16 virtual rows) and the staged activations as the B
+// operand (N = 8 batch rows per n-tile), so batch 1..32 share one code path
+// and accumulate in fp32; partial sums of several warps meet in shared memory.
 //
 // Virtual rows 0-7 and 8-15 land in the same thread's accumulators
 // (rows g and g+8 of the fragment), which is what lets RoPE partners

@@ -78,7 +78,48 @@ def lower_program(ops: List[ScheduledOp], ctx: LowerCtx) -> List[NativeOp]:
                 out.append(nop)
                 i += n
                 continue
+        if ctx.fuse and i + 1 < len(ops):
+            fused_attn = _fuse_attention(sop, ops[i + 1], ctx)
+            if fused_attn is not None:
+                out.append(fused_attn)
+                i += 2
+                continue
         lowered = sop.op_cls.lower(sop, ctx)
         out.extend(lowered)
         i += 1
     return out
+
+
+def _fuse_attention(split_sop: ScheduledOp, combine_sop: ScheduledOp, ctx: LowerCtx):
+    """Split-KV attention followed by the combine of the same partials -> one op.
+
+    The unit that completes a (batch, kv head, query tile) group combines the
+    group's splits itself, so the combine needs no dependency stage of its own
+    (and no CTA-wide event): one op boundary less per layer.
+    """
+    if split_sop.op_cls.__name__ != "FlashDecodingSplitBSHDOp" or \
+            combine_sop.op_cls.__name__ != "FlashDecodingCombineBSHDOp":
+        return None
+    ts, tc = split_sop.tensor_refs, combine_sop.tensor_refs
+    if ts["o_partial"].data_ptr() != tc["o_partial"].data_ptr() or \
+            ts["lse_partial"].data_ptr() != tc["lse_partial"].data_ptr():
+        return None
+    o = tc["o"]
+    if int(split_sop.static_dims["num_splits"]) > 128 or o.data_ptr() % 16 or any(st % 8 for st in o.stride()[:-1]):
+        return None
+    split = split_sop.op_cls.lower(split_sop, ctx)[0]
+    comb = combine_sop.op_cls.lower(combine_sop, ctx)[0]
+    groups = split.i[N.AT_B] * split.i[N.AT_HKV] * split.i[N.AT_MT]
+    arrive = torch.zeros(groups, dtype=torch.int32, device=ts["q"].device)
+    split.name = "FlashDecodingFused"
+    split.i[N.AT_FUSE_COMBINE] = 1
+    split.i[N.AT_O_T] = comb.i[N.AT_O_T]
+    split.p[N.AT_P_O], split.p[N.AT_P_LSE] = comb.p[N.AT_P_O], comb.p[N.AT_P_LSE]
+    split.p[N.AT_P_ARRIVE] = arrive.data_ptr()
+    for k in (N.AT_S_O_B, N.AT_S_O_M, N.AT_S_O_H):
+        split.s[k] = comb.s[k]
+    split.writes = list(split.writes) + list(comb.writes)
+    split.keep = list(split.keep) + list(comb.keep) + [arrive]
+    # consumers wait for the whole op (every unit signals; a group's last unit signals after its combine)
+    split.n_groups, split.unit_group = 1, None
+    return split

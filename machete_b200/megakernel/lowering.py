@@ -147,7 +147,7 @@ def attn_page_tokens(D: int, page_bytes: int) -> int:
     blk = 64 if D == 64 else 32
     tn = page_bytes // (4 * D)
     tn = (tn // blk) * blk
-    return min(tn, 128)
+    return min(tn, 64)     # short pages: more consumer warps share a split (csrc/op_attn.cuh)
 
 
 def split_bs(t: torch.Tensor) -> Tuple[int, int, int, int]:

@@ -76,17 +76,20 @@ def test_layer_schedule_dependencies_and_fusion():
     assert names[5:] == ["MatvecResidualSm100Op", "RmsGateUpSiluSm100Op", "MatvecSm100Op", "MatvecResidualSm100Op"]
     fused = Megakernel(layer.ops, config=MegakernelConfig(num_sms=16))
     plain = Megakernel(layer.ops, config=MegakernelConfig(num_sms=16, fuse=False))
-    assert [o.name for o in fused.native_ops][-1] == "FusedDownProj" and len(fused.native_ops) == 8
+    # fusion folds the combine into the split op and the four down-proj K-blocks into one matvec
+    assert [o.name for o in fused.native_ops][3] == "FlashDecodingFused"
+    assert [o.name for o in fused.native_ops][-1] == "FusedDownProj" and len(fused.native_ops) == 7
     assert len(plain.native_ops) == 9
     d = fused.program.deps
     assert d[0].coarse == [] and d[1].coarse == [] and d[2].coarse == []
     assert d[3].coarse == [0, 1, 2] and d[3].loader == [1, 2]           # split waits for q, k, v; loader for k, v
-    assert d[4].coarse == [] and list(d[4].fine) == [3]                 # combine waits per KV head
-    assert d[5].coarse == [4] and d[6].coarse == [5] and d[7].coarse == [6]
+    assert d[4].coarse == [3] and d[5].coarse == [4] and d[6].coarse == [5]
+    dp = plain.program.deps
+    assert dp[4].coarse == [] and list(dp[4].fine) == [3]               # unfused: the combine waits per KV head
     # q/k/v share one staged activation; o-proj, gate/up and down each stage their own
     keys = [int(k) for k in fused.program.ops["act_key"]]
     assert keys[0] == keys[1] == keys[2] != 0
-    assert len({keys[0], keys[5], keys[6], keys[7]}) == 4
+    assert len({keys[0], keys[4], keys[5], keys[6]}) == 4
     # only the split units that cover the appended token row carry loader waits
     ins = fused.program.instrs
     split = ins[ins["op"] == 3]
@@ -161,9 +164,11 @@ def test_flash_decoding_schedule_shapes_and_splits():
     assert split.tensor_refs["o_partial"].shape == (2, 8, 5, 1, 64)
     assert split.tensor_refs["lse_partial"].shape == (2, 8, 5, 1)
     assert split.static_dims["num_splits"] == 5 and comb.tensor_refs["lse"].shape == (2, 8, 1)
-    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8))
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8, fuse=False))
     sp = mk.native_ops[0]
-    assert sp.n_units == 2 * 2 * 1 * 5 and sp.n_groups == 4
+    assert sp.n_units == 2 * 2 * 1 * 5 and sp.n_groups == 4            # one counter per (batch, kv head)
+    fused = Megakernel(ops, config=MegakernelConfig(num_sms=8)).native_ops
+    assert len(fused) == 1 and fused[0].n_groups == 1 and fused[0].i[11] == 1   # combine folded into the split op
     ts = sp.i[9]
     assert ts % 16 == 0 and ts * 5 >= 1000
     assert int(np.sum(sp.unit_bytes)) == 2 * 2 * 1000 * 64 * 2 * 2     # K and V read exactly once
