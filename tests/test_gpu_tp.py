@@ -19,6 +19,36 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shard_programs_compile_at_llama1b_shapes(world):
+    """One GPU is enough to validate the sharded programs: every rank's shapes (K = 256 O-proj shards,
+    one KV head per rank, 16032-row vocabulary shards ...) must pass the library's checks and get their
+    tensor maps.  The program is compiled, not launched (its peers do not exist here)."""
+    from machete_b200.kernels.llama1b import schedule_decode_model_sm100
+    from machete_b200.megakernel import Megakernel, OverlapTileScheduler
+    from machete_b200.megakernel.peer import PeerBuffers
+    from tests.util import llama_weights
+
+    BF, dev = torch.bfloat16, "cuda"
+    hidden, nq, nkv, hd, inter, vocab, L, T = 2048, 32 // world, 8 // world, 64, 8192 // world, 128256 // world, 2, 512
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=3, device=dev)
+    for l in range(L):   # `llama_weights` builds square-ish layers: O-proj and down are the K-split ones
+        assert w[f"layer.{l}.W_o"].shape == (hidden, nq * hd) and w[f"layer.{l}.W_down"].shape == (hidden, inter)
+    peers = PeerBuffers(PeerBuffers.bytes_for_model(1, hidden, L), rank=world - 1, world_size=world)   # table only
+    tv, ti = torch.zeros(1, 1, device=dev), torch.zeros(1, 1, dtype=torch.int32, device=dev)
+    z = lambda *s: torch.zeros(*s, dtype=BF, device=dev)   # noqa: E731
+    ops, _keep = schedule_decode_model_sm100(
+        batch=1, cache_pos=300, weights=w, k_cache=[z(1, T, nkv, hd) for _ in range(L)],
+        v_cache=[z(1, T, nkv, hd) for _ in range(L)], x_buffers=[z(1, 1, hidden), z(1, 1, hidden)],
+        residual_buffers=[z(1, 1, hidden), z(1, 1, hidden)], q_buf=z(1, 1, nq * hd), attn_out_buf=z(1, 1, nq * hd),
+        mlp_h_buf=z(1, 1, inter), final_norm=torch.ones(hidden, dtype=BF, device=dev), lm_head=z(vocab, hidden),
+        top_values=tv, top_indices=ti, num_layers=L, hidden_size=hidden, intermediate_size=inter, num_q_heads=nq,
+        num_kv_heads=nkv, head_dim=hd, x_in=z(1, 1, hidden), residual_in=z(1, 1, hidden), tp_peers=peers)
+    mk = Megakernel(ops, scheduler=OverlapTileScheduler())
+    mk.compile()                       # mk_create: validation + tensor maps; raises on any rejected shape
+    assert mk.total_tiles > 0
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_decode_matches_single_gpu_and_oracle():
     with socket.socket() as s:

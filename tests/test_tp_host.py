@@ -24,7 +24,7 @@ from machete_b200.megakernel.peer import PeerBuffers
 from tests.util import llama_weights
 
 BF = torch.bfloat16
-DIMS = dict(hidden=256, inter=512, nq=4, nkv=2, hd=64, vocab=512, layers=2, T=128)
+DIMS = dict(hidden=256, inter=1024, nq=8, nkv=8, hd=64, vocab=1024, layers=2, T=128)
 
 
 def shard_weights(w, rank, world, d):
@@ -82,8 +82,8 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_ranks_agree_on_the_exchange_layout():
-    world = 2
+@pytest.mark.parametrize("world", [2, 8])
+def test_ranks_agree_on_the_exchange_layout(world):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -98,11 +98,12 @@ def test_two_ranks_agree_on_the_exchange_layout():
         assert p.exitcode == 0
     for rank, ok_counters, gathered, n_ops in results:
         assert ok_counters                                   # every counter reaches its expected value: no lost signal
-        a, b = gathered
-        assert len(a) == len(b) == 2 * DIMS["layers"] + 1    # O-proj + down per layer, and the key exchange
-        for ra, rb_ in zip(a, b):
-            assert ra[0] == rb_[0] and ra[2:] == rb_[2:]      # same op, world, size, mode, offsets, epoch base, units
-            assert (ra[1], rb_[1]) == (0, 1)                  # and each carries its own rank
+        a = gathered[0]
+        assert all(len(g) == 2 * DIMS["layers"] + 1 for g in gathered)   # O-proj + down per layer, the key exchange
+        for r, g in enumerate(gathered):
+            for ra, rg in zip(a, g):
+                assert ra[0] == rg[0] and ra[2:] == rg[2:]    # same op, world, size, mode, offsets, epoch base, units
+                assert rg[1] == r and rg[2] == world          # and each carries its own rank
         offs = [r[5] for r in a] + [r[6] for r in a]
         assert len(set(offs)) == len(offs)                   # regions are distinct
         assert a[-1][4] == N.AR_MAX_KEY and all(r[4] == N.AR_SUM for r in a[:-1])
