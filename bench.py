@@ -66,6 +66,9 @@ def parse_args():
     ap.add_argument("--vocab", type=int, default=LLAMA1B["vocab"])
     ap.add_argument("--kc", type=int, default=0, help="K columns per weight page (0 = default)")
     ap.add_argument("--scheduler", default="overlap", choices=["overlap", "roundrobin"])
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"],
+                    help="nvfp4: the same model shape with packed e2m1 weights, e4m3 scale per 16 values + fp32 "
+                         "global scale (single GPU only); the headline workload is bf16")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="N > 1: tensor-parallel decode of ONE stream (in-kernel all-reduce) or N independent replicas")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -89,12 +92,15 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def algorithmic_bytes(cfg, batch, kv_len, layers, vocab):
-    """Weights + LM head + KV read once per step (the byte accounting of the roofline)."""
+def algorithmic_bytes(cfg, batch, kv_len, layers, vocab, bytes_per_weight=2.0):
+    """Weights + LM head + KV read once per step (the byte accounting of the roofline).
+
+    ``bytes_per_weight``: 2 for bf16, 0.5625 for NVFP4 (4-bit code + one scale byte per 16 values).
+    """
     h, i, q, kv = cfg["hidden"], cfg["inter"], cfg["nq"] * cfg["hd"], cfg["nkv"] * cfg["hd"]
-    per_layer = (q * h + 2 * kv * h + h * q + 2 * i * h + h * i) * 2
+    per_layer = (q * h + 2 * kv * h + h * q + 2 * i * h + h * i) * bytes_per_weight
     kv_bytes = kv_len * kv * 2 * 2
-    return layers * per_layer + vocab * h * 2 + batch * layers * kv_bytes
+    return int(layers * per_layer + vocab * h * bytes_per_weight + batch * layers * kv_bytes)
 
 
 def make_weights(cfg, layers, vocab, kv_len, device, seed):
@@ -247,7 +253,7 @@ def workload_config(args, world, tp=False, note=None):
         par = f"{world} independent replicas (one sequence set per GPU)" + (f"; {note}" if note else "")
     return {
         "workload": f"llama-3.2-1b-shape {args.layers}-layer decode step, batch {args.batch}, kv {args.kv_len}, "
-                    f"vocab {args.vocab}, bf16, greedy token",
+                    f"vocab {args.vocab}, {args.weights}, greedy token",
         "global_batch": args.batch * (1 if tp else world), "kv_len": args.kv_len, "parallelism": par,
         "l2": "inputs (2.6 GB of weights per step, divided by the ranks under tp) larger than L2; no flush needed",
     }
@@ -305,7 +311,26 @@ def main():
     rb = [torch.zeros(B, 1, cfg["hidden"], dtype=bf, device=dev) for _ in range(2)]
     tv = torch.zeros(B, 1, device=dev)
     ti = torch.zeros(B, 1, dtype=torch.int32, device=dev)
-    ops, keep = schedule_decode_model_sm100(
+    nvfp4 = args.weights == "nvfp4"
+    if nvfp4 and world > 1:
+        raise SystemExit("--weights nvfp4 runs on one GPU")
+    if nvfp4:
+        from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+        from machete_b200.quantization import quantize_nvfp4_weight
+
+        packed = {k: v for k, v in weights.items() if not (".W_" in k or k == "lm_head")}
+        for k in [k for k in weights if ".W_" in k or k == "lm_head"]:
+            q4 = quantize_nvfp4_weight(weights.pop(k), group_size=16)
+            packed[f"{k}.packed"], packed[f"{k}.scales"], packed[f"{k}.global_scale"] = q4.packed, q4.scales, float(q4.global_scale)
+        weights = packed
+        torch.cuda.empty_cache()
+    ops, keep = (schedule_decode_model_nvfp4_sm100(
+        batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
+        q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
+        attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
+        mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), top_values=tv, top_indices=ti,
+        num_layers=args.layers, x_in=x_in, residual_in=r_in, num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"],
+        head_dim=cfg["hd"], eps=1e-5) if nvfp4 else None) or schedule_decode_model_sm100(
         batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
         q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
         attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
@@ -378,14 +403,14 @@ def main():
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        alg = algorithmic_bytes(cfg, B, L, args.layers, vocab)      # per GPU (this rank's shard under tp)
+        alg = algorithmic_bytes(cfg, B, L, args.layers, vocab, 0.5625 if nvfp4 else 2.0)   # per GPU (this rank's shard under tp)
         achieved = alg / (ms_step * 1e-3) / 1e9
         line = {
             "metric": "decode_tokens_per_s", "value": B * (1 if tp else world) / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
             "us_per_step": ms_step * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(args, world, tp, tp_note),
+            "vs_baseline": None, "dtype": "bf16" if not nvfp4 else "nvfp4 weights, f16 tensor-core math, fp32 accumulate",
+            "data": "synthetic", "config": workload_config(args, world, tp, tp_note),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
                          "algorithmic_bytes_per_step": alg, "kernel": "mk_persistent_kernel",
@@ -395,7 +420,7 @@ def main():
                               "page_bytes": mk.page_bytes, "instructions": mk.total_tiles,
                               "counters": mk.num_barriers, "scheduler": args.scheduler},
         }
-        if not args.no_cpu_baseline and world == 1:
+        if not args.no_cpu_baseline and world == 1 and not nvfp4:
             wcpu = {k: v.cpu() for k, v in weights.items()}
             secs, sample = cpu_step_seconds(args, cfg, wcpu)
             line["cpu_baseline"] = {"value": B / secs, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
