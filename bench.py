@@ -45,7 +45,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-LLAMA1B = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=128256, layers=16, theta=500000.0)
+LLAMA1B = dict(name="llama-3.2-1b-shape", hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=128256, layers=16,
+               theta=500000.0, kv_len=4096, eps=1e-5, qk_norm=False)
+# Qwen3-8B shape: per-head q/k RMSNorm, NVFP4 weights, KV length 8192 (run with --model qwen3-8b)
+QWEN3_8B = dict(name="qwen3-8b-shape", hidden=4096, inter=12288, nq=32, nkv=8, hd=128, vocab=151936, layers=36,
+                theta=1000000.0, kv_len=8192, eps=1e-6, qk_norm=True)
+MODELS = {"llama1b": LLAMA1B, "qwen3-8b": QWEN3_8B}
 FALLBACK_HBM_GBS = 6650.0
 # dram read + write bytes per algorithmic byte, from one ncu capture of a 4-layer + LM-head case
 # of the same kernel (profiles/mk_persistent_kernel_llama1b_decode.md); DRAM traffic is
@@ -60,20 +65,30 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default="llama1b", choices=sorted(MODELS),
+                    help="llama1b: the headline workload (bf16); qwen3-8b: 36 layers with q/k RMSNorm, NVFP4 weights")
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--kv-len", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=LLAMA1B["layers"])
-    ap.add_argument("--vocab", type=int, default=LLAMA1B["vocab"])
+    ap.add_argument("--kv-len", type=int, default=0, help="0 = the model's default (4096 / 8192)")
+    ap.add_argument("--layers", type=int, default=0, help="0 = the model's layer count")
+    ap.add_argument("--vocab", type=int, default=0, help="0 = the model's vocabulary")
     ap.add_argument("--kc", type=int, default=0, help="K columns per weight page (0 = default)")
     ap.add_argument("--scheduler", default="overlap", choices=["overlap", "roundrobin"])
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "nvfp4"],
-                    help="nvfp4: the same model shape with packed e2m1 weights, e4m3 scale per 16 values + fp32 "
-                         "global scale (single GPU only); the headline workload is bf16")
+    ap.add_argument("--weights", default="", choices=["", "bf16", "nvfp4"],
+                    help="nvfp4: packed e2m1 weights, e4m3 scale per 16 values + fp32 global scale (the default and "
+                         "only choice for qwen3-8b); the headline workload is llama1b in bf16")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="N > 1: tensor-parallel decode of ONE stream (in-kernel all-reduce) or N independent replicas")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    return ap.parse_args()
+    args = ap.parse_args()
+    model = MODELS[args.model]
+    args.kv_len = args.kv_len or model["kv_len"]
+    args.layers = args.layers or model["layers"]
+    args.vocab = args.vocab or model["vocab"]
+    args.weights = args.weights or ("nvfp4" if model["qk_norm"] else "bf16")
+    if model["qk_norm"] and args.weights != "nvfp4":
+        ap.error("the q/k-norm layer is scheduled with NVFP4 weights only")
+    return args
 
 
 def dist_env():
@@ -124,6 +139,8 @@ def make_weights(cfg, layers, vocab, kv_len, device, seed):
         weights[f"{p}.W_o"] = w(h, q)
         weights[f"{p}.W_gate"], weights[f"{p}.W_up"] = w(i, h), w(i, h)
         weights[f"{p}.W_down"] = w(h, i)
+        if cfg.get("qk_norm"):
+            weights[f"{p}.q_norm"], weights[f"{p}.k_norm"] = nw(cfg["hd"]), nw(cfg["hd"])
     weights["final_norm"] = nw(h)
     weights["lm_head"] = w(vocab, h)          # stands for the tied embedding matrix
     return weights
@@ -226,7 +243,7 @@ def run_reference(args, rank, world):
     """The reference's own path for this step is PyTorch on the host: time the CPU port."""
     if rank != 0:
         return
-    cfg = LLAMA1B
+    cfg = MODELS[args.model]
     weights = make_weights(cfg, args.layers, args.vocab, args.kv_len, "cpu", seed=0)
     # each "step" is one bounded CPU pass; W + K passes are capped to keep the run within minutes
     budget = 240.0 / max(1, args.steps + args.warmup)
@@ -252,10 +269,10 @@ def workload_config(args, world, tp=False, note=None):
     else:
         par = f"{world} independent replicas (one sequence set per GPU)" + (f"; {note}" if note else "")
     return {
-        "workload": f"llama-3.2-1b-shape {args.layers}-layer decode step, batch {args.batch}, kv {args.kv_len}, "
-                    f"vocab {args.vocab}, {args.weights}, greedy token",
+        "workload": f"{MODELS[args.model]['name']} {args.layers}-layer decode step, batch {args.batch}, "
+                    f"kv {args.kv_len}, vocab {args.vocab}, {args.weights}, greedy token",
         "global_batch": args.batch * (1 if tp else world), "kv_len": args.kv_len, "parallelism": par,
-        "l2": "inputs (2.6 GB of weights per step, divided by the ranks under tp) larger than L2; no flush needed",
+        "l2": "inputs (GBs of weights and KV per step, divided by the ranks under tp) larger than L2; no flush needed",
     }
 
 
@@ -278,7 +295,7 @@ def main():
     from machete_b200.kernels.llama1b import schedule_decode_model_sm100
     from machete_b200.megakernel import BackwardScheduler, Megakernel, MegakernelConfig, OverlapTileScheduler
 
-    cfg = dict(LLAMA1B)
+    cfg = dict(MODELS[args.model])
     B, L, bf = args.batch, args.kv_len, torch.bfloat16
     # N > 1: one decode stream sharded Megatron-style over the ranks, unless the peer mapping
     # cannot be set up on this box (then N independent replicas, and the line says so)
@@ -312,8 +329,6 @@ def main():
     tv = torch.zeros(B, 1, device=dev)
     ti = torch.zeros(B, 1, dtype=torch.int32, device=dev)
     nvfp4 = args.weights == "nvfp4"
-    if nvfp4 and world > 1:
-        raise SystemExit("--weights nvfp4 runs on one GPU")
     if nvfp4:
         from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
         from machete_b200.quantization import quantize_nvfp4_weight
@@ -330,14 +345,14 @@ def main():
         attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
         mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), top_values=tv, top_indices=ti,
         num_layers=args.layers, x_in=x_in, residual_in=r_in, num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"],
-        head_dim=cfg["hd"], eps=1e-5) if nvfp4 else None) or schedule_decode_model_sm100(
+        head_dim=cfg["hd"], eps=cfg["eps"], tp_peers=peers) if nvfp4 else None) or schedule_decode_model_sm100(
         batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
         q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
         attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
         mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), final_norm=weights["final_norm"],
         lm_head=weights["lm_head"], top_values=tv, top_indices=ti, num_layers=args.layers, x_in=x_in,
         residual_in=r_in, hidden_size=cfg["hidden"], intermediate_size=cfg["inter"], num_q_heads=cfg["nq"],
-        num_kv_heads=cfg["nkv"], head_dim=cfg["hd"], tp_peers=peers)
+        num_kv_heads=cfg["nkv"], head_dim=cfg["hd"], eps=cfg["eps"], tp_peers=peers)
     sched = OverlapTileScheduler() if args.scheduler == "overlap" else BackwardScheduler()
     mk = Megakernel(ops, config=MegakernelConfig(native_kc=args.kc or None), device=dev, scheduler=sched)
     mk.compile()

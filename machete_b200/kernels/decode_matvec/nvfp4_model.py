@@ -12,6 +12,17 @@ projection, and the greedy-token head over a packed LM head.
 (uint8 ``(rows, K/2)``) and ``...W_x.scales`` (fp16 ``(rows, K/32)`` — the
 reference's layout — or float8_e4m3fn ``(rows, K/16)`` with one fp32
 ``global_scale`` per matrix under ``...W_x.global_scale``).
+
+Qwen3-style layers: when ``weights`` holds ``layer.{i}.q_norm`` / ``.k_norm``
+(``(head_dim,)``), the Q and K projections are stored unrotated and a per-head
+RMSNorm + RoPE pass (``QKNormRopeOp``, the composition of the reference's
+src/machete/kernels/qwen_3_5/sm120.py:2986-2994) runs on ``q`` and on the new
+cache row before attention.
+
+``tp_peers`` (a ``PeerBuffers``) shards the layer Megatron-style exactly as the
+bf16 layer does: ``weights`` hold this rank's shards (row-split Q/K/V/gate/up,
+K-split O/down), head counts are the local ones, and the two K-split
+projections write fp32 partials that the in-kernel all-reduce sums.
 """
 
 from __future__ import annotations
@@ -19,8 +30,10 @@ from __future__ import annotations
 import torch
 
 from ...megakernel.ops import DEFAULT_PAGE_SIZE
+from ..qknorm_rope import QKNormRopeOp
 from .nvfp4 import (MatvecNvfp4Sm120Op, MatvecResidualNvfp4Sm120Op, RmsGateUpSiluNvfp4Sm120Op,
-                    RmsKMatvecRopeCacheNvfp4Sm120Op, RmsQMatvecRopeNvfp4Sm120Op, RmsVMatvecCacheNvfp4Sm120Op)
+                    RmsKMatvecRopeCacheNvfp4Sm120Op, RmsMatvecNvfp4Sm120Op, RmsQMatvecRopeNvfp4Sm120Op,
+                    RmsVMatvecCacheNvfp4Sm120Op)
 from .sm100 import DecodeLayerSchedule
 from .top1 import schedule_final_top1_sm100
 
@@ -34,7 +47,7 @@ def _w(weights, key):
 def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, weights, k_cache, v_cache, x_in,
                                       residual_in, x_out, residual_out, q_buf, attn_out_buf, mlp_h_buf,
                                       page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0, num_q_heads=32,
-                                      num_kv_heads=8, head_dim=128):
+                                      num_kv_heads=8, head_dim=128, tp_peers=None):
     """One decoder layer with packed weights: ``DecodeLayerSchedule`` like the bf16 layer."""
     from ..attention.flash_decoding import flash_decoding_schedule
 
@@ -53,19 +66,52 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                             global_scale=w["global_scale"], tile_sizes={"S": seq_len, "O": 16}, page_size=page_size,
                             eps=eps, head_dim=head_dim, **extra)
 
-    ops = []
-    ops += proj(RmsQMatvecRopeNvfp4Sm120Op, "W_q", residual_out=residual_out, q=q_buf)
-    ops += proj(RmsKMatvecRopeCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)
-    ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
+    ops, extra_keep = [], []
+    if f"{pfx}.q_norm" in weights:
+        if seq_len != 1 and batch != 1:
+            raise ValueError("the QK-norm layer takes one token per sequence or one sequence")
+        wq = _w(weights, f"{pfx}.W_q")
+        ops += RmsMatvecNvfp4Sm120Op.schedule(x=x_in, residual_in=residual_in, norm_weight=weights[f"{pfx}.attn_norm"],
+                                              weight_packed=wq["packed"], weight_scales=wq["scales"], y=q_buf,
+                                              residual_out=residual_out, group_size=wq["group_size"],
+                                              global_scale=wq["global_scale"], tile_sizes={"S": seq_len, "O": 16},
+                                              page_size=page_size, eps=eps)
+        ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)   # unrotated
+        ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
+        # row m = (b, s) of the (M, H, D) views takes the table row of token s
+        cos_m, sin_m = cos.repeat(batch, 1), sin.repeat(batch, 1)
+        q_rows = q_buf.view(batch * seq_len, num_q_heads, head_dim)
+        k_rows = k_cache[:, cache_pos] if seq_len == 1 else k_cache[0, cache_pos: cache_pos + seq_len]
+        ops += QKNormRopeOp.schedule(q=q_rows, norm_weight=weights[f"{pfx}.q_norm"], cos=cos_m, sin=sin_m, eps=eps,
+                                     page_size=page_size)
+        ops += QKNormRopeOp.schedule(q=k_rows, norm_weight=weights[f"{pfx}.k_norm"], cos=cos_m, sin=sin_m, eps=eps,
+                                     page_size=page_size, cache_rows=(cache_pos, cache_pos + seq_len))
+        extra_keep += [cos_m, sin_m, q_rows, k_rows]
+    else:
+        ops += proj(RmsQMatvecRopeNvfp4Sm120Op, "W_q", residual_out=residual_out, q=q_buf)
+        ops += proj(RmsKMatvecRopeCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)
+        ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
     fa_ops, fa_config = flash_decoding_schedule(q=q_4d, k=k_window, v=v_window, o=o_4d,
                                                 kv_group_size=num_q_heads // num_kv_heads, page_size=page_size,
                                                 num_splits=fa_num_splits)
     ops += fa_ops
     wo = _w(weights, f"{pfx}.W_o")
-    ops += MatvecResidualNvfp4Sm120Op.schedule(a=attn_out_buf, weight_packed=wo["packed"], weight_scales=wo["scales"],
-                                               residual_in=residual_out, residual_out=residual_out,
-                                               group_size=wo["group_size"], global_scale=wo["global_scale"],
-                                               tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
+    if tp_peers is not None:
+        from ..allreduce import AllReduceSm100Op
+
+        o_part = torch.empty(residual_out.shape, dtype=torch.float32, device=residual_out.device)
+        x_part = torch.empty(x_out.shape, dtype=torch.float32, device=x_out.device)
+        extra_keep += [o_part, x_part]
+        ops += MatvecNvfp4Sm120Op.schedule(a=attn_out_buf, weight_packed=wo["packed"], weight_scales=wo["scales"],
+                                           y=o_part, group_size=wo["group_size"], global_scale=wo["global_scale"],
+                                           tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
+        ops += AllReduceSm100Op.schedule(peers=tp_peers, x=o_part, residual_in=residual_out, y=residual_out)
+    else:
+        ops += MatvecResidualNvfp4Sm120Op.schedule(a=attn_out_buf, weight_packed=wo["packed"],
+                                                   weight_scales=wo["scales"], residual_in=residual_out,
+                                                   residual_out=residual_out, group_size=wo["group_size"],
+                                                   global_scale=wo["global_scale"],
+                                                   tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
     wg, wu = _w(weights, f"{pfx}.W_gate"), _w(weights, f"{pfx}.W_up")
     ops += RmsGateUpSiluNvfp4Sm120Op.schedule(x=residual_out, norm_weight=weights[f"{pfx}.mlp_norm"],
                                               gate_packed=wg["packed"], gate_scales=wg["scales"],
@@ -73,22 +119,27 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                                               group_size=wg["group_size"], global_scale=wg["global_scale"],
                                               tile_sizes={"S": seq_len, "D": 16}, page_size=page_size, eps=eps)
     wd = _w(weights, f"{pfx}.W_down")
-    ops += MatvecNvfp4Sm120Op.schedule(a=mlp_h_buf, weight_packed=wd["packed"], weight_scales=wd["scales"], y=x_out,
-                                       group_size=wd["group_size"], global_scale=wd["global_scale"],
-                                       tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
-    return DecodeLayerSchedule(ops=ops, attention_config=fa_config, keep_alive=[cos, sin, q_4d, k_window, v_window, o_4d])
+    ops += MatvecNvfp4Sm120Op.schedule(a=mlp_h_buf, weight_packed=wd["packed"], weight_scales=wd["scales"],
+                                       y=x_part if tp_peers is not None else x_out, group_size=wd["group_size"],
+                                       global_scale=wd["global_scale"], tile_sizes={"S": seq_len, "O": 16},
+                                       page_size=page_size)
+    if tp_peers is not None:
+        ops += AllReduceSm100Op.schedule(peers=tp_peers, x=x_part, y=x_out)
+    return DecodeLayerSchedule(ops=ops, attention_config=fa_config,
+                               keep_alive=[cos, sin, q_4d, k_window, v_window, o_4d, *extra_keep])
 
 
 def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_cache, x_buffers, residual_buffers,
                                       q_buf, attn_out_buf, mlp_h_buf, top_values, top_indices, num_layers, x_in,
                                       residual_in, seq_len=1, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0,
-                                      num_q_heads=32, num_kv_heads=8, head_dim=128):
+                                      num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None):
     """A full greedy decode step with packed weights: ``(ops, keep_alive)``.
 
     Layer ``i`` reads the pair (``x``, residual) it is given and writes the
     ping-pong pair ``x_buffers[j]`` / ``residual_buffers[j]``; the first layer
     reads ``x_in`` / ``residual_in`` so that the step can be re-launched.  The
-    LM head is ``weights['lm_head.packed']`` / ``['lm_head.scales']``.
+    LM head is ``weights['lm_head.packed']`` / ``['lm_head.scales']``.  Under ``tp_peers`` the
+    LM head is this rank's vocabulary shard and the ranks exchange their top-1 keys.
     """
     ops, keep = [], []
     cur, cur_x, cur_r = 1, x_in, residual_in
@@ -99,7 +150,7 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
             k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=cur_x, residual_in=cur_r,
             x_out=x_buffers[nxt], residual_out=residual_buffers[nxt], q_buf=q_buf, attn_out_buf=attn_out_buf,
             mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps, fa_num_splits=fa_num_splits, num_q_heads=num_q_heads,
-            num_kv_heads=num_kv_heads, head_dim=head_dim)
+            num_kv_heads=num_kv_heads, head_dim=head_dim, tp_peers=tp_peers)
         ops += layer.ops
         keep += layer.keep_alive
         cur = nxt
@@ -108,7 +159,7 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
     ops += schedule_final_top1_sm100(x=cur_x, residual_in=cur_r, final_norm=weights["final_norm"], lm_head=lm["packed"],
                                      lm_head_scales=lm["scales"], group_size=lm["group_size"],
                                      global_scale=lm["global_scale"], top_values=top_values, top_indices=top_indices,
-                                     seq_len=seq_len, page_size=page_size, eps=eps)
+                                     seq_len=seq_len, page_size=page_size, eps=eps, tp_peers=tp_peers)
     return ops, keep
 
 

@@ -25,7 +25,9 @@ class QKNormRopeOp(Op):
     dynamic_dims = ("M",)
 
     @classmethod
-    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, **tensors):
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, cache_rows=None, **tensors):
+        """``cache_rows=(lo, hi)``: ``q`` is the view of token rows [lo, hi) of a KV cache that a later
+        attention op reads; only the splits that cover those rows then wait for this op."""
         q, cos, sin = tensors["q"], tensors["cos"], tensors["sin"]
         if q.ndim != 3:
             raise ValueError(f"QKNormRopeOp: q must be (M, H, D), got {tuple(q.shape)}")
@@ -37,6 +39,8 @@ class QKNormRopeOp(Op):
         op = cls._schedule_single(tile_sizes=tile_sizes, **tensors)
         op.static_dims["page_size"] = page_size
         op.static_dims["eps"] = eps
+        if cache_rows is not None:
+            op.params["cache_rows"] = (int(cache_rows[0]), int(cache_rows[1]))
         return [op]
 
     @classmethod
@@ -64,6 +68,10 @@ class QKNormRopeOp(Op):
                     Region(meta_of(sin, "sin"))]
         op.writes = [Region(meta_of(q, "q"))]
         op.keep = [q, w, cos, sin]
+        rows = sop.params.get("cache_rows")
+        if rows is not None:
+            op.writes[-1].axis, op.writes[-1].lo, op.writes[-1].hi = 1, rows[0], rows[1]
+            op.kind = "cache_append"
         return [op]
 
 

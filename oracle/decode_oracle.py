@@ -321,10 +321,22 @@ def decode_layer(*, weights, layer_idx, x_in, residual_in, k_cache, v_cache, cac
     B, S, _ = x_in.shape
     cos = weights["cos"][cache_pos:cache_pos + S]
     sin = weights["sin"][cache_pos:cache_pos + S]
-    q, res = rms_q_matvec_rope(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_q"], cos, sin, eps,
-                               head_dim)
-    rms_kv_matvec_cache(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_k"], cos, sin, k_cache,
-                        cache_pos, eps, True)
+    if f"{p}.q_norm" in weights:
+        # Qwen3-style: unrotated projections stored in the tensor dtype, then per-head RMSNorm + RoPE
+        # (composition of src/machete/kernels/qwen_3_5/sm120.py:2986-2994 on qknorm_rope/ref.py:10-39)
+        q, res = rms_q_matvec_rope(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_q"], None, None, eps,
+                                   head_dim)
+        q = qknorm_rope(q.to(dt).view(B, S, num_q_heads, head_dim), weights[f"{p}.q_norm"], cos, sin, eps)
+        q = q.reshape(B, S, num_q_heads * head_dim).float()
+        rms_kv_matvec_cache(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_k"], cos, sin, k_cache,
+                            cache_pos, eps, False)
+        k_cache[:, cache_pos:cache_pos + S] = qknorm_rope(k_cache[:, cache_pos:cache_pos + S].clone(),
+                                                          weights[f"{p}.k_norm"], cos, sin, eps)
+    else:
+        q, res = rms_q_matvec_rope(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_q"], cos, sin, eps,
+                                   head_dim)
+        rms_kv_matvec_cache(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_k"], cos, sin, k_cache,
+                            cache_pos, eps, True)
     rms_kv_matvec_cache(x_in, residual_in, weights[f"{p}.attn_norm"], weights[f"{p}.W_v"], cos, sin, v_cache,
                         cache_pos, eps, False)
     q4 = rnd(q).view(B, S, num_q_heads, head_dim)

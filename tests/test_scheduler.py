@@ -187,3 +187,43 @@ def test_final_schedule_and_too_many_rows():
     with pytest.raises(ValueError, match="at most 32"):
         Megakernel(MatvecSm100Op.schedule(a=big, weight=torch.zeros(256, 256, dtype=BF), y=torch.zeros_like(big)),
                    config=MegakernelConfig(num_sms=4))
+
+
+def test_qk_norm_nvfp4_layer_schedules_without_deadlock():
+    """The Qwen3-style layer (unrotated Q/K projections, per-head RMSNorm + RoPE on q and on the new
+    cache row, then attention) lowers, keeps the cache-row refinement for the K pass and simulates to
+    completion on a small grid."""
+    from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+    from machete_b200.megakernel import Megakernel, MegakernelConfig, OverlapTileScheduler, simulate
+    from machete_b200.quantization import quantize_nvfp4_weight
+    from tests.util import llama_weights
+
+    BF = torch.bfloat16
+    L, T, hidden, nq, nkv, hd, inter, vocab, B = 2, 96, 512, 4, 2, 128, 1024, 256, 2
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=2)
+    packed = {"cos": w["cos"], "sin": w["sin"], "final_norm": torch.ones(hidden, dtype=BF)}
+    names = [f"layer.{l}.{m}" for l in range(L) for m in ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")]
+    w["lm_head"] = (torch.randn(vocab, hidden) * 0.02).to(BF)
+    for name in names + ["lm_head"]:
+        q = quantize_nvfp4_weight(w[name], group_size=16)
+        packed[f"{name}.packed"], packed[f"{name}.scales"], packed[f"{name}.global_scale"] = (
+            q.packed, q.scales, float(q.global_scale))
+    for l in range(L):
+        for nm in ("attn_norm", "mlp_norm"):
+            packed[f"layer.{l}.{nm}"] = w[f"layer.{l}.{nm}"]
+        packed[f"layer.{l}.q_norm"] = torch.ones(hd, dtype=BF)
+        packed[f"layer.{l}.k_norm"] = torch.ones(hd, dtype=BF)
+    z = lambda *s: torch.zeros(*s, dtype=BF)   # noqa: E731
+    ops, _keep = schedule_decode_model_nvfp4_sm100(
+        batch=B, cache_pos=40, weights=packed, k_cache=[z(B, T, nkv, hd) for _ in range(L)],
+        v_cache=[z(B, T, nkv, hd) for _ in range(L)], x_buffers=[z(B, 1, hidden), z(B, 1, hidden)],
+        residual_buffers=[z(B, 1, hidden), z(B, 1, hidden)], q_buf=z(B, 1, nq * hd), attn_out_buf=z(B, 1, nq * hd),
+        mlp_h_buf=z(B, 1, inter), top_values=torch.zeros(B, 1), top_indices=torch.zeros(B, 1, dtype=torch.int32),
+        num_layers=L, x_in=z(B, 1, hidden), residual_in=z(B, 1, hidden), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8), scheduler=OverlapTileScheduler())
+    qk = [o for o in mk.native_ops if o.name == "QKNormRopeOp"]
+    assert len(qk) == 2 * L
+    assert [o.kind for o in qk] == ["qknorm_rope", "cache_append"] * L
+    assert all(o.writes[-1].axis == 1 and (o.writes[-1].lo, o.writes[-1].hi) == (40, 41) for o in qk[1::2])
+    final = simulate(mk.program)
+    assert (final == mk.program.counter_expected[:len(final)]).all()
