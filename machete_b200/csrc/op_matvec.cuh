@@ -135,6 +135,12 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8], int ty) {
     w[i] = (ty == MK_T_BF16) ? pack_bf16(f[2 * i], f[2 * i + 1]) : pack_f16(f[2 * i], f[2 * i + 1]);
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
+// (0, 1, ..., 7) -> (0, 4, 1, 5, 2, 6, 3, 7)
+__device__ __forceinline__ void pair_order8(float (&f)[8]) {
+  const float t[8] = {f[0], f[4], f[1], f[5], f[2], f[6], f[3], f[7]};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = t[i];
+}
 // Round every element to the storage type `ty` (what a store + reload does).
 __device__ __forceinline__ void round8(float (&f)[8], int ty) {
   uint4 v = pack8(f, ty);
@@ -149,6 +155,7 @@ __device__ __forceinline__ int mv_act_type(const mk_op_t* op) {
 // all consumer threads (tid in [0, kConsumerWarps*32)); the caller places a
 // consumer barrier before and after.  `stage` = fill the buffer,
 // `write_res` = also materialise residual_out = x + residual_in in global.
+template <int WFC>
 __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, bool write_res) {
   const int tid = (c.warp - 1) * 32 + c.lane;
   constexpr int T = kConsumerWarps * 32;
@@ -223,7 +230,10 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     }
   }
   if (!stage) return;
-  if (pro == MK_PRO_NONE && xt == at) return;
+  // NVFP4 consumers pair value i with value i + 4 of every group of eight
+  // (see e2m1x8_scaled): their activations are stored in that order.
+  const bool fp4 = WFC == 0 ? false : mv_is_fp4(op->i[MK_MV_WFMT]);
+  if (pro == MK_PRO_NONE && xt == at && !fp4) return;
   named_bar_sync(kConsumerBarrier, T);
   const float eps = op->f[MK_MV_F_EPS];
   for (int m = 0; m < M; ++m) {
@@ -248,6 +258,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * w[k];
       }
+      if (fp4) pair_order8(f);
       sts128(a, pack8(f, at));
     }
     for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
@@ -262,6 +273,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
       }
+      if (fp4) pair_order8(f);
       sts128(a, pack8(f, at));
     }
   }
@@ -362,15 +374,36 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvR
 }
 
 // ---- consumer ---------------------------------------------------------------------
-// fp4 (e2m1) pair in one byte -> f16x2 (low nibble -> low half).
-__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
-  __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
-  return (uint32_t)h.x | ((uint32_t)h.y << 16);
-}
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
+}
+// Eight e2m1 codes (one 32-bit word, nibble i = value i) -> four f16x2
+// registers, register i = (value i, value i + 4), each times the f16x2 scale.
+// No conversion instruction is involved (cvt.e2m1x2 is several times slower
+// than the integer pipe here): every magnitude code 0..7 maps to an f16 whose
+// low byte is zero, so one byte permute with the codes as its selector looks
+// up four high bytes at once in an 8-byte table held in two registers; a
+// second permute per register places them (selector bit 3 replicates the
+// table byte's clear top bit, i.e. yields the zero low bytes), and the sign
+// bits are moved by one shift per register because the two values of a
+// register sit 16 bits apart in the word.  The staged activations of an
+// NVFP4 op are stored in the matching order (0, 4, 1, 5, 2, 6, 3, 7).
+// (the PTX instruction, not the __byte_perm intrinsic, which drops selector bit 3)
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ void e2m1x8_scaled(uint32_t w, uint32_t scale, uint32_t (&r)[4]) {
+  constexpr uint32_t kLut0 = 0x3E3C3800u, kLut1 = 0x46444240u;   // high bytes of f16 {0, .5, 1, 1.5 | 2, 3, 4, 6}
+  const uint32_t mag = w & 0x77777777u;
+  const uint32_t hlo = prmt(kLut0, kLut1, mag), hhi = prmt(kLut0, kLut1, mag >> 16);
+  r[0] = hmul2(prmt(hlo, hhi, 0x4808u) | ((w << 12) & 0x80008000u), scale);
+  r[1] = hmul2(prmt(hlo, hhi, 0x5818u) | ((w << 8) & 0x80008000u), scale);
+  r[2] = hmul2(prmt(hlo, hhi, 0x6828u) | ((w << 4) & 0x80008000u), scale);
+  r[3] = hmul2(prmt(hlo, hhi, 0x7838u) | (w & 0x80008000u), scale);
 }
 
 // Swizzled address of 16-byte chunk `c` of row `r` (0-7) inside a 1 KB tile.
@@ -574,11 +607,8 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
 #pragma unroll
           for (int q = 0; q < 4; ++q) {  // 8 values (4 bytes) of each row -> two mma k-slots
             uint32_t al[4], ah[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              al[b] = hmul2(e2m1x2_to_f16x2((pl[q] >> (8 * b)) & 0xffu), slo[q >> 1]);
-              ah[b] = hmul2(e2m1x2_to_f16x2((ph[q] >> (8 * b)) & 0xffu), shi[q >> 1]);
-            }
+            e2m1x8_scaled(pl[q], slo[q >> 1], al);
+            e2m1x8_scaled(ph[q], shi[q >> 1], ah);
             const int a = q % NA;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {

@@ -38,6 +38,9 @@ from .sm100 import DecodeLayerSchedule
 from .top1 import schedule_final_top1_sm100
 
 
+_STAGING_BUDGET = 100 * 1024   # bytes of staged activations that still leave six weight pages
+
+
 def _w(weights, key):
     packed, scales = weights[f"{key}.packed"], weights[f"{key}.scales"]
     group = 16 if scales.element_size() == 1 else 32
@@ -119,10 +122,28 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                                               group_size=wg["group_size"], global_scale=wg["global_scale"],
                                               tile_sizes={"S": seq_len, "D": 16}, page_size=page_size, eps=eps)
     wd = _w(weights, f"{pfx}.W_down")
-    ops += MatvecNvfp4Sm120Op.schedule(a=mlp_h_buf, weight_packed=wd["packed"], weight_scales=wd["scales"],
-                                       y=x_part if tp_peers is not None else x_out, group_size=wd["group_size"],
-                                       global_scale=wd["global_scale"], tile_sizes={"S": seq_len, "O": 16},
-                                       page_size=page_size)
+    # The activations of a matvec op are staged whole in shared memory.  When batch x intermediate
+    # does not leave room for the weight pages, the down projection runs as K-blocks accumulated
+    # into x_out, like the reference's bf16 layer (src/machete/kernels/decode_matvec/sm100.py:794-817).
+    k_down, n_blk = int(mlp_h_buf.shape[-1]), 1
+    while batch * seq_len * ((k_down // n_blk) * 2 + 64) > _STAGING_BUDGET or k_down % (n_blk * 2048):
+        n_blk += 1
+        if n_blk > k_down // 2048:
+            raise ValueError(f"batch {batch} x K {k_down}: the staged activations do not fit shared memory")
+    if n_blk > 1 and tp_peers is not None:
+        raise ValueError("tensor-parallel NVFP4 layer: batch x local intermediate size does not fit shared memory")
+    kb, g = k_down // n_blk, wd["group_size"]
+    for blk in range(n_blk):
+        a_blk = mlp_h_buf if n_blk == 1 else mlp_h_buf[:, :, blk * kb: (blk + 1) * kb]
+        wp = wd["packed"] if n_blk == 1 else wd["packed"][:, blk * kb // 2: (blk + 1) * kb // 2]
+        ws = wd["scales"] if n_blk == 1 else wd["scales"][:, blk * kb // g: (blk + 1) * kb // g]
+        extra_keep += [a_blk, wp, ws]
+        common = dict(a=a_blk, weight_packed=wp, weight_scales=ws, group_size=g, global_scale=wd["global_scale"],
+                      tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
+        if blk == 0:
+            ops += MatvecNvfp4Sm120Op.schedule(y=x_part if tp_peers is not None else x_out, **common)
+        else:
+            ops += MatvecResidualNvfp4Sm120Op.schedule(residual_in=x_out, residual_out=x_out, **common)
     if tp_peers is not None:
         ops += AllReduceSm100Op.schedule(peers=tp_peers, x=x_part, y=x_out)
     return DecodeLayerSchedule(ops=ops, attention_config=fa_config,
