@@ -137,7 +137,10 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s0 = 0; s0 < S; s0 += UN) {
-      if (s0 > 0) fetch(s0);
+      if (s0 > 0) {
+        trace(c, TRC_AT_FETCHED, (uint32_t)r0);
+        fetch(s0);
+      }
 #pragma unroll
       for (int k = 0; k < UN; ++k) {
         if (s0 + k >= S) break;
@@ -366,7 +369,11 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
       const uint32_t src = c.pages_u32 + rj.slot * (uint32_t)c.pv->page_bytes;
       float wa[2], wb[2];
+      // all of a participant's records are requested before the first is used
       const uint4 ml = lds128_sync(src + (uint32_t)(ND * 32 + c.lane) * 16u);
+      uint4 v[ND];
+#pragma unroll
+      for (int i = 0; i < ND; ++i) v[i] = lds128_sync(src + (uint32_t)(i * 32 + c.lane) * 16u);
       const float mj[2] = {__uint_as_float(ml.x), __uint_as_float(ml.y)};
       const float lj[2] = {__uint_as_float(ml.z), __uint_as_float(ml.w)};
 #pragma unroll
@@ -380,11 +387,10 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       }
 #pragma unroll
       for (int i = 0; i < ND; ++i) {
-        const uint4 v = lds128_sync(src + (uint32_t)(i * 32 + c.lane) * 16u);
-        o[i][0] = o[i][0] * wa[0] + __uint_as_float(v.x) * wb[0];
-        o[i][1] = o[i][1] * wa[0] + __uint_as_float(v.y) * wb[0];
-        o[i][2] = o[i][2] * wa[1] + __uint_as_float(v.z) * wb[1];
-        o[i][3] = o[i][3] * wa[1] + __uint_as_float(v.w) * wb[1];
+        o[i][0] = o[i][0] * wa[0] + __uint_as_float(v[i].x) * wb[0];
+        o[i][1] = o[i][1] * wa[0] + __uint_as_float(v[i].y) * wb[0];
+        o[i][2] = o[i][2] * wa[1] + __uint_as_float(v[i].z) * wb[1];
+        o[i][3] = o[i][3] * wa[1] + __uint_as_float(v[i].w) * wb[1];
       }
     }
     // hand the parked pages back (generic-proxy writes before the next TMA fill)
@@ -439,6 +445,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       if (last) *arrive = 0;   // ready for the next launch
     }
     last = __shfl_sync(0xffffffffu, last, 0);
+    trace(c, TRC_AT_COUNTED, (uint32_t)last);
     if (last) at_combine_group<D>(c, op, u);
   }
   return true;

@@ -84,7 +84,9 @@ enum {
   TRC_PAGE_CYCLES = 11, // consumer: SM cycles spent computing on the page just handed back (arg = cycles)
   TRC_MV_ARRIVED = 12,  // consumer: split-K partial handed in (arg = slot-set ordinal)
   TRC_MV_REDUCED = 13,  // consumer: partials of the unit summed, epilogue starts (arg = ordinal)
-  TRC_MV_EPILOGUE = 14  // consumer: epilogue stores issued (arg = ordinal)
+  TRC_MV_EPILOGUE = 14, // consumer: epilogue stores issued (arg = ordinal)
+  TRC_AT_COUNTED = 15,  // attention: this split counted in (arg = 1 when it completes its group)
+  TRC_AT_FETCHED = 16   // attention combine: first batch of partials accumulated (arg = row pass)
 };
 
 // Shared-memory control block (first kCtrlBytes of dynamic smem).
