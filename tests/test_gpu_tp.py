@@ -50,11 +50,13 @@ def test_shard_programs_compile_at_llama1b_shapes(world):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_decode_matches_single_gpu_and_oracle():
+@pytest.mark.parametrize("mode", ["bf16", "nvfp4"])
+def test_two_rank_decode_matches_single_gpu_and_oracle(mode):
+    """bf16: the Llama-1B-shape layers; nvfp4: Qwen3-style layers (head dim 128, q/k RMSNorm) with packed weights."""
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_MODE=mode)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)

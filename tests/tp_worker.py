@@ -22,6 +22,71 @@ from tests.util import llama_weights  # noqa: E402
 
 BF = torch.bfloat16
 D = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=32064, layers=2, T=512, pos=300)
+# TP_MODE=nvfp4: Qwen3-style geometry (head dim 128, per-head q/k RMSNorm) with packed weights
+D4 = dict(hidden=2048, inter=4096, nq=16, nkv=4, hd=128, vocab=4128, layers=2, T=256, pos=130)
+MATS = ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")
+
+
+def quantise_model(weights, lm, d):
+    """Quantise every matrix whole (one global scale per matrix); returns (packed dict, dequantised dict)."""
+    from machete_b200.quantization import dequantize_nvfp4_weight, quantize_nvfp4_weight
+
+    g = torch.Generator().manual_seed(11)
+    packed, deq = {"cos": weights["cos"], "sin": weights["sin"]}, dict(weights)
+    names = [f"layer.{l}.{m}" for l in range(d["layers"]) for m in MATS]
+    for name, mat in [(n, weights[n]) for n in names] + [("lm_head", lm)]:
+        q = quantize_nvfp4_weight(mat, group_size=16)
+        packed[f"{name}.packed"], packed[f"{name}.scales"] = q.packed, q.scales
+        packed[f"{name}.global_scale"] = float(q.global_scale)
+        deq[name] = dequantize_nvfp4_weight(q)
+    for l in range(d["layers"]):
+        for nm in ("attn_norm", "mlp_norm"):
+            packed[f"layer.{l}.{nm}"] = weights[f"layer.{l}.{nm}"]
+        for nm in ("q_norm", "k_norm"):
+            deq[f"layer.{l}.{nm}"] = packed[f"layer.{l}.{nm}"] = (1 + torch.randn(d["hd"], generator=g) * 0.1).to(BF)
+    return packed, deq
+
+
+def shard_packed(packed, rank, world):
+    """Megatron split of the packed tensors: rows for Q/K/V/gate/up/LM head, K (bytes and scale columns) for O/down."""
+    out = {}
+    for k, v in packed.items():
+        parts = k.split(".")
+        mat = parts[-2] if parts[-1] in ("packed", "scales") else None
+        if mat in ("W_q", "W_k", "W_v", "W_gate", "W_up", "lm_head"):
+            out[k] = v.chunk(world, dim=0)[rank].contiguous()
+        elif mat in ("W_o", "W_down"):
+            out[k] = v.chunk(world, dim=1)[rank].contiguous()
+        else:
+            out[k] = v
+    return out
+
+
+def build_nvfp4(packed, dev, world, rank, peers):
+    from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+
+    d = D4
+    nq, nkv, inter = d["nq"] // world, d["nkv"] // world, d["inter"] // world
+    g = torch.Generator().manual_seed(7)
+    kfull = [torch.randn(1, d["T"], d["nkv"], d["hd"], generator=g).to(BF) for _ in range(d["layers"])]
+    vfull = [torch.randn(1, d["T"], d["nkv"], d["hd"], generator=g).to(BF) for _ in range(d["layers"])]
+    x_in = torch.randn(1, 1, d["hidden"], generator=g).to(BF)
+    kc = [k.chunk(world, dim=2)[rank].contiguous().to(dev) for k in kfull]
+    vc = [v.chunk(world, dim=2)[rank].contiguous().to(dev) for v in vfull]
+    w = {k: (v.to(dev) if torch.is_tensor(v) else v)
+         for k, v in (shard_packed(packed, rank, world) if world > 1 else packed).items()}
+    w["final_norm"] = torch.ones(d["hidden"], dtype=BF, device=dev)
+    z = lambda *s: torch.zeros(*s, dtype=BF, device=dev)   # noqa: E731
+    tv = torch.zeros(1, 1, device=dev)
+    ti = torch.zeros(1, 1, dtype=torch.int32, device=dev)
+    ops, keep = schedule_decode_model_nvfp4_sm100(
+        batch=1, cache_pos=d["pos"], weights=w, k_cache=kc, v_cache=vc, x_buffers=[z(1, 1, d["hidden"]) for _ in range(2)],
+        residual_buffers=[z(1, 1, d["hidden"]) for _ in range(2)], q_buf=z(1, 1, nq * d["hd"]),
+        attn_out_buf=z(1, 1, nq * d["hd"]), mlp_h_buf=z(1, 1, inter), top_values=tv, top_indices=ti,
+        num_layers=d["layers"], x_in=x_in.to(dev), residual_in=z(1, 1, d["hidden"]), num_q_heads=nq,
+        num_kv_heads=nkv, head_dim=d["hd"], eps=1e-6, tp_peers=peers)
+    mk = Megakernel(ops, config=MegakernelConfig(timeout_ms=2000), device=dev, scheduler=OverlapTileScheduler())
+    return mk, tv, ti, None, None, (kfull, vfull, x_in), (keep, w)
 
 
 def build(weights, lm, dev, world, rank, peers):
@@ -57,12 +122,20 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    d = D
+    nvfp4 = os.environ.get("TP_MODE", "bf16") == "nvfp4"
+    d = D4 if nvfp4 else D
     weights = llama_weights(d["layers"], d["hidden"], d["inter"], d["nq"] * d["hd"], d["nkv"] * d["hd"], d["hd"] // 2,
-                            d["T"], seed=1)
+                            d["T"], seed=1, **({"theta": 1000000.0} if nvfp4 else {}))
     lm = (torch.randn(d["vocab"], d["hidden"], generator=torch.Generator().manual_seed(2)) * 0.02).to(BF)
     peers = PeerBuffers(PeerBuffers.bytes_for_model(1, d["hidden"], d["layers"]) * 2, device=dev)
-    mk, tv, ti, xb, rb, _, _keep = build(weights, lm, dev, world, rank, peers)
+    oracle_kw = {}
+    if nvfp4:
+        packed, deq = quantise_model(weights, lm, d)
+        mk, tv, ti, xb, rb, _, _keep = build_nvfp4(packed, dev, world, rank, peers)
+        weights, lm = deq, deq["lm_head"]        # what the kernel multiplies by, exactly
+        oracle_kw = dict(eps=1e-6, num_q_heads=d["nq"], num_kv_heads=d["nkv"], head_dim=d["hd"])
+    else:
+        mk, tv, ti, xb, rb, _, _keep = build(weights, lm, dev, world, rank, peers)
     mk.compile()
     tokens = []
     for _ in range(3):                       # several launches: epochs advance, inboxes alternate
@@ -74,16 +147,22 @@ def main():
     ok = all(g == gathered[0] for g in gathered) and len(set(tokens)) == 1
     msg = f"rank {rank}: tokens {tokens}"
     if rank == 0:
-        one, tv1, ti1, _, _, (kfull, vfull, x_in), _k2 = build(weights, lm, dev, 1, 0, None)
+        if nvfp4:
+            one, tv1, ti1, _, _, (kfull, vfull, x_in), _k2 = build_nvfp4(packed, dev, 1, 0, None)
+        else:
+            one, tv1, ti1, _, _, (kfull, vfull, x_in), _k2 = build(weights, lm, dev, 1, 0, None)
         one.run()
         want_idx, want_val = int(ti1.item()), float(tv1.item())
         _logits, o_val, o_idx = oracle.decode_model(weights=weights, x=x_in, residual=torch.zeros_like(x_in),
                                                     k_caches=[k.clone() for k in kfull],
                                                     v_caches=[v.clone() for v in vfull], cache_pos=d["pos"],
                                                     final_norm=torch.ones(d["hidden"], dtype=BF), lm_head=lm,
-                                                    num_layers=d["layers"])
+                                                    num_layers=d["layers"], **oracle_kw)
         ok = ok and tokens[0][0] == want_idx and abs(tokens[0][1] - want_val) < 2e-2
-        ok = ok and int(o_idx.flatten()[0]) == tokens[0][0]
+        top2 = _logits.flatten().topk(2).values
+        if float(top2[0] - top2[1]) > 4e-2:      # the greedy token is only comparable when it is not a near-tie
+            ok = ok and int(o_idx.flatten()[0]) == tokens[0][0]
+        ok = ok and abs(tokens[0][1] - float(_logits.flatten()[tokens[0][0]])) <= 4e-2
         msg += f" | single-GPU ({want_idx}, {want_val:.4f}) | oracle ({int(o_idx.flatten()[0])}, {float(o_val.flatten()[0]):.4f})"
     print(msg, flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
