@@ -125,13 +125,25 @@ enum {
   /* MK_OP_ATTN_SPLIT only: 1 = the unit that completes a (batch, kv head,
    * query tile) group also combines the group's splits into o / lse, so no
    * separate MK_OP_ATTN_COMBINE op (and no dependency stage) is needed */
-  MK_AT_FUSE_COMBINE
+  MK_AT_FUSE_COMBINE,
+  /* MK_OP_ATTN_SPLIT only: 1 = q and the cache row MK_AT_NEW_TOK of k hold
+   * UNROTATED projections; the op applies the per-head RMSNorm (weights
+   * MK_AT_P_QNW / MK_AT_P_KNW, MK_AT_F_EPS, result rounded to bf16) and the
+   * split-half rotation (row tables MK_AT_P_COS / MK_AT_P_SIN of D/2 values)
+   * to q as it loads it, and to that k row in shared memory before use, and
+   * writes the finished k row back to the cache.  Replaces the separate
+   * QKNormRopeOp pass of the reference's Qwen schedule
+   * (src/machete/kernels/qwen_3_5/sm120.py:2986-2994; numerics of
+   * qknorm_rope/ref.py:10-39).  Needs M = 1 token per sequence, H/Hkv <= 16. */
+  MK_AT_QKNORM,
+  MK_AT_NEW_TOK
 };
-enum { MK_AT_F_SCALE = 0 };
+enum { MK_AT_F_SCALE = 0, MK_AT_F_EPS };
 enum {
   MK_AT_P_Q = 0, MK_AT_P_K, MK_AT_P_V, MK_AT_P_OPART, MK_AT_P_LSEPART, MK_AT_P_O, MK_AT_P_LSE,
   /* fused combine: int32[B * Hkv * MT] arrival counters, zero before the first launch (the kernel leaves them zero) */
-  MK_AT_P_ARRIVE
+  MK_AT_P_ARRIVE,
+  MK_AT_P_QNW, MK_AT_P_KNW, MK_AT_P_COS, MK_AT_P_SIN   /* MK_AT_QKNORM: bf16, 16-byte aligned */
 };
 enum {
   MK_AT_S_Q_B = 0, MK_AT_S_Q_M, MK_AT_S_Q_H,

@@ -36,9 +36,11 @@ MV_F_EPS, MV_F_GSCALE = range(2)
 (MV_S_WROW, MV_S_X_B, MV_S_X_S, MV_S_RI_B, MV_S_RI_S, MV_S_RO_B, MV_S_RO_S, MV_S_O_B, MV_S_O_S, MV_S_O_H,
  MV_S_ER_B, MV_S_ER_S, MV_S_COS, MV_S_SCROW) = range(14)
 
-(AT_B, AT_M, AT_H, AT_HKV, AT_D, AT_N, AT_SPLITS, AT_CAUSAL, AT_MT, AT_TS, AT_O_T, AT_FUSE_COMBINE) = range(12)
-AT_F_SCALE = 0
-(AT_P_Q, AT_P_K, AT_P_V, AT_P_OPART, AT_P_LSEPART, AT_P_O, AT_P_LSE, AT_P_ARRIVE) = range(8)
+(AT_B, AT_M, AT_H, AT_HKV, AT_D, AT_N, AT_SPLITS, AT_CAUSAL, AT_MT, AT_TS, AT_O_T, AT_FUSE_COMBINE, AT_QKNORM,
+ AT_NEW_TOK) = range(14)
+AT_F_SCALE, AT_F_EPS = 0, 1
+(AT_P_Q, AT_P_K, AT_P_V, AT_P_OPART, AT_P_LSEPART, AT_P_O, AT_P_LSE, AT_P_ARRIVE, AT_P_QNW, AT_P_KNW, AT_P_COS,
+ AT_P_SIN) = range(12)
 (AT_S_Q_B, AT_S_Q_M, AT_S_Q_H, AT_S_K_B, AT_S_K_N, AT_S_K_H, AT_S_V_B, AT_S_V_N, AT_S_V_H, AT_S_O_B,
  AT_S_O_M, AT_S_O_H) = range(12)
 

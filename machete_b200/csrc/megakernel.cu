@@ -656,6 +656,12 @@ static int validate_op(const mk_program_t* p, int idx) {
         if (op.s[k] & 7) return fail(-2, "op %d: q/k/v strides must be multiples of 8 elements", idx);
       if (op.n_units != op.i[MK_AT_B] * HKV * op.i[MK_AT_MT] * op.i[MK_AT_SPLITS])
         return fail(-2, "op %d: bad unit count", idx);
+      if (op.i[MK_AT_QKNORM]) {
+        if (M != 1 || op.i[MK_AT_MT] != 1) return fail(-2, "op %d: fused q/k norm needs one token per sequence and H/Hkv <= 16", idx);
+        if (op.i[MK_AT_NEW_TOK] < 0 || op.i[MK_AT_NEW_TOK] >= op.i[MK_AT_N]) return fail(-2, "op %d: new-token row outside the cache window", idx);
+        for (int k = MK_AT_P_QNW; k <= MK_AT_P_SIN; ++k)
+          if (!op.p[k] || !aligned16(op.p[k])) return fail(-2, "op %d: fused q/k norm tables missing or unaligned", idx);
+      }
     } else {
       if (!op.p[MK_AT_P_O] || (op.p[MK_AT_P_O] & 3)) return fail(-2, "op %d: output pointer missing or unaligned", idx);
       for (int k = MK_AT_S_O_B; k <= MK_AT_S_O_H; ++k)

@@ -168,6 +168,65 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
   }
 }
 
+// ---- fused per-head RMSNorm + rotation of the new k row ------------------------------
+// The row sits unrotated in the K tile of the page (and in the cache).  Lanes
+// below D/16 take chunks l and l + D/16 (values d and d + D/2, the two halves a
+// split-half rotation pairs); the finished row replaces the raw one in shared
+// memory and in the cache.  Arithmetic as the stand-alone op: the normalised
+// value is rounded to bf16 before the rotation, the rotated one once more.
+__device__ __forceinline__ void at_unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = bf16lo(w[i]);
+    f[2 * i + 1] = bf16hi(w[i]);
+  }
+}
+__device__ __forceinline__ uint4 at_pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+template <int D>
+__device__ __forceinline__ void at_fix_k_row(Ctx& c, const mk_op_t* op, const AtUnit& u, uint32_t kpage, int tn, int row,
+                                             int tok) {
+  constexpr int HALF = D / 16;
+  const bool act = c.lane < HALF;
+  const int l = act ? c.lane : 0;
+  const uint32_t a0 = at_chunk_addr(kpage, tn, row, l), a1 = at_chunk_addr(kpage, tn, row, l + HALF);
+  float fa[8], fb[8];
+  at_unpack8(lds128_sync(a0), fa);
+  at_unpack8(lds128_sync(a1), fb);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += fa[i] * fa[i] + fb[i] * fb[i];
+  ss = warp_sum(act ? ss : 0.f);
+  const float rstd = rsqrtf(ss / (float)D + op->f[MK_AT_F_EPS]);
+  const uint16_t* nw = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_KNW]);
+  float wa[8], wb[8], cv[8], sv[8];
+  at_unpack8(*reinterpret_cast<const uint4*>(nw + 8 * l), wa);
+  at_unpack8(*reinterpret_cast<const uint4*>(nw + 8 * l + D / 2), wb);
+  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]) + 8 * l), cv);
+  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]) + 8 * l), sv);
+  float o0[8], o1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float n0 = bf16_round(fa[i] * rstd * wa[i]), n1 = bf16_round(fb[i] * rstd * wb[i]);
+    o0[i] = n0 * cv[i] - n1 * sv[i];
+    o1[i] = n1 * cv[i] + n0 * sv[i];
+  }
+  if (act) {
+    const uint4 p0 = at_pack8(o0), p1 = at_pack8(o1);
+    sts128(a0, p0);
+    sts128(a1, p1);
+    uint16_t* k = reinterpret_cast<uint16_t*>(op->p[MK_AT_P_K]) + u.b * op->s[MK_AT_S_K_B] +
+                  (int64_t)tok * op->s[MK_AT_S_K_N] + u.kvh * op->s[MK_AT_S_K_H];
+    *reinterpret_cast<uint4*>(k + 8 * l) = p0;
+    *reinterpret_cast<uint4*>(k + 8 * l + D / 2) = p1;
+  }
+  // the page goes back to the loader later: order these writes before its next TMA fill
+  fence_proxy_async();
+  __syncwarp();
+}
+
 // ---- consumer ---------------------------------------------------------------------
 // The unit's pages (blocks of tn tokens) are dealt round-robin to `parts`
 // consumer warps; each keeps its own online-softmax state (row max, row sum,
@@ -223,6 +282,50 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       qf[ks][3] = rv[1] ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
     }
   }
+  const bool qknorm = op->i[MK_AT_QKNORM] != 0;
+  if (qknorm) {
+    // q arrives unrotated: per-head RMSNorm (rounded to bf16), then the split-half
+    // rotation.  A row's D values sit in the four lanes of a quad; value d and its
+    // partner d + D/2 are k-steps ks and ks + KS/2 of the same lane.
+    const uint16_t* nw = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_QNW]);
+    const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]);
+    const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]);
+    float ss[2] = {0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float lo = bf16lo(qf[ks][r]), hi = bf16hi(qf[ks][r]);
+        ss[r & 1] += lo * lo + hi * hi;
+      }
+    float rstd[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 1);
+      ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 2);
+      rstd[e] = rsqrtf(ss[e] / (float)D + op->f[MK_AT_F_EPS]);
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS / 2; ++ks) {
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int col = ks * 16 + 2 * t + 8 * h2;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(nw + col);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(nw + col + D / 2);
+        const uint32_t cc = *reinterpret_cast<const uint32_t*>(cs + col);
+        const uint32_t sc2 = *reinterpret_cast<const uint32_t*>(sn + col);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t r0 = qf[ks][e + 2 * h2], r1 = qf[ks + KS / 2][e + 2 * h2];
+          const float n0l = bf16_round(bf16lo(r0) * rstd[e] * bf16lo(w0)), n0h = bf16_round(bf16hi(r0) * rstd[e] * bf16hi(w0));
+          const float n1l = bf16_round(bf16lo(r1) * rstd[e] * bf16lo(w1)), n1h = bf16_round(bf16hi(r1) * rstd[e] * bf16hi(w1));
+          const float cl = bf16lo(cc), ch = bf16hi(cc), sl = bf16lo(sc2), sh = bf16hi(sc2);
+          qf[ks][e + 2 * h2] = pack_bf16(n0l * cl - n1l * sl, n0h * ch - n1h * sh);
+          qf[ks + KS / 2][e + 2 * h2] = pack_bf16(n1l * cl + n0l * sl, n1h * ch + n0h * sh);
+        }
+      }
+    }
+  }
   // causal limit per row: token index <= N - M + m
   int lim[2];
 #pragma unroll
@@ -245,6 +348,10 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
     trace(c, TRC_PAGE_READY, seq + p);
     const uint32_t kpage = page, vpage = page + tile_bytes;
     const int tp0 = u.t_begin + p * tn;
+    if (qknorm) {
+      const int nt = op->i[MK_AT_NEW_TOK];
+      if (nt >= tp0 && nt < tp0 + tn && nt < u.t_end) at_fix_k_row<D>(c, op, u, kpage, tn, nt - tp0, nt);
+    }
     for (int blk = 0; blk * TN < tn; ++blk) {
       const int tb0 = tp0 + blk * TN;       // global token of column 0 of the block
       if (tb0 >= u.t_end) break;

@@ -189,6 +189,7 @@ __device__ __forceinline__ uint32_t f2bf(float f) {  // round-to-nearest-even
   asm("{ .reg .b16 h; cvt.rn.bf16.f32 h, %1; mov.b32 %0, {h, h}; }" : "=r"(u) : "f"(f));
   return u & 0xffffu;
 }
+__device__ __forceinline__ float bf16_round(float f) { return __uint_as_float(f2bf(f) << 16); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t u;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(hi), "f"(lo));

@@ -68,7 +68,13 @@ class FlashDecodingSplitBSHDOp(Op):
 
     @classmethod
     def schedule(cls, tile_sizes=None, causal=False, page_size=DEFAULT_PAGE_SIZE, kv_group_size=1,
-                 num_splits=0, **tensors):
+                 num_splits=0, qk_norm=None, **tensors):
+        """``qk_norm`` (not in the reference's signature): ``dict(q_weight, k_weight, cos, sin, eps,
+        new_token)`` makes the op take UNROTATED q and an unrotated k row ``new_token`` and apply the
+        per-head RMSNorm + split-half rotation itself (the reference schedules a separate
+        ``QKNormRopeOp`` pass for that, src/machete/kernels/qwen_3_5/sm120.py:2986-2994); the finished
+        k row is written back to the cache.  ``cos`` / ``sin`` are the ``(head_dim / 2,)`` table rows
+        of that token."""
         q, k, v = tensors["q"], tensors["k"], tensors["v"]
         if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
             raise ValueError("flash decoding expects BSHD q and KV-cache k/v (rank 4)")
@@ -103,6 +109,21 @@ class FlashDecodingSplitBSHDOp(Op):
             sd["causal"] = 1
         if kv_group_size > 1:
             sd["kv_group_size"] = kv_group_size
+        if qk_norm is not None:
+            if M != 1 or group > 16:
+                raise ValueError("fused q/k norm needs one token per sequence and at most 16 query heads per KV head")
+            for name in ("q_weight", "k_weight"):
+                w = qk_norm[name]
+                if w.dtype != torch.bfloat16 or w.numel() != D or not w.is_contiguous() or w.data_ptr() % 16:
+                    raise ValueError(f"qk_norm[{name!r}] must be a contiguous, 16-byte aligned bf16 ({D},) tensor")
+            for name in ("cos", "sin"):
+                r = qk_norm[name]
+                if r.dtype != torch.bfloat16 or r.numel() != D // 2 or r.stride(-1) != 1 or r.data_ptr() % 16:
+                    raise ValueError(f"qk_norm[{name!r}] must be the bf16 ({D // 2},) table row of the new token, "
+                                     "16-byte aligned (full split-half rotation)")
+            if not 0 <= int(qk_norm["new_token"]) < N_kv:
+                raise ValueError("qk_norm['new_token'] must be a row of the cache window")
+            op.params["qk_norm"] = dict(qk_norm)
         return [op], o_partial, lse_partial
 
     @classmethod
@@ -146,6 +167,13 @@ class FlashDecodingSplitBSHDOp(Op):
         op.reads = [Region(meta_of(q, "q")), Region(meta_of(k, "k"), loader=True), Region(meta_of(v, "v"), loader=True)]
         op.writes = [Region(meta_of(t["o_partial"], "o_partial")), Region(meta_of(t["lse_partial"], "lse_partial"))]
         op.keep = [q, k, v, t["o_partial"], t["lse_partial"]]
+        qkn = sop.params.get("qk_norm")
+        if qkn is not None:
+            op.i[N.AT_QKNORM], op.i[N.AT_NEW_TOK] = 1, int(qkn["new_token"])
+            op.f[N.AT_F_EPS] = float(qkn.get("eps", 1e-6))
+            op.p.update({N.AT_P_QNW: qkn["q_weight"].data_ptr(), N.AT_P_KNW: qkn["k_weight"].data_ptr(),
+                         N.AT_P_COS: qkn["cos"].data_ptr(), N.AT_P_SIN: qkn["sin"].data_ptr()})
+            op.keep += [qkn["q_weight"], qkn["k_weight"], qkn["cos"], qkn["sin"]]
         sp = np.arange(n_units) % S
         tb = np.minimum(N_kv, sp * ts)
         te = np.minimum(N_kv, tb + ts)
@@ -226,10 +254,10 @@ class FlashDecodingCombineBSHDOp(Op):
 
 
 def flash_decoding_schedule(q, k, v, o, num_splits=0, page_size=DEFAULT_PAGE_SIZE, causal=False,
-                            kv_group_size=1):
+                            kv_group_size=1, qk_norm=None):
     """Schedule split-KV flash decoding followed by its combine.
 
-    Returns ``(ops, config)`` like the reference.
+    Returns ``(ops, config)`` like the reference.  ``qk_norm``: see ``FlashDecodingSplitBSHDOp.schedule``.
     """
     if q.ndim != 4 or k.ndim != 4 or v.ndim != 4 or o.ndim != 4:
         raise ValueError("flash_decoding_schedule expects rank-4 BSHD tensors")
@@ -237,6 +265,7 @@ def flash_decoding_schedule(q, k, v, o, num_splits=0, page_size=DEFAULT_PAGE_SIZ
     lse = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
     split_ops, o_partial, lse_partial = FlashDecodingSplitBSHDOp.schedule(
         q=q, k=k, v=v, num_splits=num_splits, page_size=page_size, causal=causal, kv_group_size=kv_group_size,
+        qk_norm=qk_norm,
     )
     combine_ops = FlashDecodingCombineBSHDOp.schedule(o_partial=o_partial, lse_partial=lse_partial, o=o, lse=lse)
     ops = split_ops + combine_ops

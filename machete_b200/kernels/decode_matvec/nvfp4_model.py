@@ -50,8 +50,11 @@ def _w(weights, key):
 def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, weights, k_cache, v_cache, x_in,
                                       residual_in, x_out, residual_out, q_buf, attn_out_buf, mlp_h_buf,
                                       page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0, num_q_heads=32,
-                                      num_kv_heads=8, head_dim=128, tp_peers=None):
-    """One decoder layer with packed weights: ``DecodeLayerSchedule`` like the bf16 layer."""
+                                      num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True):
+    """One decoder layer with packed weights: ``DecodeLayerSchedule`` like the bf16 layer.
+
+    ``fuse_qk_norm``: with q/k norm weights present, let the attention op apply the norm and the
+    rotation itself (one dependency stage less per layer) instead of scheduling ``QKNormRopeOp``."""
     from ..attention.flash_decoding import flash_decoding_schedule
 
     pfx = f"layer.{layer_idx}"
@@ -69,7 +72,7 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                             global_scale=w["global_scale"], tile_sizes={"S": seq_len, "O": 16}, page_size=page_size,
                             eps=eps, head_dim=head_dim, **extra)
 
-    ops, extra_keep = [], []
+    ops, extra_keep, qk_norm = [], [], None
     if f"{pfx}.q_norm" in weights:
         if seq_len != 1 and batch != 1:
             raise ValueError("the QK-norm layer takes one token per sequence or one sequence")
@@ -81,22 +84,27 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                                               page_size=page_size, eps=eps)
         ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)   # unrotated
         ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
-        # row m = (b, s) of the (M, H, D) views takes the table row of token s
-        cos_m, sin_m = cos.repeat(batch, 1), sin.repeat(batch, 1)
-        q_rows = q_buf.view(batch * seq_len, num_q_heads, head_dim)
-        k_rows = k_cache[:, cache_pos] if seq_len == 1 else k_cache[0, cache_pos: cache_pos + seq_len]
-        ops += QKNormRopeOp.schedule(q=q_rows, norm_weight=weights[f"{pfx}.q_norm"], cos=cos_m, sin=sin_m, eps=eps,
-                                     page_size=page_size)
-        ops += QKNormRopeOp.schedule(q=k_rows, norm_weight=weights[f"{pfx}.k_norm"], cos=cos_m, sin=sin_m, eps=eps,
-                                     page_size=page_size, cache_rows=(cache_pos, cache_pos + seq_len))
-        extra_keep += [cos_m, sin_m, q_rows, k_rows]
+        if fuse_qk_norm and seq_len == 1 and num_q_heads // num_kv_heads <= 16 and cos.shape[1] * 2 == head_dim:
+            # the attention op normalises and rotates q and the new k row itself: no extra stage
+            qk_norm = dict(q_weight=weights[f"{pfx}.q_norm"], k_weight=weights[f"{pfx}.k_norm"], cos=cos[0], sin=sin[0],
+                           eps=eps, new_token=cache_pos)
+        else:
+            # row m = (b, s) of the (M, H, D) views takes the table row of token s
+            cos_m, sin_m = cos.repeat(batch, 1), sin.repeat(batch, 1)
+            q_rows = q_buf.view(batch * seq_len, num_q_heads, head_dim)
+            k_rows = k_cache[:, cache_pos] if seq_len == 1 else k_cache[0, cache_pos: cache_pos + seq_len]
+            ops += QKNormRopeOp.schedule(q=q_rows, norm_weight=weights[f"{pfx}.q_norm"], cos=cos_m, sin=sin_m, eps=eps,
+                                         page_size=page_size)
+            ops += QKNormRopeOp.schedule(q=k_rows, norm_weight=weights[f"{pfx}.k_norm"], cos=cos_m, sin=sin_m, eps=eps,
+                                         page_size=page_size, cache_rows=(cache_pos, cache_pos + seq_len))
+            extra_keep += [cos_m, sin_m, q_rows, k_rows]
     else:
         ops += proj(RmsQMatvecRopeNvfp4Sm120Op, "W_q", residual_out=residual_out, q=q_buf)
         ops += proj(RmsKMatvecRopeCacheNvfp4Sm120Op, "W_k", dst_cache=k_window, cache_pos=cache_pos)
         ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
     fa_ops, fa_config = flash_decoding_schedule(q=q_4d, k=k_window, v=v_window, o=o_4d,
                                                 kv_group_size=num_q_heads // num_kv_heads, page_size=page_size,
-                                                num_splits=fa_num_splits)
+                                                num_splits=fa_num_splits, qk_norm=qk_norm)
     ops += fa_ops
     wo = _w(weights, f"{pfx}.W_o")
     if tp_peers is not None:
@@ -126,9 +134,9 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
     # does not leave room for the weight pages, the down projection runs as K-blocks accumulated
     # into x_out, like the reference's bf16 layer (src/machete/kernels/decode_matvec/sm100.py:794-817).
     k_down, n_blk = int(mlp_h_buf.shape[-1]), 1
-    while batch * seq_len * ((k_down // n_blk) * 2 + 64) > _STAGING_BUDGET or k_down % (n_blk * 2048):
+    while batch * seq_len * ((k_down // n_blk) * 2 + 64) > _STAGING_BUDGET or (n_blk > 1 and k_down % (n_blk * 2048)):
         n_blk += 1
-        if n_blk > k_down // 2048:
+        if n_blk > max(1, k_down // 2048):
             raise ValueError(f"batch {batch} x K {k_down}: the staged activations do not fit shared memory")
     if n_blk > 1 and tp_peers is not None:
         raise ValueError("tensor-parallel NVFP4 layer: batch x local intermediate size does not fit shared memory")
@@ -153,7 +161,7 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
 def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_cache, x_buffers, residual_buffers,
                                       q_buf, attn_out_buf, mlp_h_buf, top_values, top_indices, num_layers, x_in,
                                       residual_in, seq_len=1, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0,
-                                      num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None):
+                                      num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True):
     """A full greedy decode step with packed weights: ``(ops, keep_alive)``.
 
     Layer ``i`` reads the pair (``x``, residual) it is given and writes the
@@ -171,7 +179,7 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
             k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=cur_x, residual_in=cur_r,
             x_out=x_buffers[nxt], residual_out=residual_buffers[nxt], q_buf=q_buf, attn_out_buf=attn_out_buf,
             mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps, fa_num_splits=fa_num_splits, num_q_heads=num_q_heads,
-            num_kv_heads=num_kv_heads, head_dim=head_dim, tp_peers=tp_peers)
+            num_kv_heads=num_kv_heads, head_dim=head_dim, tp_peers=tp_peers, fuse_qk_norm=fuse_qk_norm)
         ops += layer.ops
         keep += layer.keep_alive
         cur = nxt

@@ -19,8 +19,11 @@ BF = torch.bfloat16
 MATS = ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")
 
 
-@pytest.mark.parametrize("group,qk_norm,B", [(32, False, 1), (16, False, 1), (16, True, 1), (16, True, 3)])
+@pytest.mark.parametrize("group,qk_norm,B", [(32, False, 1), (16, False, 1), (16, True, 1), (16, True, 3),
+                                             (16, "unfused", 1), (16, "unfused", 2)])
 def test_nvfp4_model_greedy_token(group, qk_norm, B):
+    """qk_norm: False = Llama-style layers; True = q/k RMSNorm folded into the attention op;
+    "unfused" = q/k RMSNorm as a separate QKNormRopeOp pass."""
     L, T, hidden, nq, nkv, hd, inter, vocab = 2, 256, 2048, 16, 4, 128, 4096, 4096 + 32
     cache_pos = 130
     w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=4, theta=1000000.0)
@@ -53,7 +56,8 @@ def test_nvfp4_model_greedy_token(group, qk_norm, B):
         x_buffers=xb, residual_buffers=rb, q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device="cuda"),
         attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device="cuda"),
         mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device="cuda"), top_values=tv, top_indices=ti, num_layers=L,
-        x_in=x0.cuda(), residual_in=r0.cuda(), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd, eps=1e-6)
+        x_in=x0.cuda(), residual_in=r0.cuda(), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd, eps=1e-6,
+        fuse_qk_norm=qk_norm != "unfused")
     mk = Megakernel(ops, scheduler=OverlapTileScheduler())
     mk.run()
     logits, _v, want_i = oracle.decode_model(weights=deq, x=x0, residual=r0, k_caches=[k.clone() for k in kcs],

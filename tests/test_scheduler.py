@@ -189,10 +189,12 @@ def test_final_schedule_and_too_many_rows():
                    config=MegakernelConfig(num_sms=4))
 
 
-def test_qk_norm_nvfp4_layer_schedules_without_deadlock():
+@pytest.mark.parametrize("fuse", [False, True])
+def test_qk_norm_nvfp4_layer_schedules_without_deadlock(fuse):
     """The Qwen3-style layer (unrotated Q/K projections, per-head RMSNorm + RoPE on q and on the new
-    cache row, then attention) lowers, keeps the cache-row refinement for the K pass and simulates to
-    completion on a small grid."""
+    cache row, then attention) lowers and simulates to completion on a small grid: as a separate
+    pass that keeps the cache-row refinement for K, or folded into the attention op."""
+    from machete_b200 import _native as N
     from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
     from machete_b200.megakernel import Megakernel, MegakernelConfig, OverlapTileScheduler, simulate
     from machete_b200.quantization import quantize_nvfp4_weight
@@ -219,11 +221,17 @@ def test_qk_norm_nvfp4_layer_schedules_without_deadlock():
         v_cache=[z(B, T, nkv, hd) for _ in range(L)], x_buffers=[z(B, 1, hidden), z(B, 1, hidden)],
         residual_buffers=[z(B, 1, hidden), z(B, 1, hidden)], q_buf=z(B, 1, nq * hd), attn_out_buf=z(B, 1, nq * hd),
         mlp_h_buf=z(B, 1, inter), top_values=torch.zeros(B, 1), top_indices=torch.zeros(B, 1, dtype=torch.int32),
-        num_layers=L, x_in=z(B, 1, hidden), residual_in=z(B, 1, hidden), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+        num_layers=L, x_in=z(B, 1, hidden), residual_in=z(B, 1, hidden), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd,
+        fuse_qk_norm=fuse)
     mk = Megakernel(ops, config=MegakernelConfig(num_sms=8), scheduler=OverlapTileScheduler())
     qk = [o for o in mk.native_ops if o.name == "QKNormRopeOp"]
-    assert len(qk) == 2 * L
-    assert [o.kind for o in qk] == ["qknorm_rope", "cache_append"] * L
-    assert all(o.writes[-1].axis == 1 and (o.writes[-1].lo, o.writes[-1].hi) == (40, 41) for o in qk[1::2])
+    attn = [o for o in mk.native_ops if o.name == "FlashDecodingFused"]
+    if fuse:
+        assert not qk and len(attn) == L
+        assert all(o.i[N.AT_QKNORM] == 1 and o.i[N.AT_NEW_TOK] == 40 and o.p[N.AT_P_QNW] and o.p[N.AT_P_COS] for o in attn)
+    else:
+        assert len(qk) == 2 * L and not any(o.i.get(N.AT_QKNORM) for o in attn)
+        assert [o.kind for o in qk] == ["qknorm_rope", "cache_append"] * L
+        assert all(o.writes[-1].axis == 1 and (o.writes[-1].lo, o.writes[-1].hi) == (40, 41) for o in qk[1::2])
     final = simulate(mk.program)
     assert (final == mk.program.counter_expected[:len(final)]).all()
