@@ -135,12 +135,6 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8], int ty) {
     w[i] = (ty == MK_T_BF16) ? pack_bf16(f[2 * i], f[2 * i + 1]) : pack_f16(f[2 * i], f[2 * i + 1]);
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
-// (0, 1, ..., 7) -> (0, 1, 4, 5, 2, 6, 3, 7): the order e2m1x8_scaled produces
-__device__ __forceinline__ void pair_order8(float (&f)[8]) {
-  const float t[8] = {f[0], f[1], f[4], f[5], f[2], f[6], f[3], f[7]};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = t[i];
-}
 // Round every element to the storage type `ty` (what a store + reload does).
 __device__ __forceinline__ void round8(float (&f)[8], int ty) {
   uint4 v = pack8(f, ty);
@@ -155,7 +149,6 @@ __device__ __forceinline__ int mv_act_type(const mk_op_t* op) {
 // all consumer threads (tid in [0, kConsumerWarps*32)); the caller places a
 // consumer barrier before and after.  `stage` = fill the buffer,
 // `write_res` = also materialise residual_out = x + residual_in in global.
-template <int WFC>
 __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, bool write_res) {
   const int tid = (c.warp - 1) * 32 + c.lane;
   constexpr int T = kConsumerWarps * 32;
@@ -230,10 +223,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     }
   }
   if (!stage) return;
-  // NVFP4 consumers take the values of every group of eight in the order
-  // e2m1x8_scaled produces them: their activations are stored in that order.
-  const bool fp4 = WFC == 0 ? false : mv_is_fp4(op->i[MK_MV_WFMT]);
-  if (pro == MK_PRO_NONE && xt == at && !fp4) return;
+  if (pro == MK_PRO_NONE && xt == at) return;
   named_bar_sync(kConsumerBarrier, T);
   const float eps = op->f[MK_MV_F_EPS];
   for (int m = 0; m < M; ++m) {
@@ -258,7 +248,6 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * w[k];
       }
-      if (fp4) pair_order8(f);
       sts128(a, pack8(f, at));
     }
     for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
@@ -273,7 +262,6 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
       }
-      if (fp4) pair_order8(f);
       sts128(a, pack8(f, at));
     }
   }
@@ -380,42 +368,27 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   return d;
 }
 // Eight e2m1 codes (one 32-bit word, nibble i = value i) -> four f16x2
-// registers, each times the f16x2 scale: (v0, v1), (v4, v5), (v2, v6), (v3, v7).
-// The staged activations of an NVFP4 op are stored in the matching order.
-//
-// The integer pipe (64 lanes per clock per SM) bounds this loop, so the work
-// is split over two units.  Bytes 0 and 2 go through the conversion
-// instruction (slow, but a unit of its own).  The other four codes are looked
-// up with byte permutes: every magnitude code 0..7 maps to an f16 whose low
-// byte is zero, so one permute with the codes as its selector fetches four
-// high bytes from an 8-byte table held in two registers, one permute per
-// register places two of them (selector bit 3 replicates the table byte's
-// clear top bit, which yields the zero low bytes), and the sign bits move with
-// one shift per register because the two values of a register sit 16 bits
-// apart in the word.
-// (prmt is the PTX instruction: the __byte_perm intrinsic drops selector bit 3.)
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
+// registers (v0,v1) (v2,v3) (v4,v5) (v6,v7), each times the f16x2 scale.  The
+// word is split into its bytes inside the PTX block, so the conversion reads
+// each byte in place: extracting the bytes with shifts and masks first costs
+// more integer-pipe slots than the four conversions themselves (the integer
+// pipe, 64 lanes per clock per SM, is what bounds this loop).
 __device__ __forceinline__ void e2m1x8_scaled(uint32_t w, uint32_t scale, uint32_t (&r)[4]) {
-  constexpr uint32_t kLut0 = 0x3E3C3800u, kLut1 = 0x46444240u;   // high bytes of f16 {0, .5, 1, 1.5 | 2, 3, 4, 6}
-  uint32_t c0, c1;
+  uint32_t c0, c1, c2, c3;
   asm("{\n"
       ".reg .b8 b0, b1, b2, b3;\n"
-      "mov.b32 {b0, b1, b2, b3}, %2;\n"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
-      "cvt.rn.f16x2.e2m1x2 %1, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
       "}"
-      : "=r"(c0), "=r"(c1)
+      : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
       : "r"(w));
-  const uint32_t mag = w & 0x77777777u;
-  const uint32_t h = prmt(kLut0, kLut1, prmt(mag, mag, 0x0031u));   // table bytes of codes 2, 3, 6, 7
   r[0] = hmul2(c0, scale);
   r[1] = hmul2(c1, scale);
-  r[2] = hmul2(prmt(h, h, 0x2808u) | ((w << 4) & 0x80008000u), scale);
-  r[3] = hmul2(prmt(h, h, 0x3818u) | (w & 0x80008000u), scale);
+  r[2] = hmul2(c2, scale);
+  r[3] = hmul2(c3, scale);
 }
 
 // Swizzled address of 16-byte chunk `c` of row `r` (0-7) inside a 1 KB tile.

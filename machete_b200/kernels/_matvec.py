@@ -235,7 +235,6 @@ def lower_matvec(
         tuple(residual_in.stride()) if (pro == N.PRO_ADD_RMS) else (),
         norm_weight.data_ptr() if pro != N.PRO_NONE else 0, pro, float(eps), xt,
         N.T_BF16 if w0.fmt == N.W_BF16 else N.T_FP16,
-        bool(fp4),    # NVFP4 consumers read their activations in a paired order
     )
     return op
 
