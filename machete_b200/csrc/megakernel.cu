@@ -207,7 +207,7 @@ template <int NTC, int WFC>
 __device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t mv_ord) {
   switch (op->opcode) {
     case MK_OP_MATVEC: return mv_dispatch<NTC, WFC>(c, op, ins, seq, mv_ord);
-    case MK_OP_ATTN_SPLIT: return at_dispatch(c, op, ins, seq, mv_ord);
+    case MK_OP_ATTN_SPLIT: return at_dispatch<(WFC == 0 ? 0 : 1)>(c, op, ins, seq, mv_ord);
     case MK_OP_ATTN_COMBINE: at_combine_unit(c, op, ins); break;
     case MK_OP_RMSNORM: ew_rmsnorm(c, op, ins.unit); break;
     case MK_OP_ROPE: ew_rope(c, op, ins.unit); break;
@@ -780,9 +780,11 @@ struct mk_handle_s {
   mk::Layout layout;
 };
 
+// wfc -3 marks an attention op with the fused q/k norm: the kernels built for
+// bf16-only programs carry no code for it, so such a program runs the generic kernel.
 static void classify_op(const mk_op_t& op, int* ntc, int* wfc) {
   *ntc = 0;
-  *wfc = -1;
+  *wfc = (op.opcode == MK_OP_ATTN_SPLIT && op.i[MK_AT_QKNORM]) ? -3 : -1;
   if (op.opcode != MK_OP_MATVEC) return;
   const int m = op.i[MK_MV_M], wf = op.i[MK_MV_WFMT];
   *ntc = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
@@ -802,6 +804,9 @@ static int select_kernel(mk_handle_s* h) {
       mixed = true;
     }
   }
+  if (wfc == 0)
+    for (int w : h->op_wfc)
+      if (w == -3) mixed = true;
   h->kernel = g_variants[0].fn;
   if (!mixed && ntc > 0)
     for (const mk_variant& v : g_variants)

@@ -236,7 +236,8 @@ __device__ __forceinline__ void at_fix_k_row(Ctx& c, const mk_op_t* op, const At
 // releases everybody's parked page.  `ordpart`: bits 0-27 slot-set ordinal,
 // bits 28-31 participant index.  Returns true for the warp that finished the
 // unit.
-template <int D>
+// QMODE 0: the fused q/k norm is compiled out (kernels for bf16-only programs); 1: decided per op.
+template <int D, int QMODE>
 __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
   constexpr int KS = D / 16;   // k-steps of Q·K^T
   constexpr int ND = D / 8;    // n-tiles of the output
@@ -282,7 +283,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       qf[ks][3] = rv[1] ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
     }
   }
-  const bool qknorm = op->i[MK_AT_QKNORM] != 0;
+  const bool qknorm = QMODE == 0 ? false : op->i[MK_AT_QKNORM] != 0;
   if (qknorm) {
     // q arrives unrotated: per-head RMSNorm (rounded to bf16), then the split-half
     // rotation.  A row's D values sit in the four lanes of a quad; value d and its
@@ -290,6 +291,18 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
     const uint16_t* nw = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_QNW]);
     const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]);
     const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]);
+    // the tables do not depend on q: request them first, so that they share q's round trip
+    uint32_t tw0[KS / 2][2], tw1[KS / 2][2], tcs[KS / 2][2], tsn[KS / 2][2];
+#pragma unroll
+    for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int col = ks * 16 + 2 * t + 8 * h2;
+        tw0[ks][h2] = *reinterpret_cast<const uint32_t*>(nw + col);
+        tw1[ks][h2] = *reinterpret_cast<const uint32_t*>(nw + col + D / 2);
+        tcs[ks][h2] = *reinterpret_cast<const uint32_t*>(cs + col);
+        tsn[ks][h2] = *reinterpret_cast<const uint32_t*>(sn + col);
+      }
     float ss[2] = {0.f, 0.f};
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
@@ -309,11 +322,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
     for (int ks = 0; ks < KS / 2; ++ks) {
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
-        const int col = ks * 16 + 2 * t + 8 * h2;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(nw + col);
-        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(nw + col + D / 2);
-        const uint32_t cc = *reinterpret_cast<const uint32_t*>(cs + col);
-        const uint32_t sc2 = *reinterpret_cast<const uint32_t*>(sn + col);
+        const uint32_t w0 = tw0[ks][h2], w1 = tw1[ks][h2], cc = tcs[ks][h2], sc2 = tsn[ks][h2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const uint32_t r0 = qf[ks][e + 2 * h2], r1 = qf[ks + KS / 2][e + 2 * h2];
@@ -558,21 +567,22 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   return true;
 }
 
-template <int D>
+template <int D, int QMODE>
 __device__ __forceinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq, uint32_t ordpart) {
   UnitResult r;
-  r.signal = at_unit<D>(c, op, ins, seq, ordpart);
+  r.signal = at_unit<D, QMODE>(c, op, ins, seq, ordpart);
   r.dead = c.dead;
   r.trace_n = c.trace_n;
   return r;
 }
 
+template <int QMODE>
 __device__ __forceinline__ bool at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
   UnitResult r;
   if (op->i[MK_AT_D] == 64)
-    r = at_unit_call<64>(c, op, ins, seq, ordpart);
+    r = at_unit_call<64, QMODE>(c, op, ins, seq, ordpart);
   else
-    r = at_unit_call<128>(c, op, ins, seq, ordpart);
+    r = at_unit_call<128, QMODE>(c, op, ins, seq, ordpart);
   c.dead = r.dead;
   c.trace_n = r.trace_n;
   return r.signal;
