@@ -100,3 +100,42 @@ def test_linearity_in_v_at_full_size():
         Megakernel(ops).run()
         outs.append(o.float().cpu())
     assert_parity(outs[2], outs[0] + outs[1], "linearity in V", atol=3e-2)
+
+
+@pytest.mark.parametrize("B,H,Hkv,D,Nkv,splits", [
+    (1, 16, 4, 128, 700, 4),     # Qwen3 head layout
+    (3, 8, 2, 64, 130, 0),       # head dim 64, several sequences, default splits
+    (1, 4, 4, 128, 33, 1),       # one split, one query head per KV head: the unit is not shared
+])
+def test_fused_qk_norm(B, H, Hkv, D, Nkv, splits):
+    """The attention op given UNROTATED q and an unrotated last k row applies the per-head RMSNorm and
+    the rotation itself: same output as normalising first (the oracle's qknorm_rope), and the finished
+    k row is what ends up in the cache."""
+    g = torch.Generator().manual_seed(5)
+    q, k, v = qkv(B, 1, H, Hkv, D, Nkv, seed=9)
+    qw = (1 + torch.randn(D, generator=g) * 0.1).to(BF)
+    kw = (1 + torch.randn(D, generator=g) * 0.1).to(BF)
+    ang = torch.rand(D // 2, generator=g) * 6.28
+    cos, sin = torch.cos(ang).to(BF), torch.sin(ang).to(BF)
+    new = Nkv - 1
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.full_like(qd, float("nan"))
+    ops, _ = flash_decoding_schedule(qd, kd, vd, o, num_splits=splits, kv_group_size=H // Hkv,
+                                     qk_norm=dict(q_weight=qw.cuda(), k_weight=kw.cuda(), cos=cos.cuda(), sin=sin.cuda(),
+                                                  eps=1e-6, new_token=new))
+    mk = Megakernel(ops)
+    mk.run()
+    qn = oracle.qknorm_rope(q, qw, cos[None], sin[None], 1e-6)
+    kn = k.clone()
+    kn[:, new:new + 1] = oracle.qknorm_rope(k[:, new:new + 1], kw, cos[None], sin[None], 1e-6)
+    want = oracle.attention_bshd(qn.float(), kn.float(), v.float(), causal=False)
+    assert_parity(o, want, f"fused q/k norm B{B} H{H}/{Hkv} D{D} N{Nkv}")
+    # the cache: the new row finished (bf16 rounding of the rotation: one ulp), every other row untouched
+    got_k = kd.cpu()
+    assert torch.equal(got_k[:, :new], k[:, :new])
+    assert float((got_k[:, new].float() - kn[:, new].float()).abs().max()) <= 2e-2
+    first = o.clone()
+    kd.copy_(k)                 # a decode step rewrites the raw row before every launch
+    mk.run()
+    assert torch.equal(first, o)
+    assert (mk.read_counters() == 0).all()
