@@ -65,11 +65,49 @@ def build_rank_program(rank, world):
     return mk, peers
 
 
-def _worker(rank, world, port, q):
+def build_rank_program_nvfp4(rank, world):
+    """The same with packed NVFP4 weights and Qwen3-style q/k norm (head dim 128): every matrix is
+    quantised whole and the packed bytes / scale columns are split, as a loader of a real checkpoint would."""
+    from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+    from machete_b200.quantization import quantize_nvfp4_weight
+
+    d = dict(DIMS, hd=128, nq=8, nkv=8, hidden=1024, inter=16384, vocab=2048)
+    torch.manual_seed(0)
+    w = llama_weights(d["layers"], d["hidden"], d["inter"], d["nq"] * d["hd"], d["nkv"] * d["hd"], d["hd"] // 2, d["T"])
+    w["lm_head"] = (torch.randn(d["vocab"], d["hidden"]) * 0.02).to(BF)
+    packed = {"cos": w["cos"], "sin": w["sin"], "final_norm": torch.ones(d["hidden"], dtype=BF)}
+    for name in [f"layer.{l}.{m}" for l in range(d["layers"]) for m in
+                 ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")] + ["lm_head"]:
+        qz = quantize_nvfp4_weight(w[name], group_size=16)
+        mat = name.split(".")[-1]
+        dim = 1 if mat in ("W_o", "W_down") else 0
+        packed[f"{name}.packed"] = qz.packed.chunk(world, dim=dim)[rank].contiguous()
+        packed[f"{name}.scales"] = qz.scales.chunk(world, dim=dim)[rank].contiguous()
+        packed[f"{name}.global_scale"] = float(qz.global_scale)
+    for l in range(d["layers"]):
+        for nm in ("attn_norm", "mlp_norm"):
+            packed[f"layer.{l}.{nm}"] = w[f"layer.{l}.{nm}"]
+        packed[f"layer.{l}.q_norm"] = packed[f"layer.{l}.k_norm"] = torch.ones(d["hd"], dtype=BF)
+    nq, nkv, inter = d["nq"] // world, d["nkv"] // world, d["inter"] // world
+    z = lambda *s: torch.zeros(*s, dtype=BF)   # noqa: E731
+    peers = PeerBuffers(PeerBuffers.bytes_for_model(1, d["hidden"], d["layers"]), rank=rank, world_size=world)
+    ops, _ = schedule_decode_model_nvfp4_sm100(
+        batch=1, cache_pos=40, weights=packed, k_cache=[z(1, d["T"], nkv, d["hd"]) for _ in range(d["layers"])],
+        v_cache=[z(1, d["T"], nkv, d["hd"]) for _ in range(d["layers"])],
+        x_buffers=[z(1, 1, d["hidden"]) for _ in range(2)], residual_buffers=[z(1, 1, d["hidden"]) for _ in range(2)],
+        q_buf=z(1, 1, nq * d["hd"]), attn_out_buf=z(1, 1, nq * d["hd"]), mlp_h_buf=z(1, 1, inter),
+        top_values=torch.zeros(1, 1), top_indices=torch.zeros(1, 1, dtype=torch.int32), num_layers=d["layers"],
+        x_in=z(1, 1, d["hidden"]), residual_in=z(1, 1, d["hidden"]), num_q_heads=nq, num_kv_heads=nkv,
+        head_dim=d["hd"], tp_peers=peers)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=16), scheduler=OverlapTileScheduler())
+    return mk, peers
+
+
+def _worker(rank, world, port, q, nvfp4=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        mk, peers = build_rank_program(rank, world)
+        mk, peers = (build_rank_program_nvfp4 if nvfp4 else build_rank_program)(rank, world)
         final = simulate(mk.program)
         ok_counters = bool((final == mk.program.counter_expected[:len(final)]).all())
         ar = [(o.name, int(o.i[N.AR_RANK]), int(o.i[N.AR_P]), int(o.i[N.AR_N]), int(o.i[N.AR_MODE]),
@@ -82,14 +120,14 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 8])
-def test_ranks_agree_on_the_exchange_layout(world):
+@pytest.mark.parametrize("world,nvfp4", [(2, False), (8, False), (4, True)])
+def test_ranks_agree_on_the_exchange_layout(world, nvfp4):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, nvfp4)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted(q.get(timeout=180) for _ in range(world))
