@@ -1,9 +1,9 @@
-"""Tensor-parallel decode on 2 GPUs: the sharded step with the in-kernel all-reduce must
+"""Tensor-parallel decode on 2, 4 and 8 GPUs: the sharded step with the in-kernel all-reduce must
 produce the token of the unsharded step and of the CPU oracle.
 
 Each rank is its own process on its own GPU (kernels that wait on one another
-must never share a GPU), launched with torchrun; the test is skipped on a box
-with fewer than two GPUs.  All device-side waits are bounded, so a failure is
+must never share a GPU), launched with torchrun; a case is skipped on a box
+with fewer GPUs than ranks.  All device-side waits are bounded, so a failure is
 an error code, not a hang.
 """
 
@@ -49,15 +49,17 @@ def test_shard_programs_compile_at_llama1b_shapes(world):
     assert mk.total_tiles > 0
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["bf16", "nvfp4"])
-def test_two_rank_decode_matches_single_gpu_and_oracle(mode):
-    """bf16: the Llama-1B-shape layers; nvfp4: Qwen3-style layers (head dim 128, q/k RMSNorm) with packed weights."""
+@pytest.mark.parametrize("mode,world", [("bf16", 2), ("nvfp4", 2), ("bf16", 4), ("nvfp4", 4), ("bf16", 8)])
+def test_sharded_decode_matches_single_gpu_and_oracle(mode, world):
+    """bf16: the Llama-1B-shape layers; nvfp4: Qwen3-style layers (head dim 128, q/k RMSNorm, 4 KV heads)
+    with packed weights.  One process per GPU; skipped on a box with fewer GPUs than ranks."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_MODE=mode)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     tail = (r.stdout + r.stderr)[-3000:]

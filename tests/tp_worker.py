@@ -1,4 +1,4 @@
-"""One rank of the 2-GPU tensor-parallel parity check (launched by tests/test_gpu_tp.py under torchrun).
+"""One rank of the 2/4/8-GPU tensor-parallel parity check (launched by tests/test_gpu_tp.py under torchrun).
 
 Every rank builds the same seeded model, keeps its Megatron shard, runs the
 sharded decode step with the in-kernel all-reduce, and rank 0 compares the
@@ -21,9 +21,9 @@ from tests.test_tp_host import shard_weights  # noqa: E402
 from tests.util import llama_weights  # noqa: E402
 
 BF = torch.bfloat16
-D = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=32064, layers=2, T=512, pos=300)
+D = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=32256, layers=2, T=512, pos=300)
 # TP_MODE=nvfp4: Qwen3-style geometry (head dim 128, per-head q/k RMSNorm) with packed weights
-D4 = dict(hidden=2048, inter=4096, nq=16, nkv=4, hd=128, vocab=4128, layers=2, T=256, pos=130)
+D4 = dict(hidden=2048, inter=4096, nq=16, nkv=4, hd=128, vocab=4160, layers=2, T=256, pos=130)
 MATS = ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")
 
 
