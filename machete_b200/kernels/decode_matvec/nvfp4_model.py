@@ -38,7 +38,7 @@ from .sm100 import DecodeLayerSchedule
 from .top1 import schedule_final_top1_sm100
 
 
-_STAGING_BUDGET = 100 * 1024   # bytes of staged activations that still leave six weight pages
+from ...megakernel.fusion import STAGING_BUDGET as _STAGING_BUDGET
 
 
 def _w(weights, key):

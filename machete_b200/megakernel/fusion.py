@@ -22,6 +22,11 @@ from .lowering import LowerCtx, NativeOp
 from .ops import ScheduledOp, last_dim_slice_region
 
 
+# Bytes of staged activations (rows x (K * 2 + 64)) that still leave six 18 KB / three 32 KB weight
+# pages in shared memory: a matvec op stages its whole input, so batch x K is bounded by this.
+STAGING_BUDGET = 100 * 1024
+
+
 def _kblock_chain(ops: List[ScheduledOp], start: int):
     """Length of a fusable down-projection K-block chain starting at ``start`` (0 if none)."""
     first = ops[start]
@@ -52,6 +57,9 @@ def _kblock_chain(ops: List[ScheduledOp], start: int):
             break
         n += 1
     if n < 2:
+        return 0, None
+    # the fused op stages all n*k activations of every row at once: keep the K-blocks when that does not fit
+    if int(a0.shape[0]) * int(a0.shape[1]) * (n * k * a0.element_size() + 64) > STAGING_BUDGET:
         return 0, None
     # the slices must tile one contiguous row range of the parents
     if a0.stride(-2) < n * k or w0.stride(0) < n * k:

@@ -56,6 +56,31 @@ def test_config0_llama1b_layer(fuse, sched):
     assert torch.equal(first, x_out)
 
 
+def test_llama1b_layer_at_batch_16_keeps_the_down_projection_in_k_blocks():
+    """Config 3's largest batch at the real layer shape: 16 rows x 8192 intermediate values do not fit the
+    activation staging, so the four K-blocks of the down projection stay separate ops (the oracle adds them
+    in fp32; the chain rounds to bf16 in between, as the reference's does)."""
+    B, S, T, hidden, nq, nkv, hd, inter = 16, 1, 256, 2048, 32, 8, 64, 8192
+    cache_pos = 200
+    w = llama_weights(1, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=3, device="cuda")
+    kc, vc, x_in, res_in, bufs = layer_inputs(B, S, T, hidden, nq, nkv, hd, inter, cache_pos, seed=3)
+    x_out = torch.full((B, S, hidden), float("nan"), dtype=BF, device="cuda")
+    res_out = torch.full((B, S, hidden), float("nan"), dtype=BF, device="cuda")
+    kc_ref, vc_ref = kc.cpu().clone(), vc.cpu().clone()
+    layer = schedule_decode_layer_sm100(layer_idx=0, batch=B, seq_len=S, cache_pos=cache_pos, weights=w, k_cache=kc,
+                                        v_cache=vc, x_in=x_in, residual_in=res_in, x_out=x_out, residual_out=res_out,
+                                        eps=1e-5, **bufs)
+    mk = Megakernel(layer.ops, scheduler=OverlapTileScheduler())
+    mk.run()
+    names = [o.name for o in mk.native_ops]
+    assert "FusedDownProj" not in names and names.count("MatvecResidualSm100Op") == 1 + 3   # O-proj + 3 K-blocks
+    want_x, want_res = oracle.decode_layer(weights=to_cpu(w), layer_idx=0, x_in=x_in.cpu(), residual_in=res_in.cpu(),
+                                           k_cache=kc_ref, v_cache=vc_ref, cache_pos=cache_pos, eps=1e-5)
+    assert_parity(res_out, want_res, "residual stream", atol=4e-2)
+    assert_parity(x_out, want_x, "layer output at batch 16", atol=4e-2)   # three more bf16 roundings than the oracle
+    assert (mk.read_counters() == 0).all() and mk.status()[0] == 0
+
+
 def test_padded_sixteen_row_step_and_batch():
     """The reference's 16-row contract (M % 16 == 0, non-causal over the window) and batch 2."""
     B, S, T, hidden, nq, nkv, hd, inter = 2, 16, 128, 512, 8, 2, 64, 1024
@@ -78,7 +103,7 @@ def test_padded_sixteen_row_step_and_batch():
     assert_parity(res_out, want_res, "residual", atol=4e-2)
 
 
-@pytest.mark.parametrize("B", [1, 4])
+@pytest.mark.parametrize("B", [1, 4, 16])
 def test_multi_layer_model_greedy_token(B):
     """Four layers + final norm + LM head + arg-max; the token index must match exactly."""
     L, T, hidden, nq, nkv, hd, inter, vocab = 4, 512, 1024, 16, 4, 64, 2048, 8192 + 48
