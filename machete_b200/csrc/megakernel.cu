@@ -265,7 +265,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     cached_op = cur.op;
     if (op->opcode == MK_OP_MATVEC) {
       const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-      mv_stage(c, op, need, (cur.flags & MK_EVF_WRITE_RES_OUT) != 0);
+      mv_stage<!(NTC == 1 && WFC == 0)>(c, op, need, (cur.flags & MK_EVF_WRITE_RES_OUT) != 0);
       staged_key = op->act_key;
     }
     named_bar_sync(kConsumerBarrier, T);

@@ -149,6 +149,9 @@ __device__ __forceinline__ int mv_act_type(const mk_op_t* op) {
 // all consumer threads (tid in [0, kConsumerWarps*32)); the caller places a
 // consumer barrier before and after.  `stage` = fill the buffer,
 // `write_res` = also materialise residual_out = x + residual_in in global.
+// GROUPED: rows are fetched four at a time (kernels that serve batches); the kernel of the
+// batch-1 bf16 step keeps the one-row loop alone, whose code placement it is sensitive to.
+template <bool GROUPED>
 __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, bool write_res) {
   const int tid = (c.warp - 1) * 32 + c.lane;
   constexpr int T = kConsumerWarps * 32;
@@ -179,47 +182,87 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     }
   }
 
-  for (int m = 0; m < M; ++m) {
+  auto absorb = [&](int m, uint16_t* wr, float& sum, int ch, uint4 v, uint4 rv) {
+    float f[8];
+    unpack8(v, xt, f);
+    if (add) {
+      float r[8];
+      unpack8(rv, xt, r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += r[i];
+      round8(f, xt);
+      v = pack8(f, xt);
+      if (wr) *reinterpret_cast<uint4*>(wr + ch * 8) = v;
+    }
+    if (stage) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += f[i] * f[i];
+      // keep the (rounded) input in its own type for now; pass 2 rescales
+      sts128(c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u, v);
+    }
+  };
+  auto row_ptrs = [&](int m, const uint16_t*& xr, const uint16_t*& rr, uint16_t*& wr) {
     const int b = m / S, s = m - b * S;
-    const uint16_t* xr = x + b * op->s[MK_MV_S_X_B] + s * op->s[MK_MV_S_X_S];
-    const uint16_t* rr = add ? ri + b * op->s[MK_MV_S_RI_B] + s * op->s[MK_MV_S_RI_S] : nullptr;
-    uint16_t* wr = write_res ? ro + b * op->s[MK_MV_S_RO_B] + s * op->s[MK_MV_S_RO_S] : nullptr;
+    xr = x + b * op->s[MK_MV_S_X_B] + s * op->s[MK_MV_S_X_S];
+    rr = add ? ri + b * op->s[MK_MV_S_RI_B] + s * op->s[MK_MV_S_RI_S] : nullptr;
+    wr = write_res ? ro + b * op->s[MK_MV_S_RO_B] + s * op->s[MK_MV_S_RO_S] : nullptr;
+  };
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  if (!GROUPED || M == 1) {
+   for (int m = 0; m < M; ++m) {
+    const uint16_t *xr, *rr;
+    uint16_t* wr;
+    row_ptrs(m, xr, rr, wr);
     float sum = 0.f;
-    auto absorb = [&](int ch, uint4 v, uint4 rv) {
-      float f[8];
-      unpack8(v, xt, f);
-      if (add) {
-        float r[8];
-        unpack8(rv, xt, r);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] += r[i];
-        round8(f, xt);
-        v = pack8(f, xt);
-        if (wr) *reinterpret_cast<uint4*>(wr + ch * 8) = v;
-      }
-      if (stage) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sum += f[i] * f[i];
-        // keep the (rounded) input in its own type for now; pass 2 rescales
-        sts128(c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u, v);
-      }
-    };
     // two chunks per step, both requested before either is used (the stores to
     // shared memory keep the compiler from hoisting the second load itself)
     for (int ch = tid; ch < chunks; ch += 2 * T) {
       const int ch2 = ch + T;
       const bool two = ch2 < chunks;
-      const uint4 z = make_uint4(0, 0, 0, 0);
       const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
       const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
       const uint4 v2 = two ? *reinterpret_cast<const uint4*>(xr + ch2 * 8) : z;
       const uint4 r2 = (two && add) ? *reinterpret_cast<const uint4*>(rr + ch2 * 8) : z;
-      absorb(ch, v1, r1);
-      if (two) absorb(ch2, v2, r2);
+      absorb(m, wr, sum, ch, v1, r1);
+      if (two) absorb(m, wr, sum, ch2, v2, r2);
     }
     if (stage && pro != MK_PRO_NONE) {
       sum = warp_sum(sum);
       if (c.lane == 0) c.ctrl->red[m * kConsumerWarps + (c.warp - 1)] = sum;
+    }
+   }
+  } else if constexpr (GROUPED) {
+    // Several rows: every row is its own L2 round trip, so four rows' chunks are
+    // requested together before any of them is reduced.
+    constexpr int R = 4;
+    for (int m0 = 0; m0 < M; m0 += R) {
+      const int nr = min(R, M - m0);
+      const uint16_t *xr[R], *rr[R];
+      uint16_t* wr[R];
+      float sum[R];
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        row_ptrs(min(m0 + j, M - 1), xr[j], rr[j], wr[j]);
+        sum[j] = 0.f;
+      }
+      for (int ch = tid; ch < chunks; ch += T) {
+        uint4 v[R], r[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          v[j] = j < nr ? *reinterpret_cast<const uint4*>(xr[j] + ch * 8) : z;
+          r[j] = (j < nr && add) ? *reinterpret_cast<const uint4*>(rr[j] + ch * 8) : z;
+        }
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+          if (j < nr) absorb(m0 + j, wr[j], sum[j], ch, v[j], r[j]);
+      }
+      if (stage && pro != MK_PRO_NONE) {
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          const float t = warp_sum(sum[j]);
+          if (c.lane == 0 && j < nr) c.ctrl->red[(m0 + j) * kConsumerWarps + (c.warp - 1)] = t;
+        }
+      }
     }
   }
   if (!stage) return;
