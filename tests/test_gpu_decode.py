@@ -163,3 +163,38 @@ def test_logits_path_matches_top1():
     want = oracle.final_rms_lm_head(x, fn, lm, 1e-5, residual_in=r)
     assert_parity(logits, want, "logits")
     assert torch.equal(ro.cpu(), (x.float() + r.float()).to(BF))
+
+
+def test_run_is_capturable_in_a_cuda_graph():
+    """`Megakernel.run(sync=False)` issues one kernel launch and nothing else, so a step with its
+    host-to-device and device-to-host copies can be replayed as one CUDA graph (what `bench.py`'s
+    end-to-end leg does): new input in the pinned buffer, replay, read the logits."""
+    B, hidden, vocab = 1, 512, 1000
+    g = torch.Generator().manual_seed(12)
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF)
+    lm = (torch.randn(vocab, hidden, generator=g) * 0.02).to(BF)
+    x_dev = torch.zeros(B, 1, hidden, dtype=BF, device="cuda")
+    r_dev = torch.zeros(B, 1, hidden, dtype=BF, device="cuda")
+    logits = torch.empty(B, 1, vocab, dtype=BF, device="cuda")
+    ro = torch.empty(B, 1, hidden, dtype=BF, device="cuda")
+    host_x = torch.zeros(B, 1, hidden, dtype=BF).pin_memory()
+    host_logits = torch.zeros(B, 1, vocab, dtype=BF).pin_memory()
+    ops = schedule_final_sm100(x=x_dev, residual_in=r_dev, residual_out=ro, final_norm=fn.cuda(), lm_head=lm.cuda(),
+                               logits=logits, seq_len=1)
+    mk = Megakernel(ops)
+    mk.run()                                   # compiles outside the capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        x_dev.copy_(host_x, non_blocking=True)
+        mk.run(sync=False, validate=False)
+        host_logits.copy_(logits, non_blocking=True)
+    for seed in (1, 2):
+        x = torch.randn(B, 1, hidden, generator=torch.Generator().manual_seed(seed)).to(BF)
+        host_x.copy_(x)
+        graph.replay()
+        torch.cuda.synchronize()
+        mk.wait()
+        want = oracle.final_rms_lm_head(x, fn, lm, 1e-5, residual_in=torch.zeros_like(x))
+        assert_parity(host_logits, want, f"logits of replay {seed}")
