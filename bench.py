@@ -307,7 +307,11 @@ def main():
                 raise ValueError(f"heads / intermediate / vocabulary do not divide by {world}")
             from machete_b200.megakernel.peer import PeerBuffers
 
-            peers = PeerBuffers(PeerBuffers.bytes_for_model(B, cfg["hidden"], args.layers), device=dev)
+            # one exchange after the O projection, one per K-block of the down projection (a packed
+            # local K above 2048 that is not a multiple of 2048 runs as 2048-blocks)
+            k_loc = cfg["inter"] // world
+            blocks = -(-k_loc // 2048) if (args.weights == "nvfp4" and k_loc > 2048 and k_loc % 2048) else 1
+            peers = PeerBuffers(PeerBuffers.bytes_for_model(B, cfg["hidden"], args.layers, 1 + blocks), device=dev)
         except Exception as exc:  # noqa: BLE001
             ok, tp_note = 0, f"tp unavailable: {type(exc).__name__}: {exc}"[:200]
         flag = torch.tensor([ok], device=dev)

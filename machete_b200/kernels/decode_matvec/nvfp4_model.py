@@ -138,22 +138,38 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
         n_blk += 1
         if n_blk > max(1, k_down // 2048):
             raise ValueError(f"batch {batch} x K {k_down}: the staged activations do not fit shared memory")
-    if n_blk > 1 and tp_peers is not None:
-        raise ValueError("tensor-parallel NVFP4 layer: batch x local intermediate size does not fit shared memory")
-    kb, g = k_down // n_blk, wd["group_size"]
-    for blk in range(n_blk):
-        a_blk = mlp_h_buf if n_blk == 1 else mlp_h_buf[:, :, blk * kb: (blk + 1) * kb]
-        wp = wd["packed"] if n_blk == 1 else wd["packed"][:, blk * kb // 2: (blk + 1) * kb // 2]
-        ws = wd["scales"] if n_blk == 1 else wd["scales"][:, blk * kb // g: (blk + 1) * kb // g]
-        extra_keep += [a_blk, wp, ws]
-        common = dict(a=a_blk, weight_packed=wp, weight_scales=ws, group_size=g, global_scale=wd["global_scale"],
-                      tile_sizes={"S": seq_len, "O": 16}, page_size=page_size)
-        if blk == 0:
-            ops += MatvecNvfp4Sm120Op.schedule(y=x_part if tp_peers is not None else x_out, **common)
-        else:
-            ops += MatvecResidualNvfp4Sm120Op.schedule(residual_in=x_out, residual_out=x_out, **common)
+    g = wd["group_size"]
+
+    def down_block(lo, hi, **out):
+        a_blk = mlp_h_buf if (lo, hi) == (0, k_down) else mlp_h_buf[:, :, lo:hi]
+        wp = wd["packed"] if (lo, hi) == (0, k_down) else wd["packed"][:, lo // 2: hi // 2]
+        ws = wd["scales"] if (lo, hi) == (0, k_down) else wd["scales"][:, lo // g: hi // g]
+        extra_keep.extend([a_blk, wp, ws])
+        cls = MatvecResidualNvfp4Sm120Op if "residual_in" in out else MatvecNvfp4Sm120Op
+        return cls.schedule(a=a_blk, weight_packed=wp, weight_scales=ws, group_size=g, global_scale=wd["global_scale"],
+                            tile_sizes={"S": seq_len, "O": 16}, page_size=page_size, **out)
+
     if tp_peers is not None:
-        ops += AllReduceSm100Op.schedule(peers=tp_peers, x=x_part, y=x_out)
+        # this rank's K range; a packed K above 2048 must be a multiple of 2048 (one scale tile row per
+        # page), so e.g. 12 288 / 4 = 3072 runs as 2048 + 1024, each block with its own exchange:
+        # x_out = sum(block 0), then x_out = sum(block 1) + x_out
+        if n_blk > 1:
+            raise ValueError("tensor-parallel NVFP4 layer: batch x local intermediate size does not fit shared memory")
+        edges = [0, k_down] if (k_down <= 2048 or k_down % 2048 == 0) else \
+            list(range(0, k_down, 2048)) + [k_down]
+        for i, (lo, hi) in enumerate(zip(edges[:-1], edges[1:])):
+            part = x_part if i == 0 else torch.empty_like(x_part)
+            extra_keep.append(part)
+            ops += down_block(lo, hi, y=part)
+            ops += AllReduceSm100Op.schedule(peers=tp_peers, x=part, y=x_out,
+                                             **({"residual_in": x_out} if i else {}))
+    else:
+        kb = k_down // n_blk
+        for blk in range(n_blk):
+            if blk == 0:
+                ops += down_block(0, kb, y=x_out)
+            else:
+                ops += down_block(blk * kb, (blk + 1) * kb, residual_in=x_out, residual_out=x_out)
     return DecodeLayerSchedule(ops=ops, attention_config=fa_config,
                                keep_alive=[cos, sin, q_4d, k_window, v_window, o_4d, *extra_keep])
 

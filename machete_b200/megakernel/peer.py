@@ -86,7 +86,8 @@ class PeerBuffers:
         return (self._generation << 22) & 0x7FFFFFFF
 
     @staticmethod
-    def bytes_for_model(batch_rows: int, hidden: int, num_layers: int) -> int:
-        """Enough for two sum all-reduces per layer and the final key exchange."""
+    def bytes_for_model(batch_rows: int, hidden: int, num_layers: int, sums_per_layer: int = 2) -> int:
+        """Enough for ``sums_per_layer`` sum all-reduces per layer (two: after the O and the down
+        projection; more when the down projection runs as K-blocks) and the final key exchange."""
         per_sum = 2 * N.AR_MAX_RANKS * batch_rows * hidden * 8 + N.AR_MAX_RANKS * ((batch_rows * hidden + 255) // 256) * 4
-        return (2 * num_layers + 2) * (per_sum + 1024) + 65536
+        return (sums_per_layer * num_layers + 2) * (per_sum + 1024) + 65536

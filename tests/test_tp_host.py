@@ -71,7 +71,7 @@ def build_rank_program_nvfp4(rank, world):
     from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
     from machete_b200.quantization import quantize_nvfp4_weight
 
-    d = dict(DIMS, hd=128, nq=8, nkv=8, hidden=1024, inter=16384, vocab=2048)
+    d = dict(DIMS, hd=128, nq=8, nkv=8, hidden=1024, inter=12288, vocab=2048)   # 12288 / 4 ranks = 3072 = 2048 + 1024
     torch.manual_seed(0)
     w = llama_weights(d["layers"], d["hidden"], d["inter"], d["nq"] * d["hd"], d["nkv"] * d["hd"], d["hd"] // 2, d["T"])
     w["lm_head"] = (torch.randn(d["vocab"], d["hidden"]) * 0.02).to(BF)
@@ -90,7 +90,7 @@ def build_rank_program_nvfp4(rank, world):
         packed[f"layer.{l}.q_norm"] = packed[f"layer.{l}.k_norm"] = torch.ones(d["hd"], dtype=BF)
     nq, nkv, inter = d["nq"] // world, d["nkv"] // world, d["inter"] // world
     z = lambda *s: torch.zeros(*s, dtype=BF)   # noqa: E731
-    peers = PeerBuffers(PeerBuffers.bytes_for_model(1, d["hidden"], d["layers"]), rank=rank, world_size=world)
+    peers = PeerBuffers(PeerBuffers.bytes_for_model(1, d["hidden"], d["layers"], 3), rank=rank, world_size=world)
     ops, _ = schedule_decode_model_nvfp4_sm100(
         batch=1, cache_pos=40, weights=packed, k_cache=[z(1, d["T"], nkv, d["hd"]) for _ in range(d["layers"])],
         v_cache=[z(1, d["T"], nkv, d["hd"]) for _ in range(d["layers"])],
@@ -137,7 +137,10 @@ def test_ranks_agree_on_the_exchange_layout(world, nvfp4):
     for rank, ok_counters, gathered, n_ops in results:
         assert ok_counters                                   # every counter reaches its expected value: no lost signal
         a = gathered[0]
-        assert all(len(g) == 2 * DIMS["layers"] + 1 for g in gathered)   # O-proj + down per layer, the key exchange
+        # O-proj + down per layer and the key exchange; the NVFP4 case splits its local down-projection
+        # K range of 3072 into 2048 + 1024, each with its own exchange
+        per_layer = 3 if nvfp4 else 2
+        assert all(len(g) == per_layer * DIMS["layers"] + 1 for g in gathered)
         for r, g in enumerate(gathered):
             for ra, rg in zip(a, g):
                 assert ra[0] == rg[0] and ra[2:] == rg[2:]    # same op, world, size, mode, offsets, epoch base, units
