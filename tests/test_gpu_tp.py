@@ -54,7 +54,7 @@ def test_shard_programs_compile_at_llama1b_shapes(world):
 def test_sharded_decode_matches_single_gpu_and_oracle(mode, world):
     """bf16: the Llama-1B-shape layers; nvfp4: Qwen3-style layers (head dim 128, q/k RMSNorm, 4 KV heads)
     with packed weights; nvfp4_split: an intermediate size whose per-rank K range (3072) has to run as
-    2048 + 1024 with an exchange each (nvfp4 at 4 ranks takes that path too).  One process per GPU;
+    2048 + 1024 with an exchange each.  One process per GPU;
     skipped on a box with fewer GPUs than ranks."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

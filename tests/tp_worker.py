@@ -23,8 +23,8 @@ from tests.util import llama_weights  # noqa: E402
 BF = torch.bfloat16
 D = dict(hidden=2048, inter=8192, nq=32, nkv=8, hd=64, vocab=32256, layers=2, T=512, pos=300)
 # TP_MODE=nvfp4: Qwen3-style geometry (head dim 128, per-head q/k RMSNorm) with packed weights
-D4 = dict(hidden=2048, inter=12288, nq=16, nkv=4, hd=128, vocab=4160, layers=2, T=256, pos=130)   # 4 ranks: K 3072 = 2048 + 1024
-D4["inter"] = int(os.environ.get("TP_INTER", D4["inter"]))   # 6144 makes 2 ranks take the split-K-range path too
+D4 = dict(hidden=2048, inter=4096, nq=16, nkv=4, hd=128, vocab=4160, layers=2, T=256, pos=130)
+D4["inter"] = int(os.environ.get("TP_INTER", D4["inter"]))   # 6144: two ranks get a K range of 3072 = 2048 + 1024 (two blocks, two exchanges)
 MATS = ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")
 
 
