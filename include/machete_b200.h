@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define MK_ABI_VERSION 3
+#define MK_ABI_VERSION 4
 
 /* ---- opcodes ------------------------------------------------------------ */
 enum {
@@ -198,22 +198,29 @@ typedef struct mk_instr {
   int32_t n_lwaits;       /* loader-side waits (before the unit's loads)     */
   int32_t lwait_off;
   int32_t n_pages;        /* ring pages the unit consumes                    */
-  /* Loader fast path, filled in by mk_create (callers leave these zero): all
-   * the loader warp needs to issue the unit's pages, so that it never reads
-   * the op table on its critical path. */
+  /* Fast path, filled in by mk_create (callers leave these zero): all the
+   * loader warp needs to issue the unit's pages, and the row / output
+   * offsets the finishing consumer needs, so that neither reads the op table
+   * or divides on its critical path. */
   uint64_t ld_maps;       /* device address of the op's 4 tensor maps        */
-  int32_t ld_row_a;       /* first weight row of virtual rows 0-7            */
-  int32_t ld_row_b;       /* first weight row of virtual rows 8-15           */
   int32_t ld_tiles;       /* 128-byte K-tiles per page                       */
   int32_t ld_flags;       /* MK_LDF_*                                        */
-  int32_t reserved[2];
+  int32_t ld_row_a;       /* first weight row of virtual rows 0-7            */
+  int32_t ld_row_b;       /* first weight row of virtual rows 8-15           */
+  /* matvec: element offset of rows a / b inside one activation row's output
+   * (head * head stride + dim); attention: split index / query tile */
+  int32_t out_off_a;
+  int32_t out_off_b;
 } mk_instr_t;
 
-/* bits 8-11 of ld_flags: consumer warps sharing the unit (from MK_MV_SPLIT) */
+/* bits 8-11 of ld_flags: consumer warps sharing the unit (from MK_MV_SPLIT);
+ * bits 12-23: matvec RoPE units, index of the unit's 8-value chunk inside
+ * the rotary half (dim = 8 * chunk + row). */
 /* MK_LDF_ATTN marks a split-KV attention unit: ld_maps holds the K and V cache
  * maps, ld_row_a the first token, ld_row_b = kv head | batch << 16, ld_tiles
  * the tokens per page; MK_LDF_D128 = head dim 128 (two 64-wide sub-tiles). */
-enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_ATTN = 4, MK_LDF_D128 = 8, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15 };
+enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_ATTN = 4, MK_LDF_D128 = 8, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15,
+       MK_LDF_CHUNK_SHIFT = 12, MK_LDF_CHUNK_MASK = 4095 };
 
 /* Op-entry event: before a CTA executes instruction `pos` of its list, all
  * of its consumer warps meet, wait for the listed counters and stage the
@@ -225,6 +232,11 @@ typedef struct mk_event {
   int32_t wait_off;
   int32_t flags;          /* MK_EVF_* */
   int32_t bulk_units;     /* with MK_EVF_BULK_SIGNAL: units of `op` on this CTA */
+  /* filled in by mk_create (callers leave them zero): the first four
+   * (counter, expected) pairs of the wait list, so that the poll that opens a
+   * dependency stage starts without a table read */
+  int32_t w_counter[4];
+  int32_t w_expected[4];
   int32_t reserved[2];
 } mk_event_t;
 

@@ -15,7 +15,7 @@ import numpy as np
 
 from . import build as _build
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
 
 # ---- enums (keep in sync with include/machete_b200.h) ------------------------
@@ -83,16 +83,18 @@ INSTR_DTYPE = np.dtype([
     ("op", "<i4"), ("unit", "<i4"), ("signal", "<i4"), ("n_waits", "<i4"), ("wait_off", "<i4"),
     ("n_lwaits", "<i4"), ("lwait_off", "<i4"), ("n_pages", "<i4"),
     # loader fast path: left zero here, filled in by mk_create
-    ("ld_maps", "<u8"), ("ld_row_a", "<i4"), ("ld_row_b", "<i4"), ("ld_tiles", "<i4"), ("ld_flags", "<i4"),
-    ("ld_reserved", "<i4", (2,)),
+    ("ld_maps", "<u8"), ("ld_tiles", "<i4"), ("ld_flags", "<i4"), ("ld_row_a", "<i4"), ("ld_row_b", "<i4"),
+    ("out_off_a", "<i4"), ("out_off_b", "<i4"),
 ])
 EVENT_DTYPE = np.dtype([
     ("pos", "<i4"), ("op", "<i4"), ("n_waits", "<i4"), ("wait_off", "<i4"), ("flags", "<i4"),
-    ("bulk_units", "<i4"), ("reserved", "<i4", (2,)),
+    ("bulk_units", "<i4"),
+    # inline copy of the first wait pairs: left zero here, filled in by mk_create
+    ("w_counter", "<i4", (4,)), ("w_expected", "<i4", (4,)), ("reserved", "<i4", (2,)),
 ])
 WAIT_DTYPE = np.dtype([("counter", "<i4"), ("expected", "<i4")])
 assert OP_DTYPE.itemsize == 16 + 96 + 16 + 128 + 128
-assert INSTR_DTYPE.itemsize == 64 and EVENT_DTYPE.itemsize == 32 and WAIT_DTYPE.itemsize == 8
+assert INSTR_DTYPE.itemsize == 64 and EVENT_DTYPE.itemsize == 64 and WAIT_DTYPE.itemsize == 8
 
 
 class Program(C.Structure):
@@ -118,7 +120,11 @@ _lock = threading.Lock()
 
 
 def lib_path() -> Path:
-    return _build.LIB_PATH
+    """The library file; ``MACHETE_B200_LIB`` names another build of it (same ABI)."""
+    import os
+
+    override = os.environ.get("MACHETE_B200_LIB")
+    return Path(override) if override else _build.LIB_PATH
 
 
 def lib() -> C.CDLL:

@@ -26,12 +26,12 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "--use_fast_math",
     "-Xcompiler", "-fPIC",
-    "-shared",
 ]
 
 
 def _sources() -> list[Path]:
-    return [CSRC / "megakernel.cu"]
+    """The host side plus one translation unit per group of kernel variants."""
+    return [CSRC / "megakernel.cu"] + sorted(CSRC.glob("variants_*.cu"))
 
 
 def _deps() -> list[Path]:
@@ -47,23 +47,44 @@ def is_stale() -> bool:
     return any(p.stat().st_mtime > built for p in _deps() if p.exists())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, defines: tuple = (), out: Path | None = None) -> Path:
+    """Compile the library if it is missing or older than its sources.
+
+    The translation units are compiled side by side (one ``nvcc -c`` each) and
+    linked into one shared object; objects go to a scratch directory.
+    """
+    target = Path(out) if out else LIB_PATH
+    if not force and out is None and not is_stale():
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: cannot build libmachete_b200.so")
-    cmd = [nvcc, *NVCC_FLAGS]
+    import tempfile
+    from concurrent.futures import ThreadPoolExecutor
+
+    flags = [*NVCC_FLAGS, *[f"-D{d}" for d in defines]]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(s) for s in _sources()] + ["-o", str(LIB_PATH)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
-    if verbose:
-        sys.stderr.write(proc.stderr)
-    return LIB_PATH
+        flags += ["-Xptxas", "-v"]
+    with tempfile.TemporaryDirectory(prefix="machete_b200_build_") as tmp:
+        def compile_one(src: Path):
+            obj = Path(tmp) / (src.stem + ".o")
+            cmd = [nvcc, *flags, "-c", str(src), "-o", str(obj)]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+            return obj, proc.stderr
+
+        with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+            results = list(pool.map(compile_one, _sources()))
+        if verbose:
+            for _, err in results:
+                sys.stderr.write(err)
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
+               *[str(o) for o, _ in results], "-o", str(target)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"link failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    return target
 
 
 if __name__ == "__main__":

@@ -24,380 +24,9 @@
 #include <string>
 #include <vector>
 
-#include "op_allreduce.cuh"
-#include "op_attn.cuh"
-#include "op_elementwise.cuh"
-#include "op_matvec.cuh"
+#include "kernel.cuh"
 
 namespace mk {
-
-// ---------------------------------------------------------------- device side
-__device__ __forceinline__ mk_instr_t bcast_instr(const mk_instr_t& mine, int src) {
-  mk_instr_t r;
-  r.op = __shfl_sync(0xffffffffu, mine.op, src);
-  r.unit = __shfl_sync(0xffffffffu, mine.unit, src);
-  r.signal = __shfl_sync(0xffffffffu, mine.signal, src);
-  r.n_waits = __shfl_sync(0xffffffffu, mine.n_waits, src);
-  r.wait_off = __shfl_sync(0xffffffffu, mine.wait_off, src);
-  r.n_lwaits = __shfl_sync(0xffffffffu, mine.n_lwaits, src);
-  r.lwait_off = __shfl_sync(0xffffffffu, mine.lwait_off, src);
-  r.n_pages = __shfl_sync(0xffffffffu, mine.n_pages, src);
-  r.ld_flags = __shfl_sync(0xffffffffu, mine.ld_flags, src);
-  return r;
-}
-
-// Consumers need the first half of an instruction record, and whether it is a
-// matvec unit (ld_flags is reused in registers for that: bit 31).
-constexpr int kInsMatvec = (int)0x80000000;
-__device__ __forceinline__ mk_instr_t load_instr(const mk_instr_t* p) {
-  const int4* q = reinterpret_cast<const int4*>(p);
-  const int4 a = q[0], b = q[1], c2 = q[2], d = q[3];
-  mk_instr_t r;
-  r.op = a.x; r.unit = a.y; r.signal = a.z; r.n_waits = a.w;
-  r.wait_off = b.x; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
-  r.ld_maps = 0; r.ld_row_a = 0; r.ld_row_b = 0; r.ld_tiles = 0;
-  r.ld_flags = (c2.x | c2.y) != 0 ? (d.y | kInsMatvec) : 0;
-  return r;
-}
-
-// The loader's view: the second half carries everything needed to issue the
-// unit's tiled-TMA pages (tensor-map address, first rows, tiles per page).
-struct LoaderInstr {
-  int op, unit, n_lwaits, lwait_off, n_pages;
-  uint64_t maps;
-  int row_a, row_b, tiles, flags;
-};
-__device__ __forceinline__ LoaderInstr load_loader_instr(const mk_instr_t* p) {
-  const int4* q = reinterpret_cast<const int4*>(p);
-  const int4 a = q[0], b = q[1], c2 = q[2], d = q[3];
-  LoaderInstr r;
-  r.op = a.x; r.unit = a.y; r.n_lwaits = b.y; r.lwait_off = b.z; r.n_pages = b.w;
-  r.maps = (uint64_t)(uint32_t)c2.x | ((uint64_t)(uint32_t)c2.y << 32);
-  r.row_a = c2.z; r.row_b = c2.w; r.tiles = d.x; r.flags = d.y;
-  return r;
-}
-__device__ __forceinline__ LoaderInstr bcast_loader_instr(const LoaderInstr& m, int src) {
-  LoaderInstr r;
-  r.op = __shfl_sync(0xffffffffu, m.op, src);
-  r.unit = __shfl_sync(0xffffffffu, m.unit, src);
-  r.n_lwaits = __shfl_sync(0xffffffffu, m.n_lwaits, src);
-  r.lwait_off = __shfl_sync(0xffffffffu, m.lwait_off, src);
-  r.n_pages = __shfl_sync(0xffffffffu, m.n_pages, src);
-  r.maps = __shfl_sync(0xffffffffu, m.maps, src);
-  r.row_a = __shfl_sync(0xffffffffu, m.row_a, src);
-  r.row_b = __shfl_sync(0xffffffffu, m.row_b, src);
-  r.tiles = __shfl_sync(0xffffffffu, m.tiles, src);
-  r.flags = __shfl_sync(0xffffffffu, m.flags, src);
-  return r;
-}
-
-__device__ void loader_loop(Ctx& c, int ibeg, int iend) {
-  const ProgramView& pv = *c.pv;
-  const int NP = pv.n_pages;
-  const uint64_t policy = l2_evict_first_policy();
-  uint32_t seq = 0;
-  RingPos rp;
-  rp.slot = 0;
-  rp.k = 0;
-  for (int base = ibeg; base < iend && !c.dead; base += 32) {
-    const int n = min(32, iend - base);
-    LoaderInstr mine;
-    memset(&mine, 0, sizeof(mine));
-    if (c.lane < n) mine = load_loader_instr(pv.instrs + base + c.lane);
-    for (int i = 0; i < n && !c.dead; ++i) {
-      const LoaderInstr ins = bcast_loader_instr(mine, i);
-      c.instr_idx = base + i;
-      if (ins.n_pages == 0) continue;
-      if (ins.n_lwaits > 0) {
-        if (!wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
-        trace(c, TRC_LWAIT_DONE, base + i);
-      }
-      if (ins.maps != 0 && (ins.flags & MK_LDF_ATTN)) {
-        // A split-KV attention unit: one K box and one V box per page (two each
-        // for head dim 128), issued by lane 0 from the instruction record.
-        if (ins.n_lwaits > 0) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
-        int issued = 0;
-        if (c.lane == 0) {
-          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
-          RingPos q = rp;
-          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
-            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
-                               (int)(seq + issued)))
-              break;
-            trace(c, TRC_LOAD_BEGIN, seq + issued);
-            at_load_issue(maps, maps + 128, (ins.flags & MK_LDF_D128) != 0, ins.tiles, ins.row_a + issued * ins.tiles,
-                          ins.row_b & 0xffff, ins.row_b >> 16, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes,
-                          full_bar(c, q.slot), policy);
-            trace(c, TRC_LOAD_ISSUED, seq + issued);
-          }
-        }
-        issued = __shfl_sync(0xffffffffu, issued, 0);
-        if (issued < ins.n_pages) c.dead = true;
-        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
-        seq += (uint32_t)issued;
-      } else if (ins.maps != 0) {
-        // A matvec unit: tiled-TMA pages, issued by lane 0 alone in a tight
-        // loop from the fields of the instruction record (no op-table read on
-        // this path; a one-thread wait needs no vote).  Fill k of a slot needs
-        // fill k-1 handed back: empty-barrier phase k-1.
-        int issued = 0;
-        if (c.lane == 0) {
-          MvLoad ml;
-          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
-          const bool pair = (ins.flags & MK_LDF_PAIR) != 0;
-          ml.fp4 = (ins.flags & MK_LDF_FP4) != 0;
-          ml.tm_a = maps;
-          ml.tm_b = maps + (pair ? 128 : 0);
-          ml.ts_a = maps + 256;
-          ml.ts_b = maps + (pair ? 384 : 256);
-          ml.rowA0 = ins.row_a;
-          ml.rowB0 = ins.row_b;
-          ml.tiles_per_page = ins.tiles;
-          ml.half = (uint32_t)ins.tiles * 1024u;
-          RingPos q = rp;
-          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
-            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
-                               (int)(seq + issued)))
-              break;
-            trace(c, TRC_LOAD_BEGIN, seq + issued);
-            mv_load_issue(ml, issued, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes, full_bar(c, q.slot), policy);
-            trace(c, TRC_LOAD_ISSUED, seq + issued);
-          }
-        }
-        issued = __shfl_sync(0xffffffffu, issued, 0);
-        if (issued < ins.n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
-        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
-        seq += (uint32_t)issued;
-      } else {
-        const mk_op_t* op = pv.ops + ins.op;
-        const int opcode = op->opcode;
-        for (int p = 0; p < ins.n_pages; ++p) {
-          if (!wait_mbar(c, empty_bar(c, rp.slot), (rp.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY, (int)seq)) break;
-          trace(c, TRC_LOAD_BEGIN, seq);
-          const uint32_t page = c.pages_u32 + rp.slot * (uint32_t)pv.page_bytes;
-          const uint32_t bar = full_bar(c, rp.slot);
-          (void)opcode;
-          (void)page;
-          mbar_arrive(bar);  // an op without loads: hand over an empty page
-          trace(c, TRC_LOAD_ISSUED, seq);
-          ++seq;
-          ring_next(rp, NP);
-        }
-      }
-    }
-  }
-  // Every copy this warp issued must have landed before the CTA may exit.
-  // On the normal path the consumers already observed all of them; after an
-  // abandoned wait they may not have, so drain with a bounded wait.
-  if (c.dead) {
-    const uint32_t first = seq > (uint32_t)NP ? seq - NP : 0u;
-    for (uint32_t s = first; s < seq; ++s) {
-      const uint32_t bar = full_bar(c, s % NP);
-      const uint32_t par = (s / NP) & 1u;
-      const uint64_t t0 = globaltimer_ns();
-      while (!mbar_try_wait(bar, par)) {
-        if (globaltimer_ns() - t0 > pv.timeout_ns) break;
-      }
-    }
-  }
-}
-
-// Returns whether this warp completed the unit (and therefore signals it).
-template <int NTC, int WFC>
-__device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t mv_ord) {
-  switch (op->opcode) {
-    case MK_OP_MATVEC: return mv_dispatch<NTC, WFC>(c, op, ins, seq, mv_ord);
-    case MK_OP_ATTN_SPLIT: return at_dispatch<(WFC == 0 ? 0 : 1)>(c, op, ins, seq, mv_ord);
-    case MK_OP_ATTN_COMBINE: at_combine_unit(c, op, ins); break;
-    case MK_OP_RMSNORM: ew_rmsnorm(c, op, ins.unit); break;
-    case MK_OP_ROPE: ew_rope(c, op, ins.unit); break;
-    case MK_OP_QKNORM_ROPE: ew_qknorm_rope(c, op, ins.unit); break;
-    case MK_OP_GLU: ew_glu(c, op, ins.unit); break;
-    case MK_OP_ADD: ew_add(c, op, ins.unit); break;
-    case MK_OP_TOP1_FINAL: ew_top1_final(c, op, ins.unit); break;
-    case MK_OP_ALLREDUCE: ew_allreduce(c, op, ins.unit); break;
-    case MK_OP_NOP: break;
-    default:
-      if (c.lane == 0) report(c, MK_ST_BAD_OP, op->opcode, ins.op);
-      c.dead = true;
-      break;
-  }
-  return true;
-}
-
-template <int NTC, int WFC>
-__device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
-  const ProgramView& pv = *c.pv;
-  const int w = c.warp - 1;
-  constexpr int T = kConsumerWarps * 32;
-  uint32_t seq = 0;
-  uint32_t mv_ord = 0;  // shared units before the cursor (selects the split-K slot set)
-  int staged_key = 0;
-  int cached_op = -1;   // op whose record sits in the shared-memory copy
-  int bulk_units = 0;   // > 0: units of cached_op are signalled in bulk
-  int ev = ebeg;
-  mk_event_t cur;
-  cur.pos = 0x7fffffff;
-  if (ev < eend) cur = pv.events[ev];
-
-  auto do_event = [&]() {
-    // Every consumer warp runs this, dead or not: the barriers must balance.
-    // All units before the event are complete after the first barrier, so the
-    // shared copy of the op record can be replaced: unit handlers then read
-    // their parameters from shared memory instead of the op table.
-    trace(c, TRC_EVENT_BEGIN, cur.op);
-    // request the next event record now: its latency hides behind the barriers
-    mk_event_t nxt;
-    nxt.pos = 0x7fffffff;
-    if (ev + 1 < eend) nxt = pv.events[ev + 1];
-    named_bar_sync(kConsumerBarrier, T);
-    const mk_op_t* op = pv.ops + cur.op;
-    if (w == 0) {
-      wait_counters(c, cur.n_waits, cur.wait_off);
-    } else if (w == 1 && c.lane < (int)(sizeof(mk_op_t) / 16)) {
-      reinterpret_cast<uint4*>(&c.ctrl->op_cache)[c.lane] = reinterpret_cast<const uint4*>(op)[c.lane];
-      if (c.lane == 0) c.ctrl->bulk_done = 0;
-    }
-    bulk_units = (cur.flags & MK_EVF_BULK_SIGNAL) ? cur.bulk_units : 0;
-    named_bar_sync(kConsumerBarrier, T);
-    trace(c, TRC_EVENT_DEPS, cur.op);
-    op = &c.ctrl->op_cache;
-    cached_op = cur.op;
-    if (op->opcode == MK_OP_MATVEC) {
-      const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-      mv_stage<!(NTC == 1 && WFC == 0)>(c, op, need, (cur.flags & MK_EVF_WRITE_RES_OUT) != 0);
-      staged_key = op->act_key;
-    }
-    named_bar_sync(kConsumerBarrier, T);
-    trace(c, TRC_EVENT_END, cur.op);
-    ++ev;
-    cur = nxt;
-  };
-
-  // Consumer slots are handed out through a ticket counter: a unit owns as
-  // many consecutive tickets as it has participants (one for a unit that is
-  // not shared), and a consumer that becomes free draws the next ticket, so a
-  // warp that is held up (by an epilogue, by a page that is late) never has
-  // a fixed share of later work waiting behind it.  Tickets rise, so each
-  // consumer walks the instruction list forward only; passing an op-entry
-  // event on the way means taking part in it.
-  int i = ibeg;          // instruction under the cursor
-  int base = ibeg - 32;  // `mine` holds the records of [base, base + 32)
-  uint32_t first_slot = 0;  // ticket of the first slot of instruction i
-  mk_instr_t mine;
-  memset(&mine, 0, sizeof(mine));
-  for (;;) {
-    uint32_t ticket = 0;
-    if (c.lane == 0) ticket = atomicAdd(&c.ctrl->ticket, 1u);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    bool found = false;
-    int n_pages = 0, split = 0;
-    bool shared = false;
-    while (i < iend) {
-      if (i - base >= 32) {
-        base = ibeg + ((i - ibeg) & ~31);
-        memset(&mine, 0, sizeof(mine));
-        if (base + c.lane < iend) mine = load_instr(pv.instrs + base + c.lane);
-      }
-      while (cur.pos <= i - ibeg) do_event();
-      n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i - base);
-      const int lflags = __shfl_sync(0xffffffffu, mine.ld_flags, i - base);
-      shared = (lflags & kInsMatvec) != 0;
-      split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
-      const uint32_t slots = shared ? (uint32_t)split : 1u;
-      if (ticket < first_slot + slots) {
-        found = true;
-        break;
-      }
-      first_slot += slots;
-      seq += (uint32_t)n_pages;
-      if (shared && split > 1) ++mv_ord;
-      ++i;
-    }
-    if (!found) break;
-    if (!c.dead) {
-      const int part = (int)(ticket - first_slot);
-      const mk_instr_t ins = bcast_instr(mine, i - base);
-      c.instr_idx = i;
-      if (ins.n_waits == 0 || wait_counters(c, ins.n_waits, ins.wait_off)) {
-        trace(c, TRC_UNIT_BEGIN, i);
-        const mk_op_t* op = ins.op == cached_op ? &c.ctrl->op_cache : pv.ops + ins.op;
-        const bool finished = run_unit<NTC, WFC>(c, op, ins, seq, mv_ord | ((uint32_t)part << 28));
-        if (!c.dead && finished) {
-          if (bulk_units > 0 && ins.op == cached_op)
-            signal_unit_bulk(c, ins.signal, bulk_units);
-          else
-            signal_unit(c, ins.signal);
-        }
-        trace(c, TRC_UNIT_END, i);
-      }
-    }
-  }
-  while (ev < eend) do_event();
-}
-
-// NTC / WFC specialise the matvec path (see mv_dispatch); <0, -1> handles any program.
-template <int NTC, int WFC>
-__global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid_constant__ ProgramView pv) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  Ctx c;
-  c.pv = &pv;
-  c.ctrl = reinterpret_cast<Ctrl*>(smem);
-  c.act = smem + kCtrlBytes;
-  c.pages = smem + kCtrlBytes + pv.act_bytes;
-  c.act_u32 = smem_u32(c.act);
-  c.pages_u32 = smem_u32(c.pages);
-  c.warp = threadIdx.x >> 5;
-  c.lane = threadIdx.x & 31;
-  c.instr_idx = -1;
-  c.dead = false;
-  trace_init(c);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < pv.n_pages; ++i) {
-      mbar_init(smem_u32(&c.ctrl->full[i]), 32);
-      mbar_init(smem_u32(&c.ctrl->empty[i]), 1);
-    }
-    for (int i = 0; i < kMaxPages; ++i) c.ctrl->released[i] = 0;
-    for (int i = 0; i < 4; ++i) c.ctrl->mv_arrive[i] = c.ctrl->mv_done[i] = 0;
-    c.ctrl->abort_flag = 0;
-    c.ctrl->is_last = 0;
-    c.ctrl->ticket = 0;
-    c.ctrl->bulk_done = 0;
-    fence_mbar_init();
-  }
-  __syncthreads();
-
-  const int ibeg = pv.cta_instr_begin[blockIdx.x], iend = pv.cta_instr_begin[blockIdx.x + 1];
-  const int ebeg = pv.cta_event_begin[blockIdx.x], eend = pv.cta_event_begin[blockIdx.x + 1];
-  if (c.warp == 0)
-    loader_loop(c, ibeg, iend);
-  else
-    consumer_loop<NTC, WFC>(c, ibeg, iend, ebeg, eend);
-  trace_flush(c);
-  __syncthreads();
-
-  // The last CTA to finish clears the dependency counters, so the next launch
-  // (or graph replay) starts from zero without a host-side memset.
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const int prev = atomicAdd(&pv.state->done_ctas, 1);
-    c.ctrl->is_last = (prev == (int)gridDim.x - 1) ? 1 : 0;
-    __threadfence();
-  }
-  __syncthreads();
-  if (c.ctrl->is_last) {
-    const bool ok = *reinterpret_cast<volatile int32_t*>(&pv.state->abort_flag) == 0;
-    if (ok)
-      for (int i = threadIdx.x; i < pv.n_counters; i += blockDim.x) pv.counters[i] = 0;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      pv.state->done_ctas = 0;
-      pv.state->launches += 1;
-    }
-  }
-}
 
 // ------------------------------------------------------------------ host side
 static thread_local std::string g_err;
@@ -576,8 +205,63 @@ static int attn_pages(const mk_op_t& op, int unit, int page_bytes) {
   return (te - tb + tn - 1) / tn;
 }
 
-static int validate_op(const mk_program_t* p, int idx) {
-  const mk_op_t& op = p->ops[idx];
+// Everything the device would otherwise derive per unit with divisions or
+// op-table reads: the loader's tensor-map address, first rows and tiles per
+// page, the participant count, and the finisher's output offsets.
+static void fill_instr_fast_path(mk_instr_t& in, const mk_op_t& op, uint64_t dev_tmaps, int page_bytes, int n_ring_pages) {
+  in.ld_maps = 0;
+  in.ld_row_a = in.ld_row_b = in.ld_tiles = in.ld_flags = 0;
+  in.out_off_a = in.out_off_b = 0;
+  if (op.opcode == MK_OP_ATTN_SPLIT) {
+    // unit -> (batch, kv head, query tile, split)
+    const int S = op.i[MK_AT_SPLITS], MT = op.i[MK_AT_MT], HKV = op.i[MK_AT_HKV];
+    const int sp = in.unit % S, mt = (in.unit / S) % MT, kvh = (in.unit / S / MT) % HKV, b = in.unit / S / MT / HKV;
+    const int t_begin = std::min(op.i[MK_AT_N], sp * op.i[MK_AT_TS]);
+    in.ld_maps = dev_tmaps + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
+    in.ld_row_a = t_begin;
+    in.ld_row_b = kvh | (b << 16);
+    in.out_off_a = sp;
+    in.out_off_b = mt;
+    in.ld_tiles = at_page_tokens(op.i[MK_AT_D], page_bytes);
+    // every participant keeps one ring page until the unit's states are merged:
+    // leave at least two pages for the stream
+    const int split = std::max(1, std::min(std::min((int)kConsumerWarps, in.n_pages), n_ring_pages - 2));
+    in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT);
+    if (in.n_pages == 0) in.ld_maps = 0;   // an empty split: nothing to load, one consumer writes the empty partial
+    return;
+  }
+  if (op.opcode != MK_OP_MATVEC) return;
+  const bool fp4 = op.i[MK_MV_WFMT] >= MK_W_NVFP4_F16S32;
+  const int mode = op.i[MK_MV_MODE];
+  in.ld_maps = dev_tmaps + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
+  in.ld_tiles = fp4 ? op.i[MK_MV_KC] / 256 : op.i[MK_MV_KC] / 64;
+  // consumers per unit: participant j takes pages j, j + split, ...; none idle
+  int split = op.i[MK_MV_SPLIT];
+  if (split <= 0 || split > kConsumerWarps) split = kConsumerWarps;
+  split = std::min(split, std::max(1, in.n_pages));
+  int chunk = 0;
+  if (mode == MK_MV_PLAIN) {
+    in.ld_row_a = in.unit * 16;
+    in.ld_row_b = in.unit * 16 + 8;
+  } else if (mode == MK_MV_PAIR) {
+    in.ld_row_a = in.ld_row_b = in.unit * 8;
+  } else {
+    const int hd = op.i[MK_MV_HD], d2 = op.i[MK_MV_D2], upb = d2 / 8;
+    const int h = in.unit / upb;
+    chunk = in.unit - h * upb;
+    in.ld_row_a = h * hd + chunk * 8;
+    in.ld_row_b = in.ld_row_a + d2;
+  }
+  in.ld_flags = (fp4 ? MK_LDF_FP4 : 0) | (mode == MK_MV_PAIR ? MK_LDF_PAIR : 0) |
+                (std::max(1, split) << MK_LDF_SPLIT_SHIFT) | ((chunk & MK_LDF_CHUNK_MASK) << MK_LDF_CHUNK_SHIFT);
+  // output offsets of the two row groups (8 rows each never straddle a head: head dim % 8 == 0)
+  const int hd = std::max(1, op.i[MK_MV_HD]);
+  const int64_t sh = op.s[MK_MV_S_O_H];
+  in.out_off_a = (int32_t)((int64_t)(in.ld_row_a / hd) * sh + in.ld_row_a % hd);
+  in.out_off_b = (int32_t)((int64_t)(in.ld_row_b / hd) * sh + in.ld_row_b % hd);
+}
+
+static int validate_op(const mk_op_t& op, int idx, int page_bytes, int act_bytes) {
   if (op.opcode < 0 || op.opcode >= MK_OP__COUNT) return fail(-2, "op %d: unknown opcode %d", idx, op.opcode);
   if (op.n_units < 0) return fail(-2, "op %d: negative unit count", idx);
   if (op.opcode == MK_OP_MATVEC) {
@@ -596,9 +280,9 @@ static int validate_op(const mk_program_t* p, int idx) {
     if (fp4 && K > 2048 && K % 2048 != 0)
       return fail(-2, "op %d: NVFP4 matvec needs K < 2048 or K %% 2048 == 0, got %d", idx, K);
     const uint64_t need = mv_page_need(wf, Kc);
-    if (need > (uint64_t)p->page_bytes) return fail(-2, "op %d: K slice %d does not fit a %d-byte page", idx, Kc, p->page_bytes);
-    if ((uint64_t)M * ((uint64_t)K * 2 + 64) > (uint64_t)p->act_bytes)
-      return fail(-2, "op %d: %d x %d activations exceed the %d-byte staging buffer", idx, M, K, p->act_bytes);
+    if (need > (uint64_t)page_bytes) return fail(-2, "op %d: K slice %d does not fit a %d-byte page", idx, Kc, page_bytes);
+    if ((uint64_t)M * ((uint64_t)K * 2 + 64) > (uint64_t)act_bytes)
+      return fail(-2, "op %d: %d x %d activations exceed the %d-byte staging buffer", idx, M, K, act_bytes);
     if (!aligned16(op.p[MK_MV_P_W0]) || !op.p[MK_MV_P_W0] || (op.s[MK_MV_S_WROW] & 15))
       return fail(-2, "op %d: weight pointer / row stride must be 16-byte aligned", idx);
     if (mode == MK_MV_PAIR && (!aligned16(op.p[MK_MV_P_W1]) || !op.p[MK_MV_P_W1]))
@@ -619,6 +303,8 @@ static int validate_op(const mk_program_t* p, int idx) {
       return fail(-2, "op %d: residual pointers / strides must be 16-byte aligned", idx);
     if (!op.p[MK_MV_P_OUT]) return fail(-2, "op %d: output pointer missing", idx);
     if (op.i[MK_MV_HD] <= 0) return fail(-2, "op %d: head dim must be positive", idx);
+    if (op.i[MK_MV_HD] % 8 != 0 && op.s[MK_MV_S_O_H] != op.i[MK_MV_HD])
+      return fail(-2, "op %d: a strided head layout needs a head dim that is a multiple of 8", idx);
     int units;
     if (mode == MK_MV_PLAIN) {
       units = (O + 15) / 16;
@@ -649,7 +335,7 @@ static int validate_op(const mk_program_t* p, int idx) {
       if (op.i[MK_AT_MT] != (M * G + 15) / 16) return fail(-2, "op %d: bad query tile count", idx);
       if (op.i[MK_AT_TS] <= 0) return fail(-2, "op %d: tokens per split must be positive", idx);
       if ((int64_t)op.i[MK_AT_TS] * op.i[MK_AT_SPLITS] < op.i[MK_AT_N]) return fail(-2, "op %d: splits do not cover N", idx);
-      if (at_page_tokens(D, p->page_bytes) <= 0) return fail(-2, "op %d: page too small for attention", idx);
+      if (at_page_tokens(D, page_bytes) <= 0) return fail(-2, "op %d: page too small for attention", idx);
       for (int k = MK_AT_P_Q; k <= MK_AT_P_V; ++k)
         if (!op.p[k] || !aligned16(op.p[k])) return fail(-2, "op %d: q/k/v pointer missing or unaligned", idx);
       for (int k = MK_AT_S_Q_B; k <= MK_AT_S_V_H; ++k)
@@ -697,10 +383,12 @@ static int validate_op(const mk_program_t* p, int idx) {
   return 0;
 }
 
-static int validate_program(const mk_program_t* p, int smem_optin, int* smem_bytes) {
+static int validate_program(const mk_program_t* p, int smem_optin, int num_sms, int* smem_bytes) {
   if (!p) return fail(-1, "null program");
   if (p->n_ops <= 0 || !p->ops) return fail(-1, "program has no ops");
   if (p->n_ctas <= 0 || p->n_ctas > 4096) return fail(-1, "bad grid size %d", p->n_ctas);
+  if (num_sms > 0 && p->n_ctas > num_sms)
+    return fail(-1, "grid of %d CTAs exceeds the %d multiprocessors: the CTAs of a launch wait on one another, so all must be resident", p->n_ctas, num_sms);
   if (p->n_pages < 2 || p->n_pages > kMaxPages) return fail(-1, "ring depth must be in [2, %d]", kMaxPages);
   if (p->page_bytes <= 0 || (p->page_bytes & 1023)) return fail(-1, "page size must be a positive multiple of 1024");
   if (p->act_bytes < 0 || (p->act_bytes & 1023)) return fail(-1, "activation buffer must be a multiple of 1024 bytes");
@@ -712,7 +400,7 @@ static int validate_program(const mk_program_t* p, int smem_optin, int* smem_byt
   if (smem > smem_optin) return fail(-1, "program needs %lld bytes of shared memory, device offers %d", (long long)smem, smem_optin);
   *smem_bytes = (int)smem;
   for (int i = 0; i < p->n_ops; ++i) {
-    const int rc = validate_op(p, i);
+    const int rc = validate_op(p->ops[i], i, p->page_bytes, p->act_bytes);
     if (rc) return rc;
   }
   for (int i = 0; i < p->n_waits; ++i)
@@ -753,49 +441,81 @@ static int validate_program(const mk_program_t* p, int smem_optin, int* smem_byt
 
 }  // namespace mk
 
-// The kernel variants: <NT class, weight family>; the first entry handles any
-// program, the others carry the matvec code of one combination only (smaller
-// code, fewer instruction-cache misses on the hot path).
-typedef void (*mk_kernel_fn)(const mk::ProgramView);
-struct mk_variant {
-  int ntc, wfc;
-  mk_kernel_fn fn;
-};
-static const mk_variant g_variants[] = {
-    {0, -1, mk::mk_persistent_kernel<0, -1>}, {1, 0, mk::mk_persistent_kernel<1, 0>},
-    {2, 0, mk::mk_persistent_kernel<2, 0>},   {4, 0, mk::mk_persistent_kernel<4, 0>},
-    {1, 2, mk::mk_persistent_kernel<1, 2>},   {2, 2, mk::mk_persistent_kernel<2, 2>},
-    {4, 2, mk::mk_persistent_kernel<4, 2>},
-};
+// The kernel variants are compiled in groups, one translation unit per group
+// (variants_*.cu), so that they build in parallel; each group hands out its
+// table.  Variants differ in <activation-tile class, weight family, features>.
+extern "C" const mk_variant* mk_variants_generic(int* n);
+extern "C" const mk_variant* mk_variants_bf16(int* n);
+extern "C" const mk_variant* mk_variants_bf16_wide(int* n);
+extern "C" const mk_variant* mk_variants_fp4(int* n);
+extern "C" const mk_variant* mk_variants_fp4_wide(int* n);
+extern "C" const mk_variant* mk_variants_fp4_tp(int* n);
+
+static const std::vector<mk_variant>& all_variants() {
+  static const std::vector<mk_variant> v = [] {
+    std::vector<mk_variant> out;
+    typedef const mk_variant* (*group_fn)(int*);
+    const group_fn groups[] = {mk_variants_generic, mk_variants_bf16,     mk_variants_bf16_wide,
+                               mk_variants_fp4,     mk_variants_fp4_wide, mk_variants_fp4_tp};
+    for (group_fn g : groups) {
+      int n = 0;
+      const mk_variant* t = g(&n);
+      out.insert(out.end(), t, t + n);
+    }
+    return out;
+  }();
+  return v;
+}
 
 struct mk_handle_s {
   mk::ProgramView pv;
   mk_kernel_fn kernel;
   std::vector<int> op_ntc, op_wfc;   // per op: NT class and weight family (0 = not a matvec)
+  std::vector<int> op_feat;          // per op: MK_F_* bits its unit handler needs
+  int feat;                          // features of the kernel in use
+  std::vector<mk_op_t> ops;          // host copy of the op records (as uploaded)
+  std::vector<mk_instr_t> instrs;    // host copy of the instruction table (as uploaded)
   int n_ctas;
   int smem_bytes;
+  int smem_optin;
   int device;
   int n_ops;
   uint8_t* ws;
   mk::Layout layout;
 };
 
-// wfc -3 marks an attention op with the fused q/k norm: the kernels built for
-// bf16-only programs carry no code for it, so such a program runs the generic kernel.
-static void classify_op(const mk_op_t& op, int* ntc, int* wfc) {
+static void classify_op(const mk_op_t& op, int* ntc, int* wfc, int* feat) {
   *ntc = 0;
-  *wfc = (op.opcode == MK_OP_ATTN_SPLIT && op.i[MK_AT_QKNORM]) ? -3 : -1;
-  if (op.opcode != MK_OP_MATVEC) return;
+  *wfc = -1;
+  *feat = 0;
+  switch (op.opcode) {
+    case MK_OP_ATTN_SPLIT:
+      *feat = (op.i[MK_AT_D] == 64 ? mk::MK_F_AT64 : mk::MK_F_AT128) | (op.i[MK_AT_QKNORM] ? mk::MK_F_QKNORM : 0);
+      return;
+    case MK_OP_ATTN_COMBINE: *feat = mk::MK_F_COMBINE; return;
+    case MK_OP_RMSNORM: case MK_OP_ROPE: case MK_OP_QKNORM_ROPE: case MK_OP_GLU: case MK_OP_ADD:
+      *feat = mk::MK_F_EW;
+      return;
+    case MK_OP_TOP1_FINAL: *feat = mk::MK_F_TOP1; return;
+    case MK_OP_ALLREDUCE: *feat = mk::MK_F_AR; return;
+    case MK_OP_MATVEC: break;
+    default: return;
+  }
   const int m = op.i[MK_MV_M], wf = op.i[MK_MV_WFMT];
   *ntc = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
   *wfc = wf == MK_W_BF16 ? 0 : (wf >= MK_W_NVFP4_F16S32 ? 2 : 1);
+  if (op.i[MK_MV_EPI] == MK_EPI_TOP1) *feat = mk::MK_F_TOP1;
 }
 
-// Pick the most specific kernel that covers every matvec op of the program.
+// Pick the smallest kernel that covers the program: its matvec ops' tile class
+// and weight family (one combination, else the generic matvec code) and the
+// union of its ops' features.
 static int select_kernel(mk_handle_s* h) {
   int ntc = -1, wfc = -2;
   bool mixed = false;
+  int need = h->pv.trace != nullptr ? mk::MK_F_TRACE : 0;
   for (size_t i = 0; i < h->op_ntc.size(); ++i) {
+    need |= h->op_feat[i];
     if (h->op_ntc[i] == 0) continue;
     if (ntc == -1) {
       ntc = h->op_ntc[i];
@@ -804,21 +524,44 @@ static int select_kernel(mk_handle_s* h) {
       mixed = true;
     }
   }
-  if (wfc == 0)
-    for (int w : h->op_wfc)
-      if (w == -3) mixed = true;
-  h->kernel = g_variants[0].fn;
-  if (!mixed && ntc > 0)
-    for (const mk_variant& v : g_variants)
-      if (v.ntc == ntc && v.wfc == wfc) h->kernel = v.fn;
+  if (mixed || ntc <= 0 || wfc == 1) {   // fp16 weights run the generic matvec code
+    ntc = 0;
+    wfc = -1;
+  }
+  const mk_variant* best = nullptr;
+  int best_cost = 1 << 30;
+  for (const mk_variant& v : all_variants()) {
+    if ((v.feat & need) != need) continue;
+    const bool exact = v.ntc == ntc && v.wfc == wfc;
+    if (!exact && !(v.ntc == 0 && v.wfc == -1)) continue;
+    const int cost = __builtin_popcount((unsigned)v.feat) + (exact ? 0 : 100);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = &v;
+    }
+  }
+  if (!best) return mk::fail(-5, "no kernel variant covers this program (features 0x%x)", need);
+  h->kernel = best->fn;
+  h->feat = best->feat;
   h->pv.mv_sets = 4;
   for (int n : h->op_ntc)
     if (n > 0) h->pv.mv_sets = std::min(h->pv.mv_sets, n == 1 ? 4 : (n == 2 ? 2 : 1));
+  // The dynamic shared-memory limit is a property of the kernel function, shared by
+  // every handle that runs this variant: always raise it to the device's opt-in
+  // maximum, so that a later, smaller program never lowers it under a live one.
   cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->kernel),
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_bytes);
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin);
   if (e != cudaSuccess) return mk::fail(-(int)e - 1000, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   return 0;
 }
+
+// Restores the caller's current device when an entry point returns.
+struct DeviceScope {
+  int prev = -1;
+  ~DeviceScope() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
 
 extern "C" {
 
@@ -845,106 +588,80 @@ uint64_t mk_workspace_bytes(const mk_program_t* prog) {
   return mk::layout_of(prog).total;
 }
 
-int mk_create(const mk_program_t* prog, mk_handle_t* out) {
+// Builds the program in `prog->workspace`.  With `stream_ordered` every clear
+// and upload is queued on `stream` (the host buffers are pageable, so each
+// copy is staged before its call returns) and the caller may launch on the
+// same stream straight away; without it the copies are synchronous.
+static int create_program(const mk_program_t* prog, mk_handle_t* out, bool stream_ordered, cudaStream_t stream) {
   using namespace mk;
   if (!out) return fail(-1, "null output handle");
   *out = nullptr;
   if (!prog) return fail(-1, "null program");
-  int prev_dev = 0;
-  CUDA_TRY(cudaGetDevice(&prev_dev));
+  DeviceScope scope;
+  CUDA_TRY(cudaGetDevice(&scope.prev));
   CUDA_TRY(cudaSetDevice(prog->device));
-  int smem_optin = 0, cc = 0;
+  int smem_optin = 0, cc = 0, num_sms = 0;
   CUDA_TRY(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, prog->device));
   CUDA_TRY(cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, prog->device));
-  if (cc != 10) {
-    cudaSetDevice(prev_dev);
+  CUDA_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, prog->device));
+  if (cc != 10)
     return fail(-4, "device %d has compute capability %d.x; this library is built for sm_100a only", prog->device, cc);
-  }
   int smem_bytes = 0;
-  int rc = validate_program(prog, smem_optin, &smem_bytes);
-  if (rc) {
-    cudaSetDevice(prev_dev);
-    return rc;
-  }
+  int rc = validate_program(prog, smem_optin, num_sms, &smem_bytes);
+  if (rc) return rc;
   const Layout l = layout_of(prog);
-  if (!prog->workspace || prog->workspace_bytes < l.total || ((uint64_t)prog->workspace & 255)) {
-    cudaSetDevice(prev_dev);
+  if (!prog->workspace || prog->workspace_bytes < l.total || ((uint64_t)prog->workspace & 255))
     return fail(-1, "workspace must be 256-byte aligned device memory of at least %llu bytes", (unsigned long long)l.total);
-  }
   uint8_t* ws = reinterpret_cast<uint8_t*>(prog->workspace);
-  CUDA_TRY(cudaMemset(ws + l.state, 0, l.ops - l.state));
+  auto clear = [&](void* dst, size_t n) {
+    return stream_ordered ? cudaMemsetAsync(dst, 0, n, stream) : cudaMemset(dst, 0, n);
+  };
+  auto upload = [&](void* dst, const void* src, size_t n) {
+    return stream_ordered ? cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, stream)
+                          : cudaMemcpy(dst, src, n, cudaMemcpyHostToDevice);
+  };
+  CUDA_TRY(clear(ws + l.state, l.ops - l.state));
+
+  mk_handle_s* h = new mk_handle_s();
+  struct Guard {
+    mk_handle_s* h;
+    ~Guard() { delete h; }
+  } guard{h};
   {
     // tensor maps of the weight matrices, and op records that point at them
-    std::vector<mk_op_t> ops(prog->ops, prog->ops + prog->n_ops);
+    h->ops.assign(prog->ops, prog->ops + prog->n_ops);
     std::vector<CUtensorMap> maps((size_t)prog->n_ops * kMapsPerOp);
     memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
     for (int i = 0; i < prog->n_ops; ++i) {
-      rc = build_op_maps(ops[i], &maps[(size_t)i * kMapsPerOp],
+      rc = build_op_maps(h->ops[i], &maps[(size_t)i * kMapsPerOp],
                          (uint64_t)(ws + l.tmaps) + (uint64_t)i * kMapsPerOp * sizeof(CUtensorMap), prog->page_bytes);
-      if (rc) {
-        cudaSetDevice(prev_dev);
-        return rc;
-      }
+      if (rc) return rc;
     }
-    CUDA_TRY(cudaMemcpy(ws + l.tmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-    CUDA_TRY(cudaMemcpy(ws + l.ops, ops.data(), ops.size() * sizeof(mk_op_t), cudaMemcpyHostToDevice));
+    CUDA_TRY(upload(ws + l.tmaps, maps.data(), maps.size() * sizeof(CUtensorMap)));
+    CUDA_TRY(upload(ws + l.ops, h->ops.data(), h->ops.size() * sizeof(mk_op_t)));
   }
   if (prog->n_instrs) {
-    // fill the loader fast path of every matvec unit
-    std::vector<mk_instr_t> instrs(prog->instrs, prog->instrs + prog->n_instrs);
-    for (auto& in : instrs) {
-      in.ld_maps = 0;
-      in.ld_row_a = in.ld_row_b = in.ld_tiles = in.ld_flags = 0;
-      const mk_op_t& op = prog->ops[in.op];
-      if (op.opcode == MK_OP_ATTN_SPLIT) {
-        // unit -> (batch, kv head, query tile, split), as at_decode does on the device
-        const int S = op.i[MK_AT_SPLITS], MT = op.i[MK_AT_MT], HKV = op.i[MK_AT_HKV];
-        const int sp = in.unit % S, kvh = (in.unit / S / MT) % HKV, b = in.unit / S / MT / HKV;
-        const int t_begin = std::min(op.i[MK_AT_N], sp * op.i[MK_AT_TS]);
-        in.ld_maps = (uint64_t)(ws + l.tmaps) + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
-        in.ld_row_a = t_begin;
-        in.ld_row_b = kvh | (b << 16);
-        in.ld_tiles = at_page_tokens(op.i[MK_AT_D], prog->page_bytes);
-        // every participant keeps one ring page until the unit's states are merged:
-        // leave at least two pages for the stream
-        const int split = std::max(1, std::min(std::min((int)kConsumerWarps, in.n_pages), prog->n_pages - 2));
-        in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT);
-        if (in.n_pages == 0) in.ld_maps = 0;   // an empty split: nothing to load, one consumer writes the empty partial
-        continue;
-      }
-      if (op.opcode != MK_OP_MATVEC) continue;
-      const bool fp4 = op.i[MK_MV_WFMT] >= MK_W_NVFP4_F16S32;
-      const int mode = op.i[MK_MV_MODE];
-      in.ld_maps = (uint64_t)(ws + l.tmaps) + (uint64_t)in.op * kMapsPerOp * sizeof(CUtensorMap);
-      in.ld_tiles = fp4 ? op.i[MK_MV_KC] / 256 : op.i[MK_MV_KC] / 64;
-      // consumers per unit: participant j takes pages j, j + split, ...; none idle
-      int split = op.i[MK_MV_SPLIT];
-      if (split <= 0 || split > kConsumerWarps) split = kConsumerWarps;
-      split = std::min(split, std::max(1, in.n_pages));
-      in.ld_flags = (fp4 ? MK_LDF_FP4 : 0) | (mode == MK_MV_PAIR ? MK_LDF_PAIR : 0) |
-                    (std::max(1, split) << MK_LDF_SPLIT_SHIFT);
-      if (mode == MK_MV_PLAIN) {
-        in.ld_row_a = in.unit * 16;
-        in.ld_row_b = in.unit * 16 + 8;
-      } else if (mode == MK_MV_PAIR) {
-        in.ld_row_a = in.ld_row_b = in.unit * 8;
-      } else {
-        const int hd = op.i[MK_MV_HD], d2 = op.i[MK_MV_D2], upb = d2 / 8;
-        const int h = in.unit / upb, j = (in.unit - h * upb) * 8;
-        in.ld_row_a = h * hd + j;
-        in.ld_row_b = in.ld_row_a + d2;
-      }
-    }
-    CUDA_TRY(cudaMemcpy(ws + l.instrs, instrs.data(), instrs.size() * sizeof(mk_instr_t), cudaMemcpyHostToDevice));
+    // fill the fast path of every unit
+    h->instrs.assign(prog->instrs, prog->instrs + prog->n_instrs);
+    for (auto& in : h->instrs)
+      fill_instr_fast_path(in, prog->ops[in.op], (uint64_t)(ws + l.tmaps), prog->page_bytes, prog->n_pages);
+    CUDA_TRY(upload(ws + l.instrs, h->instrs.data(), h->instrs.size() * sizeof(mk_instr_t)));
   }
-  CUDA_TRY(cudaMemcpy(ws + l.ibegin, prog->cta_instr_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
-  if (prog->n_events)
-    CUDA_TRY(cudaMemcpy(ws + l.events, prog->events, (size_t)prog->n_events * sizeof(mk_event_t), cudaMemcpyHostToDevice));
-  CUDA_TRY(cudaMemcpy(ws + l.ebegin, prog->cta_event_begin, (size_t)(prog->n_ctas + 1) * 4, cudaMemcpyHostToDevice));
-  if (prog->n_waits)
-    CUDA_TRY(cudaMemcpy(ws + l.waits, prog->waits, (size_t)prog->n_waits * sizeof(mk_wait_t), cudaMemcpyHostToDevice));
+  CUDA_TRY(upload(ws + l.ibegin, prog->cta_instr_begin, (size_t)(prog->n_ctas + 1) * 4));
+  if (prog->n_events) {
+    // inline the head of every wait list into its event record
+    std::vector<mk_event_t> events(prog->events, prog->events + prog->n_events);
+    for (auto& ev : events)
+      for (int k = 0; k < 4; ++k) {
+        const bool have = k < ev.n_waits;
+        ev.w_counter[k] = have ? prog->waits[ev.wait_off + k].counter : 0;
+        ev.w_expected[k] = have ? prog->waits[ev.wait_off + k].expected : 0;
+      }
+    CUDA_TRY(upload(ws + l.events, events.data(), events.size() * sizeof(mk_event_t)));
+  }
+  CUDA_TRY(upload(ws + l.ebegin, prog->cta_event_begin, (size_t)(prog->n_ctas + 1) * 4));
+  if (prog->n_waits) CUDA_TRY(upload(ws + l.waits, prog->waits, (size_t)prog->n_waits * sizeof(mk_wait_t)));
 
-  mk_handle_s* h = new mk_handle_s();
   h->pv.ops = reinterpret_cast<const mk_op_t*>(ws + l.ops);
   h->pv.instrs = reinterpret_cast<const mk_instr_t*>(ws + l.instrs);
   h->pv.cta_instr_begin = reinterpret_cast<const int32_t*>(ws + l.ibegin);
@@ -962,23 +679,23 @@ int mk_create(const mk_program_t* prog, mk_handle_t* out) {
   h->pv.trace_cap = 0;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
+  h->smem_optin = smem_optin;
   h->op_ntc.resize(prog->n_ops);
   h->op_wfc.resize(prog->n_ops);
-  for (int i = 0; i < prog->n_ops; ++i) classify_op(prog->ops[i], &h->op_ntc[i], &h->op_wfc[i]);
+  h->op_feat.resize(prog->n_ops);
+  for (int i = 0; i < prog->n_ops; ++i) classify_op(prog->ops[i], &h->op_ntc[i], &h->op_wfc[i], &h->op_feat[i]);
   rc = select_kernel(h);
-  if (rc) {
-    delete h;
-    cudaSetDevice(prev_dev);
-    return rc;
-  }
+  if (rc) return rc;
   h->device = prog->device;
   h->n_ops = prog->n_ops;
   h->ws = ws;
   h->layout = l;
+  guard.h = nullptr;
   *out = h;
-  cudaSetDevice(prev_dev);
   return 0;
 }
+
+int mk_create(const mk_program_t* prog, mk_handle_t* out) { return create_program(prog, out, false, nullptr); }
 
 int mk_run(mk_handle_t h, void* cuda_stream) {
   using namespace mk;
@@ -1002,14 +719,15 @@ int mk_set_trace(mk_handle_t h, void* buffer, uint64_t bytes, int32_t records_pe
   if (!buffer || records_per_warp <= 0) {
     h->pv.trace = nullptr;
     h->pv.trace_cap = 0;
-    return 0;
+    return select_kernel(h);
   }
   const uint64_t warps = (uint64_t)h->n_ctas * (kConsumerWarps + 1);
   const uint64_t need = warps * records_per_warp * sizeof(TraceRec) + warps * sizeof(int32_t);
   if (bytes < need || ((uint64_t)buffer & 15)) return fail(-1, "trace buffer needs %llu bytes, 16-byte aligned", (unsigned long long)need);
+  if (records_per_warp < 8) return fail(-1, "a trace ring needs at least 8 records per warp");
   h->pv.trace = reinterpret_cast<TraceRec*>(buffer);
   h->pv.trace_cap = records_per_warp;
-  return 0;
+  return select_kernel(h);   // tracing is compiled into some kernel variants only
 }
 
 int mk_workspace_status(const void* workspace, int32_t out[16]) {
@@ -1022,8 +740,15 @@ int mk_workspace_status(const void* workspace, int32_t out[16]) {
 int mk_reset(mk_handle_t h, void* cuda_stream) {
   using namespace mk;
   if (!h) return fail(-1, "null handle");
-  CUDA_TRY(cudaMemsetAsync(h->ws + h->layout.state, 0, h->layout.ops - h->layout.state,
-                           reinterpret_cast<cudaStream_t>(cuda_stream)));
+  // Status, abort flag, the count of finished CTAs and the dependency counters
+  // are cleared; the launch count is kept: the tensor-parallel exchange tags
+  // its messages with it, and ranks stay in step only while every rank's count
+  // advances once per launch.
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  uint8_t* base = h->ws + h->layout.state;
+  CUDA_TRY(cudaMemsetAsync(base, 0, offsetof(DeviceState, launches), st));
+  const size_t after = offsetof(DeviceState, launches) + sizeof(int32_t);
+  CUDA_TRY(cudaMemsetAsync(base + after, 0, (h->layout.ops - h->layout.state) - after, st));
   return 0;
 }
 
@@ -1031,19 +756,42 @@ int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_
   using namespace mk;
   if (!h || !op) return fail(-1, "null argument");
   if (op_index < 0 || op_index >= h->n_ops) return fail(-1, "op index %d out of range", op_index);
-  // The record may carry new weight pointers: re-encode its tensor maps.
   mk_op_t rec = *op;
+  int rc = validate_op(rec, op_index, h->pv.page_bytes, h->pv.act_bytes);
+  if (rc) return rc;
+  if (rec.opcode != h->ops[op_index].opcode || rec.n_units != h->ops[op_index].n_units)
+    return fail(-2, "op %d: an update may not change the opcode or the unit count (%d units scheduled, %d given)",
+                op_index, h->ops[op_index].n_units, rec.n_units);
+  // The record may carry new pointers: re-encode its tensor maps.
   CUtensorMap maps[kMapsPerOp];
   memset(maps, 0, sizeof(maps));
   uint8_t* dev_maps = h->ws + h->layout.tmaps + (size_t)op_index * kMapsPerOp * sizeof(CUtensorMap);
-  const int rc = build_op_maps(rec, maps, (uint64_t)dev_maps, h->pv.page_bytes);
+  rc = build_op_maps(rec, maps, (uint64_t)dev_maps, h->pv.page_bytes);
   if (rc) return rc;
+  // Page counts and the per-unit fast path are derived from the record: recompute the
+  // op's instruction rows and upload the span of the table that holds them.
+  size_t lo = h->instrs.size(), hi = 0;
+  for (size_t j = 0; j < h->instrs.size(); ++j) {
+    mk_instr_t& in = h->instrs[j];
+    if (in.op != op_index) continue;
+    if (rec.opcode == MK_OP_MATVEC) in.n_pages = matvec_pages(rec);
+    else if (rec.opcode == MK_OP_ATTN_SPLIT) in.n_pages = attn_pages(rec, in.unit, h->pv.page_bytes);
+    fill_instr_fast_path(in, rec, (uint64_t)(h->ws + h->layout.tmaps), h->pv.page_bytes, h->pv.n_pages);
+    lo = std::min(lo, j);
+    hi = std::max(hi, j + 1);
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   CUDA_TRY(cudaMemcpyAsync(dev_maps, maps, sizeof(maps), cudaMemcpyHostToDevice, st));
   CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.ops + (size_t)op_index * sizeof(mk_op_t), &rec, sizeof(mk_op_t),
                            cudaMemcpyHostToDevice, st));
+  if (hi > lo)
+    CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.instrs + lo * sizeof(mk_instr_t), h->instrs.data() + lo,
+                             (hi - lo) * sizeof(mk_instr_t), cudaMemcpyHostToDevice, st));
+  // the host buffers above must outlive the copies
+  CUDA_TRY(cudaStreamSynchronize(st));
+  h->ops[op_index] = rec;
   // a changed batch size or weight format may need another kernel variant
-  classify_op(rec, &h->op_ntc[op_index], &h->op_wfc[op_index]);
+  classify_op(rec, &h->op_ntc[op_index], &h->op_wfc[op_index], &h->op_feat[op_index]);
   return select_kernel(h);
 }
 

@@ -37,6 +37,20 @@ __device__ __forceinline__ AtUnit at_decode(const mk_op_t* op, int unit) {
   u.t_end = min(N, u.t_begin + ts);
   return u;
 }
+// The same from the instruction record, where mk_create has left the result
+// of the divisions: row_a = first token, row_b = kv head | batch << 16,
+// off_a = split, off_b = query tile.
+__device__ __forceinline__ AtUnit at_decode_fast(const mk_op_t* op, const UnitArgs& a) {
+  AtUnit u;
+  const int rb = ins_field(a.mine->row_b, a.idx);
+  u.t_begin = ins_field(a.mine->row_a, a.idx);
+  u.sp = ins_field(a.mine->off_a, a.idx);
+  u.mt = ins_field(a.mine->off_b, a.idx);
+  u.kvh = rb & 0xffff;
+  u.b = rb >> 16;
+  u.t_end = min(op->i[MK_AT_N], u.t_begin + op->i[MK_AT_TS]);
+  return u;
+}
 
 // Tokens per page for head dim D and a given page size: a K block and a V
 // block of `tn` rows each; tn is a multiple of the consumer's inner block
@@ -233,20 +247,19 @@ __device__ __forceinline__ void at_fix_k_row(Ctx& c, const mk_op_t* op, const At
 // unnormalised output).  A participant parks its state in the last page it
 // consumed instead of handing that page back; the last one to arrive merges
 // the states in participant order, writes the normalised partial and then
-// releases everybody's parked page.  `ordpart`: bits 0-27 slot-set ordinal,
-// bits 28-31 participant index.  Returns true for the warp that finished the
-// unit.
+// releases everybody's parked page.  Returns true for the warp that finished
+// the unit.
 // QMODE 0: the fused q/k norm is compiled out (kernels for bf16-only programs); 1: decided per op.
 template <int D, int QMODE>
-__device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
+__device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArgs& ua) {
   constexpr int KS = D / 16;   // k-steps of Q·K^T
   constexpr int ND = D / 8;    // n-tiles of the output
   constexpr int TN = (D == 64) ? 64 : 32;  // tokens processed per inner block
   constexpr int NS = TN / 8;   // score n-tiles per block
-  const int part = (int)(ordpart >> 28);
-  const uint32_t ord = ordpart & 0x0fffffffu;
-  const int parts = (ins.ld_flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
-  const AtUnit u = at_decode(op, ins.unit);
+  const int part = ua.part;
+  const uint32_t ord = ua.ord;
+  const int parts = (ua.flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+  const AtUnit u = at_decode_fast(op, ua);
   const int g = c.lane >> 2, t = c.lane & 3;
   const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], N = op->i[MK_AT_N];
   const int G = H / HKV;
@@ -348,13 +361,13 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
   float mrow[2] = {-INFINITY, -INFINITY};
   float lrow[2] = {0.f, 0.f};   // per-lane partial row sums (summed over the quad at the end)
 
-  const int np = ins.n_pages;
-  RingPos rp = ring_at(seq + (uint32_t)part, NPG);
+  const int np = ua.n_pages;
+  RingPos rp = ua.rp;
   uint32_t park = 0;            // address of the page this warp keeps for its state
   for (int p = part; p < np; p += parts, ring_advance(rp, parts, NPG)) {
     uint32_t page;
     if (!page_acquire(c, rp, page)) return false;
-    trace(c, TRC_PAGE_READY, seq + p);
+    trace(c, TRC_PAGE_READY, rp.k * (uint32_t)NPG + rp.slot);
     const uint32_t kpage = page, vpage = page + tile_bytes;
     const int tp0 = u.t_begin + p * tn;
     if (qknorm) {
@@ -443,7 +456,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
         }
       }
     }
-    trace(c, TRC_PAGE_DONE, seq + p);
+    trace(c, TRC_PAGE_DONE, rp.k * (uint32_t)NPG + rp.slot);
     if (parts > 1 && p + parts >= np)
       park = page;              // the last page of this participant: keep it
     else
@@ -482,7 +495,8 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
     lrow[0] = lrow[1] = 0.f;
     for (int j = 0; j < parts; ++j) {
       const int pl = j + ((np - 1 - j) / parts) * parts;   // last page of participant j
-      const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
+      RingPos rj = ua.rp0;
+      ring_advance(rj, pl, NPG);
       const uint32_t src = c.pages_u32 + rj.slot * (uint32_t)c.pv->page_bytes;
       float wa[2], wb[2];
       // all of a participant's records are requested before the first is used
@@ -515,7 +529,8 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
       fence_proxy_async();
       for (int j = 0; j < parts; ++j) {
         const int pl = j + ((np - 1 - j) / parts) * parts;
-        const RingPos rj = ring_at(seq + (uint32_t)pl, NPG);
+        RingPos rj = ua.rp0;
+        ring_advance(rj, pl, NPG);
         mbar_arrive(empty_bar(c, rj.slot));
         *reinterpret_cast<volatile uint32_t*>(&c.ctrl->released[rj.slot]) = rj.k + 1u;
       }
@@ -568,30 +583,37 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const mk_inst
 }
 
 template <int D, int QMODE>
-__device__ __forceinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, mk_instr_t ins, uint32_t seq, uint32_t ordpart) {
+__device__ __forceinline__ UnitResult at_unit_call(Ctx c, const mk_op_t* op, const UnitArgs& ua) {
   UnitResult r;
-  r.signal = at_unit<D, QMODE>(c, op, ins, seq, ordpart);
+  r.signal = at_unit<D, QMODE>(c, op, ua);
   r.dead = c.dead;
   r.trace_n = c.trace_n;
   return r;
 }
 
-template <int QMODE>
-__device__ __forceinline__ bool at_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ordpart) {
+template <int FEAT>
+__device__ __forceinline__ bool at_dispatch(Ctx& c, const mk_op_t* op, const UnitArgs& ua) {
+  constexpr int QMODE = (FEAT & MK_F_QKNORM) ? 1 : 0;
   UnitResult r;
-  if (op->i[MK_AT_D] == 64)
-    r = at_unit_call<64, QMODE>(c, op, ins, seq, ordpart);
-  else
-    r = at_unit_call<128, QMODE>(c, op, ins, seq, ordpart);
+  if constexpr ((FEAT & MK_F_AT64) && (FEAT & MK_F_AT128)) {
+    if (op->i[MK_AT_D] == 64)
+      r = at_unit_call<64, QMODE>(c, op, ua);
+    else
+      r = at_unit_call<128, QMODE>(c, op, ua);
+  } else if constexpr ((FEAT & MK_F_AT64) != 0) {
+    r = at_unit_call<64, QMODE>(c, op, ua);
+  } else {
+    r = at_unit_call<128, QMODE>(c, op, ua);
+  }
   c.dead = r.dead;
   c.trace_n = r.trace_n;
   return r.signal;
 }
 
 // Combine: one unit per (b, query head); all M rows.
-__device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins) {
+__device__ __forceinline__ void at_combine_unit(Ctx& c, const mk_op_t* op, int unit) {
   const int H = op->i[MK_AT_H], M = op->i[MK_AT_M], D = op->i[MK_AT_D], S = op->i[MK_AT_SPLITS];
-  const int b = ins.unit / H, h = ins.unit - b * H;
+  const int b = unit / H, h = unit - b * H;
   const float* opart = reinterpret_cast<const float*>(op->p[MK_AT_P_OPART]);
   const float* lpart = reinterpret_cast<const float*>(op->p[MK_AT_P_LSEPART]);
   float* lse_out = reinterpret_cast<float*>(op->p[MK_AT_P_LSE]);

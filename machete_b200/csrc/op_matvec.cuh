@@ -26,46 +26,7 @@
 
 namespace mk {
 
-struct MvRows {
-  const uint8_t* wa;
-  const uint8_t* wb;
-  const uint8_t* sa;  // scales
-  const uint8_t* sb;
-  int rowA0, rowB0, nA, nB;
-};
-
 __device__ __forceinline__ int clamp8(int v) { return v < 0 ? 0 : (v > 8 ? 8 : v); }
-
-__device__ __forceinline__ MvRows mv_rows(const mk_op_t* op, int unit) {
-  MvRows r;
-  const int O = op->i[MK_MV_O];
-  const int mode = op->i[MK_MV_MODE];
-  r.wa = reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_W0]);
-  r.sa = reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_SC0]);
-  if (mode == MK_MV_PLAIN) {
-    r.wb = r.wa;
-    r.sb = r.sa;
-    r.rowA0 = unit * 16;
-    r.rowB0 = unit * 16 + 8;
-    r.nA = clamp8(O - r.rowA0);
-    r.nB = clamp8(O - r.rowB0);
-  } else if (mode == MK_MV_PAIR) {
-    r.wb = reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_W1]);
-    r.sb = reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_SC1]);
-    r.rowA0 = r.rowB0 = unit * 8;
-    r.nA = r.nB = clamp8(O - r.rowA0);
-  } else {  // MK_MV_ROPE
-    const int hd = op->i[MK_MV_HD], d2 = op->i[MK_MV_D2];
-    const int upb = d2 >> 3;
-    const int h = unit / upb, j = (unit - h * upb) * 8;
-    r.wb = r.wa;
-    r.sb = r.sa;
-    r.rowA0 = h * hd + j;
-    r.rowB0 = r.rowA0 + d2;
-    r.nA = r.nB = 8;
-  }
-  return r;
-}
 
 __device__ __forceinline__ bool mv_is_fp4(int wfmt) { return wfmt >= MK_W_NVFP4_F16S32; }
 
@@ -145,6 +106,18 @@ __device__ __forceinline__ int mv_act_type(const mk_op_t* op) {
   return op->i[MK_MV_WFMT] == MK_W_BF16 ? MK_T_BF16 : MK_T_FP16;
 }
 
+// With bf16 weights the RMSNorm scale is taken out of the staged row: the
+// row is staged as bf16(x * w) in ONE pass while its sum of squares is
+// collected, and the epilogue multiplies the accumulators by
+// rsqrt(mean(x^2) + eps) — W·(x∘w)·r = r·(W·(x∘w)), r being one scalar per
+// row.  The first mma then waits for one trip to the activations, not for a
+// CTA-wide reduction and a second pass over the row.  (f16 staging, used with
+// NVFP4 weights, keeps the two-pass form: an unnormalised row may leave the
+// f16 range.)
+__device__ __forceinline__ bool mv_rstd_in_epilogue(const mk_op_t* op) {
+  return op->i[MK_MV_PRO] != MK_PRO_NONE && op->i[MK_MV_X_T] == MK_T_BF16 && op->i[MK_MV_WFMT] == MK_W_BF16;
+}
+
 // Stage pro(x) for all M rows into the shared activation buffer.  Called by
 // all consumer threads (tid in [0, kConsumerWarps*32)); the caller places a
 // consumer barrier before and after.  `stage` = fill the buffer,
@@ -159,6 +132,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   const int pro = op->i[MK_MV_PRO];
   const int xt = op->i[MK_MV_X_T];
   const int at = mv_act_type(op);
+  const bool fused = mv_rstd_in_epilogue(op);
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const int chunks = K >> 3;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_X]);
@@ -169,10 +143,9 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   write_res = write_res && add && ro != nullptr;
   if (!stage && !write_res) return;
 
-  // The norm weights do not depend on the row sums: request this thread's
-  // first chunks now, so that their latency overlaps the activation loads and
-  // the barrier instead of following them.
-  constexpr int kNwCached = 5;
+  // The norm weights do not depend on the activations: request this thread's
+  // first chunks now, so that their latency overlaps the activation loads.
+  constexpr int kNwCached = 6;
   uint4 nwc[kNwCached];
   if (stage && pro != MK_PRO_NONE) {
 #pragma unroll
@@ -181,8 +154,13 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
       nwc[i] = ch < chunks ? *reinterpret_cast<const uint4*>(nw + ch * 8) : make_uint4(0, 0, 0, 0);
     }
   }
+  if (stage && op->i[MK_MV_TR] == MK_TR_ROPE && tid < 2 * S) {
+    // the epilogue's cos / sin rows: pull them into L1 while the activations are on their way
+    const uint8_t* tab = reinterpret_cast<const uint8_t*>(op->p[(tid & 1) ? MK_MV_P_SIN : MK_MV_P_COS]);
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + (size_t)(tid >> 1) * (size_t)op->s[MK_MV_S_COS] * 2u));
+  }
 
-  auto absorb = [&](int m, uint16_t* wr, float& sum, int ch, uint4 v, uint4 rv) {
+  auto absorb = [&](int m, uint16_t* wr, float& sum, int ch, uint4 v, uint4 rv, uint4 wv) {
     float f[8];
     unpack8(v, xt, f);
     if (add) {
@@ -197,15 +175,29 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     if (stage) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) sum += f[i] * f[i];
-      // keep the (rounded) input in its own type for now; pass 2 rescales
+      if (fused) {
+        float w[8];
+        unpack8(wv, xt, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= w[i];
+        v = pack8(f, xt);
+      }
+      // not fused: keep the (rounded) input in its own type for now; pass 2 rescales
       sts128(c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u, v);
     }
   };
   auto row_ptrs = [&](int m, const uint16_t*& xr, const uint16_t*& rr, uint16_t*& wr) {
-    const int b = m / S, s = m - b * S;
+    int b = m, s = 0;
+    if (S != 1) {
+      b = m / S;
+      s = m - b * S;
+    }
     xr = x + b * op->s[MK_MV_S_X_B] + s * op->s[MK_MV_S_X_S];
     rr = add ? ri + b * op->s[MK_MV_S_RI_B] + s * op->s[MK_MV_S_RI_S] : nullptr;
     wr = write_res ? ro + b * op->s[MK_MV_S_RO_B] + s * op->s[MK_MV_S_RO_S] : nullptr;
+  };
+  auto norm_chunk = [&](int ch) -> uint4 {
+    return fused ? *reinterpret_cast<const uint4*>(nw + ch * 8) : make_uint4(0, 0, 0, 0);
   };
   const uint4 z = make_uint4(0, 0, 0, 0);
   if (!GROUPED || M == 1) {
@@ -216,15 +208,22 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     float sum = 0.f;
     // two chunks per step, both requested before either is used (the stores to
     // shared memory keep the compiler from hoisting the second load itself)
-    for (int ch = tid; ch < chunks; ch += 2 * T) {
-      const int ch2 = ch + T;
+#pragma unroll
+    for (int i = 0; i < kNwCached; i += 2) {
+      const int ch = tid + i * T, ch2 = ch + T;
+      if (ch >= chunks) break;
       const bool two = ch2 < chunks;
       const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
       const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
       const uint4 v2 = two ? *reinterpret_cast<const uint4*>(xr + ch2 * 8) : z;
       const uint4 r2 = (two && add) ? *reinterpret_cast<const uint4*>(rr + ch2 * 8) : z;
-      absorb(m, wr, sum, ch, v1, r1);
-      if (two) absorb(m, wr, sum, ch2, v2, r2);
+      absorb(m, wr, sum, ch, v1, r1, nwc[i]);
+      if (two) absorb(m, wr, sum, ch2, v2, r2, nwc[i + 1]);
+    }
+    for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
+      const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
+      const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
+      absorb(m, wr, sum, ch, v1, r1, norm_chunk(ch));
     }
     if (stage && pro != MK_PRO_NONE) {
       sum = warp_sum(sum);
@@ -245,7 +244,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
         row_ptrs(min(m0 + j, M - 1), xr[j], rr[j], wr[j]);
         sum[j] = 0.f;
       }
-      for (int ch = tid; ch < chunks; ch += T) {
+      auto step = [&](int ch, uint4 wv) {
         uint4 v[R], r[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
@@ -254,8 +253,15 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
         }
 #pragma unroll
         for (int j = 0; j < R; ++j)
-          if (j < nr) absorb(m0 + j, wr[j], sum[j], ch, v[j], r[j]);
+          if (j < nr) absorb(m0 + j, wr[j], sum[j], ch, v[j], r[j], wv);
+      };
+#pragma unroll
+      for (int i = 0; i < kNwCached; ++i) {
+        const int ch = tid + i * T;
+        if (ch >= chunks) break;
+        step(ch, nwc[i]);
       }
+      for (int ch = tid + kNwCached * T; ch < chunks; ch += T) step(ch, norm_chunk(ch));
       if (stage && pro != MK_PRO_NONE) {
 #pragma unroll
         for (int j = 0; j < R; ++j) {
@@ -266,7 +272,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     }
   }
   if (!stage) return;
-  if (pro == MK_PRO_NONE && xt == at) return;
+  if (fused || (pro == MK_PRO_NONE && xt == at)) return;
   named_bar_sync(kConsumerBarrier, T);
   const float eps = op->f[MK_MV_F_EPS];
   for (int m = 0; m < M; ++m) {
@@ -319,18 +325,16 @@ __device__ __forceinline__ unsigned long long top1_key(float v, int idx) {
   return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (uint32_t)idx);
 }
 
-__device__ __forceinline__ void mv_store(const mk_op_t* op, int m, int o, float v) {
-  const int S = op->i[MK_MV_S], hd = op->i[MK_MV_HD];
-  const int b = m / S, s = m - b * S;
-  const int head = o / hd, dim = o - head * hd;
-  const int64_t off = b * op->s[MK_MV_S_O_B] + (int64_t)(s + op->i[MK_MV_POS]) * op->s[MK_MV_S_O_S] +
-                      head * op->s[MK_MV_S_O_H] + dim;
-  if (op->i[MK_MV_EPI] == MK_EPI_RESIDUAL) {
-    const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]);
-    const uint16_t rv = er[b * op->s[MK_MV_S_ER_B] + s * op->s[MK_MV_S_ER_S] + o];
-    v += (op->i[MK_MV_X_T] == MK_T_BF16) ? bf16lo(rv) : f16lo(rv);
-  }
-  const int ot = op->i[MK_MV_OUT_T];
+// Output addressing without divisions: the instruction record carries, for
+// virtual rows 0-7 (a) and 8-15 (b), the first weight row and the element
+// offset of that row's result inside one activation row's output (head *
+// head stride + dim); what remains per activation row m is its (batch, s)
+// offset, which at decode (S = 1) is m * batch stride.
+struct MvOut {
+  int rowA0, rowB0, offA, offB, chunk;
+};
+
+__device__ __forceinline__ void mv_put(const mk_op_t* op, int ot, int64_t off, float v) {
   if (ot == MK_T_FP32) {
     reinterpret_cast<float*>(op->p[MK_MV_P_OUT])[off] = v;
   } else if (ot == MK_T_BF16) {
@@ -340,29 +344,45 @@ __device__ __forceinline__ void mv_store(const mk_op_t* op, int m, int o, float 
   }
 }
 
-template <int NT>
-__device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvRows& r, int unit,
-                                            float (&acc)[NT][4]) {
+template <int NT, int WFC, int FEAT>
+__device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvOut& r, float (&acc)[NT][4]) {
   const int g = c.lane >> 2, t = c.lane & 3;
-  const int M = op->i[MK_MV_M];
-  const int tr = op->i[MK_MV_TR], epi = op->i[MK_MV_EPI];
-  const float gs = (op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16) ? op->f[MK_MV_F_GSCALE] : 1.f;
-  const bool va = g < r.nA, vb = g < r.nB;
+  const int O = op->i[MK_MV_O], K = op->i[MK_MV_K], M = op->i[MK_MV_M], S = op->i[MK_MV_S];
+  const int mode = op->i[MK_MV_MODE], tr = op->i[MK_MV_TR], epi = op->i[MK_MV_EPI];
+  const int xt = op->i[MK_MV_X_T], ot = op->i[MK_MV_OUT_T];
+  const float gs = (WFC != 0 && op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16) ? op->f[MK_MV_F_GSCALE] : 1.f;
+  const bool fused = WFC != 2 && mv_rstd_in_epilogue(op);
+  const float eps = op->f[MK_MV_F_EPS];
+  const int nA = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowA0);
+  const int nB = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowB0);
+  const bool va = g < nA, vb = g < nB;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int m = nt * 8 + 2 * t + e;
       const bool vm = m < M;
-      float a = acc[nt][e] * gs, b = acc[nt][2 + e] * gs;
+      float scale = gs;
+      if (fused) {
+        // the row's RMSNorm scale, from the per-warp sums of squares the staging left behind
+        const float* rs = c.ctrl->red + (vm ? m : 0) * kConsumerWarps;
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) tot += rs[w];
+        scale *= rsqrtf(tot / (float)K + eps);
+      }
+      float a = acc[nt][e] * scale, b = acc[nt][2 + e] * scale;
+      int bb = m, ss = 0;
+      if (S != 1) {
+        bb = m / S;
+        ss = m - bb * S;
+      }
       if (tr == MK_TR_ROPE) {
         if (vm) {
-          const int S = op->i[MK_MV_S], hd = op->i[MK_MV_HD];
-          const int s = m % S;
-          const int d = (r.rowA0 % hd) + g;
-          const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + s * op->s[MK_MV_S_COS] + d;
-          const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + s * op->s[MK_MV_S_COS] + d;
-          const bool bf = op->i[MK_MV_X_T] == MK_T_BF16;
+          const int d = r.chunk * 8 + g;
+          const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + ss * op->s[MK_MV_S_COS] + d;
+          const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + ss * op->s[MK_MV_S_COS] + d;
+          const bool bf = xt == MK_T_BF16;
           const float cv = bf ? bf16lo(*cs) : f16lo(*cs);
           const float sv = bf ? bf16lo(*sn) : f16lo(*sn);
           const float a2 = a * cv - b * sv, b2 = b * cv + a * sv;
@@ -378,7 +398,7 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvR
         a = silu_f(a);
         b = silu_f(b);
       }
-      if (epi == MK_EPI_TOP1) {
+      if ((FEAT & MK_F_TOP1) != 0 && epi == MK_EPI_TOP1) {
         unsigned long long key = 0ull;
         const int idx0 = op->i[MK_MV_IDX0];
         if (va) key = top1_key(a, idx0 + r.rowA0 + g);
@@ -393,12 +413,17 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvR
         }
         if (g == 0 && vm) atomicMax(reinterpret_cast<unsigned long long*>(op->p[MK_MV_P_OUT]) + m, key);
       } else if (vm) {
-        if (tr == MK_TR_SILU_MUL) {
-          if (va) mv_store(op, m, r.rowA0 + g, a);
-        } else {
-          if (va) mv_store(op, m, r.rowA0 + g, a);
-          if (vb) mv_store(op, m, r.rowB0 + g, b);
+        const bool two = tr != MK_TR_SILU_MUL;
+        if (epi == MK_EPI_RESIDUAL) {
+          const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) + bb * op->s[MK_MV_S_ER_B] +
+                               ss * op->s[MK_MV_S_ER_S];
+          const uint16_t ra = va ? er[r.rowA0 + g] : (uint16_t)0, rb = (vb && two) ? er[r.rowB0 + g] : (uint16_t)0;
+          a += (xt == MK_T_BF16) ? bf16lo(ra) : f16lo(ra);
+          b += (xt == MK_T_BF16) ? bf16lo(rb) : f16lo(rb);
         }
+        const int64_t mo = bb * op->s[MK_MV_S_O_B] + (int64_t)(ss + op->i[MK_MV_POS]) * op->s[MK_MV_S_O_S];
+        if (va) mv_put(op, ot, mo + r.offA + g, a);
+        if (vb && two) mv_put(op, ot, mo + r.offB + g, b);
       }
     }
   }
@@ -451,13 +476,11 @@ __device__ __forceinline__ uint32_t tile_chunk(uint32_t tile, int r, int c) {
 // WFC fixes the weight-format family at compile time so that a kernel built
 // for one family carries only that code: 0 = bf16, 2 = NVFP4 (either scale
 // layout), -1 = decided per op at run time.
-template <int NT, int NA, int WFC>
-__device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ord) {
-  // ord: bits 0-27 = slot-set ordinal, bits 28-31 = this consumer's participant index
-  const int unit = ins.unit;
-  const int part = (int)(ord >> 28);
-  ord &= 0x0fffffffu;
-  const int parts = (ins.ld_flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+template <int NT, int NA, int WFC, int FEAT>
+__device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const UnitArgs& u) {
+  const int part = u.part;
+  const uint32_t ord = u.ord;
+  const int parts = (u.flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
   const int p0 = part;   // participant j takes pages j, j + parts, j + 2 parts, ...
   const int g = c.lane >> 2, t = c.lane & 3;
   const int K = op->i[MK_MV_K], Kc = op->i[MK_MV_KC], M = op->i[MK_MV_M];
@@ -465,21 +488,15 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
   const bool dense = WFC == 0 ? true : (WFC == 2 ? false : (wfmt == MK_W_BF16 || wfmt == MK_W_FP16));
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const uint32_t half = mv_half_bytes(wfmt, Kc);
-  if (op->i[MK_MV_EPI] == MK_EPI_RESIDUAL && c.lane < 2 * M) {
+  const int NPG = c.pv->n_pages;
+  if (part == 0 && op->i[MK_MV_EPI] == MK_EPI_RESIDUAL && op->i[MK_MV_S] == 1) {
     // whoever finishes the unit adds this residual: pull its lines into L1 now
-    const MvRows r0 = mv_rows(op, unit);
-    const int m = c.lane >> 1, S_ = op->i[MK_MV_S];
-    const int b = m / S_, s_ = m - b * S_;
-    const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) + b * op->s[MK_MV_S_ER_B] +
-                         s_ * op->s[MK_MV_S_ER_S] + ((c.lane & 1) ? r0.rowB0 : r0.rowA0);
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(er));
-  }
-  if (op->i[MK_MV_TR] == MK_TR_ROPE && c.lane < M) {
-    // likewise the cos/sin rows of the RoPE epilogue (one row per activation row)
-    const int S_ = op->i[MK_MV_S];
-    const size_t off = (size_t)(c.lane % S_) * (size_t)op->s[MK_MV_S_COS] * 2u;
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_COS]) + off));
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(op->p[MK_MV_P_SIN]) + off));
+    const int ra = ins_field(u.mine->row_a, u.idx), rb = ins_field(u.mine->row_b, u.idx);
+    if (c.lane < 2 * M) {
+      const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) +
+                           (c.lane >> 1) * op->s[MK_MV_S_ER_B] + ((c.lane & 1) ? rb : ra);
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(er));
+    }
   }
   float acc[NA][NT][4];
 #pragma unroll
@@ -498,12 +515,12 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     xrow[nt] = c.act_u32 + (uint32_t)(xok[nt] ? m : 0) * xs;
   }
 
-  const int np = ins.n_pages;
-  RingPos rp = ring_at(seq + (uint32_t)p0, c.pv->n_pages);
-  for (int p = p0; p < np; p += parts, ring_advance(rp, parts, c.pv->n_pages)) {
+  const int np = u.n_pages;
+  RingPos rp = u.rp;
+  for (int p = p0; p < np; p += parts, ring_advance(rp, parts, NPG)) {
     uint32_t page;
     if (!page_acquire(c, rp, page)) return false;
-    trace(c, TRC_PAGE_READY, seq + p);
+    trace(c, TRC_PAGE_READY, rp.k * (uint32_t)NPG + rp.slot);
     const long long cyc0 = clock64();
     const int k0 = p * Kc;
     const int kc = min(Kc, K - k0);
@@ -651,7 +668,7 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     }
     const long long cyc1 = clock64();
     page_release(c, rp);
-    trace(c, TRC_PAGE_DONE, seq + p);
+    trace(c, TRC_PAGE_DONE, rp.k * (uint32_t)NPG + rp.slot);
     trace(c, TRC_PAGE_CYCLES, (uint32_t)(cyc1 - cyc0));
   }
 #pragma unroll
@@ -706,27 +723,32 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const mk_inst
     }
   }
   trace(c, TRC_MV_REDUCED, ord);
-  const MvRows r = mv_rows(op, unit);
-  mv_epilogue<NT>(c, op, r, unit, acc[0]);
+  MvOut r;
+  r.rowA0 = ins_field(u.mine->row_a, u.idx);
+  r.rowB0 = ins_field(u.mine->row_b, u.idx);
+  r.offA = ins_field(u.mine->off_a, u.idx);
+  r.offB = ins_field(u.mine->off_b, u.idx);
+  r.chunk = (u.flags >> MK_LDF_CHUNK_SHIFT) & MK_LDF_CHUNK_MASK;
+  mv_epilogue<NT, WFC, FEAT>(c, op, r, acc[0]);
   trace(c, TRC_MV_EPILOGUE, ord);
   return true;
 }
 
 // NTC / WFC: the activation-tile count (1, 2, 4) and weight family the kernel
 // was built for, or 0 / -1 to decide per op.
-template <int NTC, int WFC>
-__device__ __forceinline__ bool mv_dispatch(Ctx& c, const mk_op_t* op, const mk_instr_t& ins, uint32_t seq, uint32_t ord) {
+template <int NTC, int WFC, int FEAT>
+__device__ __forceinline__ bool mv_dispatch(Ctx& c, const mk_op_t* op, const UnitArgs& u) {
   if constexpr (NTC == 1) {
-    return mv_unit<1, 4, WFC>(c, op, ins, seq, ord);
+    return mv_unit<1, 4, WFC, FEAT>(c, op, u);
   } else if constexpr (NTC == 2) {
-    return mv_unit<2, 2, WFC>(c, op, ins, seq, ord);
+    return mv_unit<2, 2, WFC, FEAT>(c, op, u);
   } else if constexpr (NTC == 4) {
-    return mv_unit<4, 1, WFC>(c, op, ins, seq, ord);
+    return mv_unit<4, 1, WFC, FEAT>(c, op, u);
   } else {
     const int M = op->i[MK_MV_M];
-    if (M <= 8) return mv_unit<1, 4, WFC>(c, op, ins, seq, ord);
-    if (M <= 16) return mv_unit<2, 2, WFC>(c, op, ins, seq, ord);
-    return mv_unit<4, 1, WFC>(c, op, ins, seq, ord);
+    if (M <= 8) return mv_unit<1, 4, WFC, FEAT>(c, op, u);
+    if (M <= 16) return mv_unit<2, 2, WFC, FEAT>(c, op, u);
+    return mv_unit<4, 1, WFC, FEAT>(c, op, u);
   }
 }
 

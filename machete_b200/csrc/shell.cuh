@@ -23,6 +23,21 @@ constexpr int kPartialBytes = kConsumerWarps * 2048;
 constexpr int kCtrlBytes = kCtrlStructBytes + kPartialBytes;
 constexpr uint32_t kConsumerBarrier = 1;
 
+// What a kernel variant is built to run (template parameter FEAT).  A program
+// needs the union of its ops' features; mk_create picks the smallest variant
+// that covers it.
+enum {
+  MK_F_AT64 = 1,     // split-KV attention, head dim 64
+  MK_F_AT128 = 2,    // split-KV attention, head dim 128
+  MK_F_QKNORM = 4,   // attention with the fused per-head q/k RMSNorm + rotation
+  MK_F_EW = 8,       // the row-wise ops: RMSNorm, RoPE, QK-norm + RoPE, GLU, add
+  MK_F_COMBINE = 16, // the stand-alone log-sum-exp combine op
+  MK_F_AR = 32,      // the in-kernel all-reduce (tensor parallel)
+  MK_F_TOP1 = 64,    // top-1 epilogue and its finalise op
+  MK_F_TRACE = 128,  // event trace
+  MK_F_ALL = 255
+};
+
 // Device status codes (status[0]).
 enum {
   MK_ST_OK = 0,
@@ -86,7 +101,9 @@ enum {
   TRC_MV_REDUCED = 13,  // consumer: partials of the unit summed, epilogue starts (arg = ordinal)
   TRC_MV_EPILOGUE = 14, // consumer: epilogue stores issued (arg = ordinal)
   TRC_AT_COUNTED = 15,  // attention: this split counted in (arg = 1 when it completes its group)
-  TRC_AT_FETCHED = 16   // attention combine: first batch of partials accumulated (arg = row pass)
+  TRC_AT_FETCHED = 16,  // attention combine: first batch of partials accumulated (arg = row pass)
+  TRC_SYNC_CLOCK = 30,  // time base: t = the SM's cycle counter ...
+  TRC_SYNC_NS = 31      // ... and t = the nanosecond timer at the same moment
 };
 
 // Shared-memory control block (first kCtrlBytes of dynamic smem).
@@ -99,14 +116,19 @@ struct Ctrl {
   // the set have finished their epilogue.
   uint32_t mv_arrive[4];
   uint32_t mv_done[4];
-  uint32_t bulk_done;  // units of the current op finished on this CTA (bulk signalling)
+  // units of an op finished on this CTA (bulk signalling); one word per op-record slot
+  uint32_t bulk_done[2];
   uint32_t ticket;     // next consumer slot of the CTA (see consumer_loop)
-  int32_t pad[4];
+  uint32_t ev_arrive;  // consumer warps that have reached an op-entry event (kConsumerWarps per event)
+  int32_t pad[2];
   // released[slot] = number of fills of the slot that consumers have handed back
   uint32_t released[kMaxPages];
-  float red[kConsumerWarps * 32];  // block-reduction scratch (per row, per warp)
-  // copy of the record of the op the CTA is working on (refreshed by its op-entry event)
-  __align__(16) mk_op_t op_cache;
+  // per activation row and consumer warp: sum of squares of the staged row (RMSNorm)
+  float red[kConsumerWarps * 32];
+  // Records of the op the CTA is working on and of the op of its next op-entry
+  // event (event k uses slot k & 1; the other slot is refilled one event ahead,
+  // so an event never waits for its op record).
+  __align__(16) mk_op_t op_cache[2];
 };
 static_assert(sizeof(Ctrl) <= kCtrlStructBytes, "control block too large");
 
@@ -127,6 +149,34 @@ struct Ctx {
   TraceRec* trace_base;  // this warp's trace ring (lane 0 only), null = off
 };
 
+// The consumers' registers for one instruction record (one record per lane of
+// a 32-record window; fields are fetched from the owning lane by shuffle).
+struct InsRegs {
+  int op, unit, signal, n_waits, wait_off, n_pages;
+  int flags;                       // ld_flags, bit 31 = unit shared page by page
+  int row_a, row_b, off_a, off_b;  // see mk_instr_t
+};
+
+// Position of a ring entry: slot index and how many times the slot was filled
+// before (seq = k * n_pages + slot).  Kept incrementally, never divided.
+struct RingPos {
+  uint32_t slot, k;
+};
+
+// What the shell hands to a unit handler.
+struct UnitArgs {
+  const InsRegs* mine;  // the warp's instruction window
+  int idx;              // lane of the window that holds this unit's record
+  int op, unit, n_pages, flags;
+  int part;             // this consumer's participant index within the unit
+  uint32_t ord;         // shared units before this one on the CTA (selects the split-K slot set)
+  RingPos rp0;          // ring position of the unit's first page
+  RingPos rp;           // ring position of this participant's first page
+};
+__device__ __forceinline__ int ins_field(const int& field_of_mine, int idx) {
+  return __shfl_sync(0xffffffffu, field_of_mine, idx);
+}
+
 // What a non-inlined unit handler hands back to the shell.
 struct UnitResult {
   bool dead;
@@ -135,22 +185,46 @@ struct UnitResult {
 };
 
 // The per-warp ring base is resolved once at kernel start (null = tracing
-// off), so a disabled trace point costs one predicated branch.
+// off), so a disabled trace point costs one predicated branch.  Records are
+// stamped with the SM's cycle counter, which costs a few cycles to read (the
+// nanosecond timer costs a fraction of a microsecond, enough to distort what
+// is being measured); every ring opens and closes with a pair of records that
+// hold the cycle counter and the nanosecond timer at the same moment, from
+// which the host maps cycles to a time base common to all CTAs.
+__device__ __forceinline__ uint64_t sm_clock() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_sync_pair(Ctx& c) {
+  if (c.trace_n + 2 <= c.trace_cap) {
+    TraceRec* r = c.trace_base + c.trace_n;
+    r[0].t = sm_clock();
+    r[0].code = TRC_SYNC_CLOCK;
+    r[0].arg = 0;
+    r[1].t = globaltimer_ns();
+    r[1].code = TRC_SYNC_NS;
+    r[1].arg = 0;
+  }
+  c.trace_n += 2;
+}
+template <bool TRACED>
 __device__ __forceinline__ void trace_init(Ctx& c) {
   c.trace_n = 0;
   c.trace_cap = 0;
-  c.trace_base = nullptr;
-  TraceRec* base = c.pv->trace;
-  if (base != nullptr && c.lane == 0) {
-    c.trace_cap = c.pv->trace_cap;
-    c.trace_base = base + ((size_t)blockIdx.x * (kConsumerWarps + 1) + c.warp) * c.trace_cap;
+  c.trace_base = nullptr;   // stays null in a kernel built without tracing: every trace point folds away
+  TraceRec* base = TRACED ? c.pv->trace : nullptr;
+  if (TRACED && base != nullptr && c.lane == 0) {
+    c.trace_cap = c.pv->trace_cap - 2;   // room for the closing pair
+    c.trace_base = base + ((size_t)blockIdx.x * (kConsumerWarps + 1) + c.warp) * c.pv->trace_cap;
+    trace_sync_pair(c);
   }
 }
 __device__ __forceinline__ void trace(Ctx& c, uint32_t code, uint32_t arg) {
   if (c.trace_base == nullptr) return;
   if (c.trace_n < c.trace_cap) {
     TraceRec* r = c.trace_base + c.trace_n;
-    r->t = globaltimer_ns();
+    r->t = sm_clock();
     r->code = code;
     r->arg = arg;
   }
@@ -158,7 +232,10 @@ __device__ __forceinline__ void trace(Ctx& c, uint32_t code, uint32_t arg) {
 }
 __device__ __forceinline__ void trace_flush(Ctx& c) {
   if (c.trace_base == nullptr) return;
-  int32_t* counts = reinterpret_cast<int32_t*>(c.pv->trace + (size_t)gridDim.x * (kConsumerWarps + 1) * c.trace_cap);
+  if (c.trace_n > c.trace_cap) c.trace_n = c.trace_cap;   // overflowed: the closing pair goes into the reserve
+  c.trace_cap += 2;
+  trace_sync_pair(c);
+  int32_t* counts = reinterpret_cast<int32_t*>(c.pv->trace + (size_t)gridDim.x * (kConsumerWarps + 1) * c.pv->trace_cap);
   counts[blockIdx.x * (kConsumerWarps + 1) + c.warp] = c.trace_n;
 }
 
@@ -304,12 +381,6 @@ __device__ __forceinline__ bool wait_released(Ctx& c, uint32_t slot, uint32_t k,
   }
 }
 
-// Position of a ring entry: slot index and how many times the slot was filled
-// before (seq = k * n_pages + slot).  Kept incrementally: one division per
-// unit instead of two per page.
-struct RingPos {
-  uint32_t slot, k;
-};
 __device__ __forceinline__ RingPos ring_at(uint32_t seq, int np) {
   RingPos r;
   r.k = seq / (uint32_t)np;
@@ -380,16 +451,48 @@ __device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, ui
 // the CTA's last unit of the op publishes all of them with one device-scope
 // release (the earlier finishers' writes reach it through the cta-scope
 // fences around the shared-memory counter).
-__device__ __forceinline__ void signal_unit_bulk(Ctx& c, int counter, int units) {
+__device__ __forceinline__ void signal_unit_bulk(Ctx& c, uint32_t* done, int counter, int units) {
   __syncwarp();
   if (c.lane == 0 && counter >= 0) {
     __threadfence_block();
-    const uint32_t old = atomicAdd(&c.ctrl->bulk_done, 1u);
+    const uint32_t old = atomicAdd(done, 1u);
     if (old == (uint32_t)(units - 1)) {
       __threadfence_block();
       red_release_gpu_add(c.pv->counters + counter, units);   // the release is the device-scope fence
     }
   }
+}
+
+// The wait that opens a dependency stage.  `ev_word` is the event record held
+// one 32-bit word per lane (mk_event_t is 16 words): lanes 0-3 poll the four
+// inline (counter, expected) pairs side by side; longer lists continue in the
+// wait table.
+__device__ __forceinline__ bool wait_event(Ctx& c, int ev_word, int n, int off) {
+  if (c.dead) return false;
+  if (n <= 0) return true;
+  const int my_c = __shfl_sync(0xffffffffu, ev_word, 6 + (c.lane & 3));
+  const int my_e = __shfl_sync(0xffffffffu, ev_word, 10 + (c.lane & 3));
+  const bool mine = c.lane < (n < 4 ? n : 4);
+  const int32_t* ctr = c.pv->counters + (mine ? my_c : 0);
+  uint64_t t0 = 0;
+  for (int spin = 0;; ++spin) {
+    // relaxed polls: an acquire load drops the SM's L1 contents each time, and the
+    // other warps of the CTA are still running units while this one waits
+    const bool ok = !mine || ld_relaxed_gpu(ctr) >= my_e;
+    if (__all_sync(0xffffffffu, ok)) {
+      fence_acq_rel_gpu();
+      break;
+    }
+    if ((spin & 15) == 15) {
+      if (t0 == 0) t0 = globaltimer_ns();
+      if (give_up_check(c, t0, MK_ST_TIMEOUT_COUNTER, my_c, my_e)) {
+        c.dead = true;
+        return false;
+      }
+    }
+  }
+  if (n > 4) return wait_counters(c, n - 4, off + 4);
+  return true;
 }
 
 }  // namespace mk

@@ -310,7 +310,13 @@ class Megakernel:
             N.check(N.lib().mk_set_trace(self._handle, None, 0, 0), "mk_set_trace")
 
     def read_trace(self):
-        """Return ``{(cta, warp): structured array of (t, code, arg)}`` of the last launch."""
+        """Return ``{(cta, warp): structured array of (t, code, arg)}`` of the last launch.
+
+        ``t`` is in nanoseconds on a time base common to all CTAs.  The device
+        stamps records with its cycle counter and brackets every warp's ring
+        with (cycle counter, nanosecond timer) pairs (codes 30 / 31); the
+        cycles are mapped linearly between the two pairs here.
+        """
         torch.cuda.synchronize(self._dev)
         raw = self._trace_buf.cpu().numpy()
         warps_per_cta = NUM_CONSUMER_WARPS + NUM_DMA_WARPS
@@ -321,7 +327,18 @@ class Megakernel:
         out = {}
         for wi in range(warps):
             n = min(int(counts[wi]), cap)
-            out[(wi // warps_per_cta, wi % warps_per_cta)] = recs[wi, :n].copy()
+            arr = recs[wi, :n].copy()
+            clk = np.flatnonzero(arr["code"] == 30)
+            if len(clk) >= 2 and clk[-1] + 1 < n:
+                c0, g0 = int(arr["t"][clk[0]]), int(arr["t"][clk[0] + 1])
+                c1, g1 = int(arr["t"][clk[-1]]), int(arr["t"][clk[-1] + 1])
+                scale = (g1 - g0) / max(1, c1 - c0)
+                keep = arr["code"] < 30
+                arr = arr[keep]
+                # integer arithmetic around g0: the timer's magnitude (~2**60 ns) exceeds float64's exact range
+                delta = np.rint((arr["t"].astype(np.int64) - c0) * scale).astype(np.int64)
+                arr["t"] = (np.int64(g0) + delta).astype(np.uint64)
+            out[(wi // warps_per_cta, wi % warps_per_cta)] = arr
         return out
 
     def export_chrome_trace(self, path: str, ctas=(0,)) -> None:
