@@ -105,72 +105,48 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
         if (!wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
         trace(c, TRC_LWAIT_DONE, base + i);
       }
-      if (ins.maps != 0 && (ins.flags & MK_LDF_ATTN)) {
-        // A split-KV attention unit: one K box and one V box per page (two each
-        // for head dim 128), issued by lane 0 from the instruction record.
-        if (ins.n_lwaits > 0) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
-        int issued = 0;
-        if (c.lane == 0) {
-          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
-          RingPos q = rp;
-          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
-            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
-                               (int)(seq + issued)))
-              break;
-            trace(c, TRC_LOAD_BEGIN, seq + issued);
+      if (ins.maps == 0) continue;   // only units with tensor maps stream pages
+      // Pages are issued by lane 0 alone in a tight loop from the fields of the
+      // instruction record (no op-table read on this path; a one-thread wait
+      // needs no vote).  Fill k of a slot needs fill k-1 handed back:
+      // empty-barrier phase k-1.  A split-KV attention page is one K box and one
+      // V box (two each for head dim 128), a matvec page two weight boxes
+      // (plus two scale boxes for NVFP4).
+      const bool attn = (ins.flags & MK_LDF_ATTN) != 0;
+      if (attn && ins.n_lwaits > 0) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
+      int issued = 0;
+      if (c.lane == 0) {
+        const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
+        const bool pair = (ins.flags & MK_LDF_PAIR) != 0;
+        MvLoad ml;
+        ml.fp4 = (ins.flags & MK_LDF_FP4) != 0;
+        ml.tm_a = maps;
+        ml.tm_b = maps + (pair ? 128 : 0);
+        ml.ts_a = maps + 256;
+        ml.ts_b = maps + (pair ? 384 : 256);
+        ml.rowA0 = ins.row_a;
+        ml.rowB0 = ins.row_b;
+        ml.tiles_per_page = ins.tiles;
+        ml.half = (uint32_t)ins.tiles * 1024u;
+        RingPos q = rp;
+#pragma unroll 1
+        for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
+          if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY, (int)(seq + issued)))
+            break;
+          trace(c, TRC_LOAD_BEGIN, seq + issued);
+          const uint32_t page = c.pages_u32 + q.slot * (uint32_t)pv.page_bytes;
+          if (attn)
             at_load_issue(maps, maps + 128, (ins.flags & MK_LDF_D128) != 0, ins.tiles, ins.row_a + issued * ins.tiles,
-                          ins.row_b & 0xffff, ins.row_b >> 16, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes,
-                          full_bar(c, q.slot), policy);
-            trace(c, TRC_LOAD_ISSUED, seq + issued);
-          }
-        }
-        issued = __shfl_sync(0xffffffffu, issued, 0);
-        if (issued < ins.n_pages) c.dead = true;
-        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
-        seq += (uint32_t)issued;
-      } else if (ins.maps != 0) {
-        // A matvec unit: tiled-TMA pages, issued by lane 0 alone in a tight
-        // loop from the fields of the instruction record (no op-table read on
-        // this path; a one-thread wait needs no vote).  Fill k of a slot needs
-        // fill k-1 handed back: empty-barrier phase k-1.
-        int issued = 0;
-        if (c.lane == 0) {
-          MvLoad ml;
-          const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
-          const bool pair = (ins.flags & MK_LDF_PAIR) != 0;
-          ml.fp4 = (ins.flags & MK_LDF_FP4) != 0;
-          ml.tm_a = maps;
-          ml.tm_b = maps + (pair ? 128 : 0);
-          ml.ts_a = maps + 256;
-          ml.ts_b = maps + (pair ? 384 : 256);
-          ml.rowA0 = ins.row_a;
-          ml.rowB0 = ins.row_b;
-          ml.tiles_per_page = ins.tiles;
-          ml.half = (uint32_t)ins.tiles * 1024u;
-          RingPos q = rp;
-          for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
-            if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY,
-                               (int)(seq + issued)))
-              break;
-            trace(c, TRC_LOAD_BEGIN, seq + issued);
-            mv_load_issue(ml, issued, c.pages_u32 + q.slot * (uint32_t)pv.page_bytes, full_bar(c, q.slot), policy);
-            trace(c, TRC_LOAD_ISSUED, seq + issued);
-          }
-        }
-        issued = __shfl_sync(0xffffffffu, issued, 0);
-        if (issued < ins.n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
-        for (int p = 0; p < issued; ++p) ring_next(rp, NP);
-        seq += (uint32_t)issued;
-      } else {
-        for (int p = 0; p < ins.n_pages; ++p) {
-          if (!wait_mbar(c, empty_bar(c, rp.slot), (rp.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY, (int)seq)) break;
-          trace(c, TRC_LOAD_BEGIN, seq);
-          mbar_arrive(full_bar(c, rp.slot));  // an op without loads: hand over an empty page
-          trace(c, TRC_LOAD_ISSUED, seq);
-          ++seq;
-          ring_next(rp, NP);
+                          ins.row_b & 0xffff, ins.row_b >> 16, page, full_bar(c, q.slot), policy);
+          else
+            mv_load_issue(ml, issued, page, full_bar(c, q.slot), policy);
+          trace(c, TRC_LOAD_ISSUED, seq + issued);
         }
       }
+      issued = __shfl_sync(0xffffffffu, issued, 0);
+      if (issued < ins.n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
+      ring_advance(rp, issued, NP);
+      seq += (uint32_t)issued;
     }
   }
   // Every copy this warp issued must have landed before the CTA may exit.
@@ -316,7 +292,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     cached_rec = op;
     if (op->opcode == MK_OP_MATVEC) {
       const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-      mv_stage<!(NTC == 1 && WFC == 0)>(c, op, need, (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
+      mv_stage<!(NTC == 1 && WFC == 0), WFC>(c, op, need, (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
       staged_key = op->act_key;
     }
     if (w == 1 && have_next) {

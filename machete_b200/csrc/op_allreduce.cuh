@@ -70,12 +70,9 @@ __device__ __forceinline__ bool ar_wait_flags(Ctx& c, const uint32_t* flags, int
   for (int spin = 0;; ++spin) {
     const bool ok = !mine || (int32_t)(ld_acquire_sys_u32(f) - epoch) >= 0;
     if (__all_sync(0xffffffffu, ok)) return true;
-    if ((spin & 15) == 15) {
-      if (t0 == 0) t0 = globaltimer_ns();
-      if (give_up_check(c, t0, MK_ST_TIMEOUT_PEER, unit, (int)epoch)) {
-        c.dead = true;
-        return false;
-      }
+    if ((spin & 15) == 15 && give_up_check(c, t0, MK_ST_TIMEOUT_PEER, unit, (int)epoch)) {
+      c.dead = true;
+      return false;
     }
   }
 }
@@ -176,12 +173,9 @@ __device__ __forceinline__ void ew_allreduce(Ctx& c, const mk_op_t* op, int unit
         }
       }
       if (__all_sync(0xffffffffu, ok)) break;
-      if ((spin & 15) == 15) {
-        if (t0 == 0) t0 = globaltimer_ns();
-        if (give_up_check(c, t0, MK_ST_TIMEOUT_PEER, unit, r)) {
-          c.dead = true;
-          return;
-        }
+      if ((spin & 15) == 15 && give_up_check(c, t0, MK_ST_TIMEOUT_PEER, unit, r)) {
+        c.dead = true;
+        return;
       }
     }
     if (valid) {

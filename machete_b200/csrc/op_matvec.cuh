@@ -122,17 +122,29 @@ __device__ __forceinline__ bool mv_rstd_in_epilogue(const mk_op_t* op) {
 // all consumer threads (tid in [0, kConsumerWarps*32)); the caller places a
 // consumer barrier before and after.  `stage` = fill the buffer,
 // `write_res` = also materialise residual_out = x + residual_in in global.
-// GROUPED: rows are fetched four at a time (kernels that serve batches); the kernel of the
-// batch-1 bf16 step keeps the one-row loop alone, whose code placement it is sensitive to.
-template <bool GROUPED>
+//
+// The code is kept small on purpose (loops are not unrolled beyond what the
+// memory latency asks for): it runs once per op on every CTA, always from a
+// cold instruction cache.
+//   * no prologue, same type: the rows are copied global -> shared with
+//     16-byte asynchronous copies, all in flight at once;
+//   * RMSNorm prologue: R rows x 2 chunks per thread are requested together
+//     (one trip to L2), then reduced; R = 1 for the batch-1 kernel, 4 otherwise.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <bool GROUPED, int WFC>
 __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, bool write_res) {
   const int tid = (c.warp - 1) * 32 + c.lane;
   constexpr int T = kConsumerWarps * 32;
   const int K = op->i[MK_MV_K], M = op->i[MK_MV_M], S = op->i[MK_MV_S];
   const int pro = op->i[MK_MV_PRO];
-  const int xt = op->i[MK_MV_X_T];
-  const int at = mv_act_type(op);
-  const bool fused = mv_rstd_in_epilogue(op);
+  // a kernel built for one weight family knows its activation types
+  const int xt = WFC == 0 ? (int)MK_T_BF16 : op->i[MK_MV_X_T];
+  const int at = WFC == 0 ? (int)MK_T_BF16 : (WFC == 2 ? (int)MK_T_FP16 : mv_act_type(op));
+  const bool fused = WFC != 2 && mv_rstd_in_epilogue(op);
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const int chunks = K >> 3;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_X]);
@@ -142,172 +154,128 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   const bool add = (pro == MK_PRO_ADD_RMS) && ri != nullptr;
   write_res = write_res && add && ro != nullptr;
   if (!stage && !write_res) return;
-
-  // The norm weights do not depend on the activations: request this thread's
-  // first chunks now, so that their latency overlaps the activation loads.
-  constexpr int kNwCached = 6;
-  uint4 nwc[kNwCached];
-  if (stage && pro != MK_PRO_NONE) {
-#pragma unroll
-    for (int i = 0; i < kNwCached; ++i) {
-      const int ch = tid + i * T;
-      nwc[i] = ch < chunks ? *reinterpret_cast<const uint4*>(nw + ch * 8) : make_uint4(0, 0, 0, 0);
-    }
-  }
   if (stage && op->i[MK_MV_TR] == MK_TR_ROPE && tid < 2 * S) {
     // the epilogue's cos / sin rows: pull them into L1 while the activations are on their way
     const uint8_t* tab = reinterpret_cast<const uint8_t*>(op->p[(tid & 1) ? MK_MV_P_SIN : MK_MV_P_COS]);
     asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + (size_t)(tid >> 1) * (size_t)op->s[MK_MV_S_COS] * 2u));
   }
-
-  auto absorb = [&](int m, uint16_t* wr, float& sum, int ch, uint4 v, uint4 rv, uint4 wv) {
-    float f[8];
-    unpack8(v, xt, f);
-    if (add) {
-      float r[8];
-      unpack8(rv, xt, r);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] += r[i];
-      round8(f, xt);
-      v = pack8(f, xt);
-      if (wr) *reinterpret_cast<uint4*>(wr + ch * 8) = v;
-    }
-    if (stage) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sum += f[i] * f[i];
-      if (fused) {
-        float w[8];
-        unpack8(wv, xt, w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] *= w[i];
-        v = pack8(f, xt);
-      }
-      // not fused: keep the (rounded) input in its own type for now; pass 2 rescales
-      sts128(c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u, v);
-    }
-  };
-  auto row_ptrs = [&](int m, const uint16_t*& xr, const uint16_t*& rr, uint16_t*& wr) {
-    int b = m, s = 0;
+  auto row_off = [&](int m, int sb, int ss) -> int64_t {
+    int b = m, s2 = 0;
     if (S != 1) {
       b = m / S;
-      s = m - b * S;
+      s2 = m - b * S;
     }
-    xr = x + b * op->s[MK_MV_S_X_B] + s * op->s[MK_MV_S_X_S];
-    rr = add ? ri + b * op->s[MK_MV_S_RI_B] + s * op->s[MK_MV_S_RI_S] : nullptr;
-    wr = write_res ? ro + b * op->s[MK_MV_S_RO_B] + s * op->s[MK_MV_S_RO_S] : nullptr;
+    return b * op->s[sb] + s2 * op->s[ss];
   };
-  auto norm_chunk = [&](int ch) -> uint4 {
-    return fused ? *reinterpret_cast<const uint4*>(nw + ch * 8) : make_uint4(0, 0, 0, 0);
-  };
+
+  if (pro == MK_PRO_NONE && xt == at) {
+    // plain copy
+#pragma unroll 1
+    for (int m = 0; m < M; ++m) {
+      const uint16_t* xr = x + row_off(m, MK_MV_S_X_B, MK_MV_S_X_S);
+      const uint32_t dst = c.act_u32 + (uint32_t)m * xs;
+#pragma unroll 1
+      for (int ch = tid; ch < chunks; ch += T) cp_async16(dst + (uint32_t)ch * 16u, xr + ch * 8);
+    }
+    cp_async_wait_all();
+    return;
+  }
+
+  constexpr int R = GROUPED ? 4 : 1;
   const uint4 z = make_uint4(0, 0, 0, 0);
-  if (!GROUPED || M == 1) {
-   for (int m = 0; m < M; ++m) {
-    const uint16_t *xr, *rr;
-    uint16_t* wr;
-    row_ptrs(m, xr, rr, wr);
-    float sum = 0.f;
-    // two chunks per step, both requested before either is used (the stores to
-    // shared memory keep the compiler from hoisting the second load itself)
+#pragma unroll 1
+  for (int m0 = 0; m0 < M; m0 += R) {
+    const uint16_t *xr[R], *rr[R];
+    uint16_t* wr[R];
+    float sum[R];
 #pragma unroll
-    for (int i = 0; i < kNwCached; i += 2) {
-      const int ch = tid + i * T, ch2 = ch + T;
-      if (ch >= chunks) break;
-      const bool two = ch2 < chunks;
-      const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
-      const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
-      const uint4 v2 = two ? *reinterpret_cast<const uint4*>(xr + ch2 * 8) : z;
-      const uint4 r2 = (two && add) ? *reinterpret_cast<const uint4*>(rr + ch2 * 8) : z;
-      absorb(m, wr, sum, ch, v1, r1, nwc[i]);
-      if (two) absorb(m, wr, sum, ch2, v2, r2, nwc[i + 1]);
+    for (int j = 0; j < R; ++j) {
+      const int m = min(m0 + j, M - 1);
+      xr[j] = x + row_off(m, MK_MV_S_X_B, MK_MV_S_X_S);
+      rr[j] = add ? ri + row_off(m, MK_MV_S_RI_B, MK_MV_S_RI_S) : x;
+      wr[j] = write_res ? ro + row_off(m, MK_MV_S_RO_B, MK_MV_S_RO_S) : nullptr;
+      sum[j] = 0.f;
     }
-    for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
-      const uint4 v1 = *reinterpret_cast<const uint4*>(xr + ch * 8);
-      const uint4 r1 = add ? *reinterpret_cast<const uint4*>(rr + ch * 8) : z;
-      absorb(m, wr, sum, ch, v1, r1, norm_chunk(ch));
+#pragma unroll 1
+    for (int ch0 = tid; ch0 < chunks; ch0 += 2 * T) {
+      uint4 v[R][2], r[R][2], wv[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ch = ch0 + h * T;
+        const bool ok = ch < chunks;
+        wv[h] = (ok && fused) ? *reinterpret_cast<const uint4*>(nw + ch * 8) : z;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          v[j][h] = ok ? *reinterpret_cast<const uint4*>(xr[j] + ch * 8) : z;
+          r[j][h] = (ok && add) ? *reinterpret_cast<const uint4*>(rr[j] + ch * 8) : z;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ch = ch0 + h * T;
+        if (ch >= chunks) break;
+        float w[8];
+        unpack8(wv[h], xt, w);
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          if (m0 + j >= M) break;
+          float f[8];
+          unpack8(v[j][h], xt, f);
+          uint4 o = v[j][h];
+          if (add) {
+            float q[8];
+            unpack8(r[j][h], xt, q);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] += q[i];
+            round8(f, xt);
+            o = pack8(f, xt);
+            if (wr[j]) *reinterpret_cast<uint4*>(wr[j] + ch * 8) = o;
+          }
+          if (stage) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[j] += f[i] * f[i];
+            if (fused) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] *= w[i];
+              o = pack8(f, xt);
+            }
+            // not fused: keep the (rounded) input in its own type for now; pass 2 rescales
+            sts128(c.act_u32 + (uint32_t)(m0 + j) * xs + (uint32_t)ch * 16u, o);
+          }
+        }
+      }
     }
     if (stage && pro != MK_PRO_NONE) {
-      sum = warp_sum(sum);
-      if (c.lane == 0) c.ctrl->red[m * kConsumerWarps + (c.warp - 1)] = sum;
-    }
-   }
-  } else if constexpr (GROUPED) {
-    // Several rows: every row is its own L2 round trip, so four rows' chunks are
-    // requested together before any of them is reduced.
-    constexpr int R = 4;
-    for (int m0 = 0; m0 < M; m0 += R) {
-      const int nr = min(R, M - m0);
-      const uint16_t *xr[R], *rr[R];
-      uint16_t* wr[R];
-      float sum[R];
 #pragma unroll
       for (int j = 0; j < R; ++j) {
-        row_ptrs(min(m0 + j, M - 1), xr[j], rr[j], wr[j]);
-        sum[j] = 0.f;
-      }
-      auto step = [&](int ch, uint4 wv) {
-        uint4 v[R], r[R];
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-          v[j] = j < nr ? *reinterpret_cast<const uint4*>(xr[j] + ch * 8) : z;
-          r[j] = (j < nr && add) ? *reinterpret_cast<const uint4*>(rr[j] + ch * 8) : z;
-        }
-#pragma unroll
-        for (int j = 0; j < R; ++j)
-          if (j < nr) absorb(m0 + j, wr[j], sum[j], ch, v[j], r[j], wv);
-      };
-#pragma unroll
-      for (int i = 0; i < kNwCached; ++i) {
-        const int ch = tid + i * T;
-        if (ch >= chunks) break;
-        step(ch, nwc[i]);
-      }
-      for (int ch = tid + kNwCached * T; ch < chunks; ch += T) step(ch, norm_chunk(ch));
-      if (stage && pro != MK_PRO_NONE) {
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-          const float t = warp_sum(sum[j]);
-          if (c.lane == 0 && j < nr) c.ctrl->red[(m0 + j) * kConsumerWarps + (c.warp - 1)] = t;
-        }
+        const float t = warp_sum(sum[j]);
+        if (c.lane == 0 && m0 + j < M) c.ctrl->red[(m0 + j) * kConsumerWarps + (c.warp - 1)] = t;
       }
     }
   }
-  if (!stage) return;
-  if (fused || (pro == MK_PRO_NONE && xt == at)) return;
+  if (!stage || fused) return;
+  // second pass: normalise and convert to the mma's activation type
   named_bar_sync(kConsumerBarrier, T);
-  const float eps = op->f[MK_MV_F_EPS];
-  for (int m = 0; m < M; ++m) {
-    float rstd = 1.f;
-    if (pro != MK_PRO_NONE) {
+  if (pro != MK_PRO_NONE) {
+    if (tid < M) {
       float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) tot += c.ctrl->red[m * kConsumerWarps + w];
-      rstd = rsqrtf(tot / (float)K + eps);
+      for (int w = 0; w < kConsumerWarps; ++w) tot += c.ctrl->red[tid * kConsumerWarps + w];
+      c.ctrl->rstd[tid] = rsqrtf(tot / (float)K + op->f[MK_MV_F_EPS]);
     }
-#pragma unroll
-    for (int i = 0; i < kNwCached; ++i) {
-      const int ch = tid + i * T;
-      if (ch >= chunks) break;
+    named_bar_sync(kConsumerBarrier, T);
+  }
+#pragma unroll 1
+  for (int ch = tid; ch < chunks; ch += T) {
+    float w[8];
+    unpack8(pro != MK_PRO_NONE ? *reinterpret_cast<const uint4*>(nw + ch * 8) : z, xt, w);
+#pragma unroll 1
+    for (int m = 0; m < M; ++m) {
       const uint32_t a = c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u;
-      uint4 v = lds128(a);
       float f[8];
-      unpack8(v, xt, f);
+      unpack8(lds128(a), xt, f);
       if (pro != MK_PRO_NONE) {
-        float w[8];
-        unpack8(nwc[i], xt, w);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * w[k];
-      }
-      sts128(a, pack8(f, at));
-    }
-    for (int ch = tid + kNwCached * T; ch < chunks; ch += T) {
-      const uint32_t a = c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u;
-      uint4 v = lds128(a);
-      float f[8];
-      unpack8(v, xt, f);
-      if (pro != MK_PRO_NONE) {
-        uint4 wv = *reinterpret_cast<const uint4*>(nw + ch * 8);
-        float w[8];
-        unpack8(wv, xt, w);
+        const float rstd = c.ctrl->rstd[m];
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
       }
@@ -344,87 +312,101 @@ __device__ __forceinline__ void mv_put(const mk_op_t* op, int ot, int64_t off, f
   }
 }
 
+// One pass per (activation n-tile, column of the thread's pair): the loop is
+// kept rolled (the accumulator pair is picked with selects) so that the
+// epilogue, which runs once per unit from a cold instruction cache, stays a
+// few hundred instructions whatever the batch.
 template <int NT, int WFC, int FEAT>
 __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvOut& r, float (&acc)[NT][4]) {
   const int g = c.lane >> 2, t = c.lane & 3;
   const int O = op->i[MK_MV_O], K = op->i[MK_MV_K], M = op->i[MK_MV_M], S = op->i[MK_MV_S];
   const int mode = op->i[MK_MV_MODE], tr = op->i[MK_MV_TR], epi = op->i[MK_MV_EPI];
-  const int xt = op->i[MK_MV_X_T], ot = op->i[MK_MV_OUT_T];
+  const int xt = WFC == 0 ? (int)MK_T_BF16 : op->i[MK_MV_X_T];
+  const int ot = op->i[MK_MV_OUT_T];
   const float gs = (WFC != 0 && op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16) ? op->f[MK_MV_F_GSCALE] : 1.f;
   const bool fused = WFC != 2 && mv_rstd_in_epilogue(op);
   const float eps = op->f[MK_MV_F_EPS];
   const int nA = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowA0);
   const int nB = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowB0);
   const bool va = g < nA, vb = g < nB;
+  const bool two = tr != MK_TR_SILU_MUL;
+#pragma unroll 1
+  for (int q = 0; q < 2 * NT; ++q) {
+    const int m0 = (q >> 1) * 8 + (q & 1);   // the smallest activation row any lane has in this pass
+    if (m0 >= M) continue;
+    float a = 0.f, b = 0.f;
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int m = nt * 8 + 2 * t + e;
-      const bool vm = m < M;
-      float scale = gs;
-      if (fused) {
-        // the row's RMSNorm scale, from the per-warp sums of squares the staging left behind
-        const float* rs = c.ctrl->red + (vm ? m : 0) * kConsumerWarps;
-        float tot = 0.f;
+      for (int e = 0; e < 2; ++e)
+        if (q == 2 * nt + e) {
+          a = acc[nt][e];
+          b = acc[nt][2 + e];
+        }
+    const int m = m0 + 2 * t;
+    const bool vm = m < M;
+    float scale = gs;
+    if (fused) {
+      // the row's RMSNorm scale, from the per-warp sums of squares the staging left behind
+      const float* rs = c.ctrl->red + (vm ? m : 0) * kConsumerWarps;
+      float tot = 0.f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) tot += rs[w];
-        scale *= rsqrtf(tot / (float)K + eps);
+      for (int w = 0; w < kConsumerWarps; ++w) tot += rs[w];
+      scale *= rsqrtf(tot / (float)K + eps);
+    }
+    a *= scale;
+    b *= scale;
+    int bb = m, ss = 0;
+    if (S != 1) {
+      bb = m / S;
+      ss = m - bb * S;
+    }
+    if (tr == MK_TR_ROPE) {
+      if (vm) {
+        const int d = r.chunk * 8 + g;
+        const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + ss * op->s[MK_MV_S_COS] + d;
+        const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + ss * op->s[MK_MV_S_COS] + d;
+        const bool bf = xt == MK_T_BF16;
+        const float cv = bf ? bf16lo(*cs) : f16lo(*cs);
+        const float sv = bf ? bf16lo(*sn) : f16lo(*sn);
+        const float a2 = a * cv - b * sv, b2 = b * cv + a * sv;
+        a = a2;
+        b = b2;
       }
-      float a = acc[nt][e] * scale, b = acc[nt][2 + e] * scale;
-      int bb = m, ss = 0;
-      if (S != 1) {
-        bb = m / S;
-        ss = m - bb * S;
+    } else if (tr == MK_TR_SILU_MUL) {
+      a = silu_f(a) * b;
+    } else if (tr == MK_TR_RELU) {
+      a = fmaxf(a, 0.f);
+      b = fmaxf(b, 0.f);
+    } else if (tr == MK_TR_SILU) {
+      a = silu_f(a);
+      b = silu_f(b);
+    }
+    if ((FEAT & MK_F_TOP1) != 0 && epi == MK_EPI_TOP1) {
+      unsigned long long key = 0ull;
+      const int idx0 = op->i[MK_MV_IDX0];
+      if (va) key = top1_key(a, idx0 + r.rowA0 + g);
+      if (vb) {
+        const unsigned long long kb = top1_key(b, idx0 + r.rowB0 + g);
+        key = kb > key ? kb : key;
       }
-      if (tr == MK_TR_ROPE) {
-        if (vm) {
-          const int d = r.chunk * 8 + g;
-          const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + ss * op->s[MK_MV_S_COS] + d;
-          const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + ss * op->s[MK_MV_S_COS] + d;
-          const bool bf = xt == MK_T_BF16;
-          const float cv = bf ? bf16lo(*cs) : f16lo(*cs);
-          const float sv = bf ? bf16lo(*sn) : f16lo(*sn);
-          const float a2 = a * cv - b * sv, b2 = b * cv + a * sv;
-          a = a2;
-          b = b2;
-        }
-      } else if (tr == MK_TR_SILU_MUL) {
-        a = silu_f(a) * b;
-      } else if (tr == MK_TR_RELU) {
-        a = fmaxf(a, 0.f);
-        b = fmaxf(b, 0.f);
-      } else if (tr == MK_TR_SILU) {
-        a = silu_f(a);
-        b = silu_f(b);
-      }
-      if ((FEAT & MK_F_TOP1) != 0 && epi == MK_EPI_TOP1) {
-        unsigned long long key = 0ull;
-        const int idx0 = op->i[MK_MV_IDX0];
-        if (va) key = top1_key(a, idx0 + r.rowA0 + g);
-        if (vb) {
-          const unsigned long long kb = top1_key(b, idx0 + r.rowB0 + g);
-          key = kb > key ? kb : key;
-        }
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
-          key = other > key ? other : key;
-        }
-        if (g == 0 && vm) atomicMax(reinterpret_cast<unsigned long long*>(op->p[MK_MV_P_OUT]) + m, key);
-      } else if (vm) {
-        const bool two = tr != MK_TR_SILU_MUL;
-        if (epi == MK_EPI_RESIDUAL) {
-          const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) + bb * op->s[MK_MV_S_ER_B] +
-                               ss * op->s[MK_MV_S_ER_S];
-          const uint16_t ra = va ? er[r.rowA0 + g] : (uint16_t)0, rb = (vb && two) ? er[r.rowB0 + g] : (uint16_t)0;
-          a += (xt == MK_T_BF16) ? bf16lo(ra) : f16lo(ra);
-          b += (xt == MK_T_BF16) ? bf16lo(rb) : f16lo(rb);
-        }
-        const int64_t mo = bb * op->s[MK_MV_S_O_B] + (int64_t)(ss + op->i[MK_MV_POS]) * op->s[MK_MV_S_O_S];
-        if (va) mv_put(op, ot, mo + r.offA + g, a);
-        if (vb && two) mv_put(op, ot, mo + r.offB + g, b);
+      for (int o = 4; o < 32; o <<= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+        key = other > key ? other : key;
       }
+      if (g == 0 && vm) atomicMax(reinterpret_cast<unsigned long long*>(op->p[MK_MV_P_OUT]) + m, key);
+    } else if (vm) {
+      if (epi == MK_EPI_RESIDUAL) {
+        const uint16_t* er = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_EPI_RES]) + bb * op->s[MK_MV_S_ER_B] +
+                             ss * op->s[MK_MV_S_ER_S];
+        const uint16_t ra = va ? er[r.rowA0 + g] : (uint16_t)0, rb = (vb && two) ? er[r.rowB0 + g] : (uint16_t)0;
+        a += (xt == MK_T_BF16) ? bf16lo(ra) : f16lo(ra);
+        b += (xt == MK_T_BF16) ? bf16lo(rb) : f16lo(rb);
+      }
+      const int64_t mo = bb * op->s[MK_MV_S_O_B] + (int64_t)(ss + op->i[MK_MV_POS]) * op->s[MK_MV_S_O_S];
+      if (va) mv_put(op, ot, mo + r.offA + g, a);
+      if (vb && two) mv_put(op, ot, mo + r.offB + g, b);
     }
   }
 }
@@ -681,12 +663,12 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const UnitArg
   // Split-K reduction across the participating consumers.
   // mv_sets (1, 2 or 4) slot sets share kPartialBytes; the host picks the
   // count so that the widest matvec op of the program fits a slot.
-  const uint32_t sets = (uint32_t)c.pv->mv_sets;
-  const int kSlotFloats = kPartialBytes / 4 / kConsumerWarps / (int)sets;
-  const uint32_t set = ord % sets, gen = ord / sets;
-  float* slots = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.ctrl) + kCtrlStructBytes) +
-                 (size_t)set * kConsumerWarps * kSlotFloats;
   if (parts > 1) {
+    const int sets_log2 = __ffs(c.pv->mv_sets) - 1;
+    const int kSlotFloats = (kPartialBytes / 4 / kConsumerWarps) >> sets_log2;
+    const uint32_t set = ord & (uint32_t)(c.pv->mv_sets - 1), gen = ord >> sets_log2;
+    float* slots = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.ctrl) + kCtrlStructBytes) +
+                   (size_t)set * kConsumerWarps * kSlotFloats;
     // the set's previous users (units ord - kSets, ...) must have been reduced
     if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
     float* mine = slots + (size_t)part * kSlotFloats;
@@ -708,6 +690,8 @@ __device__ __forceinline__ bool mv_unit(Ctx& c, const mk_op_t* op, const UnitArg
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[0][nt][e] = 0.f;
+    // in participant order: the sum does not depend on who arrived when
+#pragma unroll 1
     for (int j = 0; j < parts; ++j) {
       const float* src = slots + (size_t)j * kSlotFloats;
 #pragma unroll

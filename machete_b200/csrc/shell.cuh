@@ -125,6 +125,7 @@ struct Ctrl {
   uint32_t released[kMaxPages];
   // per activation row and consumer warp: sum of squares of the staged row (RMSNorm)
   float red[kConsumerWarps * 32];
+  float rstd[32];   // per activation row: the RMSNorm scale (two-pass staging only)
   // Records of the op the CTA is working on and of the op of its next op-entry
   // event (event k uses slot k & 1; the other slot is refilled one event ahead,
   // so an event never waits for its op record).
@@ -239,18 +240,47 @@ __device__ __forceinline__ void trace_flush(Ctx& c) {
   counts[blockIdx.x * (kConsumerWarps + 1) + c.warp] = c.trace_n;
 }
 
-__device__ __forceinline__ void report(Ctx& c, int code, int aux, int aux2) {
-  DeviceState* st = c.pv->state;
+// Error reporting and the give-up decision live out of line: they run only
+// after a wait has already spun for a while, and every bounded wait would
+// otherwise carry a copy of them (the kernel's code size is what its op
+// boundaries pay for in instruction-cache misses).
+static __device__ __noinline__ void report_slow(const ProgramView* pv, Ctrl* ctrl, int instr_idx, int warp, int code,
+                                                int aux, int aux2) {
+  DeviceState* st = pv->state;
   if (atomicCAS(&st->status[0], 0, code) == 0) {
     st->status[1] = blockIdx.x;
-    st->status[2] = c.instr_idx;
+    st->status[2] = instr_idx;
     st->status[3] = aux;
     st->status[4] = aux2;
-    st->status[5] = c.warp;
+    st->status[5] = warp;
   }
   atomicExch(&st->abort_flag, 1);
-  atomicExch(&c.ctrl->abort_flag, 1);
+  atomicExch(&ctrl->abort_flag, 1);
   __threadfence();
+}
+__device__ __forceinline__ void report(Ctx& c, int code, int aux, int aux2) {
+  report_slow(c.pv, c.ctrl, c.instr_idx, c.warp, code, aux, aux2);
+}
+
+// One thread's view: 1 = stop waiting (abort seen, or the time budget since *t0 is
+// spent, which is reported); *t0 == 0 starts the clock.
+static __device__ __noinline__ int expired_slow(const ProgramView* pv, Ctrl* ctrl, uint64_t* t0, int instr_idx, int warp,
+                                                int code, int aux, int aux2) {
+  if (*reinterpret_cast<volatile int32_t*>(&ctrl->abort_flag)) return 1;
+  if (*reinterpret_cast<volatile int32_t*>(&pv->state->abort_flag)) {
+    atomicExch(&ctrl->abort_flag, 1);
+    return 1;
+  }
+  const uint64_t now = globaltimer_ns();
+  if (*t0 == 0) {
+    *t0 = now;
+    return 0;
+  }
+  if (now - *t0 > pv->timeout_ns) {
+    report_slow(pv, ctrl, instr_idx, warp, code, aux, aux2);
+    return 1;
+  }
+  return 0;
 }
 
 __device__ __forceinline__ bool aborted(Ctx& c) {
@@ -262,18 +292,11 @@ __device__ __forceinline__ bool aborted(Ctx& c) {
   return false;
 }
 
-// Slow path shared by the bounded waits: lane 0 decides whether to give up
-// (abort seen, or the time budget spent) and the decision is broadcast.
-__device__ __forceinline__ bool give_up_check(Ctx& c, uint64_t t0, int code, int aux, int aux2) {
+// Slow path shared by the warp-wide bounded waits: lane 0 decides whether to
+// give up and the decision is broadcast.
+__device__ __forceinline__ bool give_up_check(Ctx& c, uint64_t& t0, int code, int aux, int aux2) {
   int give_up = 0;
-  if (c.lane == 0) {
-    if (aborted(c)) {
-      give_up = 1;
-    } else if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
-      report(c, code, aux, aux2);
-      give_up = 1;
-    }
-  }
+  if (c.lane == 0) give_up = expired_slow(c.pv, c.ctrl, &t0, c.instr_idx, c.warp, code, aux, aux2);
   return __shfl_sync(0xffffffffu, give_up, 0) != 0;
 }
 
@@ -283,8 +306,7 @@ __device__ __forceinline__ bool give_up_check(Ctx& c, uint64_t t0, int code, int
 // Returns false (and marks the context dead) when the wait is abandoned.
 __device__ __forceinline__ bool wait_mbar(Ctx& c, uint32_t bar, uint32_t parity, int code, int aux) {
   if (c.dead) return false;
-  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
@@ -300,56 +322,39 @@ __device__ __forceinline__ bool wait_mbar(Ctx& c, uint32_t bar, uint32_t parity,
 // The same wait for a single thread (the loader's lane 0).  On give-up the
 // abort flag is raised; the caller's warp learns of it at its next __syncwarp.
 __device__ __forceinline__ bool wait_mbar_one(Ctx& c, uint32_t bar, uint32_t parity, int code, int aux) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (aborted(c)) return false;
-    if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
-      report(c, code, aux, (int)parity);
-      return false;
-    }
+    if (expired_slow(c.pv, c.ctrl, &t0, c.instr_idx, c.warp, code, aux, (int)parity)) return false;
   }
 }
 
 // Wait for every (counter >= expected) pair of a wait list.  Lane 0 polls;
-// the warp reconverges afterwards.
+// the warp reconverges afterwards.  Out of line: the op-entry events carry
+// their waits inline (wait_event), so this runs only for unit-level waits,
+// the loader's waits for rows appended in the same launch, and long lists.
+static __device__ __noinline__ int wait_counters_slow(const ProgramView* pv, Ctrl* ctrl, int instr_idx, int warp, int n,
+                                                      int off) {
+  const mk_wait_t* w = pv->waits + off;
+  for (int i = 0; i < n; ++i) {
+    const int32_t* ctr = pv->counters + w[i].counter;
+    const int32_t expected = w[i].expected;
+    uint64_t t0 = 0;
+    for (int spin = 0; ld_acquire_gpu(ctr) < expected; ++spin) {
+      nanosleep(32);
+      if ((spin & 15) == 15 && expired_slow(pv, ctrl, &t0, instr_idx, warp, MK_ST_TIMEOUT_COUNTER, w[i].counter, expected))
+        return 0;
+    }
+  }
+  return 1;
+}
 __device__ __forceinline__ bool wait_counters(Ctx& c, int n, int off) {
   if (c.dead) return false;
   int ok = 1;
-  if (c.lane == 0 && n > 0) {
-    const mk_wait_t* w = c.pv->waits + off;
-    for (int i = 0; i < n && ok; ++i) {
-      const int32_t* ctr = c.pv->counters + w[i].counter;
-      const int32_t expected = w[i].expected;
-      if (ld_acquire_gpu(ctr) >= expected) continue;
-      const uint64_t t0 = globaltimer_ns();
-      for (;;) {
-        bool hit = false;
-#pragma unroll 1
-        for (int k = 0; k < 16; ++k) {
-          if (ld_acquire_gpu(ctr) >= expected) {
-            hit = true;
-            break;
-          }
-          nanosleep(32);
-        }
-        if (hit) break;
-        if (aborted(c)) {
-          ok = 0;
-          break;
-        }
-        if (globaltimer_ns() - t0 > c.pv->timeout_ns) {
-          report(c, MK_ST_TIMEOUT_COUNTER, w[i].counter, expected);
-          ok = 0;
-          break;
-        }
-      }
-    }
-  }
+  if (c.lane == 0 && n > 0) ok = wait_counters_slow(c.pv, c.ctrl, c.instr_idx, c.warp, n, off);
   ok = __shfl_sync(0xffffffffu, ok, 0);
   if (!ok) c.dead = true;
   return ok != 0;
@@ -366,8 +371,7 @@ __device__ __forceinline__ uint32_t empty_bar(Ctx& c, int slot) { return smem_u3
 __device__ __forceinline__ bool wait_released(Ctx& c, uint32_t slot, uint32_t k, int aux) {
   if (c.dead) return false;
   volatile uint32_t* r = &c.ctrl->released[slot];
-  if (__all_sync(0xffffffffu, *r >= k)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
@@ -432,8 +436,7 @@ __device__ __forceinline__ void signal_unit(Ctx& c, int counter) {
 // Bounded wait until a shared-memory word reaches `want`.
 __device__ __forceinline__ bool wait_smem_ge(Ctx& c, volatile uint32_t* word, uint32_t want, int aux) {
   if (c.dead) return false;
-  if (__all_sync(0xffffffffu, *word >= want)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
@@ -483,12 +486,9 @@ __device__ __forceinline__ bool wait_event(Ctx& c, int ev_word, int n, int off) 
       fence_acq_rel_gpu();
       break;
     }
-    if ((spin & 15) == 15) {
-      if (t0 == 0) t0 = globaltimer_ns();
-      if (give_up_check(c, t0, MK_ST_TIMEOUT_COUNTER, my_c, my_e)) {
-        c.dead = true;
-        return false;
-      }
+    if ((spin & 15) == 15 && give_up_check(c, t0, MK_ST_TIMEOUT_COUNTER, my_c, my_e)) {
+      c.dead = true;
+      return false;
     }
   }
   if (n > 4) return wait_counters(c, n - 4, off + 4);
