@@ -112,6 +112,7 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
   float* scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.ctrl) + kCtrlStructBytes) + (c.warp - 1) * 512;
   const int rows = min(16, M * G - u.mt * 16);
   const int row = c.lane / LPR, dch = (c.lane % LPR) * 8;
+#pragma unroll 1
   for (int r0 = 0; r0 < rows; r0 += RPP) {
     const int nr = min(RPP, rows - r0);
     const bool rv = row < nr;
@@ -119,10 +120,17 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
     const int m = r / G, h = u.kvh * G + r % G;
     const float* base = opart + ((((int64_t)u.b * H + h) * S) * M + m) * D + dch;
     const int64_t sstride = (int64_t)M * D;
-    // request the first batch of partial rows together with the lse values:
-    // neither depends on the other, so they share one round trip
-    float4 a[UN], b2[UN];
-    auto fetch = [&](int s0) {
+    const float* ls = scratch + (rv ? row : 0) * S;
+    float mx = -INFINITY, sum = 0.f, inv = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    // One code path per batch of UN splits (kept rolled: this runs once per KV head and launch,
+    // always from a cold instruction cache).  The first batch of partial rows is requested
+    // together with the lse values: neither depends on the other, so they share one trip.
+#pragma unroll 1
+    for (int s0 = 0; s0 < S; s0 += UN) {
+      float4 a[UN], b2[UN];
 #pragma unroll
       for (int k = 0; k < UN; ++k) {
         a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -132,28 +140,23 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
           b2[k] = ldcg_f4(base + (s0 + k) * sstride + 4);
         }
       }
-    };
-    fetch(0);
-    for (int i = c.lane; i < nr * S; i += 32) {
-      const int rr = i / S, s = i - rr * S, r2 = u.mt * 16 + r0 + rr;
-      const int m2 = r2 / G, h2 = u.kvh * G + r2 % G;
-      scratch[i] = ldcg_f(lpart + (((int64_t)u.b * H + h2) * S + s) * M + m2);
-    }
-    __syncwarp();
-    const float* ls = scratch + (rv ? row : 0) * S;
-    float mx = -INFINITY;
-    for (int s = 0; s < S; ++s) mx = fmaxf(mx, ls[s]);
-    float sum = 0.f;
-    if (mx != -INFINITY)
-      for (int s = 0; s < S; ++s) sum += __expf(ls[s] - mx);
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int s0 = 0; s0 < S; s0 += UN) {
-      if (s0 > 0) {
+      if (s0 == 0) {
+#pragma unroll 1
+        for (int i = c.lane; i < nr * S; i += 32) {
+          const int rr = i / S, s = i - rr * S, r2 = u.mt * 16 + r0 + rr;
+          const int m2 = r2 / G, h2 = u.kvh * G + r2 % G;
+          scratch[i] = ldcg_f(lpart + (((int64_t)u.b * H + h2) * S + s) * M + m2);
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int s = 0; s < S; ++s) mx = fmaxf(mx, ls[s]);
+        if (mx != -INFINITY) {
+#pragma unroll 1
+          for (int s = 0; s < S; ++s) sum += __expf(ls[s] - mx);
+        }
+        inv = sum > 0.f ? 1.f / sum : 0.f;
+      } else {
         trace(c, TRC_AT_FETCHED, (uint32_t)r0);
-        fetch(s0);
       }
 #pragma unroll
       for (int k = 0; k < UN; ++k) {
@@ -493,6 +496,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
       for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     mrow[0] = mrow[1] = -INFINITY;
     lrow[0] = lrow[1] = 0.f;
+#pragma unroll 1
     for (int j = 0; j < parts; ++j) {
       const int pl = j + ((np - 1 - j) / parts) * parts;   // last page of participant j
       RingPos rj = ua.rp0;

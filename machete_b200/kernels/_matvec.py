@@ -115,6 +115,11 @@ def lower_matvec(
         if K % 64:
             raise ValueError(f"{name}: matvec needs K % 64 == 0, got {K}")
         kc = max(64, kc // 64 * 64)
+        # An op with a unit or two per CTA finishes when its slowest page does: shorter K-slices put
+        # more consumer warps on each unit (a page is the grain at which warps share a unit).
+        n_rows_units = -(-(w0.rows if out_rows is None else out_rows) // (8 if mode == N.MV_PAIR else 16))
+        if ctx.small_op_kc and n_rows_units <= 2 * ctx.num_sms and -(-K // kc) < 4:
+            kc = max(ctx.small_op_kc, 64 * (-(-K // 4) // 64))
     xt = elem_type(x, f"{name}: x")
     if w0.fmt == N.W_BF16 and xt != N.T_BF16:
         raise ValueError(f"{name}: bf16 weights need bf16 activations")

@@ -130,6 +130,9 @@ class LowerCtx:
     kc_bf16: int = 1024
     kc_fp4: int = 2048
     fuse: bool = True
+    # shortest bf16 K-slice to pick for ops with few units per CTA (0 = never shorten).  Off by default:
+    # on B200 the extra pages cost more than the extra warps per unit gain (931 vs 916 us per Llama-1B step)
+    small_op_kc: int = 0
 
 
 # ---- helpers shared by the matvec-family lowerings ---------------------------------------
