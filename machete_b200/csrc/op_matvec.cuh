@@ -144,7 +144,8 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   // a kernel built for one weight family knows its activation types
   const int xt = WFC == 0 ? (int)MK_T_BF16 : op->i[MK_MV_X_T];
   const int at = WFC == 0 ? (int)MK_T_BF16 : (WFC == 2 ? (int)MK_T_FP16 : mv_act_type(op));
-  const bool fused = WFC != 2 && mv_rstd_in_epilogue(op);
+  // a bf16 kernel always takes the RMSNorm scale in the epilogue: the second pass is not even compiled
+  const bool fused = WFC == 0 ? pro != MK_PRO_NONE : (WFC != 2 && mv_rstd_in_epilogue(op));
   const uint32_t xs = (uint32_t)K * 2u + 64u;
   const int chunks = K >> 3;
   const uint16_t* x = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_X]);
@@ -254,6 +255,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     }
   }
   if (!stage || fused) return;
+  if constexpr (WFC == 0) return;
   // second pass: normalise and convert to the mma's activation type
   named_bar_sync(kConsumerBarrier, T);
   if (pro != MK_PRO_NONE) {
@@ -324,7 +326,7 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
   const int xt = WFC == 0 ? (int)MK_T_BF16 : op->i[MK_MV_X_T];
   const int ot = op->i[MK_MV_OUT_T];
   const float gs = (WFC != 0 && op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16) ? op->f[MK_MV_F_GSCALE] : 1.f;
-  const bool fused = WFC != 2 && mv_rstd_in_epilogue(op);
+  const bool fused = WFC == 0 ? op->i[MK_MV_PRO] != MK_PRO_NONE : (WFC != 2 && mv_rstd_in_epilogue(op));
   const float eps = op->f[MK_MV_F_EPS];
   const int nA = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowA0);
   const int nB = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowB0);

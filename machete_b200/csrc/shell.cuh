@@ -479,13 +479,11 @@ __device__ __forceinline__ bool wait_event(Ctx& c, int ev_word, int n, int off) 
   const int32_t* ctr = c.pv->counters + (mine ? my_c : 0);
   uint64_t t0 = 0;
   for (int spin = 0;; ++spin) {
-    // relaxed polls: an acquire load drops the SM's L1 contents each time, and the
-    // other warps of the CTA are still running units while this one waits
-    const bool ok = !mine || ld_relaxed_gpu(ctr) >= my_e;
-    if (__all_sync(0xffffffffu, ok)) {
-      fence_acq_rel_gpu();
-      break;
-    }
+    // Every poll is an acquire load: the one that sees the counter complete closes
+    // the wait with no further trip to L2 (polling relaxed and acquiring once at the
+    // end costs that extra trip on every op boundary).
+    const bool ok = !mine || ld_acquire_gpu(ctr) >= my_e;
+    if (__all_sync(0xffffffffu, ok)) break;
     if ((spin & 15) == 15 && give_up_check(c, t0, MK_ST_TIMEOUT_COUNTER, my_c, my_e)) {
       c.dead = true;
       return false;
