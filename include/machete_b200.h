@@ -98,7 +98,8 @@ enum {
    * vocabulary row of this rank's shard under tensor parallelism) */
   MK_MV_IDX0
 };
-enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1 };
+/* GSCALE / GSCALE1: fp32 global scale of W0 / of W1 (MK_MV_PAIR; block-scaled NVFP4 only) */
+enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1, MK_MV_F_GSCALE1 = 2 };
 enum {
   MK_MV_P_W0 = 0, MK_MV_P_W1, MK_MV_P_X, MK_MV_P_RES_IN, MK_MV_P_NORM_W,
   MK_MV_P_RES_OUT, MK_MV_P_OUT, MK_MV_P_EPI_RES, MK_MV_P_COS, MK_MV_P_SIN,
@@ -312,9 +313,29 @@ int mk_workspace_status(const void* workspace, int32_t out[16]);
  * Takes the place of the reference's cutedsl-trace lanes
  * (megakernel/tracing.py:51-153). */
 int mk_set_trace(mk_handle_t h, void* buffer, uint64_t bytes, int32_t records_per_warp);
-/* Clear counters and status after a device-side error. */
+/* Clear status, abort flag and dependency counters after a device-side
+ * error (Megakernel.wait() does this before it raises).  The launch count is
+ * kept: the tensor-parallel exchange tags its messages with it.  Takes the
+ * place of the per-run barriers.zero_() of the reference
+ * (megakernel/megakernel.py:2149-2150). */
 int mk_reset(mk_handle_t h, void* cuda_stream);
-/* Overwrite op record `op_index` (e.g. new cache position or pointers). */
+/* The number of launches this handle's workspace has completed, aborted ones
+ * included (every CTA of an aborted launch still exits through the kernel's
+ * end).  The in-kernel all-reduce of launch n uses message epoch
+ * epoch_base + n + 1 on every rank, so ranks must agree on it: after one rank
+ * missed or repeated a launch (a peer timeout, a restart) the group sets every
+ * rank's count to the group maximum before launching again.  No counterpart in
+ * the reference, which runs all ranks from one process
+ * (megakernel/runtime_components.py:272-287). */
+int mk_launch_count(mk_handle_t h, int32_t* out);
+int mk_set_launch_count(mk_handle_t h, int32_t count, void* cuda_stream);
+/* Replace op record `op_index` (new pointers, a new cache position, a longer
+ * KV window).  The record is validated like mk_create does, the opcode and
+ * unit count must stay, the op's tensor maps are re-encoded and the
+ * instruction rows derived from the record (pages per unit, loader and
+ * finisher fast path) are recomputed and uploaded.  Synchronises
+ * `cuda_stream`.  The reference re-schedules and recompiles for a new
+ * position (kernels/decode_matvec/sm100.py:116, 704-709). */
 int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_stream);
 /* Read back the dependency counters (n_counters words) — after a completed
  * run they are all zero; used by the tests' invariant checks. */

@@ -30,7 +30,7 @@ T_BF16, T_FP16, T_FP32 = range(3)
 
 (MV_O, MV_K, MV_M, MV_S, MV_MODE, MV_PRO, MV_EPI, MV_TR, MV_HD, MV_D2, MV_POS, MV_WFMT, MV_KC, MV_OUT_T,
  MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT, MV_IDX0) = range(18)
-MV_F_EPS, MV_F_GSCALE = range(2)
+MV_F_EPS, MV_F_GSCALE, MV_F_GSCALE1 = range(3)
 (MV_P_W0, MV_P_W1, MV_P_X, MV_P_RES_IN, MV_P_NORM_W, MV_P_RES_OUT, MV_P_OUT, MV_P_EPI_RES, MV_P_COS,
  MV_P_SIN, MV_P_SC0, MV_P_SC1) = range(12)
 (MV_S_WROW, MV_S_X_B, MV_S_X_S, MV_S_RI_B, MV_S_RI_S, MV_S_RO_B, MV_S_RO_S, MV_S_O_B, MV_S_O_S, MV_S_O_H,
@@ -110,7 +110,8 @@ class Program(C.Structure):
 
 EXPORTS = [
     "mk_abi_version", "mk_last_error", "mk_device_info", "mk_workspace_bytes", "mk_create", "mk_run",
-    "mk_status", "mk_workspace_status", "mk_set_trace", "mk_reset", "mk_update_op", "mk_read_counters", "mk_destroy",
+    "mk_status", "mk_workspace_status", "mk_set_trace", "mk_reset", "mk_launch_count", "mk_set_launch_count",
+    "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
     "mk_flash_decode_noalloc",
 ]
@@ -170,6 +171,8 @@ def _declare(h: C.CDLL) -> None:
     h.mk_set_trace.argtypes = [vp, vp, u64, i32]
     h.mk_set_trace.restype = C.c_int
     h.mk_reset.argtypes = [vp, vp]
+    h.mk_launch_count.argtypes = [vp, C.POINTER(i32)]
+    h.mk_set_launch_count.argtypes = [vp, i32, vp]
     h.mk_update_op.argtypes = [vp, i32, vp, vp]
     h.mk_read_counters.argtypes = [vp, C.POINTER(i32), i32]
     h.mk_destroy.argtypes = [vp]
@@ -181,6 +184,7 @@ def _declare(h: C.CDLL) -> None:
     h.mk_flash_decode_noalloc.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp]
     h.mk_flash_decode_noalloc.restype = C.c_int
     for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op",
+                 "mk_launch_count", "mk_set_launch_count",
                  "mk_read_counters", "mk_destroy", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode"):
         getattr(h, name).restype = C.c_int
 

@@ -752,6 +752,25 @@ int mk_reset(mk_handle_t h, void* cuda_stream) {
   return 0;
 }
 
+int mk_launch_count(mk_handle_t h, int32_t* out) {
+  using namespace mk;
+  if (!h || !out) return fail(-1, "null argument");
+  CUDA_TRY(cudaMemcpy(out, h->ws + h->layout.state + offsetof(DeviceState, launches), sizeof(int32_t),
+                      cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+int mk_set_launch_count(mk_handle_t h, int32_t count, void* cuda_stream) {
+  using namespace mk;
+  if (!h) return fail(-1, "null handle");
+  if (count < 0) return fail(-1, "launch count must not be negative");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  CUDA_TRY(cudaMemcpyAsync(h->ws + h->layout.state + offsetof(DeviceState, launches), &count, sizeof(int32_t),
+                           cudaMemcpyHostToDevice, st));
+  CUDA_TRY(cudaStreamSynchronize(st));   // `count` lives on this stack frame
+  return 0;
+}
+
 int mk_update_op(mk_handle_t h, int32_t op_index, const mk_op_t* op, void* cuda_stream) {
   using namespace mk;
   if (!h || !op) return fail(-1, "null argument");

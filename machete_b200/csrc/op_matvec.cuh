@@ -325,7 +325,10 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
   const int mode = op->i[MK_MV_MODE], tr = op->i[MK_MV_TR], epi = op->i[MK_MV_EPI];
   const int xt = WFC == 0 ? (int)MK_T_BF16 : op->i[MK_MV_X_T];
   const int ot = op->i[MK_MV_OUT_T];
-  const float gs = (WFC != 0 && op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16) ? op->f[MK_MV_F_GSCALE] : 1.f;
+  // block-scaled NVFP4: one fp32 scale per matrix (rows a and b come from two matrices in pair mode)
+  const bool gscaled = WFC != 0 && op->i[MK_MV_WFMT] == MK_W_NVFP4_E4M3S16;
+  const float gs = gscaled ? op->f[MK_MV_F_GSCALE] : 1.f;
+  const float gsb = (gscaled && mode == MK_MV_PAIR) ? op->f[MK_MV_F_GSCALE1] : gs;
   const bool fused = WFC == 0 ? op->i[MK_MV_PRO] != MK_PRO_NONE : (WFC != 2 && mv_rstd_in_epilogue(op));
   const float eps = op->f[MK_MV_F_EPS];
   const int nA = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowA0);
@@ -347,17 +350,17 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
         }
     const int m = m0 + 2 * t;
     const bool vm = m < M;
-    float scale = gs;
+    float scale = 1.f;
     if (fused) {
       // the row's RMSNorm scale, from the per-warp sums of squares the staging left behind
       const float* rs = c.ctrl->red + (vm ? m : 0) * kConsumerWarps;
       float tot = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) tot += rs[w];
-      scale *= rsqrtf(tot / (float)K + eps);
+      scale = rsqrtf(tot / (float)K + eps);
     }
-    a *= scale;
-    b *= scale;
+    a *= scale * gs;
+    b *= scale * gsb;
     int bb = m, ss = 0;
     if (S != 1) {
       bb = m / S;

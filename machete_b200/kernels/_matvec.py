@@ -155,7 +155,7 @@ def lower_matvec(
         N.MV_WFMT: w0.fmt, N.MV_KC: kc, N.MV_OUT_T: elem_type(out, f"{name}: out") if epi != N.EPI_TOP1 else 0,
         N.MV_X_T: xt, N.MV_ROWS_PER_UNIT: rows_per_unit, N.MV_SPLIT: split, N.MV_IDX0: int(index_offset),
     }
-    op.f = {N.MV_F_EPS: eps, N.MV_F_GSCALE: w0.global_scale}
+    op.f = {N.MV_F_EPS: eps, N.MV_F_GSCALE: w0.global_scale, N.MV_F_GSCALE1: (w1 or w0).global_scale}
     op.p = {N.MV_P_W0: w0.data.data_ptr(), N.MV_P_W1: (w1 or w0).data.data_ptr(), N.MV_P_X: x.data_ptr(),
             N.MV_P_OUT: out.data_ptr()}
     op.s = {N.MV_S_WROW: wrow, N.MV_S_X_B: x.stride(0), N.MV_S_X_S: x.stride(1),
@@ -174,8 +174,6 @@ def lower_matvec(
         op.reads.append(Region(meta_of(w0.scales, "scales"), loader=True))
         op.keep.append(w0.scales)
         if w1 is not None:
-            if w1.global_scale != w0.global_scale:
-                raise ValueError(f"{name}: paired NVFP4 weights must share the global scale")
             op.reads.append(Region(meta_of(w1.scales, "scales1"), loader=True))
             op.keep.append(w1.scales)
     if pro != N.PRO_NONE:

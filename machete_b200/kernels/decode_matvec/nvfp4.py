@@ -57,10 +57,10 @@ class _Nvfp4Base(Op):
         return tile_sizes
 
     @staticmethod
-    def _weight(sop, packed="weight_packed", scales="weight_scales"):
+    def _weight(sop, packed="weight_packed", scales="weight_scales", scale_key="global_scale"):
         t = sop.tensor_refs
         return nvfp4_weight(t[packed], t[scales], int(sop.static_dims["group_size"]),
-                            sop.params.get("global_scale", 1.0))
+                            sop.params.get(scale_key, sop.params.get("global_scale", 1.0)))
 
 
 class _RmsProjectionNvfp4Sm120Base(_Nvfp4Base):
@@ -232,13 +232,16 @@ class RmsGateUpSiluNvfp4Sm120Op(_Nvfp4Base):
 
     @classmethod
     def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, group_size=32, prefetch_nvfp4=True,
-                 global_scale=1.0, **tensors):
+                 global_scale=1.0, up_global_scale=None, **tensors):
+        """``global_scale`` / ``up_global_scale``: the fp32 tensor scales of the gate and the up matrix
+        (block-scaled layout; ``up_global_scale=None`` = the same as the gate's)."""
         k = tensors["x"].shape[-1]
         _check_nvfp4(tensors["gate_packed"], tensors["gate_scales"], k, group_size, "gate")
         _check_nvfp4(tensors["up_packed"], tensors["up_scales"], k, group_size, "up")
         op = cls._schedule_single(tile_sizes=cls._tiles(tile_sizes, "D"), **tensors)
         op.static_dims["eps"] = eps
         op.static_dims["prefetch_nvfp4"] = bool(prefetch_nvfp4)
+        op.params["up_global_scale"] = float(global_scale if up_global_scale is None else up_global_scale)
         return _finalize(op, page_size=page_size, group_size=group_size, k_dim=k, global_scale=global_scale)
 
     @classmethod
@@ -246,7 +249,7 @@ class RmsGateUpSiluNvfp4Sm120Op(_Nvfp4Base):
         t = sop.tensor_refs
         out = t["y"]
         return [lower_matvec(cls.__name__, ctx, w0=cls._weight(sop, "gate_packed", "gate_scales"),
-                             w1=cls._weight(sop, "up_packed", "up_scales"), x=t["x"], out=out,
+                             w1=cls._weight(sop, "up_packed", "up_scales", "up_global_scale"), x=t["x"], out=out,
                              out_strides=flat_out_strides(out), mode=N.MV_PAIR, tr=N.TR_SILU_MUL, pro=N.PRO_RMS,
                              norm_weight=t["norm_weight"], eps=float(sop.static_dims.get("eps", 1e-5)),
                              kind="gate_up")]

@@ -128,6 +128,7 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
                                               gate_packed=wg["packed"], gate_scales=wg["scales"],
                                               up_packed=wu["packed"], up_scales=wu["scales"], y=mlp_h_buf,
                                               group_size=wg["group_size"], global_scale=wg["global_scale"],
+                                              up_global_scale=wu["global_scale"],
                                               tile_sizes={"S": seq_len, "D": 16}, page_size=page_size, eps=eps)
     wd = _w(weights, f"{pfx}.W_down")
     # The activations of a matvec op are staged whole in shared memory.  When batch x intermediate

@@ -71,6 +71,24 @@ class MegakernelConfig:
     fuse: bool = True                    # allow peephole fusion of op chains
 
 
+_IGNORED_CONFIG = {
+    "threads_per_block": 256, "dma_reg_count": 40, "mma_reg_count": 232, "loader_idle_sleep_ns": 100,
+    "relaxed_global_barriers": True, "global_barrier_sleep_ns": 8, "opt_level": 2, "page_size": 49152,
+}
+_warned_config = False
+
+
+def _warn_ignored_config(cfg: "MegakernelConfig") -> None:
+    """One warning per process when a caller tunes a knob the precompiled kernel does not have."""
+    global _warned_config
+    changed = sorted(k for k, default in _IGNORED_CONFIG.items() if getattr(cfg, k) != default and k != "page_size")
+    if changed and not _warned_config:
+        _warned_config = True
+        warnings.warn(
+            f"MegakernelConfig fields {changed} steer the reference's JIT and warp-role split; the precompiled "
+            "sm_100a kernel (1 loader + 7 consumer warps) accepts and ignores them", stacklevel=3)
+
+
 def _device_index(device) -> int:
     if isinstance(device, int):
         return device
@@ -104,6 +122,7 @@ class Megakernel:
         self._arrays = None
 
         cfg = self.config
+        _warn_ignored_config(cfg)
         if cfg.num_sms is not None and cfg.num_sms < 1:
             raise ValueError("num_sms must be positive")
         sms, smem = _DEFAULT_SMS, _DEFAULT_SMEM_OPTIN
@@ -252,6 +271,60 @@ class Megakernel:
         N.check(N.lib().mk_run(self._handle, C.c_void_p(handle)), "mk_run")
         if sync:
             self.wait()
+
+    def prepare_run(self, stream=None, validate: bool = True, reset_barriers: bool = True) -> dict:
+        """Everything of ``run()`` that is not the launch: validate, compile, resolve the stream.
+
+        Mirror of the reference's ``prepare_run`` (megakernel/megakernel.py:2122-2161).  Returns the
+        launch state for :meth:`launch_prepared`.  ``reset_barriers`` is accepted for signature
+        parity: the kernel clears its own dependency counters at the end of every launch.
+        """
+        if validate:
+            self._validate_tensors()
+        self.compile()
+        if stream is None:
+            handle = torch.cuda.current_stream(self._dev).cuda_stream
+        elif hasattr(stream, "cuda_stream"):
+            handle = stream.cuda_stream
+        else:
+            handle = int(stream)
+        return {"stream": handle, "handle": self._handle}
+
+    def launch_prepared(self, state: dict, stream=None, trace_buffer_ptr=None, sync: bool = False) -> None:
+        """Launch with a state from :meth:`prepare_run` (reference: megakernel/megakernel.py:2163-2181).
+
+        ``stream`` overrides the prepared stream; ``trace_buffer_ptr`` is accepted for signature
+        parity (tracing is attached with :meth:`enable_trace`).
+        """
+        handle = state["stream"] if stream is None else getattr(stream, "cuda_stream", stream)
+        N.check(N.lib().mk_run(state["handle"], C.c_void_p(int(handle))), "mk_run")
+        if sync:
+            self.wait()
+
+    def launch_count(self) -> int:
+        """Launches this handle has completed (aborted ones included); see ``mk_launch_count``."""
+        self.compile()
+        out = C.c_int32()
+        N.check(N.lib().mk_launch_count(self._handle, C.byref(out)), "mk_launch_count")
+        return int(out.value)
+
+    def set_launch_count(self, count: int) -> None:
+        self.compile()
+        N.check(N.lib().mk_set_launch_count(self._handle, int(count), None), "mk_set_launch_count")
+
+    def resync_launch_count(self, group=None) -> int:
+        """Tensor-parallel recovery: set every rank's launch count to the group maximum.
+
+        The in-kernel all-reduce tags its messages with the launch number, so after one rank missed
+        or aborted a launch (a peer timeout surfaces as ``RuntimeError`` from :meth:`wait`) the ranks
+        agree on a count here, between steps and with no kernel in flight, before launching again.
+        """
+        import torch.distributed as dist
+
+        t = torch.tensor([self.launch_count()], dtype=torch.int64, device=torch.device("cuda", self._dev))
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        self.set_launch_count(int(t.item()))
+        return int(t.item())
 
     def wait(self) -> None:
         """Drain the device and surface device-side errors."""

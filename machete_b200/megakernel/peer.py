@@ -68,6 +68,25 @@ class PeerBuffers:
             self.ptrs = [base + (r + 1) * (1 << 32) for r in range(world_size)]   # distinct, aligned, never used
             self.ptrs[self.rank] = self.buffer.data_ptr()
 
+    @classmethod
+    def local(cls, nbytes: int, rank: int, world_size: int, device) -> "PeerBuffers":
+        """Every rank's buffer as a plain allocation on ONE device (no process group).
+
+        The reference's same-device peer trick (tests/kernels/test_gemm_tp.py:80-113): it lets a
+        single GPU lower and run a rank's program, e.g. to see the bounded wait for a peer that
+        never writes give up with a status instead of hanging.
+        """
+        self = cls.__new__(cls)
+        self.rank, self.world_size, self.group = int(rank), int(world_size), None
+        self.nbytes = -(-int(nbytes) // 256) * 256
+        self._cursor = 0
+        self._generation = 0
+        self.device = torch.device(device)
+        self._locals = [torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device) for _ in range(world_size)]
+        self.buffer = self._locals[self.rank]
+        self.ptrs = [int(t.data_ptr()) for t in self._locals]
+        return self
+
     def alloc(self, nbytes: int, align: int = 256) -> int:
         """Reserve ``nbytes`` and return the offset (identical on every rank)."""
         off = -(-self._cursor // align) * align

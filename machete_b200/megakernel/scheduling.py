@@ -79,8 +79,18 @@ class OverlapTileScheduler(TileScheduler):
     scheduler does not need.
     """
 
+    _warned = False
+
     def __init__(self, fetch_stride=None, adaptive_fetch_stride=False, prefer_data_movement=True,
                  prefer_ready_consumers=False, use_controller_waits_for_readiness=False):
+        tuned = (fetch_stride is not None or adaptive_fetch_stride or not prefer_data_movement
+                 or prefer_ready_consumers or use_controller_waits_for_readiness)
+        if tuned and not OverlapTileScheduler._warned:
+            import warnings
+
+            OverlapTileScheduler._warned = True
+            warnings.warn("OverlapTileScheduler keywords tune the reference's readiness simulation; the level "
+                          "placement used here accepts and ignores them", stacklevel=2)
         self.fetch_stride = fetch_stride
         self.adaptive_fetch_stride = adaptive_fetch_stride
         self.prefer_data_movement = prefer_data_movement

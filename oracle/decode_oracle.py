@@ -350,16 +350,19 @@ def decode_layer(*, weights, layer_idx, x_in, residual_in, k_cache, v_cache, cac
 
 
 def decode_model(*, weights, x, residual, k_caches, v_caches, cache_pos, final_norm, lm_head, num_layers, eps=1e-5,
-                 num_q_heads=32, num_kv_heads=8, head_dim=64):
+                 num_q_heads=32, num_kv_heads=8, head_dim=64, return_hidden=False):
     """Whole decode step: layers, final add + norm, LM head, greedy token
     (composition of src/machete/kernels/llama1b/sm120.py:4679-4762 on the sm100 layer).
-    Returns (logits fp32 (B, S, V), top values, top indices)."""
+    Returns (logits fp32 (B, S, V), top values, top indices); with ``return_hidden`` also the last
+    layer's (x_out, residual_out), the two tensors whose sum the final norm reads."""
     for l in range(num_layers):
         x, residual = decode_layer(weights=weights, layer_idx=l, x_in=x, residual_in=residual, k_cache=k_caches[l],
                                    v_cache=v_caches[l], cache_pos=cache_pos, eps=eps, num_q_heads=num_q_heads,
                                    num_kv_heads=num_kv_heads, head_dim=head_dim)
     logits = final_rms_lm_head(x, final_norm, lm_head, eps, residual_in=residual)
     v, i = top1(logits)
+    if return_hidden:
+        return logits, v, i, x, residual
     return logits, v, i
 
 
