@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode-step megakernel.
 
-Workload at N = 1 (``config.workload``): the full 16-layer Llama-3.2-1B-shape
+Headline workload (``config.workload``): the full 16-layer Llama-3.2-1B-shape
 decode step as one persistent kernel — hidden 2048, 32 query / 8 KV heads,
 head_dim 64, GLU intermediate 8192, tied 128256-vocab LM head with the greedy
 token computed in the kernel, random-init bf16 weights ~N(0, 0.02), decode
@@ -9,28 +9,42 @@ batch 1, KV length 4096.  A "step" is one launch = one token per sequence.
 
 One JSON line is printed by rank 0:
 
-* ``value``   tokens/s with the inputs resident in HBM (CUDA events around K
-              back-to-back launches, max over ranks);
+* ``value``   tokens/s with the inputs resident in HBM: CUDA events around
+              blocks of exactly ``--steps`` back-to-back launches, max over
+              ranks; blocks are repeated until half a second has been timed and
+              the MEDIAN block is reported (``blocks`` says how many ran), so
+              the clock sampler always has rows inside the timed region;
 * ``e2e``     the same metric through the public API with host buffers: per
               step the token embedding is copied from pinned host memory, the
               step runs, and the greedy token is read back;
 * ``roofline`` algorithmic bytes per step (weights + LM head + KV, read once)
               divided by the measured kernel time, against the measured HBM
               copy bandwidth of this pool's B200s;
-* ``cpu_baseline`` the CPU oracle (a port of the reference's PyTorch reference
-              functions) timed on the host cores, as a reported baseline.
+* ``cpu_baseline`` / ``parity`` the CPU oracle (a port of the reference's
+              PyTorch reference functions) on the host cores, on the SAME
+              weights, KV cache and input as the GPU step: its time, and
+              whether both produced the same greedy token;
+* ``cfg4``    the tensor-parallel configuration at this N: 36-layer
+              Qwen3-8B-shape step with block-scaled NVFP4 weights, batch 1 and
+              8 (µs/step, tokens/s, per-GPU algorithmic bytes, fraction);
+* ``cfg0`` / ``cfg1`` / ``cfg2`` (N = 1): one layer at KV 1024, the small-M
+              GEMM sweep in bf16 and NVFP4, flash decoding at batch 8 x 32 768.
 
-``--impl reference`` times that CPU port alone (the reference ships no
-compiled code; its own path is PyTorch on the host).
+``--impl reference`` times the CPU port alone (the reference ships no
+compiled code; its own path for this step is PyTorch on the host).
 
-Multi-GPU (``--gpus N`` under torchrun): every rank decodes its own sequence
-with a full replica of the model (no data-path collective), so the aggregate
-is N independent steps per step time ("weak" scaling).
+Multi-GPU (``--gpus N`` under torchrun).  The headline model fits one GPU and
+its decode streams are independent, so N ranks decode N sequences with a full
+replica each and no data-path collective (``scaling: weak``).  The model the
+task shards is the 8B-shape one: ``cfg4`` runs it Megatron tensor-parallel
+over the N ranks with the all-reduce inside the kernel (``--model qwen3-8b``
+makes it the headline, ``--parallel tp`` shards the Llama shape too).
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -57,12 +71,14 @@ FALLBACK_HBM_GBS = 6650.0
 # proportional to the layers streamed, so the ratio carries over to the full workload.
 NCU_TRAFFIC_RATIO = 1.006
 NOMINAL_HBM_GBS = 8000.0
+MIN_TIMED_SECONDS = 0.5
+L2_BYTES = 126 << 20
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="llama1b", choices=sorted(MODELS),
@@ -76,18 +92,27 @@ def parse_args():
     ap.add_argument("--weights", default="", choices=["", "bf16", "nvfp4"],
                     help="nvfp4: packed e2m1 weights, e4m3 scale per 16 values + fp32 global scale (the default and "
                          "only choice for qwen3-8b); the headline workload is llama1b in bf16")
-    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
-                    help="N > 1: tensor-parallel decode of ONE stream (in-kernel all-reduce) or N independent replicas")
+    ap.add_argument("--parallel", default="", choices=["", "tp", "replicas"],
+                    help="N > 1: tensor-parallel decode of ONE stream (in-kernel all-reduce) or N independent "
+                         "replicas; default: replicas for llama1b (it fits one GPU), tp for qwen3-8b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="skip the cfg0 / cfg1 / cfg2 / cfg4 sub-records")
+    ap.add_argument("--sub-steps", type=int, default=30, help="launches per timed block of a sub-record")
     args = ap.parse_args()
+    fill_defaults(args)
+    if MODELS[args.model]["qk_norm"] and args.weights != "nvfp4":
+        ap.error("the q/k-norm layer is scheduled with NVFP4 weights only")
+    return args
+
+
+def fill_defaults(args):
     model = MODELS[args.model]
     args.kv_len = args.kv_len or model["kv_len"]
     args.layers = args.layers or model["layers"]
     args.vocab = args.vocab or model["vocab"]
     args.weights = args.weights or ("nvfp4" if model["qk_norm"] else "bf16")
-    if model["qk_norm"] and args.weights != "nvfp4":
-        ap.error("the q/k-norm layer is scheduled with NVFP4 weights only")
+    args.parallel = args.parallel or ("tp" if model["qk_norm"] else "replicas")
     return args
 
 
@@ -142,7 +167,8 @@ def make_weights(cfg, layers, vocab, kv_len, device, seed):
         if cfg.get("qk_norm"):
             weights[f"{p}.q_norm"], weights[f"{p}.k_norm"] = nw(cfg["hd"]), nw(cfg["hd"])
     weights["final_norm"] = nw(h)
-    weights["lm_head"] = w(vocab, h)          # stands for the tied embedding matrix
+    if vocab:
+        weights["lm_head"] = w(vocab, h)          # stands for the tied embedding matrix
     return weights
 
 
@@ -180,7 +206,7 @@ class ClockSampler:
 
     def stop(self, first=0, last=None):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -197,46 +223,48 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_step_seconds(args, cfg, weights_cpu, budget_s=25.0):
-    """Time the CPU oracle on the same workload; bounded: whole step if it fits, else a layer sample."""
+# ---- the CPU leg --------------------------------------------------------------------------------------------
+def cpu_step(args, cfg, weights_cpu, kcs, vcs, x, r, budget_s=25.0):
+    """The CPU oracle on the given weights, caches and input; bounded: whole steps if they fit the
+    budget, else one layer + LM head extrapolated.  Returns (seconds per step, what was sampled,
+    (logits, token) of a whole step or None)."""
     import oracle
 
     torch.set_num_threads(os.cpu_count() or 1)
-    B, L = args.batch, args.kv_len
-    g = torch.Generator().manual_seed(1)
-    bf = torch.bfloat16
-    kc = (torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g)).to(bf)
-    vc = (torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g)).to(bf)
-    x = torch.randn(B, 1, cfg["hidden"], generator=g).to(bf)
-    r = torch.zeros(B, 1, cfg["hidden"], dtype=bf)
+    L = args.kv_len
+    kw = dict(num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"], head_dim=cfg["hd"])
 
-    def layer(l):
-        return oracle.decode_layer(weights=weights_cpu, layer_idx=l, x_in=x, residual_in=r, k_cache=kc, v_cache=vc,
-                                   cache_pos=L - 1, num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"], head_dim=cfg["hd"])
+    def layer(l, xx, rr, kc, vc):
+        return oracle.decode_layer(weights=weights_cpu, layer_idx=l, x_in=xx, residual_in=rr, k_cache=kc, v_cache=vc,
+                                   cache_pos=L - 1, eps=cfg["eps"], **kw)
 
-    def head():
-        return oracle.top1(oracle.final_rms_lm_head(x, weights_cpu["final_norm"], weights_cpu["lm_head"], 1e-5, r))
+    def head(xx, rr):
+        return oracle.final_rms_lm_head(xx, weights_cpu["final_norm"], weights_cpu["lm_head"], cfg["eps"], rr)
 
-    layer(0)  # warm-up
+    def whole():
+        xx, rr = x, r
+        for l in range(args.layers):
+            xx, rr = layer(l, xx, rr, kcs[l].clone(), vcs[l].clone())
+        return head(xx, rr)
+
+    layer(0, x, r, kcs[0].clone(), vcs[0].clone())  # warm-up
     t0 = time.perf_counter()
-    layer(0)
+    layer(0, x, r, kcs[0].clone(), vcs[0].clone())
     t_layer = time.perf_counter() - t0
     t0 = time.perf_counter()
-    head()
+    head(x, r)
     t_head = time.perf_counter() - t0
-    n_layers = args.layers
-    est = t_layer * n_layers + t_head
+    est = t_layer * args.layers + t_head
     if est <= budget_s:
         reps = max(1, min(5, int(budget_s // max(est, 1e-3))))
-        times = []
+        times, logits = [], None
         for _ in range(reps):
             t0 = time.perf_counter()
-            for l in range(n_layers):
-                layer(l)
-            head()
+            logits = whole()
             times.append(time.perf_counter() - t0)
-        return statistics.median(times), f"{reps} full steps ({n_layers} layers + LM head), median"
-    return est, f"1 layer + LM head timed once, extrapolated to {n_layers} layers"
+        v, i = oracle.top1(logits)
+        return statistics.median(times), f"{reps} full steps ({args.layers} layers + LM head), median", (logits, i)
+    return est, f"1 layer + LM head timed once, extrapolated to {args.layers} layers", None
 
 
 def run_reference(args, rank, world):
@@ -245,9 +273,16 @@ def run_reference(args, rank, world):
         return
     cfg = MODELS[args.model]
     weights = make_weights(cfg, args.layers, args.vocab, args.kv_len, "cpu", seed=0)
+    g = torch.Generator().manual_seed(100)
+    bf = torch.bfloat16
+    B, L = args.batch, args.kv_len
+    kcs = [torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g).to(bf) for _ in range(args.layers)]
+    vcs = [torch.randn(B, L, cfg["nkv"], cfg["hd"], generator=g).to(bf) for _ in range(args.layers)]
+    x = torch.randn(B, 1, cfg["hidden"], generator=g).to(bf)
+    r = torch.zeros(B, 1, cfg["hidden"], dtype=bf)
     # each "step" is one bounded CPU pass; W + K passes are capped to keep the run within minutes
     budget = 240.0 / max(1, args.steps + args.warmup)
-    secs, sample = cpu_step_seconds(args, cfg, weights, budget_s=max(5.0, budget))
+    secs, sample, _ = cpu_step(args, cfg, weights, kcs, vcs, x, r, budget_s=max(5.0, budget))
     tok_s = args.batch / secs
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
@@ -267,7 +302,7 @@ def workload_config(args, world, tp=False, note=None):
     elif tp:
         par = f"tp{world}: Megatron tensor parallel, all-reduce after O-proj and down-proj inside the kernel"
     else:
-        par = f"{world} independent replicas (one sequence set per GPU)" + (f"; {note}" if note else "")
+        par = f"{world} independent replicas (one sequence set per GPU, no collective)" + (f"; {note}" if note else "")
     return {
         "workload": f"{MODELS[args.model]['name']} {args.layers}-layer decode step, batch {args.batch}, "
                     f"kv {args.kv_len}, vocab {args.vocab}, {args.weights}, greedy token",
@@ -276,28 +311,22 @@ def workload_config(args, world, tp=False, note=None):
     }
 
 
-def main():
-    args = parse_args()
-    rank, world, local = dist_env()
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the native path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    use_dist = world > 1
-    if use_dist:
-        import torch.distributed as dist
+# ---- building and timing one decode workload ----------------------------------------------------------------
+class Workload:
+    pass
 
-        dist.init_process_group("nccl", device_id=dev)
 
+def build_workload(args, dev, rank, world, use_dist):
+    """Weights, caches and the scheduled program of one decode workload on this rank."""
     from machete_b200.kernels.llama1b import schedule_decode_model_sm100
     from machete_b200.megakernel import BackwardScheduler, Megakernel, MegakernelConfig, OverlapTileScheduler
 
+    if use_dist:
+        import torch.distributed as dist
+    w = Workload()
     cfg = dict(MODELS[args.model])
     B, L, bf = args.batch, args.kv_len, torch.bfloat16
-    # N > 1: one decode stream sharded Megatron-style over the ranks, unless the peer mapping
+    # tensor parallel: one decode stream sharded Megatron-style over the ranks, unless the peer mapping
     # cannot be set up on this box (then N independent replicas, and the line says so)
     peers, tp_note, vocab = None, None, args.vocab
     if use_dist and args.parallel == "tp":
@@ -333,6 +362,9 @@ def main():
     tv = torch.zeros(B, 1, device=dev)
     ti = torch.zeros(B, 1, dtype=torch.int32, device=dev)
     nvfp4 = args.weights == "nvfp4"
+    bufs = dict(q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
+                attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
+                mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev))
     if nvfp4:
         from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
         from machete_b200.quantization import quantize_nvfp4_weight
@@ -343,23 +375,32 @@ def main():
             packed[f"{k}.packed"], packed[f"{k}.scales"], packed[f"{k}.global_scale"] = q4.packed, q4.scales, float(q4.global_scale)
         weights = packed
         torch.cuda.empty_cache()
-    ops, keep = (schedule_decode_model_nvfp4_sm100(
-        batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
-        q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
-        attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
-        mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), top_values=tv, top_indices=ti,
-        num_layers=args.layers, x_in=x_in, residual_in=r_in, num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"],
-        head_dim=cfg["hd"], eps=cfg["eps"], tp_peers=peers) if nvfp4 else None) or schedule_decode_model_sm100(
-        batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
-        q_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
-        attn_out_buf=torch.zeros(B, 1, cfg["nq"] * cfg["hd"], dtype=bf, device=dev),
-        mlp_h_buf=torch.zeros(B, 1, cfg["inter"], dtype=bf, device=dev), final_norm=weights["final_norm"],
-        lm_head=weights["lm_head"], top_values=tv, top_indices=ti, num_layers=args.layers, x_in=x_in,
-        residual_in=r_in, hidden_size=cfg["hidden"], intermediate_size=cfg["inter"], num_q_heads=cfg["nq"],
-        num_kv_heads=cfg["nkv"], head_dim=cfg["hd"], eps=cfg["eps"], tp_peers=peers)
+        ops, keep = schedule_decode_model_nvfp4_sm100(
+            batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
+            top_values=tv, top_indices=ti, num_layers=args.layers, x_in=x_in, residual_in=r_in,
+            num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"], head_dim=cfg["hd"], eps=cfg["eps"], tp_peers=peers, **bufs)
+    else:
+        ops, keep = schedule_decode_model_sm100(
+            batch=B, cache_pos=L - 1, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
+            final_norm=weights["final_norm"], lm_head=weights["lm_head"], top_values=tv, top_indices=ti,
+            num_layers=args.layers, x_in=x_in, residual_in=r_in, hidden_size=cfg["hidden"],
+            intermediate_size=cfg["inter"], num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"], head_dim=cfg["hd"],
+            eps=cfg["eps"], tp_peers=peers, **bufs)
     sched = OverlapTileScheduler() if args.scheduler == "overlap" else BackwardScheduler()
     mk = Megakernel(ops, config=MegakernelConfig(native_kc=args.kc or None), device=dev, scheduler=sched)
     mk.compile()
+    w.mk, w.cfg, w.tp, w.tp_note, w.vocab, w.nvfp4 = mk, cfg, tp, tp_note, vocab, nvfp4
+    w.weights, w.kcs, w.vcs, w.x_in, w.r_in, w.ti, w.tv, w.keep = weights, kcs, vcs, x_in, r_in, ti, tv, (keep, xb, rb, bufs, peers)
+    w.alg_bytes = algorithmic_bytes(cfg, B, L, args.layers, vocab, 0.5625 if nvfp4 else 2.0)   # per GPU
+    return w
+
+
+def time_launches(launch, steps, warmup, dev, use_dist, sampler=None, min_seconds=MIN_TIMED_SECONDS, max_blocks=200):
+    """Blocks of exactly ``steps`` launches between CUDA events on the launching stream, repeated
+    until ``min_seconds`` have been timed; returns (median ms per step over the blocks — each block
+    the max over ranks —, number of blocks, clock-sample row range)."""
+    if use_dist:
+        import torch.distributed as dist
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -368,35 +409,227 @@ def main():
             torch.cuda.synchronize(dev)
 
     stream = torch.cuda.current_stream(dev)
-    for _ in range(max(3, args.warmup)):
-        mk.run(sync=False, validate=False)
-    mk.wait()
+    for _ in range(max(3, warmup)):
+        launch()
+    barrier()
+    first_row = sampler.mark() if sampler else 0
+    per_step, total = [], 0.0
+    while True:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record(stream)
+        for _ in range(steps):
+            launch()
+        stop.record(stream)
+        barrier()
+        t = torch.tensor([start.elapsed_time(stop)], device=dev)
+        if use_dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        per_step.append(ms / steps)
+        total += ms * 1e-3
+        if total >= min_seconds or len(per_step) >= max_blocks:
+            break
+    last_row = sampler.mark() if sampler else 0
+    return statistics.median(per_step), len(per_step), (first_row, max(last_row, first_row + 1))
+
+
+def time_workload(w, steps, warmup, dev, use_dist, sampler=None):
+    ms, blocks, rows = time_launches(lambda: w.mk.run(sync=False, validate=False), steps, warmup, dev, use_dist, sampler)
+    w.mk.wait()
+    return ms, blocks, rows
+
+
+# ---- sub-records ----------------------------------------------------------------------------------------------
+def sub_args(args, **over):
+    a = argparse.Namespace(**vars(args))
+    a.kv_len = a.layers = a.vocab = 0
+    a.weights = a.parallel = ""
+    for k, v in over.items():
+        setattr(a, k, v)
+    return fill_defaults(a)
+
+
+def record_cfg4(args, dev, rank, world, use_dist, peak):
+    """The tensor-parallel configuration at this N: Qwen3-8B shape, block-scaled NVFP4, batch 1 and 8."""
+    out = {"workload": "qwen3-8b-shape 36-layer decode step, kv 8192, vocab 151936, nvfp4 (e4m3 scale per 16 "
+                       "values + fp32 global scale), greedy token", "n_gpus": world,
+           "parallelism": "single gpu" if world == 1 else f"tp{world} (in-kernel all-reduce)", "batches": {}}
+    for batch in (1, 8):
+        a = sub_args(args, model="qwen3-8b", batch=batch, parallel="tp")
+        try:
+            w = build_workload(a, dev, rank, world, use_dist)
+            ms, blocks, _ = time_workload(w, args.sub_steps, 5, dev, use_dist)
+            tp = w.tp or world == 1
+            achieved = w.alg_bytes / (ms * 1e-3) / 1e9
+            out["batches"][str(batch)] = {
+                "us_per_step": ms * 1e3, "tokens_per_s": batch * (1 if tp else world) / (ms * 1e-3),
+                "algorithmic_bytes_per_gpu": w.alg_bytes, "achieved_gbs_per_gpu": achieved, "frac": achieved / peak,
+                "steps": args.sub_steps, "blocks": blocks, "tensor_parallel": bool(w.tp), "note": w.tp_note}
+            del w
+        except Exception as exc:  # noqa: BLE001
+            out["batches"][str(batch)] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def rotating(make, nbytes, floor=3):
+    """Enough independent copies of a small workload that consecutive launches miss in L2."""
+    return [make(i) for i in range(max(floor, -(-2 * L2_BYTES // max(1, nbytes)) + 1))]
+
+
+def record_cfg1(args, dev, peak):
+    """Small-M GEMM sweep, bf16 and block-scaled NVFP4: weights are smaller than L2, so launches
+    rotate over copies of the weight matrix (together more than twice L2)."""
+    from machete_b200.kernels.decode_matvec import MatvecNvfp4Sm120Op
+    from machete_b200.kernels.gemm import GemmOp
+    from machete_b200.megakernel import Megakernel
+    from machete_b200.quantization import quantize_nvfp4_weight
+
+    bf = torch.bfloat16
+    shapes = [(M, N_, 4096) for M in (1, 4, 16) for N_ in (4096, 14336)] + [(16, 1024, 1024)]
+    out = {"l2": "launches rotate over weight copies totalling more than twice L2", "bf16": {}, "nvfp4": {}}
+    for fmt in ("bf16", "nvfp4"):
+        for (M, Nout, K) in shapes:
+            g = torch.Generator(device=dev).manual_seed(7)
+            x = torch.randn(1, M, K, generator=g, device=dev).to(bf)
+            y = torch.zeros(1, M, Nout, dtype=bf, device=dev)
+            wbytes = Nout * K * (2 if fmt == "bf16" else 0.5625)
+
+            def make(i, fmt=fmt, Nout=Nout, K=K, x=x, y=y, g=g):
+                wt = (torch.randn(Nout, K, generator=g, device=dev) * 0.02).to(bf)
+                if fmt == "bf16":
+                    return Megakernel(GemmOp.schedule(a=x, b=wt, c=y)).compile()
+                q = quantize_nvfp4_weight(wt, group_size=16)
+                return Megakernel(MatvecNvfp4Sm120Op.schedule(a=x, weight_packed=q.packed, weight_scales=q.scales, y=y,
+                                                              group_size=16, global_scale=q.global_scale)).compile()
+
+            mks = rotating(make, int(wbytes))
+            it = [0]
+
+            def launch():
+                mks[it[0] % len(mks)].run(sync=False, validate=False)
+                it[0] += 1
+
+            ms, blocks, _ = time_launches(launch, args.sub_steps, 5, dev, False, min_seconds=0.05)
+            alg = wbytes + M * K * 2 + M * Nout * 2
+            out[fmt][f"{M}x{K}x{Nout}"] = {"us": ms * 1e3, "algorithmic_bytes": int(alg),
+                                           "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak}
+            del mks
+            gc.collect()
+            torch.cuda.empty_cache()
+    return out
+
+
+def record_cfg2(args, dev, peak):
+    """Flash decoding alone: batch 8, 32 query / 8 KV heads, head dim 128, 32 768 tokens, 32 splits + combine."""
+    from machete_b200.kernels.attention import flash_decoding_schedule
+    from machete_b200.megakernel import Megakernel
+
+    B, H, Hkv, D, Nkv, S = 8, 32, 8, 128, 32768, 32
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(8)
+    q = torch.randn(B, 1, H, D, generator=g, device=dev).to(bf)
+    k = torch.randn(B, Nkv, Hkv, D, generator=g, device=dev).to(bf)
+    v = torch.randn(B, Nkv, Hkv, D, generator=g, device=dev).to(bf)
+    o = torch.zeros_like(q)
+    ops, _ = flash_decoding_schedule(q, k, v, o, num_splits=S, kv_group_size=H // Hkv)
+    mk = Megakernel(ops).compile()
+    ms, blocks, _ = time_launches(lambda: mk.run(sync=False, validate=False), args.sub_steps, 5, dev, False, min_seconds=0.1)
+    alg = 2 * B * Nkv * Hkv * D * 2
+    return {"workload": f"flash decoding B{B} H{H}/{Hkv} D{D} N{Nkv}, {S} splits + log-sum-exp combine (one fused op)",
+            "us": ms * 1e3, "algorithmic_bytes": alg, "achieved_gbs": alg / (ms * 1e-3) / 1e9,
+            "frac": alg / (ms * 1e-3) / 1e9 / peak, "l2": "1 GiB of K/V per launch, larger than L2"}
+
+
+def record_cfg0(args, dev, peak):
+    """One Llama-1B-shape layer, batch 1, KV 1024 (the case the reference can run on the CPU): the GPU
+    time over rotating weight copies, and the CPU oracle's time for the same layer."""
+    import oracle
+    from machete_b200.kernels.decode_matvec import schedule_decode_layer_sm100
+    from machete_b200.megakernel import Megakernel, OverlapTileScheduler
+
+    cfg, bf, T = LLAMA1B, torch.bfloat16, 1024
+    keepers = []
+
+    def make(i):
+        wts = make_weights(cfg, 1, 0, T, dev, seed=50 + i)
+        g = torch.Generator(device=dev).manual_seed(60 + i)
+        kc = torch.randn(1, T, cfg["nkv"], cfg["hd"], generator=g, device=dev).to(bf)
+        vc = torch.randn(1, T, cfg["nkv"], cfg["hd"], generator=g, device=dev).to(bf)
+        x = torch.randn(1, 1, cfg["hidden"], generator=g, device=dev).to(bf)
+        r = torch.randn(1, 1, cfg["hidden"], generator=g, device=dev).to(bf)
+        xo, ro = torch.zeros_like(x), torch.zeros_like(x)
+        layer = schedule_decode_layer_sm100(
+            layer_idx=0, batch=1, seq_len=1, cache_pos=T - 1, weights=wts, k_cache=kc, v_cache=vc, x_in=x, residual_in=r,
+            x_out=xo, residual_out=ro, q_buf=torch.zeros(1, 1, 2048, dtype=bf, device=dev),
+            attn_out_buf=torch.zeros(1, 1, 2048, dtype=bf, device=dev),
+            mlp_h_buf=torch.zeros(1, 1, cfg["inter"], dtype=bf, device=dev), eps=cfg["eps"])
+        keepers.append((wts, kc, vc, x, r, xo, ro, layer))
+        return Megakernel(layer.ops, scheduler=OverlapTileScheduler()).compile()
+
+    alg = algorithmic_bytes(cfg, 1, T, 1, 0)
+    mks = rotating(make, alg)
+    it = [0]
+
+    def launch():
+        mks[it[0] % len(mks)].run(sync=False, validate=False)
+        it[0] += 1
+
+    ms, blocks, _ = time_launches(launch, args.sub_steps, 5, dev, False, min_seconds=0.05)
+    wts, kc, vc, x, r = [t if isinstance(t, dict) else t.cpu() for t in keepers[0][:5]]
+    wcpu = {k_: v_.cpu() for k_, v_ in wts.items()}
+    torch.set_num_threads(os.cpu_count() or 1)
+    times = []
+    for _ in range(4):
+        t0 = time.perf_counter()
+        oracle.decode_layer(weights=wcpu, layer_idx=0, x_in=x, residual_in=r, k_cache=kc.clone(), v_cache=vc.clone(),
+                            cache_pos=T - 1, eps=cfg["eps"])
+        times.append(time.perf_counter() - t0)
+    return {"workload": "one llama-3.2-1b-shape layer, batch 1, kv 1024, bf16", "us": ms * 1e3, "algorithmic_bytes": alg,
+            "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak,
+            "cpu_oracle_ms": statistics.median(times[1:]) * 1e3, "cpu_cores": os.cpu_count(),
+            "l2": "launches rotate over layer copies totalling more than twice L2"}
+
+
+def main():
+    args = parse_args()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the native path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = build_workload(args, dev, rank, world, use_dist)
+    mk, cfg, tp, B, bf = w.mk, w.cfg, w.tp, args.batch, torch.bfloat16
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         sampler.wait_first()
-    barrier()
-    first_row = sampler.mark()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    for _ in range(args.steps):
-        mk.run(sync=False, validate=False)
-    stop.record(stream)
-    barrier()
-    mk.wait()
-    last_row = sampler.mark()
-    ms_total = start.elapsed_time(stop)
-    clocks = sampler.stop(first_row, max(last_row, first_row + 1)) if rank == 0 else None
-    t = torch.tensor([ms_total], device=dev)
-    if use_dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    ms_step, blocks, rows = time_workload(w, args.steps, args.warmup, dev, use_dist, sampler if rank == 0 else None)
+    clocks = sampler.stop(*rows) if rank == 0 else None
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if use_dist:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
 
     # end to end through the public API with host buffers
     e2e = None
     if not args.no_e2e:
-        host_x = torch.randn(B, 1, cfg["hidden"]).to(bf).pin_memory()
+        x_in, ti = w.x_in, w.ti
+        host_x = x_in.cpu().pin_memory()           # the same embedding: the token must not change
         host_tok = torch.zeros(B, 1, dtype=torch.int32).pin_memory()
         n_e2e = max(10, min(args.steps, 100))
         for _ in range(3):
@@ -404,10 +637,10 @@ def main():
             mk.run(sync=False, validate=False)
             host_tok.copy_(ti, non_blocking=True)
             torch.cuda.synchronize(dev)
-        # the copy in, the step and the copy out as ONE CUDA graph launch per step (single GPU; under
-        # tensor parallelism the plain calls are used): three driver calls become one
+        # the copy in, the step and the copy out as ONE CUDA graph launch per step (single process per
+        # GPU without a peer exchange; under tensor parallelism the plain calls are used)
         graph = None
-        if not use_dist:
+        if not tp:
             try:
                 side = torch.cuda.Stream(dev)
                 side.wait_stream(torch.cuda.current_stream(dev))
@@ -450,30 +683,61 @@ def main():
                else "x_in.copy_(pinned), Megakernel.run(), token.copy_ to pinned"}
         mk.wait()
 
+    line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
-        alg = algorithmic_bytes(cfg, B, L, args.layers, vocab, 0.5625 if nvfp4 else 2.0)   # per GPU (this rank's shard under tp)
-        achieved = alg / (ms_step * 1e-3) / 1e9
+        achieved = w.alg_bytes / (ms_step * 1e-3) / 1e9
         line = {
             "metric": "decode_tokens_per_s", "value": B * (1 if tp else world) / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
-            "us_per_step": ms_step * 1e3, "higher_is_better": True, "scaling": "strong" if tp else "weak",
-            "vs_baseline": None, "dtype": "bf16" if not nvfp4 else "nvfp4 weights, f16 tensor-core math, fp32 accumulate",
-            "data": "synthetic", "config": workload_config(args, world, tp, tp_note),
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "blocks": blocks,
+            "ms_per_step": ms_step, "us_per_step": ms_step * 1e3, "higher_is_better": True,
+            "scaling": "strong" if tp else "weak", "vs_baseline": None,
+            "dtype": "bf16" if not w.nvfp4 else "nvfp4 weights, f16 tensor-core math, fp32 accumulate",
+            "data": "synthetic", "config": workload_config(args, world, tp, w.tp_note),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
-                         "algorithmic_bytes_per_step": alg, "kernel": "mk_persistent_kernel",
-                         "traffic": int(alg * NCU_TRAFFIC_RATIO)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
+                         "algorithmic_bytes_per_step": w.alg_bytes, "kernel": "mk_persistent_kernel",
+                         "traffic": int(w.alg_bytes * NCU_TRAFFIC_RATIO),
+                         "traffic_from": "ncu dram bytes of a 4-layer capture x layers (profiles/), not this run"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * blocks,
             "kernel_config": {"ctas": mk.grid[0], "threads": mk.block[0], "smem": mk.smem_size, "pages": mk.num_pages,
                               "page_bytes": mk.page_bytes, "instructions": mk.total_tiles,
                               "counters": mk.num_barriers, "scheduler": args.scheduler},
         }
-        if not args.no_cpu_baseline and world == 1 and not nvfp4:
-            wcpu = {k: v.cpu() for k, v in weights.items()}
-            secs, sample = cpu_step_seconds(args, cfg, wcpu)
+        if not args.no_cpu_baseline and world == 1 and not w.nvfp4:
+            # the CPU oracle on the very same weights, caches and embedding
+            mk.run()
+            got_tok, got_val = int(w.ti[0, 0]), float(w.tv[0, 0])
+            wcpu = {k: v.cpu() for k, v in w.weights.items()}
+            secs, sample, full = cpu_step(args, cfg, wcpu, [t.cpu() for t in w.kcs], [t.cpu() for t in w.vcs],
+                                          w.x_in.cpu(), w.r_in.cpu())
             line["cpu_baseline"] = {"value": B / secs, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": sample, "ms_per_step": secs * 1e3}
+            if full is not None:
+                logits, tok = full
+                line["parity"] = {"token_equal": bool(int(tok[0, 0]) == got_tok), "gpu_token": got_tok,
+                                  "cpu_token": int(tok[0, 0]),
+                                  "logit_abs_err": abs(got_val - float(logits[0, 0, got_tok]))}
+            del wcpu
+    # sub-records: the other configurations (every rank takes part in cfg4, which is tensor parallel)
+    if not args.no_sub:
+        peak = measured_peak()[0]
+        del w, mk
+        gc.collect()
+        torch.cuda.empty_cache()
+        if args.model == "llama1b":
+            cfg4 = record_cfg4(args, dev, rank, world, use_dist, peak)
+            if rank == 0:
+                line["cfg4"] = cfg4
+        if world == 1 and rank == 0 and args.model == "llama1b":
+            for name, fn in (("cfg0", record_cfg0), ("cfg1", record_cfg1), ("cfg2", record_cfg2)):
+                try:
+                    line[name] = fn(args, dev, peak)
+                except Exception as exc:  # noqa: BLE001
+                    line[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                gc.collect()
+                torch.cuda.empty_cache()
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()

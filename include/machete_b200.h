@@ -383,10 +383,19 @@ int mk_flash_decode(const void* q, const void* k, const void* v, void* o, void* 
  *     message, use mk_flash_decode for them.
  *   - The array is shared by all calls on a device and keeps its last
  *     contents; the call clears the part that must start at zero itself.
- *     Calls that overlap in time on one device race: serialise them. */
+ *     Calls that overlap in time on one device race: serialise them.  Every
+ *     clear and upload of a call is queued on `cuda_stream` ahead of its
+ *     launch, so calls issued one after another on one stream need nothing
+ *     more; calls on different streams need an event or a host
+ *     synchronisation between them. */
 int mk_flash_decode_noalloc(const void* q, const void* k, const void* v, void* o, void* lse,
                             int32_t B, int32_t M, int32_t H, int32_t Hkv, int32_t D, int32_t N,
                             int32_t splits, int32_t causal, float scale, void* cuda_stream);
+
+/* Device status block of the last mk_flash_decode_noalloc call on the current
+ * device (out[0] == 0: no bounded wait expired).  Synchronises the device.
+ * No counterpart in the reference. */
+int mk_flash_decode_noalloc_status(int32_t out[16]);
 
 #ifdef __cplusplus
 }

@@ -113,7 +113,7 @@ EXPORTS = [
     "mk_status", "mk_workspace_status", "mk_set_trace", "mk_reset", "mk_launch_count", "mk_set_launch_count",
     "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
-    "mk_flash_decode_noalloc",
+    "mk_flash_decode_noalloc", "mk_flash_decode_noalloc_status",
 ]
 
 _lib = None
@@ -183,6 +183,8 @@ def _declare(h: C.CDLL) -> None:
                                   vp, u64, vp]
     h.mk_flash_decode_noalloc.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp]
     h.mk_flash_decode_noalloc.restype = C.c_int
+    h.mk_flash_decode_noalloc_status.argtypes = [C.POINTER(i32)]
+    h.mk_flash_decode_noalloc_status.restype = C.c_int
     for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op",
                  "mk_launch_count", "mk_set_launch_count",
                  "mk_read_counters", "mk_destroy", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode"):
