@@ -49,12 +49,14 @@ def test_shard_programs_compile_at_llama1b_shapes(world):
     assert mk.total_tiles > 0
 
 
-@pytest.mark.parametrize("mode,world", [("bf16", 2), ("nvfp4", 2), ("nvfp4_split", 2), ("bf16", 4), ("nvfp4", 4),
-                                        ("bf16", 8)])
+@pytest.mark.parametrize("mode,world", [("bf16", 2), ("nvfp4", 2), ("nvfp4_split", 2), ("bf16_fault", 2), ("bf16", 4),
+                                        ("nvfp4", 4), ("bf16", 8)])
 def test_sharded_decode_matches_single_gpu_and_oracle(mode, world):
     """bf16: the Llama-1B-shape layers; nvfp4: Qwen3-style layers (head dim 128, q/k RMSNorm, 4 KV heads)
     with packed weights; nvfp4_split: an intermediate size whose per-rank K range (3072) has to run as
-    2048 + 1024 with an exchange each.  One process per GPU;
+    2048 + 1024 with an exchange each; bf16_fault: after the normal steps the last rank skips one
+    step, the others' wait for it times out with a status, the group re-agrees on the launch count
+    (``Megakernel.resync_launch_count``) and the step after that matches again.  One process per GPU;
     skipped on a box with fewer GPUs than ranks."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -64,6 +66,8 @@ def test_sharded_decode_matches_single_gpu_and_oracle(mode, world):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_MODE=mode.split("_")[0])
     if mode == "nvfp4_split":
         env["TP_INTER"] = "6144"
+    if mode == "bf16_fault":
+        env.update(TP_FAULT="1", TP_TIMEOUT_MS="300")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)

@@ -86,7 +86,7 @@ def build_nvfp4(packed, dev, world, rank, peers):
         attn_out_buf=z(1, 1, nq * d["hd"]), mlp_h_buf=z(1, 1, inter), top_values=tv, top_indices=ti,
         num_layers=d["layers"], x_in=x_in.to(dev), residual_in=z(1, 1, d["hidden"]), num_q_heads=nq,
         num_kv_heads=nkv, head_dim=d["hd"], eps=1e-6, tp_peers=peers)
-    mk = Megakernel(ops, config=MegakernelConfig(timeout_ms=2000), device=dev, scheduler=OverlapTileScheduler())
+    mk = Megakernel(ops, config=MegakernelConfig(timeout_ms=int(os.environ.get("TP_TIMEOUT_MS", "2000"))), device=dev, scheduler=OverlapTileScheduler())
     return mk, tv, ti, None, None, (kfull, vfull, x_in), (keep, w)
 
 
@@ -114,7 +114,7 @@ def build(weights, lm, dev, world, rank, peers):
         top_values=tv, top_indices=ti, num_layers=d["layers"], hidden_size=d["hidden"], intermediate_size=inter,
         num_q_heads=nq, num_kv_heads=nkv, head_dim=d["hd"], x_in=x_in.to(dev),
         residual_in=torch.zeros(1, 1, d["hidden"], dtype=BF, device=dev), tp_peers=peers)
-    mk = Megakernel(ops, config=MegakernelConfig(timeout_ms=2000), device=dev, scheduler=OverlapTileScheduler())
+    mk = Megakernel(ops, config=MegakernelConfig(timeout_ms=int(os.environ.get("TP_TIMEOUT_MS", "2000"))), device=dev, scheduler=OverlapTileScheduler())
     return mk, tv, ti, xb, rb, (kfull, vfull, x_in), keep
 
 
@@ -143,9 +143,33 @@ def main():
         dist.barrier()
         mk.run()
         tokens.append((int(ti.item()), float(tv.item())))
+    recovered = True
+    if os.environ.get("TP_FAULT") == "1":
+        # A rank that never joins one step (the failure is made on the host: the last rank simply
+        # does not launch).  The others' bounded wait for its words gives up with a status, nobody
+        # hangs; then, between steps and with no kernel in flight, the group agrees on a launch
+        # count again and the next step must give the same token as before.
+        failed = True
+        if rank != world - 1:
+            try:
+                mk.run()
+                failed = False
+            except RuntimeError as exc:
+                # the first wait to run out names the abort: the wait for the peer's words, or another
+                # CTA's wait for the exchange op to complete
+                failed = "megakernel aborted" in str(exc)
+        dist.barrier()
+        counts = [None] * world
+        dist.all_gather_object(counts, mk.launch_count())
+        agreed = mk.resync_launch_count()
+        dist.barrier()
+        mk.run()
+        again = (int(ti.item()), float(tv.item()))
+        recovered = failed and len(set(counts)) == 2 and agreed == max(counts) and again == tokens[0]
+        print(f"rank {rank}: launch counts {counts} -> {agreed}, token after recovery {again}", flush=True)
     gathered = [None] * world
     dist.all_gather_object(gathered, tokens)
-    ok = all(g == gathered[0] for g in gathered) and len(set(tokens)) == 1
+    ok = all(g == gathered[0] for g in gathered) and len(set(tokens)) == 1 and recovered
     msg = f"rank {rank}: tokens {tokens}"
     if rank == 0:
         if nvfp4:
@@ -159,11 +183,18 @@ def main():
                                                     v_caches=[v.clone() for v in vfull], cache_pos=d["pos"],
                                                     final_norm=torch.ones(d["hidden"], dtype=BF), lm_head=lm,
                                                     num_layers=d["layers"], **oracle_kw)
-        ok = ok and tokens[0][0] == want_idx and abs(tokens[0][1] - want_val) < 2e-2
+        # One bar for every comparison (tests/util.py): 2e-2 or two bf16 ulps of the largest logit.  The
+        # sharded step, the unsharded step and the oracle must agree on the greedy token unless the
+        # oracle's own top two logits are closer than that bar (the three sum K in different orders).
+        from tests.util import parity_bar
+
+        bar = parity_bar(_logits, roundings=2)
         top2 = _logits.flatten().topk(2).values
-        if float(top2[0] - top2[1]) > 4e-2:      # the greedy token is only comparable when it is not a near-tie
-            ok = ok and int(o_idx.flatten()[0]) == tokens[0][0]
-        ok = ok and abs(tokens[0][1] - float(_logits.flatten()[tokens[0][0]])) <= 4e-2
+        clear_winner = float(top2[0] - top2[1]) > bar
+        ok = ok and abs(tokens[0][1] - want_val) <= bar
+        if clear_winner:
+            ok = ok and tokens[0][0] == want_idx and int(o_idx.flatten()[0]) == tokens[0][0]
+        ok = ok and abs(tokens[0][1] - float(_logits.flatten()[tokens[0][0]])) <= bar
         msg += f" | single-GPU ({want_idx}, {want_val:.4f}) | oracle ({int(o_idx.flatten()[0])}, {float(o_val.flatten()[0]):.4f})"
     print(msg, flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
