@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define MK_ABI_VERSION 4
+#define MK_ABI_VERSION 5
 
 /* ---- opcodes ------------------------------------------------------------ */
 enum {
@@ -96,7 +96,14 @@ enum {
   MK_MV_SPLIT,
   /* MK_EPI_TOP1: added to the row index packed into the key (the first
    * vocabulary row of this rank's shard under tensor parallelism) */
-  MK_MV_IDX0
+  MK_MV_IDX0,
+  /* 1 = the op follows the program's device-resident cache position p
+   * (mk_program_t.position): the output row offset becomes (s + POS + p) and
+   * the RoPE tables are read at row (s + p), so cos / sin point at row 0 of
+   * the full tables and POS is 0.  The reference bakes the position into the
+   * schedule and re-schedules per token (kernels/decode_matvec/sm100.py:116,
+   * 704-709). */
+  MK_MV_DYNPOS
 };
 /* GSCALE / GSCALE1: fp32 global scale of W0 / of W1 (MK_MV_PAIR; block-scaled NVFP4 only) */
 enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1, MK_MV_F_GSCALE1 = 2 };
@@ -137,7 +144,13 @@ enum {
    * (src/machete/kernels/qwen_3_5/sm120.py:2986-2994; numerics of
    * qknorm_rope/ref.py:10-39).  Needs M = 1 token per sequence, H/Hkv <= 16. */
   MK_AT_QKNORM,
-  MK_AT_NEW_TOK
+  MK_AT_NEW_TOK,
+  /* 1 = the KV window follows the device-resident cache position p: the op
+   * attends to tokens [0, p + M); MK_AT_N is then the cache CAPACITY (tensor
+   * maps, split bounds and the per-unit page limits derive from it; loader
+   * and consumers compute the pages in use from p), and the new-token row of
+   * the fused q/k norm is p. */
+  MK_AT_DYNPOS
 };
 enum { MK_AT_F_SCALE = 0, MK_AT_F_EPS };
 enum {
@@ -162,7 +175,12 @@ enum { MK_EW_F_EPS = 0 };
 enum { MK_EW_P_X = 0, MK_EW_P_Y, MK_EW_P_W, MK_EW_P_RES_IN, MK_EW_P_RES_OUT, MK_EW_P_GATE, MK_EW_P_COS, MK_EW_P_SIN };
 enum { MK_EW_S_X = 0, MK_EW_S_Y, MK_EW_S_W, MK_EW_S_RI, MK_EW_S_RO, MK_EW_S_G, MK_EW_S_COS, MK_EW_S_X_H };
 /* MK_EW_FLAGS bits */
-enum { MK_EWF_RESIDUAL = 1, MK_EWF_GEMMA = 2, MK_EWF_FUSED_ADD = 4, MK_EWF_GATED = 8, MK_EWF_ROW_WEIGHT = 16 };
+enum { MK_EWF_RESIDUAL = 1, MK_EWF_GEMMA = 2, MK_EWF_FUSED_ADD = 4, MK_EWF_GATED = 8, MK_EWF_ROW_WEIGHT = 16,
+       /* MK_OP_TOP1_FINAL: feed the greedy token back for the next launch — copy row
+        * `token` of the embedding table p[MK_EW_P_RES_IN] (row stride s[MK_EW_S_RI],
+        * MK_EW_D 16-bit values) into row m of p[MK_EW_P_RES_OUT] (row stride
+        * s[MK_EW_S_RO]) and add MK_EW_S to the position scalar p[MK_EW_P_GATE] */
+       MK_EWF_FEEDBACK = 32 };
 
 /* MK_OP_ALLREDUCE: one-shot all-reduce over peer-mapped inboxes.  Every rank
  * runs the same op with its own MK_AR_RANK; p[MK_AR_P_PEER0 + r] is rank r's
@@ -220,8 +238,10 @@ typedef struct mk_instr {
 /* MK_LDF_ATTN marks a split-KV attention unit: ld_maps holds the K and V cache
  * maps, ld_row_a the first token, ld_row_b = kv head | batch << 16, ld_tiles
  * the tokens per page; MK_LDF_D128 = head dim 128 (two 64-wide sub-tiles). */
-enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_ATTN = 4, MK_LDF_D128 = 8, MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15,
-       MK_LDF_CHUNK_SHIFT = 12, MK_LDF_CHUNK_MASK = 4095 };
+enum { MK_LDF_FP4 = 1, MK_LDF_PAIR = 2, MK_LDF_ATTN = 4, MK_LDF_D128 = 8,
+       /* attention unit of an MK_AT_DYNPOS op: n_pages is the limit, the pages in use follow the position */
+       MK_LDF_DYN = 16,
+       MK_LDF_SPLIT_SHIFT = 8, MK_LDF_SPLIT_MASK = 15, MK_LDF_CHUNK_SHIFT = 12, MK_LDF_CHUNK_MASK = 4095 };
 
 /* Op-entry event: before a CTA executes instruction `pos` of its list, all
  * of its consumer warps meet, wait for the listed counters and stage the
@@ -277,6 +297,12 @@ typedef struct mk_program {
   const mk_wait_t* waits;
   void* workspace;                /* DEVICE memory, >= mk_workspace_bytes()  */
   uint64_t workspace_bytes;
+  /* Optional device-resident cache position (one int32 in DEVICE memory, NULL =
+   * none): ops scheduled with MK_MV_DYNPOS / MK_AT_DYNPOS read it at the start
+   * of every launch, the feedback form of MK_OP_TOP1_FINAL advances it at the
+   * end, so consecutive launches (or replays of one CUDA graph) decode
+   * consecutive tokens with no host work in between. */
+  const int32_t* position;
 } mk_program_t;
 
 typedef struct mk_handle_s* mk_handle_t;

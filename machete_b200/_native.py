@@ -15,7 +15,7 @@ import numpy as np
 
 from . import build as _build
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 NUM_CONSUMER_WARPS = 7   # csrc/shell.cuh kConsumerWarps
 
 # ---- enums (keep in sync with include/machete_b200.h) ------------------------
@@ -29,7 +29,7 @@ W_BF16, W_FP16, W_NVFP4_F16S32, W_NVFP4_E4M3S16 = range(4)
 T_BF16, T_FP16, T_FP32 = range(3)
 
 (MV_O, MV_K, MV_M, MV_S, MV_MODE, MV_PRO, MV_EPI, MV_TR, MV_HD, MV_D2, MV_POS, MV_WFMT, MV_KC, MV_OUT_T,
- MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT, MV_IDX0) = range(18)
+ MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT, MV_IDX0, MV_DYNPOS) = range(19)
 MV_F_EPS, MV_F_GSCALE, MV_F_GSCALE1 = range(3)
 (MV_P_W0, MV_P_W1, MV_P_X, MV_P_RES_IN, MV_P_NORM_W, MV_P_RES_OUT, MV_P_OUT, MV_P_EPI_RES, MV_P_COS,
  MV_P_SIN, MV_P_SC0, MV_P_SC1) = range(12)
@@ -37,7 +37,7 @@ MV_F_EPS, MV_F_GSCALE, MV_F_GSCALE1 = range(3)
  MV_S_ER_B, MV_S_ER_S, MV_S_COS, MV_S_SCROW) = range(14)
 
 (AT_B, AT_M, AT_H, AT_HKV, AT_D, AT_N, AT_SPLITS, AT_CAUSAL, AT_MT, AT_TS, AT_O_T, AT_FUSE_COMBINE, AT_QKNORM,
- AT_NEW_TOK) = range(14)
+ AT_NEW_TOK, AT_DYNPOS) = range(15)
 AT_F_SCALE, AT_F_EPS = 0, 1
 (AT_P_Q, AT_P_K, AT_P_V, AT_P_OPART, AT_P_LSEPART, AT_P_O, AT_P_LSE, AT_P_ARRIVE, AT_P_QNW, AT_P_KNW, AT_P_COS,
  AT_P_SIN) = range(12)
@@ -53,7 +53,7 @@ AR_SUM, AR_MAX_KEY = 0, 1
 (AR_P_X, AR_P_RES, AR_P_Y, AR_P_PEER0) = range(4)
 AR_S_INBOX, AR_S_FLAGS = 0, 1
 AR_MAX_RANKS = 8
-EWF_RESIDUAL, EWF_GEMMA, EWF_FUSED_ADD, EWF_GATED, EWF_ROW_WEIGHT = 1, 2, 4, 8, 16
+EWF_RESIDUAL, EWF_GEMMA, EWF_FUSED_ADD, EWF_GATED, EWF_ROW_WEIGHT, EWF_FEEDBACK = 1, 2, 4, 8, 16, 32
 EVF_WRITE_RES_OUT, EVF_BULK_SIGNAL = 1, 2
 
 # Device status codes (csrc/shell.cuh).
@@ -104,7 +104,7 @@ class Program(C.Structure):
         ("act_bytes", C.c_int32), ("timeout_ms", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
         ("ops", C.c_void_p), ("instrs", C.c_void_p), ("cta_instr_begin", C.c_void_p),
         ("events", C.c_void_p), ("cta_event_begin", C.c_void_p), ("waits", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("position", C.c_void_p),
     ]
 
 

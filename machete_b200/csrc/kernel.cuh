@@ -101,7 +101,17 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
       const LoaderInstr ins = bcast_loader_instr(mine, i);
       c.instr_idx = base + i;
       if (ins.n_pages == 0) continue;
-      if (ins.n_lwaits > 0) {
+      int n_pages = ins.n_pages;
+      bool need_wait = ins.n_lwaits > 0;
+      if (ins.flags & MK_LDF_DYN) {
+        // the window follows the device-resident position: tokens [0, pos + 1); only the unit
+        // that holds the row appended in this launch waits for it
+        const int pos = c.ctrl->pos;
+        n_pages = at_dyn_pages(ins.row_a, ins.n_pages, ins.tiles, pos + 1);
+        need_wait = need_wait && pos >= ins.row_a && pos < ins.row_a + ins.n_pages * ins.tiles;
+        if (n_pages == 0) continue;
+      }
+      if (need_wait) {
         if (!wait_counters(c, ins.n_lwaits, ins.lwait_off)) break;
         trace(c, TRC_LWAIT_DONE, base + i);
       }
@@ -113,7 +123,7 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
       // V box (two each for head dim 128), a matvec page two weight boxes
       // (plus two scale boxes for NVFP4).
       const bool attn = (ins.flags & MK_LDF_ATTN) != 0;
-      if (attn && ins.n_lwaits > 0) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
+      if (attn && need_wait) fence_proxy_async_all();   // the awaited K/V rows were written by plain stores
       int issued = 0;
       if (c.lane == 0) {
         const uint8_t* maps = reinterpret_cast<const uint8_t*>(ins.maps);
@@ -130,7 +140,7 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
         ml.half = (uint32_t)ins.tiles * 1024u;
         RingPos q = rp;
 #pragma unroll 1
-        for (; issued < ins.n_pages; ++issued, ring_next(q, NP)) {
+        for (; issued < n_pages; ++issued, ring_next(q, NP)) {
           if (!wait_mbar_one(c, empty_bar(c, q.slot), (q.k & 1u) ^ 1u, MK_ST_TIMEOUT_PAGE_EMPTY, (int)(seq + issued)))
             break;
           trace(c, TRC_LOAD_BEGIN, seq + issued);
@@ -144,7 +154,7 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
         }
       }
       issued = __shfl_sync(0xffffffffu, issued, 0);
-      if (issued < ins.n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
+      if (issued < n_pages) c.dead = true;   // lane 0 gave up (abort flag is already raised)
       ring_advance(rp, issued, NP);
       seq += (uint32_t)issued;
     }
@@ -327,7 +337,16 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
       n_pages = __shfl_sync(0xffffffffu, mine.n_pages, i - base);
       lflags = __shfl_sync(0xffffffffu, mine.flags, i - base);
       const bool shared = (lflags & kInsMatvec) != 0;
-      const int split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+      int split = (lflags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
+      if (lflags & MK_LDF_DYN) {
+        // an attention unit whose window follows the device-resident position: the pages in use, and
+        // with them the participants, are a function of the position (the same on every warp)
+        const int t_begin = __shfl_sync(0xffffffffu, mine.row_a, i - base);
+        n_pages = at_dyn_pages(t_begin, n_pages, at_page_tokens((lflags & MK_LDF_D128) ? 128 : 64, pv.page_bytes),
+                               c.ctrl->pos + 1);
+        split = max(1, min(split, n_pages));
+        lflags = (lflags & ~(MK_LDF_SPLIT_MASK << MK_LDF_SPLIT_SHIFT)) | (split << MK_LDF_SPLIT_SHIFT);
+      }
       const uint32_t slots = shared ? (uint32_t)split : 1u;
       if (ticket < first_slot + slots) {
         found = true;
@@ -401,6 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
     c.ctrl->is_last = 0;
     c.ctrl->ticket = 0;
     c.ctrl->ev_arrive = 0;
+    c.ctrl->pos = pv.dyn_pos != nullptr ? *reinterpret_cast<const volatile int32_t*>(pv.dyn_pos) : 0;
     c.ctrl->bulk_done[0] = c.ctrl->bulk_done[1] = 0;
     fence_mbar_init();
   }

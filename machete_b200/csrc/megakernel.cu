@@ -226,7 +226,8 @@ static void fill_instr_fast_path(mk_instr_t& in, const mk_op_t& op, uint64_t dev
     // every participant keeps one ring page until the unit's states are merged:
     // leave at least two pages for the stream
     const int split = std::max(1, std::min(std::min((int)kConsumerWarps, in.n_pages), n_ring_pages - 2));
-    in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT);
+    in.ld_flags = MK_LDF_ATTN | (op.i[MK_AT_D] == 128 ? MK_LDF_D128 : 0) | (split << MK_LDF_SPLIT_SHIFT) |
+                  (op.i[MK_AT_DYNPOS] ? MK_LDF_DYN : 0);
     if (in.n_pages == 0) in.ld_maps = 0;   // an empty split: nothing to load, one consumer writes the empty partial
     return;
   }
@@ -342,6 +343,8 @@ static int validate_op(const mk_op_t& op, int idx, int page_bytes, int act_bytes
         if (op.s[k] & 7) return fail(-2, "op %d: q/k/v strides must be multiples of 8 elements", idx);
       if (op.n_units != op.i[MK_AT_B] * HKV * op.i[MK_AT_MT] * op.i[MK_AT_SPLITS])
         return fail(-2, "op %d: bad unit count", idx);
+      if (op.i[MK_AT_DYNPOS] && (M != 1 || op.i[MK_AT_CAUSAL]))
+        return fail(-2, "op %d: a KV window that follows the cache position needs one token per sequence, non-causal", idx);
       if (op.i[MK_AT_QKNORM]) {
         if (M != 1 || op.i[MK_AT_MT] != 1) return fail(-2, "op %d: fused q/k norm needs one token per sequence and H/Hkv <= 16", idx);
         if (op.i[MK_AT_NEW_TOK] < 0 || op.i[MK_AT_NEW_TOK] >= op.i[MK_AT_N]) return fail(-2, "op %d: new-token row outside the cache window", idx);
@@ -366,6 +369,11 @@ static int validate_op(const mk_op_t& op, int idx, int page_bytes, int act_bytes
     if (op.i[MK_EW_T] < 0 || op.i[MK_EW_T] > MK_T_FP32) return fail(-2, "op %d: bad element type", idx);
   } else if (op.opcode == MK_OP_TOP1_FINAL) {
     if (!op.p[MK_EW_P_X] || !op.p[MK_EW_P_W] || (op.p[MK_EW_P_X] & 7)) return fail(-2, "op %d: top-1 buffers missing", idx);
+    if (op.i[MK_EW_FLAGS] & MK_EWF_FEEDBACK) {
+      if (!op.p[MK_EW_P_RES_IN] || !op.p[MK_EW_P_RES_OUT] || ((op.p[MK_EW_P_RES_IN] | op.p[MK_EW_P_RES_OUT]) & 15) ||
+          (op.i[MK_EW_D] & 7) || op.i[MK_EW_D] <= 0 || ((op.s[MK_EW_S_RI] | op.s[MK_EW_S_RO]) & 7) || (op.p[MK_EW_P_GATE] & 3))
+        return fail(-2, "op %d: token feedback needs 16-byte aligned embedding and input rows of a multiple of 8 values", idx);
+    }
   } else if (op.opcode == MK_OP_ALLREDUCE) {
     const int P = op.i[MK_AR_P], rank = op.i[MK_AR_RANK], n = op.i[MK_AR_N];
     if (P < 2 || P > MK_AR_MAX_RANKS || rank < 0 || rank >= P) return fail(-2, "op %d: bad all-reduce world %d / rank %d", idx, P, rank);
@@ -403,6 +411,13 @@ static int validate_program(const mk_program_t* p, int smem_optin, int num_sms, 
     const int rc = validate_op(p->ops[i], i, p->page_bytes, p->act_bytes);
     if (rc) return rc;
   }
+  if (p->position == nullptr)
+    for (int i = 0; i < p->n_ops; ++i) {
+      const mk_op_t& op = p->ops[i];
+      if ((op.opcode == MK_OP_MATVEC && op.i[MK_MV_DYNPOS]) || (op.opcode == MK_OP_ATTN_SPLIT && op.i[MK_AT_DYNPOS]))
+        return fail(-2, "op %d follows a device-resident cache position, but the program has none (mk_program_t.position)", i);
+    }
+  if (p->position != nullptr && ((uint64_t)p->position & 3)) return fail(-1, "position scalar must be 4-byte aligned");
   for (int i = 0; i < p->n_waits; ++i)
     if (p->waits[i].counter < 0 || p->waits[i].counter >= p->n_counters)
       return fail(-3, "wait %d: counter %d out of range", i, p->waits[i].counter);
@@ -677,6 +692,7 @@ static int create_program(const mk_program_t* prog, mk_handle_t* out, bool strea
   h->pv.timeout_ns = (uint64_t)(prog->timeout_ms > 0 ? prog->timeout_ms : 1000) * 1000000ull;
   h->pv.trace = nullptr;
   h->pv.trace_cap = 0;
+  h->pv.dyn_pos = prog->position;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
   h->smem_optin = smem_optin;

@@ -48,7 +48,7 @@ __device__ __forceinline__ AtUnit at_decode_fast(const mk_op_t* op, const UnitAr
   u.mt = ins_field(a.mine->off_b, a.idx);
   u.kvh = rb & 0xffff;
   u.b = rb >> 16;
-  u.t_end = min(op->i[MK_AT_N], u.t_begin + op->i[MK_AT_TS]);
+  u.t_end = u.t_begin + op->i[MK_AT_TS];   // the caller clips both to the window
   return u;
 }
 
@@ -262,9 +262,14 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
   const int part = ua.part;
   const uint32_t ord = ua.ord;
   const int parts = (ua.flags >> MK_LDF_SPLIT_SHIFT) & MK_LDF_SPLIT_MASK;
-  const AtUnit u = at_decode_fast(op, ua);
+  AtUnit u = at_decode_fast(op, ua);
   const int g = c.lane >> 2, t = c.lane & 3;
-  const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], N = op->i[MK_AT_N];
+  const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV];
+  // the window: the scheduled length, or (device-resident position) every token up to this step's
+  const bool dyn = op->i[MK_AT_DYNPOS] != 0;
+  const int N = dyn ? min(op->i[MK_AT_N], c.ctrl->pos + M) : op->i[MK_AT_N];
+  u.t_begin = min(u.t_begin, N);
+  u.t_end = min(u.t_end, N);
   const int G = H / HKV;
   const int S = op->i[MK_AT_SPLITS];
   const bool causal = op->i[MK_AT_CAUSAL] != 0;
@@ -374,7 +379,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
     const uint32_t kpage = page, vpage = page + tile_bytes;
     const int tp0 = u.t_begin + p * tn;
     if (qknorm) {
-      const int nt = op->i[MK_AT_NEW_TOK];
+      const int nt = dyn ? c.ctrl->pos : op->i[MK_AT_NEW_TOK];
       if (nt >= tp0 && nt < tp0 + tn && nt < u.t_end) at_fix_k_row<D>(c, op, u, kpage, tn, nt - tp0, nt);
     }
     for (int blk = 0; blk * TN < tn; ++blk) {

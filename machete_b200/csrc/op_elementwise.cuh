@@ -170,6 +170,25 @@ __device__ __forceinline__ void ew_top1_final(Ctx& c, const mk_op_t* op, int uni
     idxs[m] = (int32_t)(0xffffffffu - (uint32_t)(k & 0xffffffffull));
   }
   (void)unit;
+  if (op->i[MK_EW_FLAGS] & MK_EWF_FEEDBACK) {
+    // Feed the greedy token back: its embedding row becomes the next launch's input row, and
+    // the device-resident cache position moves on.  Every other unit of this launch is complete
+    // (this op waits for the whole LM head), so nothing still reads either of them.
+    __syncwarp();
+    const int D = op->i[MK_EW_D];
+    const uint16_t* emb = reinterpret_cast<const uint16_t*>(op->p[MK_EW_P_RES_IN]);
+    uint16_t* xin = reinterpret_cast<uint16_t*>(op->p[MK_EW_P_RES_OUT]);
+    for (int m = 0; m < rows; ++m) {
+      const int tok = *reinterpret_cast<volatile int32_t*>(idxs + m);
+      const uint4* src = reinterpret_cast<const uint4*>(emb + (int64_t)tok * op->s[MK_EW_S_RI]);
+      uint4* dst = reinterpret_cast<uint4*>(xin + (int64_t)m * op->s[MK_EW_S_RO]);
+      for (int ch = c.lane; ch < D / 8; ch += 32) dst[ch] = src[ch];
+    }
+    if (c.lane == 0) {
+      int32_t* pos = reinterpret_cast<int32_t*>(op->p[MK_EW_P_GATE]);
+      if (pos != nullptr) *pos = *pos + op->i[MK_EW_S];
+    }
+  }
 }
 
 }  // namespace mk

@@ -77,6 +77,7 @@ struct ProgramView {
   struct TraceRec* trace;
   int32_t trace_cap;
   int32_t mv_sets;  // split-K slot sets in use: 4 (every matvec has M <= 8), 2 (M <= 16) or 1
+  const int32_t* dyn_pos;  // device-resident cache position, or null
 };
 
 // One trace event: a globaltimer stamp, an event code and an argument.
@@ -120,7 +121,8 @@ struct Ctrl {
   uint32_t bulk_done[2];
   uint32_t ticket;     // next consumer slot of the CTA (see consumer_loop)
   uint32_t ev_arrive;  // consumer warps that have reached an op-entry event (kConsumerWarps per event)
-  int32_t pad[2];
+  int32_t pos;         // the device-resident cache position as read when the launch started (0 without one)
+  int32_t pad[1];
   // released[slot] = number of fills of the slot that consumers have handed back
   uint32_t released[kMaxPages];
   // per activation row and consumer warp: sum of squares of the staged row (RMSNorm)
@@ -404,6 +406,16 @@ __device__ __forceinline__ void ring_next(RingPos& r, int np) {
     r.slot = 0;
     ++r.k;
   }
+}
+
+// Pages in use of a split-KV attention unit whose window follows the cache
+// position: `limit` pages of `tn` tokens were scheduled for tokens
+// [t_begin, ...); the window ends at token `n_tokens`.
+__device__ __forceinline__ int at_dyn_pages(int t_begin, int limit, int tn, int n_tokens) {
+  const int left = n_tokens - t_begin;
+  if (left <= 0) return 0;
+  const int need = (left + tn - 1) / tn;
+  return need < limit ? need : limit;
 }
 
 // Consumer side: wait until the ring entry holds data; returns its address.

@@ -68,7 +68,7 @@ class FlashDecodingSplitBSHDOp(Op):
 
     @classmethod
     def schedule(cls, tile_sizes=None, causal=False, page_size=DEFAULT_PAGE_SIZE, kv_group_size=1,
-                 num_splits=0, qk_norm=None, **tensors):
+                 num_splits=0, qk_norm=None, dynamic_len=False, **tensors):
         """``qk_norm`` (not in the reference's signature): ``dict(q_weight, k_weight, cos, sin, eps,
         new_token)`` makes the op take UNROTATED q and an unrotated k row ``new_token`` and apply the
         per-head RMSNorm + split-half rotation itself (the reference schedules a separate
@@ -105,6 +105,12 @@ class FlashDecodingSplitBSHDOp(Op):
         sd.update({"M": M, "N": N_kv, "H": H, "SPLIT": num_splits})
         sd["k_b_stride"], sd["k_n_stride"], sd["k_h_stride"] = k.stride(0), k.stride(1), k.stride(2)
         sd["v_b_stride"], sd["v_n_stride"], sd["v_h_stride"] = v.stride(0), v.stride(1), v.stride(2)
+        if dynamic_len:
+            # not in the reference: k / v are the FULL caches and the op attends to tokens [0, p + 1),
+            # p being the program's device-resident cache position (MegakernelConfig.position)
+            if causal or M != 1:
+                raise ValueError("dynamic_len needs one token per sequence and no causal mask")
+            sd["dynamic_len"] = 1
         if causal:
             sd["causal"] = 1
         if kv_group_size > 1:
@@ -167,6 +173,8 @@ class FlashDecodingSplitBSHDOp(Op):
         op.reads = [Region(meta_of(q, "q")), Region(meta_of(k, "k"), loader=True), Region(meta_of(v, "v"), loader=True)]
         op.writes = [Region(meta_of(t["o_partial"], "o_partial")), Region(meta_of(t["lse_partial"], "lse_partial"))]
         op.keep = [q, k, v, t["o_partial"], t["lse_partial"]]
+        if sop.static_dims.get("dynamic_len"):
+            op.i[N.AT_DYNPOS] = 1
         qkn = sop.params.get("qk_norm")
         if qkn is not None:
             op.i[N.AT_QKNORM], op.i[N.AT_NEW_TOK] = 1, int(qkn["new_token"])
@@ -187,6 +195,8 @@ class FlashDecodingSplitBSHDOp(Op):
 
         def loader_dep_units(producer, unit, tb=tb, te=te):
             # a cache-append producer writes token rows [lo, hi): only splits that cover them wait
+            # (with a device-resident position hi is the cache length: every unit carries the wait
+            # and the loader decides per launch which one holds the new row)
             for w in producer.writes:
                 if w.axis == 1 and producer.kind == "cache_append":
                     return bool(tb[unit] < w.hi and te[unit] > w.lo)
@@ -254,7 +264,7 @@ class FlashDecodingCombineBSHDOp(Op):
 
 
 def flash_decoding_schedule(q, k, v, o, num_splits=0, page_size=DEFAULT_PAGE_SIZE, causal=False,
-                            kv_group_size=1, qk_norm=None):
+                            kv_group_size=1, qk_norm=None, dynamic_len=False):
     """Schedule split-KV flash decoding followed by its combine.
 
     Returns ``(ops, config)`` like the reference.  ``qk_norm``: see ``FlashDecodingSplitBSHDOp.schedule``.
@@ -265,7 +275,7 @@ def flash_decoding_schedule(q, k, v, o, num_splits=0, page_size=DEFAULT_PAGE_SIZ
     lse = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
     split_ops, o_partial, lse_partial = FlashDecodingSplitBSHDOp.schedule(
         q=q, k=k, v=v, num_splits=num_splits, page_size=page_size, causal=causal, kv_group_size=kv_group_size,
-        qk_norm=qk_norm,
+        qk_norm=qk_norm, dynamic_len=dynamic_len,
     )
     combine_ops = FlashDecodingCombineBSHDOp.schedule(o_partial=o_partial, lse_partial=lse_partial, o=o, lse=lse)
     ops = split_ops + combine_ops

@@ -79,14 +79,22 @@ class _RmsProjectionSm100Base(_DecodeMatvecSm100Base):
     write_cache = 0
 
     @classmethod
-    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, cache_pos=0, **tensors):
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, cache_pos=0, dynamic_pos=False,
+                 **tensors):
+        """``dynamic_pos`` (not in the reference, which re-schedules per position): the op follows the
+        program's device-resident cache position p (``MegakernelConfig.position``) — ``cos`` / ``sin``
+        are then the FULL tables (row p is read), ``dst_cache`` the full cache (row p is written) and
+        ``cache_pos`` must be 0."""
         tile_sizes = cls._default_tiles(tile_sizes, "O")
         if tile_sizes["O"] != 16:
             raise ValueError(f"{cls.__name__}: tile size O must be 16")
+        if dynamic_pos and cache_pos:
+            raise ValueError(f"{cls.__name__}: with dynamic_pos the position comes from the device, cache_pos must be 0")
         op = cls._schedule_single(tile_sizes=tile_sizes, **tensors)
         op.static_dims["page_size"] = page_size
         op.static_dims["eps"] = eps
         op.static_dims["cache_pos"] = cache_pos
+        op.static_dims["dynamic_pos"] = int(bool(dynamic_pos))
         op.static_dims["head_dim"] = tensors["cos"].shape[1] * 2
         op.static_dims["reduction_tile_K"] = min(SM100_DECODE_REDUCTION_DIM_PER_WARP, tensors["x"].shape[-1])
         return [op]
@@ -113,10 +121,14 @@ class _RmsProjectionSm100Base(_DecodeMatvecSm100Base):
                 raise ValueError(f"{cls.__name__}: cache_pos {pos} + S exceeds the cache length {out.shape[1]}")
             kw.update(out=out, out_strides=(out.stride(0), out.stride(1), out.stride(2)), pos=pos)
         nop = lower_matvec(cls.__name__, ctx, kind="rms_proj", **kw)
+        dyn = bool(sop.static_dims.get("dynamic_pos", 0))
+        if dyn:
+            nop.i[N.MV_DYNPOS] = 1
         if cls.write_cache:
-            # only rows [cache_pos, cache_pos + S) of the cache are written
+            # only rows [cache_pos, cache_pos + S) of the cache are written (any row, with a dynamic position)
             pos = int(sop.static_dims.get("cache_pos", 0))
-            nop.writes[-1].axis, nop.writes[-1].lo, nop.writes[-1].hi = 1, pos, pos + int(t["x"].shape[1])
+            hi = int(t["dst_cache"].shape[1]) if dyn else pos + int(t["x"].shape[1])
+            nop.writes[-1].axis, nop.writes[-1].lo, nop.writes[-1].hi = 1, pos, hi
             nop.kind = "cache_append"
         return [nop]
 
@@ -328,6 +340,7 @@ def schedule_decode_layer_sm100(
     kv_group_size=SM100_DECODE_KV_GROUP_SIZE_DEFAULT,
     matvec_block=SM100_DECODE_MATVEC_BLOCK,
     tp_peers=None,
+    dynamic_position=False,
 ):
     """One decoder layer: RMS+Q/RoPE, RMS+K/RoPE/cache, RMS+V/cache, split-KV
     attention + combine, O-proj + residual, RMS+gate/up+SiLU and the down
@@ -346,15 +359,25 @@ def schedule_decode_layer_sm100(
     from ..attention.flash_decoding import flash_decoding_schedule
 
     pfx = f"layer.{layer_idx}"
-    cos = weights["cos"][cache_pos: cache_pos + seq_len]
-    sin = weights["sin"][cache_pos: cache_pos + seq_len]
+    if dynamic_position:
+        # ``dynamic_position`` (not in the reference): the step follows the program's device-resident
+        # cache position (MegakernelConfig.position) instead of ``cache_pos``: the ops get the full
+        # RoPE tables and the full caches, and read / write the row of the current position.
+        if seq_len != 1:
+            raise ValueError("a device-resident position decodes one token per sequence and step")
+        cache_pos = 0
+        cos, sin = weights["cos"][:seq_len], weights["sin"][:seq_len]   # row 0: the kernel adds the position
+        k_window, v_window = k_cache, v_cache
+    else:
+        cos = weights["cos"][cache_pos: cache_pos + seq_len]
+        sin = weights["sin"][cache_pos: cache_pos + seq_len]
+        k_window = k_cache[:, : cache_pos + seq_len]
+        v_window = v_cache[:, : cache_pos + seq_len]
     q_4d = q_buf.view(batch, seq_len, num_q_heads, head_dim)
-    k_window = k_cache[:, : cache_pos + seq_len]
-    v_window = v_cache[:, : cache_pos + seq_len]
     o_4d = attn_out_buf.view(batch, seq_len, num_q_heads, head_dim)
     tiles = {"S": seq_len, "O": matvec_block}
     common = dict(x=x_in, residual_in=residual_in, norm_weight=weights[f"{pfx}.attn_norm"], cos=cos, sin=sin,
-                  tile_sizes=tiles, page_size=page_size, eps=eps)
+                  tile_sizes=tiles, page_size=page_size, eps=eps, dynamic_pos=dynamic_position)
 
     ops = []
     ops += RmsQMatvecRopeSm100Op.schedule(weight=weights[f"{pfx}.W_q"], residual_out=residual_out, q=q_buf,
@@ -365,7 +388,7 @@ def schedule_decode_layer_sm100(
                                            cache_pos=cache_pos, **common)
     fa_ops, fa_config = flash_decoding_schedule(
         q=q_4d, k=k_window, v=v_window, o=o_4d, kv_group_size=kv_group_size, page_size=page_size,
-        num_splits=fa_num_splits,
+        num_splits=fa_num_splits, dynamic_len=dynamic_position,
     )
     ops += fa_ops
     tp_keep = []

@@ -106,12 +106,24 @@ class ReduceTop1Sm100Op(Op):
     dynamic_dims = ("B", "S")
 
     @classmethod
-    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, **tensors):
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, feedback=None, **tensors):
+        """``feedback`` (not in the reference): ``dict(embedding=(V, hidden) table, x_in=(B, S, hidden)
+        input rows of the next step, position=one-element int32 CUDA tensor or None)`` makes the op
+        copy each greedy token's embedding row into ``x_in`` and advance the position by S, so the
+        next launch decodes the next token with no host work in between."""
         for name, dt in (("top_values", torch.float32), ("top_indices", torch.int32)):
             if tensors[name].dtype != dt or not tensors[name].is_contiguous():
                 raise ValueError(f"{name} must be a contiguous {dt} (B, S) tensor")
         op = cls._schedule_single(tile_sizes={}, **tensors)
         op.static_dims["page_size"] = page_size
+        if feedback is not None:
+            emb, x_in = feedback["embedding"], feedback["x_in"]
+            if emb.ndim != 2 or emb.stride(1) != 1 or x_in.ndim != 3 or x_in.stride(2) != 1 or emb.dtype != x_in.dtype \
+                    or emb.shape[1] != x_in.shape[2] or x_in.shape[0] * x_in.shape[1] != tensors["top_indices"].numel():
+                raise ValueError("feedback: embedding must be (V, hidden) and x_in (B, S, hidden) of one 16-bit dtype")
+            if not x_in.is_contiguous():
+                raise ValueError("feedback: x_in must be contiguous")
+            op.params["feedback"] = dict(feedback)
         return [op]
 
     @classmethod
@@ -125,12 +137,22 @@ class ReduceTop1Sm100Op(Op):
         op.writes = [Region(meta_of(keys, "top_keys")), Region(meta_of(vals, "top_values")),
                      Region(meta_of(idxs, "top_indices"))]
         op.keep = [keys, vals, idxs]
+        fb = sop.params.get("feedback")
+        if fb is not None:
+            emb, x_in, pos = fb["embedding"], fb["x_in"], fb.get("position")
+            op.i.update({N.EW_FLAGS: N.EWF_FEEDBACK, N.EW_D: int(emb.shape[1]), N.EW_S: int(x_in.shape[1])})
+            op.p.update({N.EW_P_RES_IN: emb.data_ptr(), N.EW_P_RES_OUT: x_in.data_ptr(),
+                         N.EW_P_GATE: pos.data_ptr() if pos is not None else 0})
+            op.s = {N.EW_S_RI: emb.stride(0), N.EW_S_RO: int(emb.shape[1])}
+            op.reads.append(Region(meta_of(emb, "embedding")))
+            op.writes.append(Region(meta_of(x_in, "x_in")))
+            op.keep += [emb, x_in] + ([pos] if pos is not None else [])
         return [op]
 
 
 def schedule_final_top1_sm100(*, x, residual_in, final_norm, lm_head, top_values, top_indices, seq_len,
                               page_size=DEFAULT_PAGE_SIZE, eps=1e-5, lm_head_scales=None, group_size=32,
-                              global_scale=1.0, tp_peers=None):
+                              global_scale=1.0, tp_peers=None, feedback=None):
     """Final add + RMSNorm + LM head + greedy token, without materialising logits.
 
     With ``tp_peers`` the LM head is this rank's vocabulary shard (rows
@@ -156,7 +178,7 @@ def schedule_final_top1_sm100(*, x, residual_in, final_norm, lm_head, top_values
         final_keys = torch.zeros_like(keys)
         ops += AllReduceTop1KeysSm100Op.schedule(peers=tp_peers, top_keys=keys, top_keys_out=final_keys)
     ops += ReduceTop1Sm100Op.schedule(top_keys=final_keys, top_values=top_values, top_indices=top_indices,
-                                      page_size=page_size)
+                                      page_size=page_size, feedback=feedback)
     return ops
 
 

@@ -66,6 +66,8 @@ def schedule_decode_model_sm100(
     x_in=None,
     residual_in=None,
     tp_peers=None,
+    position=None,
+    embedding=None,
 ):
     """Schedule a full decode step: ``(ops, keep_alive)``.
 
@@ -83,6 +85,18 @@ def schedule_decode_model_sm100(
     shards (see ``schedule_decode_layer_sm100``); full logits are not
     supported under tensor parallelism, only the greedy-token head.
     """
+    dynamic = position is not None
+    if dynamic:
+        # Generation loop (not in the reference, which re-schedules for every position,
+        # src/machete/kernels/decode_matvec/sm100.py:116, 704-709): ``position`` is a one-element
+        # int32 CUDA tensor holding the cache position of the token being decoded; the program
+        # reads it at the start of every launch (pass it as ``MegakernelConfig(position=...)`` too),
+        # writes the greedy token's embedding row (``embedding``, default: the tied ``lm_head``)
+        # into ``x_in`` and advances the position, so every further launch decodes the next token.
+        if x_in is None or top_indices is None or logits is not None or seq_len != 1:
+            raise ValueError("position= needs x_in, the top-1 head and one token per step")
+        if tp_peers is not None and embedding is None:
+            raise ValueError("position= under tensor parallelism needs the full embedding table (embedding=)")
     if tp_peers is not None and logits is not None:
         raise ValueError("tensor parallelism supports the top-1 head only (logits would need an all-gather)")
     if len(x_buffers) < 2 or len(residual_buffers) < 2:
@@ -103,7 +117,7 @@ def schedule_decode_model_sm100(
             q_buf=q_buf, attn_out_buf=attn_out_buf, mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps,
             fa_num_splits=fa_num_splits, hidden_size=hidden_size, intermediate_size=intermediate_size,
             num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-            kv_group_size=num_q_heads // num_kv_heads, tp_peers=tp_peers,
+            kv_group_size=num_q_heads // num_kv_heads, tp_peers=tp_peers, dynamic_position=dynamic,
         )
         ops += layer.ops
         keep += layer.keep_alive
@@ -121,7 +135,9 @@ def schedule_decode_model_sm100(
             ops += schedule_final_top1_sm100(x=x_buffers[cur], residual_in=residual_buffers[cur],
                                              final_norm=final_norm, lm_head=lm_head, top_values=top_values,
                                              top_indices=top_indices, seq_len=seq_len, page_size=page_size,
-                                             eps=eps, tp_peers=tp_peers)
+                                             eps=eps, tp_peers=tp_peers,
+                                             feedback=dict(embedding=lm_head if embedding is None else embedding,
+                                                           x_in=x_in, position=position) if dynamic else None)
         else:
             raise ValueError("logits or both top_values/top_indices must be provided when lm_head is scheduled")
     return ops, keep

@@ -69,6 +69,10 @@ class MegakernelConfig:
     native_kc_fp4: Optional[int] = None  # K columns per NVFP4 weight page (default 2048)
     timeout_ms: int = 1000               # bound of every device-side wait
     fuse: bool = True                    # allow peephole fusion of op chains
+    # Device-resident cache position: a one-element int32 CUDA tensor that ops scheduled with a
+    # dynamic position read at the start of every launch and that the token-feedback form of the
+    # top-1 head advances at the end (consecutive launches decode consecutive tokens).
+    position: Optional[Any] = None
 
 
 _IGNORED_CONFIG = {
@@ -238,6 +242,11 @@ class Megakernel:
         prog.events = arrays["events"].ctypes.data
         prog.cta_event_begin = arrays["eb"].ctypes.data
         prog.waits = arrays["waits"].ctypes.data
+        pos = self.config.position
+        if pos is not None:
+            if pos.dtype != torch.int32 or pos.numel() != 1 or not pos.is_cuda:
+                raise ValueError("MegakernelConfig.position must be a one-element int32 CUDA tensor")
+            prog.position = pos.data_ptr()
         nbytes = int(lib.mk_workspace_bytes(C.byref(prog)))
         self._workspace = torch.empty(nbytes + 256, dtype=torch.uint8, device=torch.device("cuda", dev))
         base = self._workspace.data_ptr()

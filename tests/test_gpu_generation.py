@@ -1,0 +1,123 @@
+"""Decoding consecutive tokens from ONE handle with a device-resident cache position.
+
+The program is scheduled once.  Every launch reads the position from a device
+scalar, appends this token's K/V rows at it, attends to the window that ends
+there, picks the greedy token, copies its embedding row into the input buffer
+and advances the position — no host work between launches.  The oracle runs
+the same loop on the CPU: the tokens must agree step by step.
+"""
+
+import pytest
+import torch
+
+import oracle
+from machete_b200.kernels.llama1b import schedule_decode_model_sm100
+from machete_b200.megakernel import Megakernel, MegakernelConfig, OverlapTileScheduler
+from tests.util import llama_weights, parity_bar, to_cpu
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.mark.parametrize("B,start", [(1, 60), (2, 125)])
+def test_eight_consecutive_tokens_match_the_oracle(B, start):
+    """`start` is chosen so that the window crosses a 64-token page (and a split boundary) on the way."""
+    L, T, hidden, nq, nkv, hd, inter, vocab = 2, 256, 512, 8, 2, 64, 1024, 1024
+    steps = 8
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=31, device="cuda")
+    g = torch.Generator().manual_seed(32)
+    kcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    vcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF)
+    emb = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF)       # tied embedding / LM head
+    x0 = emb[torch.arange(B) + 3].view(B, 1, hidden).clone()
+    r0 = torch.zeros(B, 1, hidden, dtype=BF)
+    dev = "cuda"
+    x_in, kd, vd = x0.to(dev), [t.to(dev) for t in kcs], [t.to(dev) for t in vcs]
+    position = torch.tensor([start], dtype=torch.int32, device=dev)
+    tv = torch.zeros(B, 1, device=dev)
+    ti = torch.zeros(B, 1, dtype=torch.int32, device=dev)
+    dims = dict(hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+    ops, _keep = schedule_decode_model_sm100(
+        batch=B, cache_pos=0, weights=w, k_cache=kd, v_cache=vd,
+        x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+        mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), final_norm=fn.to(dev), lm_head=emb.to(dev),
+        top_values=tv, top_indices=ti, num_layers=L, x_in=x_in, residual_in=r0.to(dev), position=position, **dims)
+    mk = Megakernel(ops, config=MegakernelConfig(position=position), scheduler=OverlapTileScheduler())
+    wc = to_cpu(w)
+    x = x0.clone()
+    for step in range(steps):
+        pos = start + step
+        mk.run()
+        assert int(position.item()) == pos + 1                     # the kernel advanced the position itself
+        logits, _v, want_i = oracle.decode_model(weights=wc, x=x, residual=r0, k_caches=kcs, v_caches=vcs, cache_pos=pos,
+                                                 final_norm=fn, lm_head=emb, num_layers=L, num_q_heads=nq,
+                                                 num_kv_heads=nkv, head_dim=hd)
+        got = ti.cpu()
+        bar = parity_bar(logits, roundings=2)
+        top2 = logits.topk(2, dim=-1).values
+        for b in range(B):
+            # a near-tie would let the two loops drift apart for good: the seeds of this test have none
+            assert float(top2[b, 0, 0] - top2[b, 0, 1]) > bar, "test input has a near-tie: pick another seed"
+            assert int(got[b, 0]) == int(want_i[b, 0]), f"step {step}, row {b}: token differs"
+            assert abs(float(tv[b, 0]) - float(logits[b, 0, int(got[b, 0])])) <= bar
+        # the K/V rows of this position were appended (the oracle did the same to its caches)
+        for l in range(L):
+            assert float((kd[l][:, pos].cpu().float() - kcs[l][:, pos].float()).abs().max()) <= 2 * bar
+        # the fed-back input row is the embedding of the greedy token, bit for bit
+        x = emb[got[:, 0].long()].view(B, 1, hidden).clone()
+        assert torch.equal(x_in.cpu(), x)
+        assert mk.status()[0] == 0 and (mk.read_counters() == 0).all()
+
+
+def test_graph_replay_decodes_consecutive_tokens():
+    """One captured launch, replayed: each replay is the next token (what an e2e serving loop does)."""
+    B, L, T, hidden, nq, nkv, hd, inter, vocab, start = 1, 1, 192, 512, 8, 2, 64, 1024, 512, 100
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=33, device="cuda")
+    g = torch.Generator().manual_seed(34)
+    dev = "cuda"
+    kd = [torch.randn(B, T, nkv, hd, generator=g).to(BF).to(dev)]
+    vd = [torch.randn(B, T, nkv, hd, generator=g).to(BF).to(dev)]
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF).to(dev)
+    emb = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF).to(dev)
+    x_in = emb[5].view(1, 1, hidden).clone()
+    position = torch.tensor([start], dtype=torch.int32, device=dev)
+    tv, ti = torch.zeros(B, 1, device=dev), torch.zeros(B, 1, dtype=torch.int32, device=dev)
+
+    def build(pos_tensor, x, k, v):
+        ops, _ = schedule_decode_model_sm100(
+            batch=B, cache_pos=0, weights=w, k_cache=k, v_cache=v,
+            x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+            residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+            q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+            mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), final_norm=fn, lm_head=emb, top_values=tv,
+            top_indices=ti, num_layers=L, x_in=x, residual_in=torch.zeros(B, 1, hidden, dtype=BF, device=dev),
+            position=pos_tensor, hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+        return Megakernel(ops, config=MegakernelConfig(position=pos_tensor), scheduler=OverlapTileScheduler())
+
+    # reference run: plain launches on copies of the state
+    k2, v2, x2, p2 = [kd[0].clone()], [vd[0].clone()], x_in.clone(), position.clone()
+    plain = build(p2, x2, k2, v2)
+    want = []
+    for _ in range(6):
+        plain.run()
+        want.append(int(ti.item()))
+    mk = build(position, x_in, kd, vd)
+    mk.compile()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    host_tok = torch.zeros(B, 1, dtype=torch.int32).pin_memory()
+    with torch.cuda.graph(graph, stream=side):
+        mk.run(sync=False, validate=False)
+        host_tok.copy_(ti, non_blocking=True)
+    # the capture itself does not run the kernel: the position is still `start`
+    got = []
+    for _ in range(6):
+        graph.replay()
+        torch.cuda.synchronize()
+        got.append(int(host_tok.item()))
+    assert got == want
+    assert int(position.item()) == start + 6
