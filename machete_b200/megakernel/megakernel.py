@@ -23,6 +23,7 @@ import torch
 
 from .. import _native as N
 from .lowering import LowerCtx, NativeOp
+from .paged_memory import NativeSmemPlan
 from .ops import ScheduledOp
 from .scheduling import BackwardScheduler, BuiltProgram, InstructionStreamBuilder, TileScheduler
 
@@ -152,8 +153,8 @@ class Megakernel:
         self.program: BuiltProgram = builder.build(self.scheduler)
 
         self._act_bytes = -(-self.program.act_bytes // 1024) * 1024
-        avail = smem - CTRL_BYTES - self._act_bytes
-        n_pages = min(MAX_PAGES, avail // self._page_bytes)
+        plan = NativeSmemPlan(CTRL_BYTES, self._act_bytes, self._page_bytes, smem_optin=smem, max_pages=MAX_PAGES)
+        n_pages = plan.num_pages
         if cfg.num_pages is not None:
             n_pages = min(n_pages, int(cfg.num_pages))
         if n_pages < 2:

@@ -31,6 +31,7 @@ import numpy as np
 
 from .. import _native as N
 from .lowering import NativeOp, Region
+from .ops import tensor_meta_overlaps
 
 INSTRUCTION_WORDS = 8
 """int32 words per instruction row (``mk_instr_t``)."""
@@ -171,6 +172,106 @@ def infer_dependencies(ops: Sequence[NativeOp]) -> List[OpDeps]:
         for w in op.writes:
             writes_by_storage.setdefault(w.meta.storage_ptr, []).append((j, w))
     return result, closure
+
+
+# ---- op-pair resolution on scheduled ops ----------------------------------------------------
+def resolve_dep_pairs(ops) -> List[Tuple[int, int, str, str]]:
+    """Ordered ``(producer, consumer, producer buffer, consumer buffer)`` pairs of a scheduled-op list.
+
+    The op-level contract of the reference builder (src/machete/megakernel/scheduling.py:915-1120),
+    stated on ``ScheduledOp`` records before any lowering or fusion:
+
+    * read-after-write: each declared input depends on the nearest earlier op that writes a buffer
+      of the same name at the same address, else on the latest earlier op with an output that
+      overlaps it in memory; every earlier accumulating (reduce-store) writer that overlaps the
+      input is a producer as well;
+    * ordering of storage reuse: an op that writes a tensor follows every earlier op that reads or
+      writes overlapping memory (two accumulating writers of the same memory commute);
+    * the second kind is dropped where another path already orders the two ops; read-after-write
+      pairs are always kept, because consumers take their tile mapping from them.
+
+    ``infer_dependencies`` below works on lowered ops and reduces every kind of edge; the two agree
+    on the ordering they impose (their transitive closures are equal on unfused programs).
+    """
+    def outs(op):
+        return [(n, op.tensor_metas.get(n)) for n in op.op_cls.OUTPUTS]
+
+    def ins(op):
+        return [(n, op.tensor_metas.get(n)) for n in op.op_cls.INPUTS]
+
+    def accumulates(op, name):
+        return name in getattr(op.op_cls, "_TMA_REDUCE_STORES", ())
+
+    def touching(metas, m):
+        return next((n for n, x in metas if x is not None and tensor_meta_overlaps(x, m)), None)
+
+    pairs: Dict[Tuple[int, int, str, str], bool] = {}       # insertion-ordered; value: read-after-write?
+    for j, op in enumerate(ops):
+        for name, meta in ins(op):
+            ptr = op.tensor_ptrs.get(name)
+            prod = None
+            for i in range(j - 1, -1, -1):                  # same name, same address: nearest wins
+                if name in ops[i].op_cls.OUTPUTS:
+                    p = ops[i].tensor_ptrs.get(name)
+                    if p is None or ptr is None or p == ptr:
+                        prod = i
+                        break
+            if prod is None and meta is not None:           # another name for the same memory: latest wins
+                prod = next((i for i in range(j - 1, -1, -1) if touching(outs(ops[i]), meta)), None)
+            if prod is not None:
+                src = name
+                same_name = name in ops[prod].op_cls.OUTPUTS and (
+                    ops[prod].tensor_ptrs.get(name) is None or ptr is None or ops[prod].tensor_ptrs.get(name) == ptr)
+                if not same_name and meta is not None:
+                    src = touching(outs(ops[prod]), meta) or name
+                pairs.setdefault((prod, j, src, name), True)
+            if meta is not None:
+                for i in range(j - 1, -1, -1):
+                    for n, m in outs(ops[i]):
+                        if m is not None and accumulates(ops[i], n) and tensor_meta_overlaps(m, meta):
+                            pairs[(i, j, n, name)] = True
+    raw = {(p, c) for (p, c, _, _), is_raw in pairs.items() if is_raw}
+    for j, op in enumerate(ops):
+        for name, meta in outs(op):
+            if meta is None:
+                continue
+            for i in range(j - 1, -1, -1):
+                hit = touching(ins(ops[i]), meta) or touching(outs(ops[i]), meta)
+                if hit is None:
+                    continue
+                both_accumulate = any(
+                    accumulates(op, a) and accumulates(ops[i], b) and ma is not None and mb is not None
+                    and tensor_meta_overlaps(ma, mb) for a, ma in outs(op) for b, mb in outs(ops[i]))
+                if not both_accumulate:
+                    pairs.setdefault((i, j, hit, name), False)
+    succ: Dict[int, set] = {}
+    for p, c, _, _ in pairs:
+        succ.setdefault(p, set()).add(c)
+
+    def other_path(src, dst):
+        todo, seen = [n for n in succ.get(src, ()) if n != dst], set()
+        while todo:
+            n = todo.pop()
+            if n == dst:
+                return True
+            if n not in seen:
+                seen.add(n)
+                todo.extend(succ.get(n, ()))
+        return False
+
+    return [k for k in pairs if (k[0], k[1]) in raw or not other_path(k[0], k[1])]
+
+
+def closure_of(pairs, n_ops: int) -> List[int]:
+    """Bitset per op of every op that must be complete before it (transitive closure of ``pairs``)."""
+    before = [0] * n_ops
+    by_consumer: Dict[int, List[int]] = {}
+    for p, c in pairs:
+        by_consumer.setdefault(c, []).append(p)
+    for j in range(n_ops):                                  # producers always precede consumers in program order
+        for i in by_consumer.get(j, ()):
+            before[j] |= before[i] | (1 << i)
+    return before
 
 
 # ---- program tables -------------------------------------------------------------------------
