@@ -97,14 +97,17 @@ enum {
   /* MK_EPI_TOP1: added to the row index packed into the key (the first
    * vocabulary row of this rank's shard under tensor parallelism) */
   MK_MV_IDX0,
-  /* 1 = the op follows the program's device-resident cache position p
-   * (mk_program_t.position): the output row offset becomes (s + POS + p) and
-   * the RoPE tables are read at row (s + p), so cos / sin point at row 0 of
-   * the full tables and POS is 0.  The reference bakes the position into the
-   * schedule and re-schedules per token (kernels/decode_matvec/sm100.py:116,
-   * 704-709). */
+  /* The op follows the program's device-resident cache position p
+   * (mk_program_t.position), a bit mask: MK_MV_DYN_TABLES = the RoPE tables
+   * are read at row (s + p), so cos / sin point at row 0 of the full tables;
+   * MK_MV_DYN_OUT = the output row offset becomes (s + POS + p) with POS 0
+   * (a cache append: the output is the whole cache).  A projection into a
+   * one-token buffer (q) sets the first bit only.  The reference bakes the
+   * position into the schedule and re-schedules per token
+   * (kernels/decode_matvec/sm100.py:116, 704-709). */
   MK_MV_DYNPOS
 };
+enum { MK_MV_DYN_TABLES = 1, MK_MV_DYN_OUT = 2 };
 /* GSCALE / GSCALE1: fp32 global scale of W0 / of W1 (MK_MV_PAIR; block-scaled NVFP4 only) */
 enum { MK_MV_F_EPS = 0, MK_MV_F_GSCALE = 1, MK_MV_F_GSCALE1 = 2 };
 enum {
@@ -303,6 +306,13 @@ typedef struct mk_program {
    * end, so consecutive launches (or replays of one CUDA graph) decode
    * consecutive tokens with no host work in between. */
   const int32_t* position;
+  /* With `position`: the first position the program's caches and tables do NOT
+   * hold (the smallest cache length of its position-following ops).  A launch
+   * that finds the position outside [0, position_limit) runs no op and ends
+   * with device status 7; mk_create refuses a program with `position` set and
+   * a limit < 1. */
+  int32_t position_limit;
+  int32_t reserved0;
 } mk_program_t;
 
 typedef struct mk_handle_s* mk_handle_t;

@@ -30,6 +30,7 @@ T_BF16, T_FP16, T_FP32 = range(3)
 
 (MV_O, MV_K, MV_M, MV_S, MV_MODE, MV_PRO, MV_EPI, MV_TR, MV_HD, MV_D2, MV_POS, MV_WFMT, MV_KC, MV_OUT_T,
  MV_X_T, MV_ROWS_PER_UNIT, MV_SPLIT, MV_IDX0, MV_DYNPOS) = range(19)
+MV_DYN_TABLES, MV_DYN_OUT = 1, 2
 MV_F_EPS, MV_F_GSCALE, MV_F_GSCALE1 = range(3)
 (MV_P_W0, MV_P_W1, MV_P_X, MV_P_RES_IN, MV_P_NORM_W, MV_P_RES_OUT, MV_P_OUT, MV_P_EPI_RES, MV_P_COS,
  MV_P_SIN, MV_P_SC0, MV_P_SC1) = range(12)
@@ -65,6 +66,7 @@ STATUS_NAMES = {
     4: "unknown opcode",
     5: "ring-slot turn wait timed out",
     6: "a peer rank's all-reduce flag never arrived",
+    7: "the device-resident cache position is outside the caches (nothing ran)",
 }
 
 
@@ -104,7 +106,7 @@ class Program(C.Structure):
         ("act_bytes", C.c_int32), ("timeout_ms", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
         ("ops", C.c_void_p), ("instrs", C.c_void_p), ("cta_instr_begin", C.c_void_p),
         ("events", C.c_void_p), ("cta_event_begin", C.c_void_p), ("waits", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("position", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("position", C.c_void_p), ("position_limit", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 

@@ -428,10 +428,16 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
 
   const int ibeg = pv.cta_instr_begin[blockIdx.x], iend = pv.cta_instr_begin[blockIdx.x + 1];
   const int ebeg = pv.cta_event_begin[blockIdx.x], eend = pv.cta_event_begin[blockIdx.x + 1];
-  if (c.warp == 0)
+  // A position outside the caches the program was scheduled for would write past them: every CTA
+  // reads the same scalar, so all of them skip the program together and the launch ends at once.
+  const bool bad_pos = pv.dyn_pos != nullptr && (uint32_t)c.ctrl->pos >= (uint32_t)pv.pos_limit;
+  if (bad_pos) {
+    if (threadIdx.x == 0) report(c, MK_ST_BAD_POSITION, c.ctrl->pos, pv.pos_limit);
+  } else if (c.warp == 0) {
     loader_loop(c, ibeg, iend);
-  else
+  } else {
     consumer_loop<NTC, WFC, FEAT>(c, ibeg, iend, ebeg, eend);
+  }
   trace_flush(c);
   __syncthreads();
 

@@ -418,6 +418,8 @@ static int validate_program(const mk_program_t* p, int smem_optin, int num_sms, 
         return fail(-2, "op %d follows a device-resident cache position, but the program has none (mk_program_t.position)", i);
     }
   if (p->position != nullptr && ((uint64_t)p->position & 3)) return fail(-1, "position scalar must be 4-byte aligned");
+  if (p->position != nullptr && p->position_limit < 1)
+    return fail(-1, "position_limit must be the cache length of the position-following ops (got %d)", p->position_limit);
   for (int i = 0; i < p->n_waits; ++i)
     if (p->waits[i].counter < 0 || p->waits[i].counter >= p->n_counters)
       return fail(-3, "wait %d: counter %d out of range", i, p->waits[i].counter);
@@ -693,6 +695,7 @@ static int create_program(const mk_program_t* prog, mk_handle_t* out, bool strea
   h->pv.trace = nullptr;
   h->pv.trace_cap = 0;
   h->pv.dyn_pos = prog->position;
+  h->pv.pos_limit = prog->position_limit;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
   h->smem_optin = smem_optin;

@@ -158,7 +158,7 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   if (stage && op->i[MK_MV_TR] == MK_TR_ROPE && tid < 2 * S) {
     // the epilogue's cos / sin rows: pull them into L1 while the activations are on their way
     const uint8_t* tab = reinterpret_cast<const uint8_t*>(op->p[(tid & 1) ? MK_MV_P_SIN : MK_MV_P_COS]);
-    const int row = (tid >> 1) + (op->i[MK_MV_DYNPOS] ? c.ctrl->pos : 0);
+    const int row = (tid >> 1) + ((op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) ? c.ctrl->pos : 0);
     asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + (size_t)row * (size_t)op->s[MK_MV_S_COS] * 2u));
   }
   auto row_off = [&](int m, int sb, int ss) -> int64_t {
@@ -336,7 +336,9 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
   const int nB = mode == MK_MV_ROPE ? 8 : clamp8(O - r.rowB0);
   const bool va = g < nA, vb = g < nB;
   const bool two = tr != MK_TR_SILU_MUL;
-  const int dpos = op->i[MK_MV_DYNPOS] ? c.ctrl->pos : 0;   // device-resident cache position
+  // device-resident cache position: which of the table row and the output row follow it
+  const int tpos = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) ? c.ctrl->pos : 0;
+  const int dpos = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_OUT) ? c.ctrl->pos : 0;
 #pragma unroll 1
   for (int q = 0; q < 2 * NT; ++q) {
     const int m0 = (q >> 1) * 8 + (q & 1);   // the smallest activation row any lane has in this pass
@@ -371,8 +373,8 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
     if (tr == MK_TR_ROPE) {
       if (vm) {
         const int d = r.chunk * 8 + g;
-        const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + (ss + dpos) * op->s[MK_MV_S_COS] + d;
-        const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + (ss + dpos) * op->s[MK_MV_S_COS] + d;
+        const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_COS]) + (ss + tpos) * op->s[MK_MV_S_COS] + d;
+        const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_MV_P_SIN]) + (ss + tpos) * op->s[MK_MV_S_COS] + d;
         const bool bf = xt == MK_T_BF16;
         const float cv = bf ? bf16lo(*cs) : f16lo(*cs);
         const float sv = bf ? bf16lo(*sn) : f16lo(*sn);

@@ -46,7 +46,8 @@ enum {
   MK_ST_TIMEOUT_PAGE_EMPTY = 3,
   MK_ST_BAD_OP = 4,
   MK_ST_TIMEOUT_PAGE_TURN = 5,  // earlier fills of a ring slot were never handed back
-  MK_ST_TIMEOUT_PEER = 6        // a peer rank's all-reduce flag never arrived
+  MK_ST_TIMEOUT_PEER = 6,       // a peer rank's all-reduce flag never arrived
+  MK_ST_BAD_POSITION = 7        // the device-resident cache position is outside [0, position_limit): nothing ran
 };
 
 // Device memory block owned by a handle (lives in the caller's workspace).
@@ -78,6 +79,7 @@ struct ProgramView {
   int32_t trace_cap;
   int32_t mv_sets;  // split-K slot sets in use: 4 (every matvec has M <= 8), 2 (M <= 16) or 1
   const int32_t* dyn_pos;  // device-resident cache position, or null
+  int32_t pos_limit;       // positions >= this end the launch with MK_ST_BAD_POSITION before any op runs
 };
 
 // One trace event: a globaltimer stamp, an event code and an argument.

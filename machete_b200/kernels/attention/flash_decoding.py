@@ -175,6 +175,7 @@ class FlashDecodingSplitBSHDOp(Op):
         op.keep = [q, k, v, t["o_partial"], t["lse_partial"]]
         if sop.static_dims.get("dynamic_len"):
             op.i[N.AT_DYNPOS] = 1
+            op.pos_limit = int(k.shape[1])
         qkn = sop.params.get("qk_norm")
         if qkn is not None:
             op.i[N.AT_QKNORM], op.i[N.AT_NEW_TOK] = 1, int(qkn["new_token"])

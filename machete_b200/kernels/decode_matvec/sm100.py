@@ -123,7 +123,10 @@ class _RmsProjectionSm100Base(_DecodeMatvecSm100Base):
         nop = lower_matvec(cls.__name__, ctx, kind="rms_proj", **kw)
         dyn = bool(sop.static_dims.get("dynamic_pos", 0))
         if dyn:
-            nop.i[N.MV_DYNPOS] = 1
+            # q lands in a one-token buffer: only its RoPE row follows the position
+            nop.i[N.MV_DYNPOS] = N.MV_DYN_TABLES | (N.MV_DYN_OUT if cls.write_cache else 0)
+            if cls.write_cache:
+                nop.pos_limit = int(t["dst_cache"].shape[1])
         if cls.write_cache:
             # only rows [cache_pos, cache_pos + S) of the cache are written (any row, with a dynamic position)
             pos = int(sop.static_dims.get("cache_pos", 0))
@@ -366,6 +369,8 @@ def schedule_decode_layer_sm100(
         if seq_len != 1:
             raise ValueError("a device-resident position decodes one token per sequence and step")
         cache_pos = 0
+        if weights["cos"].shape[0] < k_cache.shape[1]:
+            raise ValueError(f"RoPE tables hold {weights['cos'].shape[0]} positions, the cache {k_cache.shape[1]}")
         cos, sin = weights["cos"][:seq_len], weights["sin"][:seq_len]   # row 0: the kernel adds the position
         k_window, v_window = k_cache, v_cache
     else:

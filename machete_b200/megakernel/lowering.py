@@ -89,6 +89,8 @@ class NativeOp:
     page_need: int = 0     # bytes one page of this op needs (for ring sizing)
     keep: list = field(default_factory=list)  # tensors kept alive
     kind: str = ""         # free-form tag used by peephole rules and tests
+    # an op that follows the device-resident cache position: first position its tensors do not hold
+    pos_limit: Optional[int] = None
 
     def record(self, act_key: int) -> np.void:
         rec = np.zeros((), dtype=N.OP_DTYPE)

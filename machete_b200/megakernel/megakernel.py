@@ -74,6 +74,9 @@ class MegakernelConfig:
     # dynamic position read at the start of every launch and that the token-feedback form of the
     # top-1 head advances at the end (consecutive launches decode consecutive tokens).
     position: Optional[Any] = None
+    # first position the caches do not hold (None: the smallest cache length of the position-following ops);
+    # a launch that finds the position outside [0, position_limit) runs nothing and reports status 7
+    position_limit: Optional[int] = None
 
 
 _IGNORED_CONFIG = {
@@ -248,6 +251,12 @@ class Megakernel:
             if pos.dtype != torch.int32 or pos.numel() != 1 or not pos.is_cuda:
                 raise ValueError("MegakernelConfig.position must be a one-element int32 CUDA tensor")
             prog.position = pos.data_ptr()
+            limits = [op.pos_limit for op in self.native_ops if op.pos_limit is not None]
+            if self.config.position_limit is not None:
+                limits.append(int(self.config.position_limit))
+            if not limits:
+                raise ValueError("MegakernelConfig.position is set but no op follows it (schedule with a dynamic position)")
+            prog.position_limit = min(limits)
         nbytes = int(lib.mk_workspace_bytes(C.byref(prog)))
         self._workspace = torch.empty(nbytes + 256, dtype=torch.uint8, device=torch.device("cuda", dev))
         base = self._workspace.data_ptr()

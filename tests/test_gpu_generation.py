@@ -56,7 +56,7 @@ def test_eight_consecutive_tokens_match_the_oracle(B, start):
                                                  final_norm=fn, lm_head=emb, num_layers=L, num_q_heads=nq,
                                                  num_kv_heads=nkv, head_dim=hd)
         got = ti.cpu()
-        bar = parity_bar(logits, roundings=2)
+        bar = parity_bar(logits, roundings=2 * L)      # the depth-aware bar of the whole-model tests
         top2 = logits.topk(2, dim=-1).values
         for b in range(B):
             # a near-tie would let the two loops drift apart for good: the seeds of this test have none
@@ -121,3 +121,42 @@ def test_graph_replay_decodes_consecutive_tokens():
         got.append(int(host_tok.item()))
     assert got == want
     assert int(position.item()) == start + 6
+
+
+def test_position_past_the_cache_runs_nothing_and_reports_it():
+    """A position outside the cache would append past its end: the launch does no work, the status
+    names the position, and the handle decodes again once the position is back inside."""
+    B, L, T, hidden, nq, nkv, hd, inter, vocab = 1, 1, 128, 512, 8, 2, 64, 1024, 512
+    dev = "cuda"
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=35, device=dev)
+    g = torch.Generator().manual_seed(36)
+    kd = [torch.randn(B, T, nkv, hd, generator=g).to(BF).to(dev)]
+    vd = [torch.randn(B, T, nkv, hd, generator=g).to(BF).to(dev)]
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF).to(dev)
+    emb = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF).to(dev)
+    x_in = emb[5].view(1, 1, hidden).clone()
+    position = torch.tensor([T], dtype=torch.int32, device=dev)              # one past the last row
+    tv, ti = torch.zeros(B, 1, device=dev), torch.full((B, 1), -1, dtype=torch.int32, device=dev)
+    q_buf = torch.zeros(B, 1, nq * hd, dtype=BF, device=dev)
+    ops, _ = schedule_decode_model_sm100(
+        batch=B, cache_pos=0, weights=w, k_cache=kd, v_cache=vd,
+        x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        q_buf=q_buf, attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+        mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), final_norm=fn, lm_head=emb, top_values=tv,
+        top_indices=ti, num_layers=L, x_in=x_in, residual_in=torch.zeros(B, 1, hidden, dtype=BF, device=dev),
+        position=position, hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+    mk = Megakernel(ops, config=MegakernelConfig(position=position), scheduler=OverlapTileScheduler())
+    k_before, x_before = kd[0].clone(), x_in.clone()
+    with pytest.raises(RuntimeError, match="position is outside"):
+        mk.run()
+    assert torch.equal(kd[0], k_before) and torch.equal(x_in, x_before) and int(ti.item()) == -1
+    assert int(position.item()) == T and float(q_buf.abs().max()) == 0.0
+    for bad in (-1, T + 5):
+        position.fill_(bad)
+        with pytest.raises(RuntimeError, match="position is outside"):
+            mk.run()
+    position.fill_(T - 1)                                                   # the last row: a normal step
+    mk.run()
+    assert mk.status()[0] == 0 and int(position.item()) == T and 0 <= int(ti.item()) < vocab
+    assert not torch.equal(kd[0][:, T - 1], k_before[:, T - 1]) and torch.equal(kd[0][:, :T - 1], k_before[:, :T - 1])

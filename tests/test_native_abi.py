@@ -31,7 +31,7 @@ def test_struct_layouts_match_header():
     assert N.OP_DTYPE.fields["i"][1] == 16 and N.OP_DTYPE.fields["f"][1] == 112
     assert N.OP_DTYPE.fields["p"][1] == 128 and N.OP_DTYPE.fields["s"][1] == 256
     assert N.INSTR_DTYPE.itemsize == 64 and N.EVENT_DTYPE.itemsize == 64 and N.WAIT_DTYPE.itemsize == 8
-    assert ctypes.sizeof(N.Program) == 12 * 4 + 9 * 8
+    assert ctypes.sizeof(N.Program) == 12 * 4 + 9 * 8 + 2 * 4
 
 
 def test_enum_values_match_header():
