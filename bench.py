@@ -16,7 +16,10 @@ One JSON line is printed by rank 0:
               the clock sampler always has rows inside the timed region;
 * ``e2e``     the same metric through the public API with host buffers: per
               step the token embedding is copied from pinned host memory, the
-              step runs, and the greedy token is read back;
+              step runs, and the greedy token is read back.  For the bf16
+              single-GPU-per-sequence workload the steps decode CONSECUTIVE
+              positions from one handle (the cache position lives on the device
+              and the kernel advances it), ending at the workload's KV length;
 * ``roofline`` algorithmic bytes per step (weights + LM head + KV, read once)
               divided by the measured kernel time, against the measured HBM
               copy bandwidth of this pool's B200s;
@@ -316,7 +319,7 @@ class Workload:
     pass
 
 
-def build_workload(args, dev, rank, world, use_dist):
+def build_workload(args, dev, rank, world, use_dist, gen=False):
     """Weights, caches and the scheduled program of one decode workload on this rank."""
     from machete_b200.kernels.llama1b import schedule_decode_model_sm100
     from machete_b200.megakernel import BackwardScheduler, Megakernel, MegakernelConfig, OverlapTileScheduler
@@ -389,6 +392,20 @@ def build_workload(args, dev, rank, world, use_dist):
     sched = OverlapTileScheduler() if args.scheduler == "overlap" else BackwardScheduler()
     mk = Megakernel(ops, config=MegakernelConfig(native_kc=args.kc or None), device=dev, scheduler=sched)
     mk.compile()
+    w.mk_gen = w.position = None
+    if gen and not tp and not nvfp4:
+        # the same step scheduled once for ANY position: the end-to-end leg decodes consecutive tokens with it
+        w.position = torch.zeros(1, dtype=torch.int32, device=dev)
+        ops_g, keep_g = schedule_decode_model_sm100(
+            batch=B, cache_pos=0, weights=weights, k_cache=kcs, v_cache=vcs, x_buffers=xb, residual_buffers=rb,
+            final_norm=weights["final_norm"], lm_head=weights["lm_head"], top_values=tv, top_indices=ti,
+            num_layers=args.layers, x_in=x_in, residual_in=r_in, hidden_size=cfg["hidden"],
+            intermediate_size=cfg["inter"], num_q_heads=cfg["nq"], num_kv_heads=cfg["nkv"], head_dim=cfg["hd"],
+            eps=cfg["eps"], position=w.position, **bufs)
+        w.mk_gen = Megakernel(ops_g, config=MegakernelConfig(native_kc=args.kc or None, position=w.position),
+                              device=dev, scheduler=OverlapTileScheduler() if args.scheduler == "overlap" else BackwardScheduler())
+        w.mk_gen.compile()
+        w.keep_gen = keep_g
     w.mk, w.cfg, w.tp, w.tp_note, w.vocab, w.nvfp4 = mk, cfg, tp, tp_note, vocab, nvfp4
     w.weights, w.kcs, w.vcs, w.x_in, w.r_in, w.ti, w.tv, w.keep = weights, kcs, vcs, x_in, r_in, ti, tv, (keep, xb, rb, bufs, peers)
     w.alg_bytes = algorithmic_bytes(cfg, B, L, args.layers, vocab, 0.5625 if nvfp4 else 2.0)   # per GPU
@@ -609,7 +626,7 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
 
-    w = build_workload(args, dev, rank, world, use_dist)
+    w = build_workload(args, dev, rank, world, use_dist, gen=not args.no_e2e)
     mk, cfg, tp, B, bf = w.mk, w.cfg, w.tp, args.batch, torch.bfloat16
 
     sampler = ClockSampler(local)
@@ -632,6 +649,13 @@ def main():
         host_x = x_in.cpu().pin_memory()           # the same embedding: the token must not change
         host_tok = torch.zeros(B, 1, dtype=torch.int32).pin_memory()
         n_e2e = max(10, min(args.steps, 100))
+        # consecutive positions from one handle where the workload has the position on the device: the
+        # 3 + 3 warm-up steps and the timed ones end exactly at the workload's KV length
+        run_mk, first_pos = mk, None
+        if w.mk_gen is not None and n_e2e + 6 < args.kv_len:
+            run_mk, first_pos = w.mk_gen, args.kv_len - (n_e2e + 6)
+            w.position.fill_(first_pos)
+        mk_static, mk = mk, run_mk
         for _ in range(3):
             x_in.copy_(host_x, non_blocking=True)
             mk.run(sync=False, validate=False)
@@ -682,6 +706,15 @@ def main():
                "launch": "one CUDA graph per step: copy in, Megakernel.run(), copy out" if graph is not None
                else "x_in.copy_(pinned), Megakernel.run(), token.copy_ to pinned"}
         mk.wait()
+        if first_pos is not None:
+            last = int(w.position.item())       # kv_len, or 3 short of it when the graph warm-up did not run
+            e2e["positions"] = {"first_timed": last - n_e2e, "end": last, "kv_len": args.kv_len,
+                                "how": "one handle, device-resident cache position advanced by the kernel"}
+        else:
+            e2e["positions"] = {"fixed": args.kv_len - 1, "how": "the static program of the timed region"}
+        mk = mk_static
+        x_in.copy_(host_x)                       # the fed-back row goes; the parity leg below uses the original input
+        torch.cuda.synchronize(dev)
 
     line = None
     if rank == 0:

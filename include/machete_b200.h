@@ -433,6 +433,31 @@ int mk_flash_decode_noalloc(const void* q, const void* k, const void* v, void* o
  * No counterpart in the reference. */
 int mk_flash_decode_noalloc_status(int32_t out[16]);
 
+/* ---- small-M GEMM on tcgen05 tensor cores ------------------------------------
+ * C[M,N] = A[M,K] x B[N,K]^T, bf16 operands (row strides lda / ldb / ldc in
+ * elements, K contiguous), fp32 accumulation in tensor memory, bf16 output.
+ * Replaces the reference's GemmSm100Op for the rows-per-launch range the decode
+ * matvec ops do not cover (src/machete/kernels/gemm/gemm_sm100.py:56-658: a
+ * (B,S,K), b (N,K), c (B,S,N); here B*S = M is flattened by the caller).  The
+ * weight rows are the 128-row operand of tcgen05.mma and up to 256 activation
+ * rows its N operand; more rows run as further CTAs along M.
+ *   K, lda, ldb multiples of 8; a and b 16-byte aligned.
+ *   workspace: mk_gemm_bf16_workspace_bytes(M, N, K) bytes of device memory,
+ *     256-byte aligned, ZERO before its first use; the kernel leaves it zero,
+ *     so one memset serves any number of calls (calls sharing a workspace must
+ *     be ordered on one stream).
+ *   split_k: CTAs that share one output tile's K range (0 = chosen so that
+ *     the grid fills the device).  timeout_ms bounds every device-side wait
+ *     (0 = 1000).
+ * Returns 0 or a negative code (mk_gemm_last_error); a device-side time-out
+ * shows in mk_gemm_bf16_status (out[0] != 0: 1 stage-free, 2 stage-full,
+ * 3 accumulator wait; [1] CTA, [2] role, [3] step), which synchronises. */
+uint64_t mk_gemm_bf16_workspace_bytes(int M, int N, int K);
+int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                 void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream);
+int mk_gemm_bf16_status(const void* workspace, int32_t out[4]);
+const char* mk_gemm_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,8 +7,8 @@ a=, b=, c=)``, ``tile_sizes`` keys ``S, N, K`` (``K`` is popped into
 
 Up to 32 rows (``B*S``) run as one pass of the weight-streaming tensor-core
 matvec unit; more rows are processed in chunks of 32, each chunk re-streaming
-the weights (correct, but the dense tcgen05 tile for prefill-size M is not
-part of this build yet).  ``has_a_scale`` (a training-backward feature) is
+the weights; from 64 rows up ``GemmSm100Op`` / ``gemm_sm100`` (a tcgen05 tile, its own
+launch) is the faster path.  ``has_a_scale`` (a training-backward feature) is
 rejected.
 """
 
@@ -88,4 +88,6 @@ class GemmOp(Op):
         return out
 
 
-__all__ = ["GemmOp", "ACT_MAP"]
+from .gemm_sm100 import GemmSm100Op, gemm_sm100, gemm_workspace  # noqa: E402
+
+__all__ = ["GemmOp", "ACT_MAP", "GemmSm100Op", "gemm_sm100", "gemm_workspace"]

@@ -1,0 +1,118 @@
+"""``GemmSm100Op``: ``C[B,S,N] = A[B,S,K] @ W[N,K]^T`` on the tcgen05 tensor cores.
+
+API mirror of the reference's SM100 GEMM op (src/machete/kernels/gemm/gemm_sm100.py:56-658:
+``reads a (B,S,K), b (N,K)``, ``writes c (B,S,N)``, ``schedule(tile_sizes=None, page_size, a=, b=,
+c=)``).  There the op is a handler inside the interpreter; here it is a launch of its own
+(``mk_gemm_bf16`` in ``csrc/gemm_sm100.cu``) next to the decode megakernel, which keeps the
+mma.sync matvec units for up to 32 rows.  ``gemm_sm100(a, b, c)`` is the call; ``GemmSm100Op.schedule``
+returns the scheduled-op record (tile grid, tensor metadata) and ``GemmSm100Op.launch`` runs it.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ... import _native as N
+from ...megakernel.ops import DEFAULT_PAGE_SIZE, Op
+
+TILE_N = 128     # weight rows per CTA
+TILE_M = 256     # activation rows per CTA
+TILE_K = 64
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    msg = f"{what}: {N.lib().mk_gemm_last_error().decode('utf-8', 'replace')} (code {rc})"
+    raise ValueError(msg) if rc in (-2, -3) else RuntimeError(msg)
+
+
+def gemm_workspace(M: int, N_out: int, K: int, device) -> torch.Tensor:
+    """A zeroed workspace for ``gemm_sm100`` (cached per device and size; the kernel leaves it zero)."""
+    need = int(N.lib().mk_gemm_bf16_workspace_bytes(M, N_out, K))
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), need)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def gemm_sm100(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, split_k: int = 0, timeout_ms: int = 1000,
+               workspace: Optional[torch.Tensor] = None, check_status: bool = False) -> torch.Tensor:
+    """``c[..., N] = a[..., K] @ b[N, K]^T`` (bf16, fp32 accumulate) on the current stream.
+
+    ``a`` and ``c`` may have any leading dims as long as their rows are equally spaced
+    (``a.view(-1, K)`` must be a view).  ``check_status`` synchronises and raises if a device-side
+    wait ran out.
+    """
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise RuntimeError("gemm_sm100 runs on a CUDA device only; there is no CPU path")
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or c.dtype != torch.bfloat16:
+        raise ValueError("gemm_sm100: a, b and c must be bfloat16")
+    K, n_out = int(a.shape[-1]), int(b.shape[0])
+    if b.dim() != 2 or int(b.shape[1]) != K or int(c.shape[-1]) != n_out or a.shape[:-1] != c.shape[:-1]:
+        raise ValueError(f"gemm_sm100: shapes a{tuple(a.shape)} b{tuple(b.shape)} c{tuple(c.shape)} do not match")
+    if a.stride(-1) != 1 or b.stride(-1) != 1 or c.stride(-1) != 1:
+        raise ValueError("gemm_sm100: K (a, b) and N (c) must be contiguous")
+    a2, c2 = a.view(-1, K), c.view(-1, n_out)          # raises if the rows are not equally spaced
+    M = int(a2.shape[0])
+    ws = workspace if workspace is not None else gemm_workspace(M, n_out, K, a.device)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    with torch.cuda.device(a.device):
+        _check(N.lib().mk_gemm_bf16(a2.data_ptr(), b.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0), b.stride(0),
+                                    c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
+                                    int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16")
+        if check_status:
+            st = (C.c_int32 * 4)()
+            _check(N.lib().mk_gemm_bf16_status(C.c_void_p(base), st), "mk_gemm_bf16_status")
+            if st[0] != 0:
+                torch.cuda.synchronize(a.device)
+                ws.zero_()
+                raise RuntimeError(f"gemm_sm100 aborted: wait {st[0]} ran out (cta={st[1]}, role={st[2]}, step={st[3]})")
+    return c
+
+
+class GemmSm100Op(Op):
+    """The reference's op declaration; execution is a launch of its own (see the module docstring)."""
+
+    reads = {"a": (None, ("B", "S", "K")), "b": (None, ("N", "K"))}
+    writes = {"c": (None, ("B", "S", "N"))}
+    tile = ("B", "S", "N")
+    dynamic_dims = ("B", "S")
+    tma_loads = {"a", "b"}
+    tma_stores = {"c"}
+
+    @classmethod
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, **tensors):
+        ts = dict(tile_sizes or {})
+        ts.setdefault("B", 1)
+        ts.setdefault("S", TILE_M)
+        ts.setdefault("N", TILE_N)
+        tile_k = ts.pop("K", TILE_K)
+        if ts["N"] != TILE_N or ts["S"] > TILE_M or tile_k != TILE_K:
+            raise ValueError(f"GemmSm100Op: this build's tile is S<={TILE_M}, N={TILE_N}, K={TILE_K}")
+        op = cls._schedule_single(tile_sizes=ts, **tensors)
+        op.static_dims["tile_K"] = tile_k
+        op.static_dims["page_size"] = page_size
+        return [op]
+
+    @classmethod
+    def launch(cls, sop, **kw) -> torch.Tensor:
+        t = sop.tensor_refs
+        return gemm_sm100(t["a"], t["b"], t["c"], **kw)
+
+    @classmethod
+    def lower(cls, sop, ctx):
+        raise NotImplementedError("GemmSm100Op runs as its own launch (GemmSm100Op.launch / gemm_sm100), "
+                                  "not as an op of the decode megakernel; use GemmOp for up to 32 rows per pass")
+
+
+__all__ = ["GemmSm100Op", "gemm_sm100", "gemm_workspace", "TILE_M", "TILE_N", "TILE_K"]
