@@ -53,6 +53,7 @@ struct Params {
   int M, N, K;
   int split_k, k_tiles;
   int stages;
+  int m_box;             // rows of one activation box (what one TMA copy delivers, whatever this CTA uses of it)
   uint64_t timeout_ns;
 };
 
@@ -166,7 +167,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int m0 = blockIdx.z * kMaxM;
   const int m_here = min(kMaxM, p.M - m0);
   const int mpad = (m_here + 15) & ~15;                       // the MMA's N: a multiple of 16
-  const uint32_t a_bytes = (uint32_t)mpad * kTileK * 2;
+  const uint32_t a_bytes = (uint32_t)p.m_box * kTileK * 2;
   const uint32_t stage_bytes = (kWBytes + a_bytes + 1023u) & ~1023u;
   Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -421,7 +422,7 @@ int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
   p.partial = reinterpret_cast<float*>(ws + l.partial_off);
   p.ldc = ldc;
   p.M = M, p.N = N, p.K = K;
-  p.split_k = split_k, p.k_tiles = k_tiles, p.stages = stages;
+  p.split_k = split_k, p.k_tiles = k_tiles, p.stages = stages, p.m_box = m_box;
   p.timeout_ns = (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
   const dim3 grid((N + kTileN - 1) / kTileN, split_k, (M + kMaxM - 1) / kMaxM);
   gemm_bf16_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(map_a, map_b, p);

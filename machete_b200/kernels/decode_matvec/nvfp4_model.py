@@ -30,6 +30,7 @@ from __future__ import annotations
 import torch
 
 from ...megakernel.ops import DEFAULT_PAGE_SIZE
+from .._batching import pick_batch_chunk, schedule_in_batch_chunks
 from ..qknorm_rope import QKNormRopeOp
 from .nvfp4 import (MatvecNvfp4Sm120Op, MatvecResidualNvfp4Sm120Op, RmsGateUpSiluNvfp4Sm120Op,
                     RmsKMatvecRopeCacheNvfp4Sm120Op, RmsMatvecNvfp4Sm120Op, RmsQMatvecRopeNvfp4Sm120Op,
@@ -178,7 +179,8 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
 def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_cache, x_buffers, residual_buffers,
                                       q_buf, attn_out_buf, mlp_h_buf, top_values, top_indices, num_layers, x_in,
                                       residual_in, seq_len=1, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0,
-                                      num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True):
+                                      num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True,
+                                      batch_chunk=None):
     """A full greedy decode step with packed weights: ``(ops, keep_alive)``.
 
     Layer ``i`` reads the pair (``x``, residual) it is given and writes the
@@ -187,6 +189,19 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
     LM head is ``weights['lm_head.packed']`` / ``['lm_head.scales']``.  Under ``tp_peers`` the
     LM head is this rank's vocabulary shard and the ranks exchange their top-1 keys.
     """
+    # ``batch_chunk`` (None = as many rows as one op can stage, 0 = never chunk): a batch whose
+    # activations do not fit shared memory runs as interleaved chunks (kernels/_batching.py)
+    if batch_chunk is None:
+        batch_chunk = 0
+        if tp_peers is None:
+            c = pick_batch_chunk(batch, seq_len, max(int(x_in.shape[-1]), num_q_heads * head_dim))
+            batch_chunk = c if c < batch else 0
+    if batch_chunk and batch_chunk < batch:
+        kw = dict(locals())
+        kw.pop("batch_chunk")
+        kw.pop("c", None)
+        return schedule_in_batch_chunks(lambda **sub: schedule_decode_model_nvfp4_sm100(batch_chunk=0, **sub),
+                                        batch_chunk, **kw)
     ops, keep = [], []
     cur, cur_x, cur_r = 1, x_in, residual_in
     for layer_idx in range(num_layers):

@@ -11,6 +11,7 @@ either bf16 logits or the fused greedy-token head.
 from __future__ import annotations
 
 from ...megakernel.ops import DEFAULT_PAGE_SIZE
+from .._batching import pick_batch_chunk, schedule_in_batch_chunks
 from ..decode_matvec.sm100 import DecodeLayerSchedule as Llama1BLayerSchedule
 from ..decode_matvec.sm100 import FinalRmsLmHeadSm100Op as Llama1BFinalRmsLmHeadSm100Op
 from ..decode_matvec.sm100 import MatvecResidualSm100Op as Llama1BMatvecResidualSm100Op
@@ -68,6 +69,7 @@ def schedule_decode_model_sm100(
     tp_peers=None,
     position=None,
     embedding=None,
+    batch_chunk=None,
 ):
     """Schedule a full decode step: ``(ops, keep_alive)``.
 
@@ -85,6 +87,18 @@ def schedule_decode_model_sm100(
     shards (see ``schedule_decode_layer_sm100``); full logits are not
     supported under tensor parallelism, only the greedy-token head.
     """
+    # ``batch_chunk`` (None = as many rows as one op can stage, 0 = never chunk): a batch whose
+    # activations do not fit shared memory runs as interleaved chunks (kernels/_batching.py)
+    if batch_chunk is None:
+        batch_chunk = 0
+        if tp_peers is None and position is None:
+            c = pick_batch_chunk(batch, seq_len, max(hidden_size, num_q_heads * head_dim))
+            batch_chunk = c if c < batch else 0
+    if batch_chunk and batch_chunk < batch:
+        kw = dict(locals())
+        kw.pop("batch_chunk")
+        kw.pop("c", None)
+        return schedule_in_batch_chunks(lambda **sub: schedule_decode_model_sm100(batch_chunk=0, **sub), batch_chunk, **kw)
     dynamic = position is not None
     if dynamic:
         # Generation loop (not in the reference, which re-schedules for every position,

@@ -103,9 +103,10 @@ def test_padded_sixteen_row_step_and_batch():
     assert_parity(res_out, want_res, "residual", roundings=2)
 
 
-@pytest.mark.parametrize("B", [1, 4, 16])
-def test_multi_layer_model_greedy_token(B):
-    """Four layers + final norm + LM head + arg-max; the token index must match exactly."""
+@pytest.mark.parametrize("B,chunk", [(1, None), (4, None), (16, None), (32, 8), (12, 4)])
+def test_multi_layer_model_greedy_token(B, chunk):
+    """Four layers + final norm + LM head + arg-max; the token index must match exactly.  ``chunk``: the
+    batch runs as interleaved chunks of that many rows (what a batch too large to stage does by itself)."""
     L, T, hidden, nq, nkv, hd, inter, vocab = 4, 512, 1024, 16, 4, 64, 2048, 8192 + 48
     cache_pos = 300
     w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=2, device="cuda")
@@ -126,9 +127,12 @@ def test_multi_layer_model_greedy_token(B):
         q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device="cuda"),
         attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device="cuda"),
         mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device="cuda"), final_norm=fn.cuda(), lm_head=lm.cuda(),
-        top_values=tv, top_indices=ti, num_layers=L, x_in=x0.cuda(), residual_in=r0.cuda(), **dims)
+        top_values=tv, top_indices=ti, num_layers=L, x_in=x0.cuda(), residual_in=r0.cuda(), batch_chunk=chunk, **dims)
     kc_ref, vc_ref = [t.cpu().clone() for t in kcs], [t.cpu().clone() for t in vcs]
     mk = Megakernel(ops, scheduler=OverlapTileScheduler())
+    if chunk:
+        assert len(ops) == (B // chunk) * (L * 9 + 2)           # every op once per chunk (2 down-projection K-blocks)
+        assert [o.name for o in mk.native_ops].count("FlashDecodingFused") == (B // chunk) * L
     mk.run()
     logits, want_v, want_i = oracle.decode_model(weights=to_cpu(w), x=x0, residual=r0, k_caches=kc_ref, v_caches=vc_ref,
                                                  cache_pos=cache_pos, final_norm=fn, lm_head=lm, num_layers=L,

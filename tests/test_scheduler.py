@@ -235,3 +235,59 @@ def test_qk_norm_nvfp4_layer_schedules_without_deadlock(fuse):
         assert all(o.writes[-1].axis == 1 and (o.writes[-1].lo, o.writes[-1].hi) == (40, 41) for o in qk[1::2])
     final = simulate(mk.program)
     assert (final == mk.program.counter_expected[:len(final)]).all()
+
+
+def test_batch_chunks_interleave_groups_and_keep_chunks_independent():
+    """A batch too large to stage: the model is scheduled per chunk on row views and interleaved;
+    the chunks' dependency chains do not touch each other."""
+    import torch
+
+    from machete_b200.kernels._batching import pick_batch_chunk, rows_that_fit, schedule_in_batch_chunks
+    from machete_b200.kernels.llama1b import schedule_decode_model_sm100
+    from machete_b200.megakernel.scheduling import resolve_dep_pairs
+    from tests.util import llama_weights
+
+    assert rows_that_fit(4096) == 12 and pick_batch_chunk(32, 1, 4096) == 8 and pick_batch_chunk(8, 1, 4096) == 8
+    assert pick_batch_chunk(7, 1, 16384) == 1 and pick_batch_chunk(30, 1, 4096) == 10
+    BF = torch.bfloat16
+    B, L, T, hidden, nq, nkv, hd, inter, vocab = 32, 2, 64, 4096, 32, 8, 128, 8192, 256
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=1)
+    z = lambda *s: torch.zeros(*s, dtype=BF)          # noqa: E731
+    kw = dict(batch=B, cache_pos=40, weights=w, k_cache=[z(B, T, nkv, hd) for _ in range(L)],
+              v_cache=[z(B, T, nkv, hd) for _ in range(L)], x_buffers=[z(B, 1, hidden) for _ in range(2)],
+              residual_buffers=[z(B, 1, hidden) for _ in range(2)], q_buf=z(B, 1, nq * hd), attn_out_buf=z(B, 1, nq * hd),
+              mlp_h_buf=z(B, 1, inter), final_norm=z(hidden), lm_head=z(vocab, hidden), top_values=torch.zeros(B, 1),
+              top_indices=torch.zeros(B, 1, dtype=torch.int32), num_layers=L, x_in=z(B, 1, hidden),
+              residual_in=z(B, 1, hidden), hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv,
+              head_dim=hd)
+    ops, _ = schedule_decode_model_sm100(**kw)                  # chunking picked by itself: 4 chunks of 8
+    one, _ = schedule_decode_model_sm100(**{**kw, "batch": 8, **{k: (v[:8] if isinstance(v, torch.Tensor) and v.shape[0] == B
+                                                                       else [t[:8] for t in v] if isinstance(v, list) else v)
+                                                                   for k, v in kw.items() if k != "batch"}})
+    assert len(ops) == 4 * len(one)
+    names = [o.op_cls.__name__ for o in ops]
+    assert names[:4] == ["RmsQMatvecRopeSm100Op"] * 4
+    # split + combine stay adjacent (they fuse), and so does the down projection's K-block chain
+    i = names.index("FlashDecodingSplitBSHDOp")
+    assert names[i:i + 4] == ["FlashDecodingSplitBSHDOp", "FlashDecodingCombineBSHDOp"] * 2
+    j = names.index("MatvecSm100Op")
+    assert names[j:j + 4] == ["MatvecSm100Op", "MatvecResidualSm100Op", "MatvecSm100Op", "MatvecResidualSm100Op"]
+    # the same x row range in every op of a chunk, and no dependency pair across chunks
+    rows = [int(o.tensor_refs[o.op_cls.INPUTS[0]].shape[0]) for o in ops]
+    assert set(rows) == {8}
+    chunk_of = {}
+    base = kw["q_buf"].data_ptr()
+    for idx, o in enumerate(ops):
+        t = o.tensor_refs
+        probe = t.get("q", t.get("a", None))
+        if probe is not None and probe.untyped_storage().data_ptr() == kw["q_buf"].untyped_storage().data_ptr():
+            chunk_of[idx] = (probe.data_ptr() - base) // (8 * nq * hd * 2)
+    pairs = resolve_dep_pairs(ops)
+    assert pairs and all(chunk_of[p] == chunk_of[c] for p, c, _, _ in pairs if p in chunk_of and c in chunk_of)
+    mk = Megakernel(ops)
+    final = simulate(mk.program)                  # no deadlock: every counter reaches its expected count
+    assert (final == mk.program.counter_expected[:len(final)]).all()
+    with pytest.raises(ValueError):
+        schedule_in_batch_chunks(schedule_decode_model_sm100, 5, **kw)
+    with pytest.raises(ValueError):
+        schedule_decode_model_sm100(**{**kw, "batch_chunk": 8, "position": torch.zeros(1, dtype=torch.int32)})
