@@ -31,7 +31,9 @@ One JSON line is printed by rank 0:
               Qwen3-8B-shape step with block-scaled NVFP4 weights, batch 1 and
               8 (µs/step, tokens/s, per-GPU algorithmic bytes, fraction);
 * ``cfg0`` / ``cfg1`` / ``cfg2`` (N = 1): one layer at KV 1024, the small-M
-              GEMM sweep in bf16 and NVFP4, flash decoding at batch 8 x 32 768.
+              GEMM sweep in bf16 and NVFP4, flash decoding at batch 8 x 32 768;
+* ``gemm_sm100`` (N = 1): the tcgen05 GEMM tile at 64 / 128 / 256 rows, with
+              cuBLAS timed beside it.
 
 ``--impl reference`` times the CPU port alone (the reference ships no
 compiled code; its own path for this step is PyTorch on the host).
@@ -468,11 +470,13 @@ def sub_args(args, **over):
 
 
 def record_cfg4(args, dev, rank, world, use_dist, peak):
-    """The tensor-parallel configuration at this N: Qwen3-8B shape, block-scaled NVFP4, batch 1 and 8."""
+    """The tensor-parallel configuration at this N: Qwen3-8B shape, block-scaled NVFP4, batch 1, 8 and (one GPU) 32."""
     out = {"workload": "qwen3-8b-shape 36-layer decode step, kv 8192, vocab 151936, nvfp4 (e4m3 scale per 16 "
                        "values + fp32 global scale), greedy token", "n_gpus": world,
            "parallelism": "single gpu" if world == 1 else f"tp{world} (in-kernel all-reduce)", "batches": {}}
-    for batch in (1, 8):
+    # batch 32 does not fit the activation staging as one op: on one GPU it runs as interleaved chunks of 8
+    # rows (kernels/_batching.py); the chunked schedule is not combined with tensor parallelism
+    for batch in ((1, 8, 32) if world == 1 else (1, 8)):
         a = sub_args(args, model="qwen3-8b", batch=batch, parallel="tp")
         try:
             w = build_workload(a, dev, rank, world, use_dist)
@@ -536,6 +540,63 @@ def record_cfg1(args, dev, peak):
             del mks
             gc.collect()
             torch.cuda.empty_cache()
+    return out
+
+
+def record_gemm_sm100(args, dev, peak):
+    """The tcgen05 GEMM tile at 64 / 128 / 256 activation rows.  Launches are captured in one CUDA graph
+    (the host side of a call, two tensor-map encodes, costs more than these kernels run) and rotate
+    over weight copies totalling more than twice L2; cuBLAS through torch.matmul is timed the same way."""
+    from machete_b200.kernels.gemm import gemm_pack_weight, gemm_sm100
+
+    bf = torch.bfloat16
+    tflops_peak = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            tflops_peak = float(json.load(fh)["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        tflops_peak = 1590.0
+    out = {"l2": "launches rotate over weight copies totalling more than twice L2; one CUDA graph of all launches",
+           "tensor_peak_tflops": tflops_peak, "shapes": {}}
+    iters = 40
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                fn(i)
+        torch.cuda.synchronize(dev)
+        graph.replay()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / (5 * iters) * 1e3
+
+    for (Nout, K) in ((4096, 4096), (14336, 4096), (4096, 14336)):
+        g = torch.Generator(device=dev).manual_seed(9)
+        ws = rotating(lambda i: (torch.randn(Nout, K, generator=g, device=dev) * 0.02).to(bf), Nout * K * 2)
+        for M in (64, 128, 256):
+            a = torch.randn(1, M, K, generator=g, device=dev).to(bf)
+            c = torch.zeros(1, M, Nout, dtype=bf, device=dev)
+            us = timed(lambda i: gemm_sm100(a, ws[i % len(ws)], c))
+            us_lib = timed(lambda i: torch.matmul(a[0], ws[i % len(ws)].t(), out=c[0]))
+            alg = (Nout * K + M * K + M * Nout) * 2
+            flops = 2.0 * M * Nout * K
+            out["shapes"][f"{M}x{K}x{Nout}"] = {
+                "us": us, "tflops": flops / us / 1e6, "frac_tensor": flops / us / 1e6 / tflops_peak,
+                "achieved_gbs": alg / us / 1e3, "frac_hbm": alg / us / 1e3 / peak, "cublas_us": us_lib}
+        del ws
+        gc.collect()
+        torch.cuda.empty_cache()
     return out
 
 
@@ -763,7 +824,8 @@ def main():
             if rank == 0:
                 line["cfg4"] = cfg4
         if world == 1 and rank == 0 and args.model == "llama1b":
-            for name, fn in (("cfg0", record_cfg0), ("cfg1", record_cfg1), ("cfg2", record_cfg2)):
+            for name, fn in (("cfg0", record_cfg0), ("cfg1", record_cfg1), ("cfg2", record_cfg2),
+                             ("gemm_sm100", record_gemm_sm100)):
                 try:
                     line[name] = fn(args, dev, peak)
                 except Exception as exc:  # noqa: BLE001

@@ -116,7 +116,7 @@ EXPORTS = [
     "mk_update_op", "mk_read_counters", "mk_destroy",
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
     "mk_flash_decode_noalloc", "mk_flash_decode_noalloc_status",
-    "mk_gemm_bf16_workspace_bytes", "mk_gemm_bf16", "mk_gemm_bf16_status", "mk_gemm_last_error",
+    "mk_gemm_bf16_workspace_bytes", "mk_gemm_bf16", "mk_gemm_bf16_packed", "mk_gemm_bf16_status", "mk_gemm_last_error",
 ]
 
 _lib = None
@@ -193,6 +193,8 @@ def _declare(h: C.CDLL) -> None:
     h.mk_gemm_bf16_workspace_bytes.restype = u64
     h.mk_gemm_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, u64, i32, i32, vp]
     h.mk_gemm_bf16.restype = C.c_int
+    h.mk_gemm_bf16_packed.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, u64, i32, i32, vp]
+    h.mk_gemm_bf16_packed.restype = C.c_int
     h.mk_gemm_bf16_status.argtypes = [vp, C.POINTER(i32)]
     h.mk_gemm_bf16_status.restype = C.c_int
     h.mk_gemm_last_error.restype = C.c_char_p

@@ -12,9 +12,14 @@
 //   warp 1   allocates tensor memory, issues tcgen05.mma (one thread), hands
 //            stages back with tcgen05.commit;
 //   warps 2-5 epilogue: tcgen05.ld of the fp32 accumulator (TMEM lane = weight
-//            row, column = activation row), bf16 stores, or fp32 red.add into a
-//            workspace when the K range is split over several CTAs (the last CTA
-//            of a tile converts and re-zeroes the workspace).
+//            row, column = activation row) and bf16 stores.
+//
+// One SM cannot keep enough reads in flight to draw more than roughly 1/148 of the
+// HBM bandwidth, so a weight with few 128-row tiles is also split along K: the CTAs
+// of one output tile form a thread-block cluster, each leaves its fp32 partial tile
+// in its own shared memory (the stage ring is free by then), and after a cluster
+// barrier every CTA sums one slice of the rows over all peers through distributed
+// shared memory and stores it.  No global workspace and no atomics are involved.
 //
 // Takes the place of the reference's GemmSm100Op (src/machete/kernels/gemm/
 // gemm_sm100.py:56-658), which tiles (S, N) with a double-buffered K loop inside
@@ -46,13 +51,13 @@ constexpr uint32_t kWBytes = kTileN * kTileK * 2;
 
 struct Params {
   __nv_bfloat16* c;
-  float* partial;        // [M, N] fp32, zero between calls (split-K only)
-  int32_t* tile_count;   // arrivals per (m chunk, n tile), zero between calls
   int32_t* status;       // [0] code, [1] cta, [2] role, [3] aux
   int64_t ldc;
   int M, N, K;
   int split_k, k_tiles;
   int stages;
+  uint32_t ring_bytes;   // stages x stage bytes, or the fp32 partial tile if that is larger (split-K)
+  int b_packed;          // the weight is stored K-tile-major: [K/64][N][64] (one box = 16 KB contiguous)
   int m_box;             // rows of one activation box (what one TMA copy delivers, whatever this CTA uses of it)
   uint64_t timeout_ns;
 };
@@ -65,7 +70,6 @@ struct Shared {
   uint64_t acc_ready;
   uint32_t tmem_base;
   int32_t abort_flag;
-  int32_t is_last;
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
@@ -80,6 +84,25 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap,
       "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
       "l"(tmap), "r"(c0), "r"(c1), "r"(bar), "l"(pol)
       : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of `addr` (a shared address of this CTA) in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -143,13 +166,16 @@ __device__ __forceinline__ void give_up(const Params& p, Shared* sh, int code, i
 }
 // One thread waits for an mbarrier phase; false = aborted or out of time (recorded).
 __device__ __forceinline__ bool wait_bar(const Params& p, Shared* sh, uint32_t bar, uint32_t parity, int code, int role, int aux) {
-  if (mk::mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = mk::globaltimer_ns();
+  // The clock is read only after a batch of failed polls: reading the global timer costs about as
+  // much as a whole K step, and almost every wait succeeds within a few polls.
+  uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if (mk::mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
+    if ((spin & 255u) == 255u) {
       if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) return false;
-      if (mk::globaltimer_ns() - t0 > p.timeout_ns) {
+      const uint64_t now = mk::globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > p.timeout_ns) {
         give_up(p, sh, code, role, aux);
         return false;
       }
@@ -169,7 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int mpad = (m_here + 15) & ~15;                       // the MMA's N: a multiple of 16
   const uint32_t a_bytes = (uint32_t)p.m_box * kTileK * 2;
   const uint32_t stage_bytes = (kWBytes + a_bytes + 1023u) & ~1023u;
-  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
+  Shared* sh = reinterpret_cast<Shared*>(smem + p.ring_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kTileN;
   // this CTA's K steps
@@ -186,7 +212,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     mk::mbar_init(mk::smem_u32(&sh->acc_ready), 1);
     sh->abort_flag = 0;
-    sh->is_last = 0;
     mk::fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(mk::smem_u32(&sh->tmem_base), tmem_cols);
@@ -206,7 +231,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t dst = base + (uint32_t)s * stage_bytes;
         const uint32_t bar = mk::smem_u32(&sh->full[s]);
         mk::mbar_arrive_expect_tx(bar, kWBytes + a_bytes);
-        tma_load_2d_hint(dst, &map_b, (kt0 + i) * kTileK, n0, bar, pol);
+        if (p.b_packed)
+          mk::tma_load_3d(dst, &map_b, 0, n0, kt0 + i, bar, pol);
+        else
+          tma_load_2d_hint(dst, &map_b, (kt0 + i) * kTileK, n0, bar, pol);
         tma_load_2d(dst + kWBytes, &map_a, (kt0 + i) * kTileK, m0, bar);
       }
       if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) {
@@ -247,54 +275,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < p.N;
-    if (ready) {
-      for (int c = 0; c < mpad; c += 32) {
-        uint32_t r[32];
+    // split-K: the partial tile goes to this CTA's shared memory as fp32 [activation row][128 weight rows]
+    // (the stage ring is free: every copy was consumed before the accumulator was declared ready)
+    float* part = reinterpret_cast<float*>(smem) + q * 32 + lane;
+    for (int c = 0; c < mpad; c += 32) {
+      uint32_t r[32];
+      if (ready) {
         tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
-        if (p.split_k == 1) {
+      } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int m = m0 + c + j;
-            if (n_ok && m < p.M) p.c[(int64_t)m * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
-          }
-        } else {
+        for (int j = 0; j < 32; ++j) r[j] = 0u;      // an empty K range (or an aborted CTA) adds nothing
+      }
+      if (p.split_k == 1) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int m = m0 + c + j;
-            if (n_ok && m < p.M) atomicAdd(&p.partial[(int64_t)m * p.N + n], __uint_as_float(r[j]));
-          }
+        for (int j = 0; j < 32; ++j) {
+          const int m = m0 + c + j;
+          if (ready && n_ok && m < p.M) p.c[(int64_t)m * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
         }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c + j < mpad) part[(c + j) * kTileN] = __uint_as_float(r[j]);
       }
     }
-    if (p.split_k > 1) __threadfence();
     tc_fence_before();
   }
   __syncthreads();
 
   if (p.split_k > 1) {
-    // the last CTA of this (m chunk, n tile) turns the summed fp32 tile into bf16 and leaves the
-    // workspace zero for the next call
-    int32_t* cnt = p.tile_count + blockIdx.z * gridDim.x + blockIdx.x;
-    if (threadIdx.x == 0) {
-      __threadfence();
-      const int prev = atomicAdd(cnt, 1);
-      sh->is_last = (prev == p.split_k - 1) ? 1 : 0;
-      __threadfence();
-    }
-    __syncthreads();
-    if (sh->is_last) {
-      __threadfence();
-      const bool clean = *reinterpret_cast<volatile int32_t*>(&p.status[0]) == 0;
-      for (int idx = threadIdx.x; idx < m_here * kTileN; idx += kThreads) {
-        const int m = m0 + idx / kTileN, n = n0 + idx % kTileN;
-        if (n >= p.N) continue;
-        float* src = &p.partial[(int64_t)m * p.N + n];
-        const float v = __ldcg(src);
-        if (clean) p.c[(int64_t)m * p.ldc + n] = __float2bfloat16_rn(v);
-        __stcg(src, 0.f);
+    // The CTAs of this output tile are one cluster (its rank = the K split).  Each sums its slice of
+    // the activation rows over every peer's partial tile and stores it.
+    cluster_sync_all();
+    const int rank = (int)cluster_ctarank();
+    const int rows_per = (mpad + p.split_k - 1) / p.split_k;
+    const int r_lo = rank * rows_per, r_hi = min(mpad, r_lo + rows_per);
+    for (int idx = threadIdx.x; idx < (r_hi - r_lo) * (kTileN / 4); idx += kThreads) {
+      const int ml = r_lo + idx / (kTileN / 4), nl = (idx % (kTileN / 4)) * 4;
+      const uint32_t off = base + (uint32_t)(ml * kTileN + nl) * 4u;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int peer = 0; peer < p.split_k; ++peer) {
+        const float4 v = ld_cluster_f4(peer_smem(off, (uint32_t)peer));
+        acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
       }
-      if (threadIdx.x == 0) *cnt = 0;
+      const int m = m0 + ml, n = n0 + nl;
+      if (m < p.M) {
+        __nv_bfloat16* dst = p.c + (int64_t)m * p.ldc + n;
+        const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (n + e < p.N) dst[e] = __float2bfloat16_rn(v[e]);
+      }
     }
+    cluster_sync_all();        // nobody leaves while a peer may still read its partial tile
   }
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem, tmem_cols);
@@ -340,6 +372,22 @@ static int encode_bf16_map(CUtensorMap* out, const void* base, int rows, int K, 
   return 0;
 }
 
+// The same matrix stored K-tile-major, [K/64][N][64]: dims (64, N, K/64), one box = 128 rows of one K tile,
+// which is one contiguous 16 KB piece of memory.
+static int encode_packed_map(CUtensorMap* out, const void* base, int N, int k_tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(-5, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)kTileK, (cuuint64_t)N, (cuuint64_t)k_tiles};
+  cuuint64_t strides[2] = {(cuuint64_t)kTileK * 2, (cuuint64_t)N * kTileK * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kTileK, (cuuint32_t)kTileN, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled (packed weight) failed with CUresult %d", (int)r);
+  return 0;
+}
+
 static int pick_split(int M, int N, int K, int sms) {
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + kMaxM - 1) / kMaxM);
   const int k_tiles = (K + kTileK - 1) / kTileK;
@@ -350,15 +398,12 @@ static int pick_split(int M, int N, int K, int sms) {
 }
 
 struct Layout {
-  uint64_t status_off, count_off, partial_off, total;
+  uint64_t status_off, total;     // the workspace holds the status block only
 };
-static Layout layout_of(int M, int N) {
+static Layout layout_of(int, int) {
   Layout l;
   l.status_off = 0;
-  l.count_off = 64;
-  const uint64_t tiles = (uint64_t)((N + kTileN - 1) / kTileN) * ((M + kMaxM - 1) / kMaxM);
-  l.partial_off = (l.count_off + tiles * 4 + 255) / 256 * 256;
-  l.total = l.partial_off + (uint64_t)M * N * 4;
+  l.total = 256;
   return l;
 }
 
@@ -374,9 +419,12 @@ uint64_t mk_gemm_bf16_workspace_bytes(int M, int N, int K) {
   return mkg::layout_of(M, N).total;
 }
 
-int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                 void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream) {
-  using namespace mkg;
+}  // extern "C"
+
+namespace mkg {
+static int gemm_launch(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                       void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream,
+                       bool b_packed) {
   if (!a || !b || !c || !workspace) return fail(-1, "mk_gemm_bf16: null pointer");
   if (M < 1 || N < 1 || K < 1) return fail(-2, "mk_gemm_bf16: M, N, K must be positive (got %d, %d, %d)", M, N, K);
   if (K % 8 || lda % 8 || ldb % 8 || ((uint64_t)a & 15) || ((uint64_t)b & 15))
@@ -395,11 +443,12 @@ int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
   const int k_tiles = (K + kTileK - 1) / kTileK;
   if (split_k <= 0) split_k = pick_split(M, N, K, sms);
   if (split_k > k_tiles) split_k = k_tiles;
+  if (split_k > 8) return fail(-2, "mk_gemm_bf16: split_k is at most 8 (one portable thread-block cluster)");
   const int m_box = ((M < kMaxM ? M : kMaxM) + 15) & ~15;
   CUtensorMap map_a, map_b;
   int rc = encode_bf16_map(&map_a, a, M, K, lda, m_box);
   if (rc) return rc;
-  rc = encode_bf16_map(&map_b, b, N, K, ldb, kTileN);
+  rc = b_packed ? encode_packed_map(&map_b, b, N, k_tiles) : encode_bf16_map(&map_b, b, N, K, ldb, kTileN);
   if (rc) return rc;
   const uint32_t stage_bytes = (kWBytes + (uint32_t)m_box * kTileK * 2 + 1023u) & ~1023u;
   int stages = (smem_optin - 2048) / (int)stage_bytes;
@@ -407,7 +456,9 @@ int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
   if (stages < 2) return fail(-4, "mk_gemm_bf16: shared memory holds fewer than two stages");
   const int per = (k_tiles + split_k - 1) / split_k;
   if (stages > per) stages = per < 2 ? 2 : per;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + sizeof(Shared);
+  uint32_t ring_bytes = (uint32_t)stages * stage_bytes;
+  if (split_k > 1 && ring_bytes < (uint32_t)m_box * kTileN * 4u) ring_bytes = (uint32_t)m_box * kTileN * 4u;
+  const size_t smem = 1024 + (size_t)ring_bytes + sizeof(Shared);
   static bool attr_set[64] = {};
   if (dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess)
@@ -418,17 +469,44 @@ int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   p.c = reinterpret_cast<__nv_bfloat16*>(c);
   p.status = reinterpret_cast<int32_t*>(ws + l.status_off);
-  p.tile_count = reinterpret_cast<int32_t*>(ws + l.count_off);
-  p.partial = reinterpret_cast<float*>(ws + l.partial_off);
   p.ldc = ldc;
   p.M = M, p.N = N, p.K = K;
-  p.split_k = split_k, p.k_tiles = k_tiles, p.stages = stages, p.m_box = m_box;
+  p.split_k = split_k, p.k_tiles = k_tiles, p.stages = stages, p.m_box = m_box, p.b_packed = b_packed ? 1 : 0;
+  p.ring_bytes = ring_bytes;
   p.timeout_ns = (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
   const dim3 grid((N + kTileN - 1) / kTileN, split_k, (M + kMaxM - 1) / kMaxM);
-  gemm_bf16_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(map_a, map_b, p);
-  const cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)split_k;      // the K splits of one output tile share a cluster
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = split_k > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel, map_a, map_b, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(-(int)e - 1000, "mk_gemm_bf16 launch: %s", cudaGetErrorString(e));
   return 0;
+}
+}  // namespace mkg
+
+extern "C" {
+
+int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                 void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream) {
+  return mkg::gemm_launch(a, b, c, M, N, K, lda, ldb, ldc, workspace, workspace_bytes, split_k, timeout_ms, cuda_stream,
+                          false);
+}
+
+int mk_gemm_bf16_packed(const void* a, const void* b_packed, void* c, int M, int N, int K, int64_t lda, int64_t ldc,
+                        void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream) {
+  if (K % 64) return mkg::fail(-2, "mk_gemm_bf16_packed: K must be a multiple of 64 (the packer pads with zeros)");
+  return mkg::gemm_launch(a, b_packed, c, M, N, K, lda, K, ldc, workspace, workspace_bytes, split_k, timeout_ms,
+                          cuda_stream, true);
 }
 
 int mk_gemm_bf16_status(const void* workspace, int32_t out[4]) {

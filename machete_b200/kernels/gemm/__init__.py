@@ -88,6 +88,7 @@ class GemmOp(Op):
         return out
 
 
-from .gemm_sm100 import GemmSm100Op, gemm_sm100, gemm_workspace  # noqa: E402
+from .gemm_sm100 import GemmSm100Op, PackedWeight, gemm_pack_weight, gemm_sm100, gemm_workspace  # noqa: E402
 
-__all__ = ["GemmOp", "ACT_MAP", "GemmSm100Op", "gemm_sm100", "gemm_workspace"]
+__all__ = ["GemmOp", "ACT_MAP", "GemmSm100Op", "gemm_sm100", "gemm_workspace", "gemm_pack_weight",
+           "PackedWeight"]

@@ -44,7 +44,30 @@ def gemm_workspace(M: int, N_out: int, K: int, device) -> torch.Tensor:
     return ws
 
 
-def gemm_sm100(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, split_k: int = 0, timeout_ms: int = 1000,
+class PackedWeight:
+    """A weight stored K-tile-major, ``[K/64][N][64]`` (see :func:`gemm_pack_weight`)."""
+
+    def __init__(self, data: torch.Tensor, n: int, k: int):
+        self.data, self.n, self.k = data, int(n), int(k)
+
+    @property
+    def shape(self):
+        return (self.n, self.k)
+
+
+def gemm_pack_weight(b: torch.Tensor) -> PackedWeight:
+    """Offline re-layout of an ``(N, K)`` bf16 weight for ``gemm_sm100``: K is cut into 64-column
+    tiles (zero-padded) and each tile stores its 64 columns of every row contiguously, so one
+    128-row box of the kernel is one contiguous 16 KB read."""
+    if b.dim() != 2 or b.dtype != torch.bfloat16:
+        raise ValueError("gemm_pack_weight: an (N, K) bfloat16 matrix is required")
+    n, k = int(b.shape[0]), int(b.shape[1])
+    kp = -(-k // TILE_K) * TILE_K
+    src = b if kp == k else torch.nn.functional.pad(b, (0, kp - k))
+    return PackedWeight(src.view(n, kp // TILE_K, TILE_K).permute(1, 0, 2).contiguous(), n, kp)
+
+
+def gemm_sm100(a: torch.Tensor, b, c: torch.Tensor, *, split_k: int = 0, timeout_ms: int = 1000,
                workspace: Optional[torch.Tensor] = None, check_status: bool = False) -> torch.Tensor:
     """``c[..., N] = a[..., K] @ b[N, K]^T`` (bf16, fp32 accumulate) on the current stream.
 
@@ -52,14 +75,19 @@ def gemm_sm100(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, split_k: in
     (``a.view(-1, K)`` must be a view).  ``check_status`` synchronises and raises if a device-side
     wait ran out.
     """
-    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+    if not (a.is_cuda and c.is_cuda):
         raise RuntimeError("gemm_sm100 runs on a CUDA device only; there is no CPU path")
-    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or c.dtype != torch.bfloat16:
+    packed = isinstance(b, PackedWeight)
+    bt = b.data if packed else b
+    if not bt.is_cuda:
+        raise RuntimeError("gemm_sm100 runs on a CUDA device only; there is no CPU path")
+    if a.dtype != torch.bfloat16 or bt.dtype != torch.bfloat16 or c.dtype != torch.bfloat16:
         raise ValueError("gemm_sm100: a, b and c must be bfloat16")
     K, n_out = int(a.shape[-1]), int(b.shape[0])
-    if b.dim() != 2 or int(b.shape[1]) != K or int(c.shape[-1]) != n_out or a.shape[:-1] != c.shape[:-1]:
-        raise ValueError(f"gemm_sm100: shapes a{tuple(a.shape)} b{tuple(b.shape)} c{tuple(c.shape)} do not match")
-    if a.stride(-1) != 1 or b.stride(-1) != 1 or c.stride(-1) != 1:
+    if (not packed and b.dim() != 2) or int(b.shape[1]) != K or int(c.shape[-1]) != n_out or a.shape[:-1] != c.shape[:-1]:
+        raise ValueError(f"gemm_sm100: shapes a{tuple(a.shape)} b{tuple(b.shape)} c{tuple(c.shape)} do not match"
+                         + (" (a packed weight pads K to a multiple of 64: pad the activations too)" if packed else ""))
+    if a.stride(-1) != 1 or (not packed and b.stride(-1) != 1) or c.stride(-1) != 1:
         raise ValueError("gemm_sm100: K (a, b) and N (c) must be contiguous")
     a2, c2 = a.view(-1, K), c.view(-1, n_out)          # raises if the rows are not equally spaced
     M = int(a2.shape[0])
@@ -67,9 +95,14 @@ def gemm_sm100(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, split_k: in
     base = (ws.data_ptr() + 255) // 256 * 256
     stream = torch.cuda.current_stream(a.device).cuda_stream
     with torch.cuda.device(a.device):
-        _check(N.lib().mk_gemm_bf16(a2.data_ptr(), b.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0), b.stride(0),
-                                    c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
-                                    int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16")
+        if packed:
+            _check(N.lib().mk_gemm_bf16_packed(a2.data_ptr(), bt.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0),
+                                               c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
+                                               int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16_packed")
+        else:
+            _check(N.lib().mk_gemm_bf16(a2.data_ptr(), b.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0), b.stride(0),
+                                        c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
+                                        int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16")
         if check_status:
             st = (C.c_int32 * 4)()
             _check(N.lib().mk_gemm_bf16_status(C.c_void_p(base), st), "mk_gemm_bf16_status")
@@ -115,4 +148,4 @@ class GemmSm100Op(Op):
                                   "not as an op of the decode megakernel; use GemmOp for up to 32 rows per pass")
 
 
-__all__ = ["GemmSm100Op", "gemm_sm100", "gemm_workspace", "TILE_M", "TILE_N", "TILE_K"]
+__all__ = ["GemmSm100Op", "gemm_sm100", "gemm_workspace", "gemm_pack_weight", "PackedWeight", "TILE_M", "TILE_N", "TILE_K"]
