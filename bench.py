@@ -102,6 +102,10 @@ def parse_args():
                          "replicas; default: replicas for llama1b (it fits one GPU), tp for qwen3-8b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--stage-trace", action="store_true",
+                    help="trace one launch of the workload on the device and print the per-op table (analysis only)")
+    ap.add_argument("--only", default="", choices=["", "cfg0", "cfg1", "cfg2", "gemm_sm100"],
+                    help="run one single-GPU sub-record alone and print it (for profiling that kernel)")
     ap.add_argument("--no-sub", action="store_true", help="skip the cfg0 / cfg1 / cfg2 / cfg4 sub-records")
     ap.add_argument("--sub-steps", type=int, default=30, help="launches per timed block of a sub-record")
     args = ap.parse_args()
@@ -687,9 +691,33 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.only:
+        fn = {"cfg0": record_cfg0, "cfg1": record_cfg1, "cfg2": record_cfg2, "gemm_sm100": record_gemm_sm100}[args.only]
+        if rank == 0:
+            print(json.dumps({"only": args.only, args.only: fn(args, dev, measured_peak()[0])}), flush=True)
+        if use_dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     w = build_workload(args, dev, rank, world, use_dist, gen=not args.no_e2e)
     mk, cfg, tp, B, bf = w.mk, w.cfg, w.tp, args.batch, torch.bfloat16
 
+    if args.stage_trace:
+        # per-op timeline of ONE traced launch (tracing costs a few stores per page: the untraced time is
+        # printed beside it); rank 0 only
+        for _ in range(5):
+            mk.run()
+        ms_plain, _, _ = time_launches(lambda: mk.run(sync=False, validate=False), 50, 5, dev, False, min_seconds=0.05)
+        mk.enable_trace(4096)
+        mk.run()
+        rows = mk.stage_table()
+        if rank == 0:
+            print(json.dumps({"stage_trace": {"untraced_us_per_step": ms_plain * 1e3, "layers": args.layers,
+                                              "vocab": args.vocab, "ops": rows}}), flush=True)
+        if use_dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

@@ -456,6 +456,56 @@ class Megakernel:
         with open(path, "w") as fh:
             json.dump({"traceEvents": events}, fh)
 
+    def stage_table(self) -> list:
+        """Where the last traced launch spent its time, op by op (microseconds from the first record).
+
+        One dict per native op: ``begin`` = first unit started on any CTA, ``end`` = last unit
+        signalled, ``gap`` = begin minus the latest end of any earlier op (negative when ops overlap),
+        ``poll`` / ``stage`` = median over CTAs of the op-entry event's wait for the producers and of
+        the activation staging, ``page`` = median time a consumer warp held one page, ``units``.
+        """
+        tr = self.read_trace()
+        instr_op = self.program.instrs["op"]
+        n = len(self.native_ops)
+        t0 = min((int(a["t"][0]) for a in tr.values() if len(a)), default=0)
+        begin, end = np.full(n, np.iinfo(np.int64).max), np.zeros(n, dtype=np.int64)
+        poll = [[] for _ in range(n)]
+        stage = [[] for _ in range(n)]
+        page = [[] for _ in range(n)]
+        for (cta, warp), arr in tr.items():
+            if warp == 0:
+                continue
+            ev_begin, ev_deps, ready, cur = {}, {}, 0, None
+            for r in arr:
+                code, arg, t = int(r["code"]), int(r["arg"]), int(r["t"]) - t0
+                if code == 7:
+                    ev_begin[arg] = t
+                elif code == 8:
+                    ev_deps[arg] = t
+                    if arg in ev_begin:
+                        poll[arg].append(t - ev_begin[arg])
+                elif code == 9 and arg in ev_deps:
+                    stage[arg].append(t - ev_deps[arg])
+                elif code == 5:
+                    cur = int(instr_op[arg])
+                    begin[cur] = min(begin[cur], t)
+                elif code == 3:
+                    ready = t
+                elif code == 4 and cur is not None:
+                    page[cur].append(t - ready)
+                elif code == 6:
+                    o = int(instr_op[arg])
+                    end[o] = max(end[o], t)
+        med = lambda v: float(np.median(v)) / 1e3 if v else None          # noqa: E731
+        rows, latest = [], 0
+        for o, nop in enumerate(self.native_ops):
+            b = int(begin[o]) if begin[o] != np.iinfo(np.int64).max else 0
+            rows.append({"op": o, "name": nop.name, "units": int(nop.n_units), "begin": b / 1e3, "end": int(end[o]) / 1e3,
+                         "span": (int(end[o]) - b) / 1e3, "gap": (b - latest) / 1e3, "poll": med(poll[o]),
+                         "stage": med(stage[o]), "page": med(page[o])})
+            latest = max(latest, int(end[o]))
+        return rows
+
     def bench_spec(self, setup_fn=None, keep_alive=None) -> dict:
         """A launch closure plus byte accounting for benchmark harnesses."""
         self.compile()

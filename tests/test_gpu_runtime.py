@@ -79,6 +79,10 @@ def test_trace_records_and_chrome_export(tmp_path):
     events = json.loads(path.read_text())["traceEvents"]
     assert events and all(e["ph"] == "X" and e["dur"] >= 0 for e in events)
     assert {e["name"].split()[0] for e in events} >= {"load", "page", "unit"}
+    # the per-op table of the same launch: one op, all of its units, a positive span inside the launch
+    (row,) = mk.stage_table()
+    assert row["name"] == "MatvecSm100Op" and row["units"] == 64 and 0 < row["span"] < 1000
+    assert row["begin"] >= 0 and row["end"] == pytest.approx(row["begin"] + row["span"]) and row["page"] > 0
     mk.disable_trace()
     mk.run()
     assert torch.equal(plain, y)
