@@ -58,11 +58,13 @@ class FinalAddRmsTop1LmHeadSm100Op(Op):
     def lower(cls, sop, ctx):
         t = sop.tensor_refs
         has_res = "residual_in" in t and t["residual_in"] is not None
-        return [lower_matvec(cls.__name__, ctx, w0=cls._weight(sop), x=t["x"], out=t["top_keys"],
-                             out_strides=(0, 0, 0), pro=N.PRO_ADD_RMS if has_res else N.PRO_RMS,
-                             norm_weight=t["norm_weight"], residual_in=t.get("residual_in"), epi=N.EPI_TOP1,
-                             eps=float(sop.static_dims.get("eps", 1e-5)), kind="lm_head_top1",
-                             index_offset=int(sop.static_dims.get("index_offset", 0)))]
+        nop = lower_matvec(cls.__name__, ctx, w0=cls._weight(sop), x=t["x"], out=t["top_keys"],
+                           out_strides=(0, 0, 0), pro=N.PRO_ADD_RMS if has_res else N.PRO_RMS,
+                           norm_weight=t["norm_weight"], residual_in=t.get("residual_in"), epi=N.EPI_TOP1,
+                           eps=float(sop.static_dims.get("eps", 1e-5)), kind="lm_head_top1",
+                           index_offset=int(sop.static_dims.get("index_offset", 0)))
+        nop.zero_on_reset = [t["top_keys"]]      # the finalise op clears them; an aborted launch may not get there
+        return [nop]
 
 
 class FinalAddRmsTop1LmHeadNvfp4Sm100Op(FinalAddRmsTop1LmHeadSm100Op):

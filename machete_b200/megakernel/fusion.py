@@ -128,6 +128,7 @@ def _fuse_attention(split_sop: ScheduledOp, combine_sop: ScheduledOp, ctx: Lower
         split.s[k] = comb.s[k]
     split.writes = list(split.writes) + list(comb.writes)
     split.keep = list(split.keep) + list(comb.keep) + [arrive]
+    split.zero_on_reset = [arrive]
     # consumers wait for the whole op (every unit signals; a group's last unit signals after its combine)
     split.n_groups, split.unit_group = 1, None
     return split

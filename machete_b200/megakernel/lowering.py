@@ -91,6 +91,8 @@ class NativeOp:
     kind: str = ""         # free-form tag used by peephole rules and tests
     # an op that follows the device-resident cache position: first position its tensors do not hold
     pos_limit: Optional[int] = None
+    # scratch that must be zero when a launch starts; the kernel leaves it zero unless a launch aborted
+    zero_on_reset: list = field(default_factory=list)
 
     def record(self, act_key: int) -> np.void:
         rec = np.zeros((), dtype=N.OP_DTYPE)

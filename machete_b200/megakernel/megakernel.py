@@ -351,6 +351,11 @@ class Megakernel:
         st = self.status()
         if st[0] != 0:
             N.lib().mk_reset(self._handle, None)
+            # scratch the kernel keeps at zero between launches (top-1 keys, attention arrival counters)
+            # may hold values of the aborted launch
+            for nop in self.native_ops:
+                for t in nop.zero_on_reset:
+                    t.zero_()
             torch.cuda.synchronize(self._dev)
             raise RuntimeError(
                 f"megakernel aborted: {N.STATUS_NAMES.get(int(st[0]), st[0])} "
