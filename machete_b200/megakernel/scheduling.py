@@ -31,6 +31,7 @@ import numpy as np
 
 from .. import _native as N
 from .lowering import NativeOp, Region
+from .instruction_format import BarrierFormula, TileInstruction  # noqa: F401  (the reference exports them here)
 from .ops import tensor_meta_overlaps
 
 INSTRUCTION_WORDS = 8
