@@ -448,13 +448,16 @@ int mk_flash_decode_noalloc_status(int32_t out[16]);
  *   split_k: CTAs that share one output tile's K range, at most 8 (0 = chosen
  *     so that the grid fills the device).  They form one thread-block cluster
  *     and add their fp32 partial tiles through distributed shared memory.
+ *   activation: applied to the fp32 sum before the bf16 store, 0 = none, 1 = relu,
+ *     2 = silu (the reference op's `activation=` keyword).
  *     timeout_ms bounds every device-side wait (0 = 1000).
  * Returns 0 or a negative code (mk_gemm_last_error); a device-side time-out
  * shows in mk_gemm_bf16_status (out[0] != 0: 1 stage-free, 2 stage-full,
  * 3 accumulator wait; [1] CTA, [2] role, [3] step), which synchronises. */
 uint64_t mk_gemm_bf16_workspace_bytes(int M, int N, int K);
 int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                 void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream);
+                 void* workspace, uint64_t workspace_bytes, int split_k, int activation, int timeout_ms,
+                 void* cuda_stream);
 /* The same product with the weight stored K-tile-major: b_packed[K/64][N][64]
  * (tile kt holds columns kt*64 .. kt*64+63 of every row; K a multiple of 64,
  * zero-padded by the packer).  One 128-row x 64-column box is then ONE
@@ -463,7 +466,8 @@ int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
  * re-layout of inference weights, like the reference's per-KV-head interleaved
  * QKV weight (src/machete/kernels/llama1b/sm120.py:4330-4345). */
 int mk_gemm_bf16_packed(const void* a, const void* b_packed, void* c, int M, int N, int K, int64_t lda, int64_t ldc,
-                        void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream);
+                        void* workspace, uint64_t workspace_bytes, int split_k, int activation, int timeout_ms,
+                        void* cuda_stream);
 int mk_gemm_bf16_status(const void* workspace, int32_t out[4]);
 const char* mk_gemm_last_error(void);
 

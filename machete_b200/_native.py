@@ -191,9 +191,9 @@ def _declare(h: C.CDLL) -> None:
     i64 = C.c_int64
     h.mk_gemm_bf16_workspace_bytes.argtypes = [i32, i32, i32]
     h.mk_gemm_bf16_workspace_bytes.restype = u64
-    h.mk_gemm_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, u64, i32, i32, vp]
+    h.mk_gemm_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, u64, i32, i32, i32, vp]
     h.mk_gemm_bf16.restype = C.c_int
-    h.mk_gemm_bf16_packed.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, u64, i32, i32, vp]
+    h.mk_gemm_bf16_packed.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, u64, i32, i32, i32, vp]
     h.mk_gemm_bf16_packed.restype = C.c_int
     h.mk_gemm_bf16_status.argtypes = [vp, C.POINTER(i32)]
     h.mk_gemm_bf16_status.restype = C.c_int

@@ -57,6 +57,7 @@ struct Params {
   int split_k, k_tiles;
   int stages;
   uint32_t ring_bytes;   // stages x stage bytes, or the fp32 partial tile if that is larger (split-K)
+  int activation;        // applied to the fp32 sum before the bf16 store: 0 none, 1 relu, 2 silu
   int b_packed;          // the weight is stored K-tile-major: [K/64][N][64] (one box = 16 KB contiguous)
   int m_box;             // rows of one activation box (what one TMA copy delivers, whatever this CTA uses of it)
   uint64_t timeout_ns;
@@ -153,6 +154,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 // kind::f16 instruction descriptor: fp32 accumulator, bf16 x bf16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return fmaxf(v, 0.f);
+  if (act == 2) return v / (1.f + __expf(-v));
+  return v;
 }
 
 __device__ __forceinline__ void give_up(const Params& p, Shared* sh, int code, int role, int aux) {
@@ -290,7 +297,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int m = m0 + c + j;
-          if (ready && n_ok && m < p.M) p.c[(int64_t)m * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          if (ready && n_ok && m < p.M)
+            p.c[(int64_t)m * p.ldc + n] = __float2bfloat16_rn(apply_act(__uint_as_float(r[j]), p.activation));
         }
       } else {
 #pragma unroll
@@ -323,7 +331,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const float v[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (n + e < p.N) dst[e] = __float2bfloat16_rn(v[e]);
+          if (n + e < p.N) dst[e] = __float2bfloat16_rn(apply_act(v[e], p.activation));
       }
     }
     cluster_sync_all();        // nobody leaves while a peer may still read its partial tile
@@ -424,8 +432,9 @@ uint64_t mk_gemm_bf16_workspace_bytes(int M, int N, int K) {
 namespace mkg {
 static int gemm_launch(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                        void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream,
-                       bool b_packed) {
+                       bool b_packed, int activation) {
   if (!a || !b || !c || !workspace) return fail(-1, "mk_gemm_bf16: null pointer");
+  if (activation < 0 || activation > 2) return fail(-2, "mk_gemm_bf16: activation must be 0 (none), 1 (relu) or 2 (silu)");
   if (M < 1 || N < 1 || K < 1) return fail(-2, "mk_gemm_bf16: M, N, K must be positive (got %d, %d, %d)", M, N, K);
   if (K % 8 || lda % 8 || ldb % 8 || ((uint64_t)a & 15) || ((uint64_t)b & 15))
     return fail(-2, "mk_gemm_bf16: K and the row strides of A and B must be multiples of 8 elements, bases 16-byte aligned");
@@ -473,6 +482,7 @@ static int gemm_launch(const void* a, const void* b, void* c, int M, int N, int 
   p.M = M, p.N = N, p.K = K;
   p.split_k = split_k, p.k_tiles = k_tiles, p.stages = stages, p.m_box = m_box, p.b_packed = b_packed ? 1 : 0;
   p.ring_bytes = ring_bytes;
+  p.activation = activation;
   p.timeout_ns = (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
   const dim3 grid((N + kTileN - 1) / kTileN, split_k, (M + kMaxM - 1) / kMaxM);
   cudaLaunchConfig_t cfg = {};
@@ -497,16 +507,18 @@ static int gemm_launch(const void* a, const void* b, void* c, int M, int N, int 
 extern "C" {
 
 int mk_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                 void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream) {
+                 void* workspace, uint64_t workspace_bytes, int split_k, int activation, int timeout_ms,
+                 void* cuda_stream) {
   return mkg::gemm_launch(a, b, c, M, N, K, lda, ldb, ldc, workspace, workspace_bytes, split_k, timeout_ms, cuda_stream,
-                          false);
+                          false, activation);
 }
 
 int mk_gemm_bf16_packed(const void* a, const void* b_packed, void* c, int M, int N, int K, int64_t lda, int64_t ldc,
-                        void* workspace, uint64_t workspace_bytes, int split_k, int timeout_ms, void* cuda_stream) {
+                        void* workspace, uint64_t workspace_bytes, int split_k, int activation, int timeout_ms,
+                        void* cuda_stream) {
   if (K % 64) return mkg::fail(-2, "mk_gemm_bf16_packed: K must be a multiple of 64 (the packer pads with zeros)");
   return mkg::gemm_launch(a, b_packed, c, M, N, K, lda, K, ldc, workspace, workspace_bytes, split_k, timeout_ms,
-                          cuda_stream, true);
+                          cuda_stream, true, activation);
 }
 
 int mk_gemm_bf16_status(const void* workspace, int32_t out[4]) {

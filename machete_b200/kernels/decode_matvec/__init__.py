@@ -3,6 +3,7 @@
 from .nvfp4 import (FinalRmsLmHeadNvfp4Sm120Op, MatvecNvfp4Sm120Op, MatvecResidualNvfp4Sm120Op,
                     RmsGateUpSiluNvfp4Sm120Op, RmsKMatvecRopeCacheNvfp4Sm120Op, RmsMatvecNvfp4Sm120Op,
                     RmsQMatvecRopeNvfp4Sm120Op, RmsVMatvecCacheNvfp4Sm120Op)
+from .norm import RmsAddNormSm100Op, RmsAddNormSm120Op
 from .sm100 import DecodeLayerSchedule as DecodeLayerScheduleSm100
 from .sm100 import (FinalRmsLmHeadSm100Op, MatvecResidualSm100Op, MatvecSm100Op, ResidualAddSm100Op,
                     RmsGateUpSiluSm100Op, RmsKMatvecRopeCacheSm100Op, RmsQMatvecRopeSm100Op,

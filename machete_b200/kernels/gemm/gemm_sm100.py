@@ -67,7 +67,10 @@ def gemm_pack_weight(b: torch.Tensor) -> PackedWeight:
     return PackedWeight(src.view(n, kp // TILE_K, TILE_K).permute(1, 0, 2).contiguous(), n, kp)
 
 
-def gemm_sm100(a: torch.Tensor, b, c: torch.Tensor, *, split_k: int = 0, timeout_ms: int = 1000,
+ACTIVATIONS = {None: 0, "relu": 1, "silu": 2}
+
+
+def gemm_sm100(a: torch.Tensor, b, c: torch.Tensor, *, activation=None, split_k: int = 0, timeout_ms: int = 1000,
                workspace: Optional[torch.Tensor] = None, check_status: bool = False) -> torch.Tensor:
     """``c[..., N] = a[..., K] @ b[N, K]^T`` (bf16, fp32 accumulate) on the current stream.
 
@@ -77,6 +80,8 @@ def gemm_sm100(a: torch.Tensor, b, c: torch.Tensor, *, split_k: int = 0, timeout
     """
     if not (a.is_cuda and c.is_cuda):
         raise RuntimeError("gemm_sm100 runs on a CUDA device only; there is no CPU path")
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"Unknown activation: {activation}")
     packed = isinstance(b, PackedWeight)
     bt = b.data if packed else b
     if not bt.is_cuda:
@@ -98,11 +103,12 @@ def gemm_sm100(a: torch.Tensor, b, c: torch.Tensor, *, split_k: int = 0, timeout
         if packed:
             _check(N.lib().mk_gemm_bf16_packed(a2.data_ptr(), bt.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0),
                                                c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
-                                               int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16_packed")
+                                               ACTIVATIONS[activation], int(timeout_ms), C.c_void_p(stream)),
+                   "mk_gemm_bf16_packed")
         else:
             _check(N.lib().mk_gemm_bf16(a2.data_ptr(), b.data_ptr(), c2.data_ptr(), M, n_out, K, a2.stride(0), b.stride(0),
                                         c2.stride(0), base, ws.numel() - (base - ws.data_ptr()), int(split_k),
-                                        int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16")
+                                        ACTIVATIONS[activation], int(timeout_ms), C.c_void_p(stream)), "mk_gemm_bf16")
         if check_status:
             st = (C.c_int32 * 4)()
             _check(N.lib().mk_gemm_bf16_status(C.c_void_p(base), st), "mk_gemm_bf16_status")
@@ -124,23 +130,36 @@ class GemmSm100Op(Op):
     tma_stores = {"c"}
 
     @classmethod
-    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, **tensors):
+    def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, activation=None, **tensors):
+        """``tile_sizes`` (``S`` in {64, 128, 256}, ``N``, ``K``) shape the scheduled-op record as in the
+        reference; the kernel's own tile is fixed (128 weight rows x up to 256 activation rows x 64)."""
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"Unknown activation: {activation}")
         ts = dict(tile_sizes or {})
         ts.setdefault("B", 1)
         ts.setdefault("S", TILE_M)
         ts.setdefault("N", TILE_N)
         tile_k = ts.pop("K", TILE_K)
-        if ts["N"] != TILE_N or ts["S"] > TILE_M or tile_k != TILE_K:
-            raise ValueError(f"GemmSm100Op: this build's tile is S<={TILE_M}, N={TILE_N}, K={TILE_K}")
+        if ts["S"] not in (64, 128, 256):
+            raise ValueError(f"GemmSm100Op: tile size S must be 64, 128 or 256, got {ts['S']}")
         op = cls._schedule_single(tile_sizes=ts, **tensors)
         op.static_dims["tile_K"] = tile_k
         op.static_dims["page_size"] = page_size
+        if activation is not None:
+            op.static_dims["activation"] = ACTIVATIONS[activation]
+        op.params["activation"] = activation
         return [op]
+
+    @classmethod
+    def kernel_config(cls, ops):
+        from ...megakernel import MegakernelConfig
+
+        return MegakernelConfig(page_size=max(op.static_dims.get("page_size", DEFAULT_PAGE_SIZE) for op in ops))
 
     @classmethod
     def launch(cls, sop, **kw) -> torch.Tensor:
         t = sop.tensor_refs
-        return gemm_sm100(t["a"], t["b"], t["c"], **kw)
+        return gemm_sm100(t["a"], t["b"], t["c"], activation=sop.params.get("activation"), **kw)
 
     @classmethod
     def lower(cls, sop, ctx):

@@ -46,6 +46,13 @@ def test_fused_add_and_gated_rmsnorm(cases):
     r2 = r.clone()
     Megakernel(RMSNormOp.schedule(x=x, weight=w, y=y, residual_in=r2, residual_out=r2, eps=c["eps"])).run()
     assert torch.equal(r2.cpu(), c["residual_out"])
+    # the decode helper with the same contract (x, residual_in, norm_weight -> residual_out, y)
+    from machete_b200.kernels.decode_matvec import RmsAddNormSm120Op
+
+    y2, ro2 = torch.empty_like(x), torch.empty_like(x)
+    Megakernel(RmsAddNormSm120Op.schedule(x=x, residual_in=r, norm_weight=w, residual_out=ro2, y=y2, eps=c["eps"])).run()
+    assert torch.equal(ro2.cpu(), c["residual_out"])
+    assert_parity(y2, c["y"], "RmsAddNormSm120Op")
     c = next(x for x in cases if x["op"] == "rmsnorm_gated")
     y = torch.empty_like(x)
     Megakernel(RMSNormOp.schedule(x=c["x"].cuda(), weight=c["weight"].cuda(), gate=c["gate"].cuda(), y=y,

@@ -75,6 +75,16 @@ def test_op_mirror_schedules_and_launches():
     assert sop.tile_counts == (2, 1, 3) and sop.static_dims["tile_K"] == 64
     GemmSm100Op.launch(sop, check_status=True)
     _check(a, b, c)
+    # the reference's keywords: tile sizes shape the record, the activation is fused into the epilogue
+    (s2,) = GemmSm100Op.schedule(a=a, b=b, c=c, tile_sizes={"S": 64, "N": 64, "K": 64}, activation="silu")
+    assert s2.tile_counts == (2, 1, 6) and s2.static_dims["activation"] == 2
+    GemmSm100Op.launch(s2, check_status=True)
+    want = torch.nn.functional.silu(_ref(a, b))
+    assert float((c.double().view(-1, 384) - want).abs().max()) <= float(want.abs().max()) * 2.0 ** -7
+    gemm_sm100(a, b, c, activation="relu", split_k=2, check_status=True)
+    assert float((c.double().view(-1, 384) - _ref(a, b).clamp_min(0)).abs().max()) <= float(want.abs().max()) * 2.0 ** -7
+    with pytest.raises(ValueError):
+        GemmSm100Op.schedule(a=a, b=b, c=c, activation="gelu")
     with pytest.raises(NotImplementedError):
         GemmSm100Op.lower(sop, None)
 
