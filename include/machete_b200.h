@@ -471,6 +471,29 @@ int mk_gemm_bf16_packed(const void* a, const void* b_packed, void* c, int M, int
 int mk_gemm_bf16_status(const void* workspace, int32_t out[4]);
 const char* mk_gemm_last_error(void);
 
+/* ---- prefill attention on tcgen05 tensor cores -----------------------------------
+ * O = softmax(scale * Q K^T) V for M query rows per head against N cached tokens,
+ * bf16, fp32 softmax and accumulation in tensor memory; grouped-query heads
+ * (head h reads KV head h / (H / Hkv)); causal = the queries are the LAST M of
+ * the N tokens (row m sees tokens 0 .. N - M + m).  Replaces the reference's
+ * FlashAttentionSm100Op (src/machete/kernels/attention/sm_100.py:88,
+ * attention/__init__.py:16-130) as a launch of its own: it lets a prompt fill
+ * the KV cache that the decode kernel then reads.
+ *   q [B][H][M][D], k / v [B][Hkv][N][D], o [B][H][M][D], each with element
+ *   strides {batch, head, row} (so both the reference's (B,H,M,D) tensors and
+ *   (B,N,Hkv,D) cache views fit), D = 64 or 128 contiguous, every stride a
+ *   multiple of 8 elements, bases 16-byte aligned.  lse: [B][H][M] fp32 or NULL.
+ *   workspace: 256 bytes of device memory, 256-byte aligned, ZERO before first
+ *   use (the device status block; it stays zero unless a wait ran out).
+ * Returns 0 or a negative code (mk_flash_prefill_last_error); a device-side
+ * time-out shows in mk_flash_prefill_status (out[0] != 0), which synchronises. */
+int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Hkv, int M,
+                          int N, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                          const int64_t v_strides[3], const int64_t o_strides[3], float scale, int causal,
+                          void* workspace, uint64_t workspace_bytes, int timeout_ms, void* cuda_stream);
+int mk_flash_prefill_status(const void* workspace, int32_t out[4]);
+const char* mk_flash_prefill_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -117,6 +117,7 @@ EXPORTS = [
     "mk_standalone_workspace_bytes", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode",
     "mk_flash_decode_noalloc", "mk_flash_decode_noalloc_status",
     "mk_gemm_bf16_workspace_bytes", "mk_gemm_bf16", "mk_gemm_bf16_packed", "mk_gemm_bf16_status", "mk_gemm_last_error",
+    "mk_flash_prefill_bf16", "mk_flash_prefill_status", "mk_flash_prefill_last_error",
 ]
 
 _lib = None
@@ -198,6 +199,13 @@ def _declare(h: C.CDLL) -> None:
     h.mk_gemm_bf16_status.argtypes = [vp, C.POINTER(i32)]
     h.mk_gemm_bf16_status.restype = C.c_int
     h.mk_gemm_last_error.restype = C.c_char_p
+    p64 = C.POINTER(C.c_int64)
+    h.mk_flash_prefill_bf16.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, p64, p64, p64, p64, f32, i32,
+                                        vp, u64, i32, vp]
+    h.mk_flash_prefill_bf16.restype = C.c_int
+    h.mk_flash_prefill_status.argtypes = [vp, C.POINTER(i32)]
+    h.mk_flash_prefill_status.restype = C.c_int
+    h.mk_flash_prefill_last_error.restype = C.c_char_p
     for name in ("mk_device_info", "mk_create", "mk_run", "mk_status", "mk_workspace_status", "mk_reset", "mk_update_op",
                  "mk_launch_count", "mk_set_launch_count",
                  "mk_read_counters", "mk_destroy", "mk_matvec_bf16", "mk_matvec_nvfp4", "mk_flash_decode"):

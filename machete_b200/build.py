@@ -31,7 +31,7 @@ NVCC_FLAGS = [
 
 def _sources() -> list[Path]:
     """The host side plus one translation unit per group of kernel variants."""
-    return [CSRC / "megakernel.cu", CSRC / "gemm_sm100.cu"] + sorted(CSRC.glob("variants_*.cu"))
+    return [CSRC / "megakernel.cu", CSRC / "gemm_sm100.cu", CSRC / "attn_prefill_sm100.cu"] + sorted(CSRC.glob("variants_*.cu"))
 
 
 def _deps() -> list[Path]:

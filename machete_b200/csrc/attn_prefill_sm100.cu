@@ -1,0 +1,502 @@
+// Prefill attention on the 5th-generation tensor cores: O = softmax(scale · Q Kᵀ) V for a block of
+// query rows against a KV cache, bf16, causal or not, grouped-query heads.
+//
+// The decode megakernel's own attention op streams K/V once per KV head for a handful of query rows
+// (mma.sync).  A prompt has hundreds of query rows per head, which is tensor-core work: this kernel
+// takes the place of the reference's FlashAttentionSm100Op (src/machete/kernels/attention/
+// sm_100.py:88-…, dispatch attention/__init__.py:16-130) as a launch of its own, so that a prompt can
+// fill the KV cache the decode kernel then reads.
+//
+// One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 128 tokens:
+//
+//   warp 0     TMA: Q once, then K and V tiles (K double-buffered) as 128-row x 64-column boxes,
+//              128-byte swizzle;
+//   warp 1     tcgen05.mma issuer: S = Q Kᵀ (accumulator: tensor-memory columns [0, 128)), later
+//              O += P V (columns [128, 128 + D)); V is the N operand in MN-major form (its head
+//              dimension is contiguous in shared memory exactly as the cache stores it);
+//   warps 2-5  one thread per query row (= tensor-memory lane): tcgen05.ld of the row of S, scale,
+//              mask, running maximum and sum kept in registers (no shuffles: a thread owns its row),
+//              P written to shared memory as bf16 in the K-major operand layout, O rescaled in
+//              tensor memory when a maximum moved (tcgen05.ld / st), normalised bf16 store at the end.
+//
+// Every wait is bounded; on expiry the CTA records a status, raises its abort flag, all roles fall
+// through to the common exit and tensor memory is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/machete_b200.h"
+#include "prims.cuh"
+
+namespace mkp {
+
+constexpr int kThreads = 192;
+constexpr int kBM = 128;   // query rows per CTA
+constexpr int kBN = 128;   // tokens per KV tile
+constexpr uint32_t kBox = 128 * 64 * 2;   // one 128-row x 64-column bf16 box
+
+struct Params {
+  __nv_bfloat16* o;
+  float* lse;            // [B, H, M] or null
+  int32_t* status;
+  int64_t o_sb, o_sh, o_sm;
+  int B, H, Hkv, M, N, D;
+  int causal;
+  float scale_log2;      // scale * log2(e)
+  uint64_t timeout_ns;
+};
+
+enum { PF_ST_TIMEOUT_EMPTY = 1, PF_ST_TIMEOUT_FULL = 2, PF_ST_TIMEOUT_S = 3, PF_ST_TIMEOUT_P = 4, PF_ST_TIMEOUT_O = 5 };
+
+struct Shared {
+  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_ready, p_ready, pv_done;
+  uint32_t tmem_base;
+  int32_t abort_flag;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major bf16 tile of 128-byte swizzled rows (8-row groups 1024 bytes apart): Q, K and P.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// MN-major bf16 tile: V as stored, [token][64 head-dim values = 128 bytes], 128-byte swizzle.  Along K (tokens)
+// the 8-row groups are 1024 bytes apart (stride offset); along N (head dim) the next 64 values are the next
+// box, `next_box` bytes further (leading offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t next_box) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((next_box >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, fp32 accumulate, bf16 operands, M = 128, N = n; b_mn = the N operand is MN-major.
+__device__ __forceinline__ uint32_t idesc_bf16(int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void give_up(const Params& p, Shared* sh, int code, int aux) {
+  if (atomicCAS(&p.status[0], 0, code) == 0) {
+    p.status[1] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    p.status[2] = threadIdx.x >> 5;
+    p.status[3] = aux;
+  }
+  atomicExch(&sh->abort_flag, 1);
+  __threadfence();
+}
+__device__ __forceinline__ bool wait_bar(const Params& p, Shared* sh, uint32_t bar, uint32_t parity, int code, int aux) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mk::mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 255u) {
+      if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) return false;
+      const uint64_t now = mk::globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > p.timeout_ns) {
+        give_up(p, sh, code, aux);
+        return false;
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const Params p) {
+  constexpr int NB = D / 64;                       // 64-column boxes per row tile
+  constexpr uint32_t kTile = NB * kBox;            // one 128 x D tile
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = mk::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  // layout: Q | K0 | K1 | V | P (two 128 x 64 boxes) | control
+  const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kTile, p_s = v_s + kTile;
+  Shared* sh = reinterpret_cast<Shared*>(smem + 4 * kTile + 2 * kBox);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.H / p.Hkv);
+  const int m0 = mt * kBM;
+  // tokens this query tile can see: all N, or (causal) up to the diagonal of its last row
+  const int n_vis = p.causal ? min(p.N, p.N - p.M + m0 + kBM) : p.N;
+  const int n_tiles = n_vis > 0 ? (n_vis + kBN - 1) / kBN : 0;
+  constexpr uint32_t kCols = 256;                  // S: [0, 128), O: [128, 128 + D)
+
+  if (threadIdx.x == 0) {
+    mk::mbar_init(mk::smem_u32(&sh->q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mk::mbar_init(mk::smem_u32(&sh->k_full[s]), 1);
+      mk::mbar_init(mk::smem_u32(&sh->k_empty[s]), 1);
+    }
+    mk::mbar_init(mk::smem_u32(&sh->v_full), 1);
+    mk::mbar_init(mk::smem_u32(&sh->v_empty), 1);
+    mk::mbar_init(mk::smem_u32(&sh->s_ready), 1);
+    mk::mbar_init(mk::smem_u32(&sh->p_ready), 128);
+    mk::mbar_init(mk::smem_u32(&sh->pv_done), 1);
+    sh->abort_flag = 0;
+    mk::fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(mk::smem_u32(&sh->tmem_base), kCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t qb = mk::smem_u32(&sh->q_full);
+      mk::mbar_arrive_expect_tx(qb, kTile);
+      for (int x = 0; x < NB; ++x) tma_load_4d(q_s + x * kBox, &map_q, x * 64, m0, h, b, qb);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t it = (uint32_t)(j >> 1);
+        if (!wait_bar(p, sh, mk::smem_u32(&sh->k_empty[s]), (it & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
+        const uint32_t kb = mk::smem_u32(&sh->k_full[s]);
+        mk::mbar_arrive_expect_tx(kb, kTile);
+        for (int x = 0; x < NB; ++x) tma_load_4d(k_s + s * kTile + x * kBox, &map_k, x * 64, j * kBN, kvh, b, kb);
+        if (!wait_bar(p, sh, mk::smem_u32(&sh->v_empty), ((uint32_t)j & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
+        const uint32_t vb = mk::smem_u32(&sh->v_full);
+        mk::mbar_arrive_expect_tx(vb, kTile);
+        for (int x = 0; x < NB; ++x) tma_load_4d(v_s + x * kBox, &map_v, x * 64, j * kBN, kvh, b, vb);
+      }
+      if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) {
+        // shared memory must outlive the copies in flight: a bounded wait for whatever was issued last
+        const uint64_t t0 = mk::globaltimer_ns();
+        while (mk::globaltimer_ns() - t0 < 20000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_s = idesc_bf16(kBN, false), id_o = idesc_bf16(D, true);
+      bool ok = wait_bar(p, sh, mk::smem_u32(&sh->q_full), 0, PF_ST_TIMEOUT_FULL, -1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        ok = wait_bar(p, sh, mk::smem_u32(&sh->k_full[s]), (uint32_t)(j >> 1) & 1u, PF_ST_TIMEOUT_FULL, j);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q Kᵀ: D / 16 steps; step k sits in box k / 4, 32 bytes per step inside the swizzle atom
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u;
+          tc_mma(tmem, desc_kmajor(q_s + off), desc_kmajor(k_s + s * kTile + off), id_s, k > 0 ? 1u : 0u);
+        }
+        tc_commit(mk::smem_u32(&sh->s_ready));
+        tc_commit(mk::smem_u32(&sh->k_empty[s]));
+        // O += P V once the row threads have written P (and rescaled O)
+        ok = wait_bar(p, sh, mk::smem_u32(&sh->p_ready), (uint32_t)j & 1u, PF_ST_TIMEOUT_P, j) &&
+             wait_bar(p, sh, mk::smem_u32(&sh->v_full), (uint32_t)j & 1u, PF_ST_TIMEOUT_FULL, j);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kBN / 16; ++k) {
+          // P: K-major, token step k in box k / 4; V: MN-major, 16 tokens = 16 rows of 128 bytes
+          const uint64_t dp = desc_kmajor(p_s + (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u);
+          const uint64_t dv = desc_mnmajor(v_s + (uint32_t)k * 2048u, kBox);
+          tc_mma(tmem + 128u, dp, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(mk::smem_u32(&sh->pv_done));
+        tc_commit(mk::smem_u32(&sh->v_empty));
+      }
+    }
+  } else {
+    // row threads: warp w may touch tensor-memory lanes 32 * (w % 4) ..
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;                 // query row inside the tile = TMEM lane
+    const int m = m0 + row;
+    const int lim = p.causal ? (p.N - p.M + m) : (p.N - 1);   // last visible token of this row
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    float mx = -INFINITY, sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = wait_bar(p, sh, mk::smem_u32(&sh->s_ready), (uint32_t)j & 1u, PF_ST_TIMEOUT_S, j);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      // pass 1: the row's maximum over this tile
+      float tmax = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + (uint32_t)c, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int tok = j * kBN + c + i;
+          const float s = (tok <= lim && tok < p.N) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
+          tmax = fmaxf(tmax, s);
+        }
+      }
+      const float mnew = fmaxf(mx, tmax);
+      const float muse = mnew == -INFINITY ? 0.f : mnew;
+      const float alpha = exp2f(mx - muse);          // 0 when mx = -inf
+      // O may be rescaled only after the previous P V has finished with it
+      if (j > 0) {
+        ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + 128u + (uint32_t)c, r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(lane_addr + 128u + (uint32_t)c, r);
+          }
+          tmem_wait_st();
+        }
+      }
+      // pass 2: P = exp2(s - max) as bf16 into the K-major operand tile (this thread's row)
+      float tsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + (uint32_t)c, r);
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int tok = j * kBN + c + i + u;
+            const bool vis = tok <= lim && tok < p.N;
+            e[u] = vis ? exp2f(__uint_as_float(r[i + u]) * p.scale_log2 - muse) : 0.f;
+          }
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
+          // the sum uses the values the tensor cores will see
+          tsum += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+          w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c >> 3) + q4;            // 0..15 over the 128 tokens
+          const uint32_t addr = p_s + (uint32_t)(chunk >> 3) * kBox + (uint32_t)row * 128u +
+                                (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * q4]), "r"(w[4 * q4 + 1]),
+                       "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3])
+                       : "memory");
+        }
+      }
+      sum = sum * alpha + tsum;
+      mx = mnew;
+      // P (generic-proxy stores) must be visible to the tensor cores (async proxy); O's rescale is done
+      mk::fence_proxy_async();
+      tc_fence_before();
+      mk::mbar_arrive(mk::smem_u32(&sh->p_ready));
+    }
+    // epilogue: O / sum -> bf16
+    if (ok && n_tiles > 0) {
+      ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(n_tiles - 1) & 1u, PF_ST_TIMEOUT_O, n_tiles);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    tc_fence_after();
+    if (ok) {
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)m * p.o_sm;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t r[32];
+        if (n_tiles > 0) {
+          tmem_ld32(lane_addr + 128u + (uint32_t)c, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (m < p.M) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * u]) * inv,
+                                                              __uint_as_float(r[i + 2 * u + 1]) * inv);
+              w[u] = *reinterpret_cast<const uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (p.lse != nullptr && m < p.M)
+        p.lse[((int64_t)b * p.H + h) * p.M + m] = sum > 0.f ? (mx + log2f(sum)) * 0.6931471805599453f : -INFINITY;
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem, kCols);
+}
+
+static std::string g_err;
+static int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+// [batch][head][row][D] with element strides (s_b, s_h, s_r), D contiguous: dims (D, rows, heads, batch),
+// one box = 64 columns x 128 rows of one head of one batch entry.
+static int encode_rows_map(CUtensorMap* out, const void* base, int D, int rows, int heads, int batch, int64_t s_r,
+                           int64_t s_h, int64_t s_b, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(-5, "cuTensorMapEncodeTiled is not available from this driver");
+  if (((uint64_t)base & 15) || (s_r * 2) % 16 || (s_h * 2) % 16 || (s_b * 2) % 16 || s_r <= 0 || s_h <= 0 || s_b <= 0)
+    return fail(-2, "mk_flash_prefill_bf16: %s must be 16-byte aligned with positive row / head / batch strides that are "
+                    "multiples of 8 elements", what);
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)s_r * 2, (cuuint64_t)s_h * 2, (cuuint64_t)s_b * 2};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled (%s) failed with CUresult %d", what, (int)r);
+  return 0;
+}
+
+}  // namespace mkp
+
+extern "C" {
+
+const char* mk_flash_prefill_last_error(void) { return mkp::g_err.c_str(); }
+
+int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Hkv, int M,
+                          int N, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                          const int64_t v_strides[3], const int64_t o_strides[3], float scale, int causal,
+                          void* workspace, uint64_t workspace_bytes, int timeout_ms, void* cuda_stream) {
+  using namespace mkp;
+  if (!q || !k || !v || !o || !workspace || !q_strides || !k_strides || !v_strides || !o_strides)
+    return fail(-1, "mk_flash_prefill_bf16: null pointer");
+  if (B < 1 || H < 1 || Hkv < 1 || M < 1 || N < 1 || H % Hkv)
+    return fail(-2, "mk_flash_prefill_bf16: B, H, Hkv, M, N must be positive and H a multiple of Hkv");
+  if (D != 64 && D != 128) return fail(-2, "mk_flash_prefill_bf16: head dim must be 64 or 128, got %d", D);
+  if (causal && M > N) return fail(-2, "mk_flash_prefill_bf16: causal attention needs M <= N (the queries are the last M tokens)");
+  if (workspace_bytes < 256 || ((uint64_t)workspace & 255)) return fail(-2, "mk_flash_prefill_bf16: workspace of 256 aligned bytes");
+  if (((uint64_t)o & 15) || o_strides[2] % 8 || o_strides[1] % 8 || o_strides[0] % 8)
+    return fail(-2, "mk_flash_prefill_bf16: o must be 16-byte aligned with strides that are multiples of 8 elements");
+  int dev = 0, smem_optin = 0, cc = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(-1001, "cudaGetDevice failed");
+  cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
+  if (cc != 10) return fail(-6, "mk_flash_prefill_bf16 needs an sm_100 device (compute capability %d.x found)", cc);
+  CUtensorMap mq, mkk, mv;
+  int rc = encode_rows_map(&mq, q, D, M, H, B, q_strides[2], q_strides[1], q_strides[0], "q");
+  if (rc) return rc;
+  rc = encode_rows_map(&mkk, k, D, N, Hkv, B, k_strides[2], k_strides[1], k_strides[0], "k");
+  if (rc) return rc;
+  rc = encode_rows_map(&mv, v, D, N, Hkv, B, v_strides[2], v_strides[1], v_strides[0], "v");
+  if (rc) return rc;
+  const size_t tile = (size_t)(D / 64) * kBox;
+  const size_t smem = 1024 + 4 * tile + 2 * kBox + sizeof(Shared);
+  if ((int)smem > smem_optin) return fail(-4, "mk_flash_prefill_bf16: %zu bytes of shared memory needed, %d available", smem, smem_optin);
+  Params p;
+  p.o = reinterpret_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.status = reinterpret_cast<int32_t*>(workspace);
+  p.o_sb = o_strides[0], p.o_sh = o_strides[1], p.o_sm = o_strides[2];
+  p.B = B, p.H = H, p.Hkv = Hkv, p.M = M, p.N = N, p.D = D;
+  p.causal = causal ? 1 : 0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.timeout_ns = (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
+  const dim3 grid((M + kBM - 1) / kBM, H, B);
+  static bool attr64[64] = {}, attr128[64] = {};
+  cudaError_t e = cudaSuccess;
+  if (D == 64) {
+    if (dev < 64 && !attr64[dev]) {
+      e = cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      attr64[dev] = e == cudaSuccess;
+    }
+    if (e == cudaSuccess) prefill_kernel<64><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+  } else {
+    if (dev < 64 && !attr128[dev]) {
+      e = cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      attr128[dev] = e == cudaSuccess;
+    }
+    if (e == cudaSuccess) prefill_kernel<128><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(-(int)e - 1000, "mk_flash_prefill_bf16 launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+int mk_flash_prefill_status(const void* workspace, int32_t out[4]) {
+  if (!workspace || !out) return mkp::fail(-1, "mk_flash_prefill_status: null pointer");
+  if (cudaDeviceSynchronize() != cudaSuccess) return mkp::fail(-1001, "mk_flash_prefill_status: device synchronise failed");
+  if (cudaMemcpy(out, workspace, 16, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return mkp::fail(-1001, "mk_flash_prefill_status: copy failed");
+  return 0;
+}
+
+}  // extern "C"
