@@ -17,7 +17,8 @@
 //   warps 2-5  one thread per query row (= tensor-memory lane): tcgen05.ld of the row of S, scale,
 //              mask, running maximum and sum kept in registers (no shuffles: a thread owns its row),
 //              P written to shared memory as bf16 in the K-major operand layout, O rescaled in
-//              tensor memory when a maximum moved (tcgen05.ld / st), normalised bf16 store at the end.
+//              tensor memory only when a row maximum outgrew the exponent reference by 2^8
+//              (tcgen05.ld / st), normalised bf16 store at the end.
 //
 // Every wait is bounded; on expiry the CTA records a status, raises its abort flag, all roles fall
 // through to the common exit and tensor memory is freed.
@@ -279,9 +280,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tmax = fmaxf(tmax, s);
         }
       }
-      const float mnew = fmaxf(mx, tmax);
+      // mx is the exponent reference in use, not always the running maximum: it moves only when the
+      // maximum has grown by more than 2^8 since it was set, so O is rescaled rarely (P stays <= 256)
+      float alpha = 1.f;
+      float mnew = mx;
+      if (tmax > mx + 8.f) {                         // also the first visible tile (mx = -inf)
+        alpha = exp2f(mx - tmax);                    // 0 when mx = -inf
+        mnew = tmax;
+      }
       const float muse = mnew == -INFINITY ? 0.f : mnew;
-      const float alpha = exp2f(mx - muse);          // 0 when mx = -inf
       // O may be rescaled only after the previous P V has finished with it
       if (j > 0) {
         ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
