@@ -32,8 +32,9 @@ One JSON line is printed by rank 0:
               8 (µs/step, tokens/s, per-GPU algorithmic bytes, fraction);
 * ``cfg0`` / ``cfg1`` / ``cfg2`` (N = 1): one layer at KV 1024, the small-M
               GEMM sweep in bf16 and NVFP4, flash decoding at batch 8 x 32 768;
-* ``gemm_sm100`` (N = 1): the tcgen05 GEMM tile at 64 / 128 / 256 rows, with
-              cuBLAS timed beside it.
+* ``gemm_sm100`` / ``prefill_attention`` (N = 1): the tcgen05 GEMM tile at
+              64 / 128 / 256 rows and the tcgen05 prefill attention, with the
+              library kernels (cuBLAS, torch SDPA) timed beside them.
 
 ``--impl reference`` times the CPU port alone (the reference ships no
 compiled code; its own path for this step is PyTorch on the host).
@@ -104,7 +105,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--stage-trace", action="store_true",
                     help="trace one launch of the workload on the device and print the per-op table (analysis only)")
-    ap.add_argument("--only", default="", choices=["", "cfg0", "cfg1", "cfg2", "gemm_sm100"],
+    ap.add_argument("--only", default="", choices=["", "cfg0", "cfg1", "cfg2", "gemm_sm100", "prefill_attention"],
                     help="run one single-GPU sub-record alone and print it (for profiling that kernel)")
     ap.add_argument("--no-sub", action="store_true", help="skip the cfg0 / cfg1 / cfg2 / cfg4 sub-records")
     ap.add_argument("--sub-steps", type=int, default=30, help="launches per timed block of a sub-record")
@@ -604,6 +605,46 @@ def record_gemm_sm100(args, dev, peak):
     return out
 
 
+def record_prefill_attention(args, dev, peak):
+    """The tcgen05 prefill attention at the two model shapes (32 query / 8 KV heads, causal), with the library
+    kernel behind torch's scaled_dot_product_attention timed beside it.  K and V (16-34 MB) stay in L2 by
+    design: every query tile of a head re-reads them, so the bound is the tensor pipe, not HBM."""
+    from machete_b200.kernels.attention import flash_prefill
+
+    bf = torch.bfloat16
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            tflops_peak = float(json.load(fh)["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        tflops_peak = 1590.0
+    out = {"tensor_peak_tflops": tflops_peak, "shapes": {}}
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    for (H, Hkv, M, D) in ((32, 8, 4096, 64), (32, 8, 4096, 128), (32, 8, 1024, 128)):
+        g = torch.Generator(device=dev).manual_seed(10)
+        q = torch.randn(1, H, M, D, generator=g, device=dev).to(bf)
+        k = torch.randn(1, Hkv, M, D, generator=g, device=dev).to(bf)
+        v = torch.randn(1, Hkv, M, D, generator=g, device=dev).to(bf)
+        o = torch.zeros_like(q)
+        us = timed(lambda: flash_prefill(q, k, v, o, causal=True))
+        us_lib = timed(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True))
+        flops = 4.0 * H * M * M * D * 0.5
+        out["shapes"][f"H{H}/{Hkv} M{M} D{D} causal"] = {"us": us, "tflops": flops / us / 1e6,
+                                                        "frac_tensor": flops / us / 1e6 / tflops_peak, "sdpa_us": us_lib}
+    return out
+
+
 def record_cfg2(args, dev, peak):
     """Flash decoding alone: batch 8, 32 query / 8 KV heads, head dim 128, 32 768 tokens, 32 splits + combine."""
     from machete_b200.kernels.attention import flash_decoding_schedule
@@ -692,7 +733,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     if args.only:
-        fn = {"cfg0": record_cfg0, "cfg1": record_cfg1, "cfg2": record_cfg2, "gemm_sm100": record_gemm_sm100}[args.only]
+        fn = {"cfg0": record_cfg0, "cfg1": record_cfg1, "cfg2": record_cfg2, "gemm_sm100": record_gemm_sm100,
+              "prefill_attention": record_prefill_attention}[args.only]
         if rank == 0:
             print(json.dumps({"only": args.only, args.only: fn(args, dev, measured_peak()[0])}), flush=True)
         if use_dist:
@@ -853,7 +895,7 @@ def main():
                 line["cfg4"] = cfg4
         if world == 1 and rank == 0 and args.model == "llama1b":
             for name, fn in (("cfg0", record_cfg0), ("cfg1", record_cfg1), ("cfg2", record_cfg2),
-                             ("gemm_sm100", record_gemm_sm100)):
+                             ("gemm_sm100", record_gemm_sm100), ("prefill_attention", record_prefill_attention)):
                 try:
                     line[name] = fn(args, dev, peak)
                 except Exception as exc:  # noqa: BLE001
