@@ -9,11 +9,12 @@
 //
 // One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 128 tokens:
 //
-//   warp 0     TMA: Q once, then K and V tiles (K double-buffered) as 128-row x 64-column boxes,
-//              128-byte swizzle;
-//   warp 1     tcgen05.mma issuer: S = Q Kᵀ (accumulator: tensor-memory columns [0, 128)), later
-//              O += P V (columns [128, 128 + D)); V is the N operand in MN-major form (its head
-//              dimension is contiguous in shared memory exactly as the cache stores it);
+//   warp 0     TMA: Q once, then K tiles (double-buffered, one tile ahead of V) and V tiles as
+//              128-row x 64-column boxes, 128-byte swizzle;
+//   warp 1     tcgen05.mma issuer: S(j) = Q K(j)ᵀ into one of two tensor-memory accumulators (columns
+//              [0, 128) / [128, 256)), one tile ahead of the softmax for head dim 128, and O += P V
+//              (columns [256, 256 + D)); V is the N operand in MN-major form (its head dimension is
+//              contiguous in shared memory exactly as the cache stores it);
 //   warps 2-5  one thread per query row (= tensor-memory lane): tcgen05.ld of the row of S, scale,
 //              mask, running maximum and sum kept in registers (no shuffles: a thread owns its row),
 //              P written to shared memory as bf16 in the K-major operand layout, O rescaled in
@@ -56,7 +57,7 @@ struct Params {
 enum { PF_ST_TIMEOUT_EMPTY = 1, PF_ST_TIMEOUT_FULL = 2, PF_ST_TIMEOUT_S = 3, PF_ST_TIMEOUT_P = 4, PF_ST_TIMEOUT_O = 5 };
 
 struct Shared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_ready, p_ready, pv_done;
+  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_ready[2], p_ready, pv_done;
   uint32_t tmem_base;
   int32_t abort_flag;
 };
@@ -174,7 +175,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // tokens this query tile can see: all N, or (causal) up to the diagonal of its last row
   const int n_vis = p.causal ? min(p.N, p.N - p.M + m0 + kBM) : p.N;
   const int n_tiles = n_vis > 0 ? (n_vis + kBN - 1) / kBN : 0;
-  constexpr uint32_t kCols = 256;                  // S: [0, 128), O: [128, 128 + D)
+  // Head dim 128: two S accumulators at columns [0, 128) / [128, 256), O at [256, 384): 512 columns, one CTA
+  // per SM (shared memory allows no more).  Head dim 64: one S accumulator, O at [128, 192): 256 columns, so
+  // that the TWO CTAs per SM that shared memory allows can both hold tensor memory (with 512 columns each the
+  // second one waits in its allocation: 323 -> 460 us).
+  constexpr bool kAhead = D == 128;
+  constexpr uint32_t kCols = kAhead ? 512 : 256, kOCol = kAhead ? 256 : 128, kSBuf = kAhead ? 128 : 0;
 
   if (threadIdx.x == 0) {
     mk::mbar_init(mk::smem_u32(&sh->q_full), 1);
@@ -184,7 +190,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     mk::mbar_init(mk::smem_u32(&sh->v_full), 1);
     mk::mbar_init(mk::smem_u32(&sh->v_empty), 1);
-    mk::mbar_init(mk::smem_u32(&sh->s_ready), 1);
+    mk::mbar_init(mk::smem_u32(&sh->s_ready[0]), 1);
+    mk::mbar_init(mk::smem_u32(&sh->s_ready[1]), 1);
     mk::mbar_init(mk::smem_u32(&sh->p_ready), 128);
     mk::mbar_init(mk::smem_u32(&sh->pv_done), 1);
     sh->abort_flag = 0;
@@ -201,13 +208,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const uint32_t qb = mk::smem_u32(&sh->q_full);
       mk::mbar_arrive_expect_tx(qb, kTile);
       for (int x = 0; x < NB; ++x) tma_load_4d(q_s + x * kBox, &map_q, x * 64, m0, h, b, qb);
-      for (int j = 0; j < n_tiles; ++j) {
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t it = (uint32_t)(j >> 1);
-        if (!wait_bar(p, sh, mk::smem_u32(&sh->k_empty[s]), (it & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
+        if (!wait_bar(p, sh, mk::smem_u32(&sh->k_empty[s]), (it & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) return false;
         const uint32_t kb = mk::smem_u32(&sh->k_full[s]);
         mk::mbar_arrive_expect_tx(kb, kTile);
         for (int x = 0; x < NB; ++x) tma_load_4d(k_s + s * kTile + x * kBox, &map_k, x * 64, j * kBN, kvh, b, kb);
+        return true;
+      };
+      bool pok = n_tiles > 0 ? load_k(0) : true;
+      for (int j = 0; j < n_tiles && pok; ++j) {
+        if (j + 1 < n_tiles && !load_k(j + 1)) break;
         if (!wait_bar(p, sh, mk::smem_u32(&sh->v_empty), ((uint32_t)j & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
         const uint32_t vb = mk::smem_u32(&sh->v_full);
         mk::mbar_arrive_expect_tx(vb, kTile);
@@ -224,19 +236,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (lane == 0) {
       const uint32_t id_s = idesc_bf16(kBN, false), id_o = idesc_bf16(D, true);
       bool ok = wait_bar(p, sh, mk::smem_u32(&sh->q_full), 0, PF_ST_TIMEOUT_FULL, -1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
-        ok = wait_bar(p, sh, mk::smem_u32(&sh->k_full[s]), (uint32_t)(j >> 1) & 1u, PF_ST_TIMEOUT_FULL, j);
-        if (!ok) break;
+        if (!wait_bar(p, sh, mk::smem_u32(&sh->k_full[s]), (uint32_t)(j >> 1) & 1u, PF_ST_TIMEOUT_FULL, j)) return false;
         tc_fence_after();
-        // S = Q Kᵀ: D / 16 steps; step k sits in box k / 4, 32 bytes per step inside the swizzle atom
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u;
-          tc_mma(tmem, desc_kmajor(q_s + off), desc_kmajor(k_s + s * kTile + off), id_s, k > 0 ? 1u : 0u);
+          tc_mma(tmem + (uint32_t)s * kSBuf, desc_kmajor(q_s + off), desc_kmajor(k_s + s * kTile + off), id_s, k > 0 ? 1u : 0u);
         }
-        tc_commit(mk::smem_u32(&sh->s_ready));
+        tc_commit(mk::smem_u32(&sh->s_ready[s]));
         tc_commit(mk::smem_u32(&sh->k_empty[s]));
+        return true;
+      };
+      // With head dim 128 S(j + 1) is issued BEFORE P(j) is awaited, into the other accumulator, so the
+      // tensor cores work on it while the row threads run the softmax of tile j (461 -> 372 us at
+      // 32 heads x 4096 x 4096).  With head dim 64 the same order measured slower (323 -> 383 us).
+      if (kAhead && ok && n_tiles > 0) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (kAhead) {
+          if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        } else {
+          ok = issue_s(j);
+        }
+        if (!ok) break;
         // O += P V once the row threads have written P (and rescaled O)
         ok = wait_bar(p, sh, mk::smem_u32(&sh->p_ready), (uint32_t)j & 1u, PF_ST_TIMEOUT_P, j) &&
              wait_bar(p, sh, mk::smem_u32(&sh->v_full), (uint32_t)j & 1u, PF_ST_TIMEOUT_FULL, j);
@@ -247,7 +270,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           // P: K-major, token step k in box k / 4; V: MN-major, 16 tokens = 16 rows of 128 bytes
           const uint64_t dp = desc_kmajor(p_s + (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u);
           const uint64_t dv = desc_mnmajor(v_s + (uint32_t)k * 2048u, kBox);
-          tc_mma(tmem + 128u, dp, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma(tmem + kOCol, dp, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(mk::smem_u32(&sh->pv_done));
         tc_commit(mk::smem_u32(&sh->v_empty));
@@ -263,7 +286,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     float mx = -INFINITY, sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = wait_bar(p, sh, mk::smem_u32(&sh->s_ready), (uint32_t)j & 1u, PF_ST_TIMEOUT_S, j);
+      ok = wait_bar(p, sh, mk::smem_u32(&sh->s_ready[j & 1]), (uint32_t)(j >> 1) & 1u, PF_ST_TIMEOUT_S, j);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -272,7 +295,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < kBN; c += 32) {
         uint32_t r[32];
-        tmem_ld32(lane_addr + (uint32_t)c, r);
+        tmem_ld32(lane_addr + (uint32_t)(j & 1) * kSBuf + (uint32_t)c, r);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int tok = j * kBN + c + i;
@@ -299,10 +322,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t r[32];
-            tmem_ld32(lane_addr + 128u + (uint32_t)c, r);
+            tmem_ld32(lane_addr + kOCol + (uint32_t)c, r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(lane_addr + 128u + (uint32_t)c, r);
+            tmem_st32(lane_addr + kOCol + (uint32_t)c, r);
           }
           tmem_wait_st();
         }
@@ -312,7 +335,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < kBN; c += 32) {
         uint32_t r[32];
-        tmem_ld32(lane_addr + (uint32_t)c, r);
+        tmem_ld32(lane_addr + (uint32_t)(j & 1) * kSBuf + (uint32_t)c, r);
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -359,7 +382,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int c = 0; c < D; c += 32) {
         uint32_t r[32];
         if (n_tiles > 0) {
-          tmem_ld32(lane_addr + 128u + (uint32_t)c, r);
+          tmem_ld32(lane_addr + kOCol + (uint32_t)c, r);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
