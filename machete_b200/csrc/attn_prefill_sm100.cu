@@ -7,7 +7,8 @@
 // sm_100.py:88-…, dispatch attention/__init__.py:16-130) as a launch of its own, so that a prompt can
 // fill the KV cache the decode kernel then reads.
 //
-// One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 128 tokens:
+// One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 128 tokens (head dim 64) or 64
+// tokens (head dim 128); two CTAs share an SM:
 //
 //   warp 0     TMA: Q once, then K tiles (double-buffered, one tile ahead of V) and V tiles as
 //              128-row x 64-column boxes, 128-byte swizzle;
@@ -40,7 +41,7 @@ namespace mkp {
 
 constexpr int kThreads = 192;
 constexpr int kBM = 128;   // query rows per CTA
-constexpr int kBN = 128;   // tokens per KV tile
+// tokens per KV tile: 128 for head dim 64, 64 for head dim 128 (template parameter BN below)
 constexpr uint32_t kBox = 128 * 64 * 2;   // one 128-row x 64-column bf16 box
 
 struct Params {
@@ -155,19 +156,22 @@ __device__ __forceinline__ bool wait_bar(const Params& p, Shared* sh, uint32_t b
   }
 }
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, int BN>
+__global__ void __launch_bounds__(kThreads, 2)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const Params p) {
   constexpr int NB = D / 64;                       // 64-column boxes per row tile
-  constexpr uint32_t kTile = NB * kBox;            // one 128 x D tile
+  constexpr uint32_t kTile = NB * kBox;            // the 128 x D query tile
+  constexpr uint32_t kKVBox = BN * 64 * 2;         // one BN-token x 64-column box of K or V
+  constexpr uint32_t kKVTile = NB * kKVBox;
+  constexpr int kBN = BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = mk::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
   // layout: Q | K0 | K1 | V | P (two 128 x 64 boxes) | control
-  const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kTile, p_s = v_s + kTile;
-  Shared* sh = reinterpret_cast<Shared*>(smem + 4 * kTile + 2 * kBox);
+  const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kKVTile, p_s = v_s + kKVTile;
+  Shared* sh = reinterpret_cast<Shared*>(smem + kTile + 3 * kKVTile + (BN / 64) * kBox);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (p.H / p.Hkv);
@@ -175,12 +179,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // tokens this query tile can see: all N, or (causal) up to the diagonal of its last row
   const int n_vis = p.causal ? min(p.N, p.N - p.M + m0 + kBM) : p.N;
   const int n_tiles = n_vis > 0 ? (n_vis + kBN - 1) / kBN : 0;
-  // Head dim 128: two S accumulators at columns [0, 128) / [128, 256), O at [256, 384): 512 columns, one CTA
-  // per SM (shared memory allows no more).  Head dim 64: one S accumulator, O at [128, 192): 256 columns, so
-  // that the TWO CTAs per SM that shared memory allows can both hold tensor memory (with 512 columns each the
-  // second one waits in its allocation: 323 -> 460 us).
+  // 256 tensor-memory columns and at most ~100 KB of shared memory per CTA, so that TWO CTAs share an SM and
+  // one's softmax runs beside the other's tensor work (with 512 columns each the second CTA waits in its
+  // allocation: 323 -> 460 us at head dim 64).  Head dim 64: KV tiles of 128 tokens, S at columns [0, 128),
+  // O at [128, 192).  Head dim 128: KV tiles of 64 tokens, two S accumulators [0, 64) / [64, 128), O at
+  // [128, 256).
   constexpr bool kAhead = D == 128;
-  constexpr uint32_t kCols = kAhead ? 512 : 256, kOCol = kAhead ? 256 : 128, kSBuf = kAhead ? 128 : 0;
+  constexpr uint32_t kSBuf = kAhead ? BN : 0, kOCol = kAhead ? 2 * BN : BN, kCols = 256;
+  static_assert(kOCol + D <= kCols, "accumulators must fit the allocation");
 
   if (threadIdx.x == 0) {
     mk::mbar_init(mk::smem_u32(&sh->q_full), 1);
@@ -213,8 +219,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t it = (uint32_t)(j >> 1);
         if (!wait_bar(p, sh, mk::smem_u32(&sh->k_empty[s]), (it & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) return false;
         const uint32_t kb = mk::smem_u32(&sh->k_full[s]);
-        mk::mbar_arrive_expect_tx(kb, kTile);
-        for (int x = 0; x < NB; ++x) tma_load_4d(k_s + s * kTile + x * kBox, &map_k, x * 64, j * kBN, kvh, b, kb);
+        mk::mbar_arrive_expect_tx(kb, kKVTile);
+        for (int x = 0; x < NB; ++x) tma_load_4d(k_s + s * kKVTile + x * kKVBox, &map_k, x * 64, j * kBN, kvh, b, kb);
         return true;
       };
       bool pok = n_tiles > 0 ? load_k(0) : true;
@@ -222,8 +228,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (j + 1 < n_tiles && !load_k(j + 1)) break;
         if (!wait_bar(p, sh, mk::smem_u32(&sh->v_empty), ((uint32_t)j & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
         const uint32_t vb = mk::smem_u32(&sh->v_full);
-        mk::mbar_arrive_expect_tx(vb, kTile);
-        for (int x = 0; x < NB; ++x) tma_load_4d(v_s + x * kBox, &map_v, x * 64, j * kBN, kvh, b, vb);
+        mk::mbar_arrive_expect_tx(vb, kKVTile);
+        for (int x = 0; x < NB; ++x) tma_load_4d(v_s + x * kKVBox, &map_v, x * 64, j * kBN, kvh, b, vb);
       }
       if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) {
         // shared memory must outlive the copies in flight: a bounded wait for whatever was issued last
@@ -242,8 +248,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u;
-          tc_mma(tmem + (uint32_t)s * kSBuf, desc_kmajor(q_s + off), desc_kmajor(k_s + s * kTile + off), id_s, k > 0 ? 1u : 0u);
+          const uint32_t in_box = (uint32_t)(k & 3) * 32u;
+          tc_mma(tmem + (uint32_t)s * kSBuf, desc_kmajor(q_s + (uint32_t)(k >> 2) * kBox + in_box),
+                 desc_kmajor(k_s + s * kKVTile + (uint32_t)(k >> 2) * kKVBox + in_box), id_s, k > 0 ? 1u : 0u);
         }
         tc_commit(mk::smem_u32(&sh->s_ready[s]));
         tc_commit(mk::smem_u32(&sh->k_empty[s]));
@@ -269,7 +276,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int k = 0; k < kBN / 16; ++k) {
           // P: K-major, token step k in box k / 4; V: MN-major, 16 tokens = 16 rows of 128 bytes
           const uint64_t dp = desc_kmajor(p_s + (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u);
-          const uint64_t dv = desc_mnmajor(v_s + (uint32_t)k * 2048u, kBox);
+          const uint64_t dv = desc_mnmajor(v_s + (uint32_t)k * 2048u, kKVBox);
           tc_mma(tmem + kOCol, dp, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(mk::smem_u32(&sh->pv_done));
@@ -439,7 +446,7 @@ static EncodeTiledFn encode_fn() {
 // [batch][head][row][D] with element strides (s_b, s_h, s_r), D contiguous: dims (D, rows, heads, batch),
 // one box = 64 columns x 128 rows of one head of one batch entry.
 static int encode_rows_map(CUtensorMap* out, const void* base, int D, int rows, int heads, int batch, int64_t s_r,
-                           int64_t s_h, int64_t s_b, const char* what) {
+                           int64_t s_h, int64_t s_b, int box_rows, const char* what) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(-5, "cuTensorMapEncodeTiled is not available from this driver");
   if (((uint64_t)base & 15) || (s_r * 2) % 16 || (s_h * 2) % 16 || (s_b * 2) % 16 || s_r <= 0 || s_h <= 0 || s_b <= 0)
@@ -447,7 +454,7 @@ static int encode_rows_map(CUtensorMap* out, const void* base, int D, int rows, 
                     "multiples of 8 elements", what);
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
   cuuint64_t strides[3] = {(cuuint64_t)s_r * 2, (cuuint64_t)s_h * 2, (cuuint64_t)s_b * 2};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -481,15 +488,16 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
   if (cc != 10) return fail(-6, "mk_flash_prefill_bf16 needs an sm_100 device (compute capability %d.x found)", cc);
+  const int bn = D == 128 ? 64 : 128;              // tokens per KV tile
   CUtensorMap mq, mkk, mv;
-  int rc = encode_rows_map(&mq, q, D, M, H, B, q_strides[2], q_strides[1], q_strides[0], "q");
+  int rc = encode_rows_map(&mq, q, D, M, H, B, q_strides[2], q_strides[1], q_strides[0], kBM, "q");
   if (rc) return rc;
-  rc = encode_rows_map(&mkk, k, D, N, Hkv, B, k_strides[2], k_strides[1], k_strides[0], "k");
+  rc = encode_rows_map(&mkk, k, D, N, Hkv, B, k_strides[2], k_strides[1], k_strides[0], bn, "k");
   if (rc) return rc;
-  rc = encode_rows_map(&mv, v, D, N, Hkv, B, v_strides[2], v_strides[1], v_strides[0], "v");
+  rc = encode_rows_map(&mv, v, D, N, Hkv, B, v_strides[2], v_strides[1], v_strides[0], bn, "v");
   if (rc) return rc;
-  const size_t tile = (size_t)(D / 64) * kBox;
-  const size_t smem = 1024 + 4 * tile + 2 * kBox + sizeof(Shared);
+  const size_t tile = (size_t)(D / 64) * kBox, kv_tile = (size_t)(D / 64) * bn * 128;
+  const size_t smem = 1024 + tile + 3 * kv_tile + (size_t)(bn / 64) * kBox + sizeof(Shared);
   if ((int)smem > smem_optin) return fail(-4, "mk_flash_prefill_bf16: %zu bytes of shared memory needed, %d available", smem, smem_optin);
   Params p;
   p.o = reinterpret_cast<__nv_bfloat16*>(o);
@@ -505,16 +513,16 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   cudaError_t e = cudaSuccess;
   if (D == 64) {
     if (dev < 64 && !attr64[dev]) {
-      e = cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      e = cudaFuncSetAttribute(prefill_kernel<64, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
       attr64[dev] = e == cudaSuccess;
     }
-    if (e == cudaSuccess) prefill_kernel<64><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+    if (e == cudaSuccess) prefill_kernel<64, 128><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
   } else {
     if (dev < 64 && !attr128[dev]) {
-      e = cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      e = cudaFuncSetAttribute(prefill_kernel<128, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
       attr128[dev] = e == cudaSuccess;
     }
-    if (e == cudaSuccess) prefill_kernel<128><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+    if (e == cudaSuccess) prefill_kernel<128, 64><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(-(int)e - 1000, "mk_flash_prefill_bf16 launch: %s", cudaGetErrorString(e));
