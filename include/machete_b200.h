@@ -312,7 +312,11 @@ typedef struct mk_program {
    * with device status 7; mk_create refuses a program with `position` set and
    * a limit < 1. */
   int32_t position_limit;
-  int32_t reserved0;
+  /* Entries behind `position`: 0 or 1 = one position shared by every batch row,
+   * else one int32 per batch row (<= 32): sequences of different lengths decode
+   * side by side, each row reads and appends at its own position and attends to
+   * its own window, and the feedback op advances every entry. */
+  int32_t position_count;
 } mk_program_t;
 
 typedef struct mk_handle_s* mk_handle_t;

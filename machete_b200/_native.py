@@ -106,7 +106,7 @@ class Program(C.Structure):
         ("act_bytes", C.c_int32), ("timeout_ms", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
         ("ops", C.c_void_p), ("instrs", C.c_void_p), ("cta_instr_begin", C.c_void_p),
         ("events", C.c_void_p), ("cta_event_begin", C.c_void_p), ("waits", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("position", C.c_void_p), ("position_limit", C.c_int32), ("reserved0", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("position", C.c_void_p), ("position_limit", C.c_int32), ("position_count", C.c_int32),
     ]
 
 

@@ -106,7 +106,7 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
       if (ins.flags & MK_LDF_DYN) {
         // the window follows the device-resident position: tokens [0, pos + 1); only the unit
         // that holds the row appended in this launch waits for it
-        const int pos = c.ctrl->pos;
+        const int pos = c.ctrl->pos[(ins.row_b >> 16) & 31];      // the unit's batch row
         n_pages = at_dyn_pages(ins.row_a, ins.n_pages, ins.tiles, pos + 1);
         need_wait = need_wait && pos >= ins.row_a && pos < ins.row_a + ins.n_pages * ins.tiles;
         if (n_pages == 0) continue;
@@ -342,8 +342,9 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
         // an attention unit whose window follows the device-resident position: the pages in use, and
         // with them the participants, are a function of the position (the same on every warp)
         const int t_begin = __shfl_sync(0xffffffffu, mine.row_a, i - base);
+        const int brow = (__shfl_sync(0xffffffffu, mine.row_b, i - base) >> 16) & 31;
         n_pages = at_dyn_pages(t_begin, n_pages, at_page_tokens((lflags & MK_LDF_D128) ? 128 : 64, pv.page_bytes),
-                               c.ctrl->pos + 1);
+                               c.ctrl->pos[brow] + 1);
         split = max(1, min(split, n_pages));
         lflags = (lflags & ~(MK_LDF_SPLIT_MASK << MK_LDF_SPLIT_SHIFT)) | (split << MK_LDF_SPLIT_SHIFT);
       }
@@ -420,19 +421,29 @@ __global__ void __launch_bounds__(kThreads, 1) mk_persistent_kernel(const __grid
     c.ctrl->is_last = 0;
     c.ctrl->ticket = 0;
     c.ctrl->ev_arrive = 0;
-    c.ctrl->pos = pv.dyn_pos != nullptr ? *reinterpret_cast<const volatile int32_t*>(pv.dyn_pos) : 0;
+    c.ctrl->pos_bad = 0;
     c.ctrl->bulk_done[0] = c.ctrl->bulk_done[1] = 0;
     fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // one position per batch row (or one for all): a warp reads them side by side
+    int v = 0;
+    if (pv.dyn_pos != nullptr) {
+      v = reinterpret_cast<const volatile int32_t*>(pv.dyn_pos)[min((int)threadIdx.x, pv.pos_count - 1)];
+      if ((int)threadIdx.x < pv.pos_count && (uint32_t)v >= (uint32_t)pv.pos_limit) c.ctrl->pos_bad = 1 + (int)threadIdx.x;
+    }
+    c.ctrl->pos[threadIdx.x] = v;
   }
   __syncthreads();
 
   const int ibeg = pv.cta_instr_begin[blockIdx.x], iend = pv.cta_instr_begin[blockIdx.x + 1];
   const int ebeg = pv.cta_event_begin[blockIdx.x], eend = pv.cta_event_begin[blockIdx.x + 1];
   // A position outside the caches the program was scheduled for would write past them: every CTA
-  // reads the same scalar, so all of them skip the program together and the launch ends at once.
-  const bool bad_pos = pv.dyn_pos != nullptr && (uint32_t)c.ctrl->pos >= (uint32_t)pv.pos_limit;
+  // reads the same values, so all of them skip the program together and the launch ends at once.
+  const int bad_pos = c.ctrl->pos_bad;          // 1 + the batch row of an offending position
   if (bad_pos) {
-    if (threadIdx.x == 0) report(c, MK_ST_BAD_POSITION, c.ctrl->pos, pv.pos_limit);
+    if (threadIdx.x == 0) report(c, MK_ST_BAD_POSITION, c.ctrl->pos[bad_pos - 1], pv.pos_limit);
   } else if (c.warp == 0) {
     loader_loop(c, ibeg, iend);
   } else {

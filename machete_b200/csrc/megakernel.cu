@@ -418,6 +418,8 @@ static int validate_program(const mk_program_t* p, int smem_optin, int num_sms, 
         return fail(-2, "op %d follows a device-resident cache position, but the program has none (mk_program_t.position)", i);
     }
   if (p->position != nullptr && ((uint64_t)p->position & 3)) return fail(-1, "position scalar must be 4-byte aligned");
+  if (p->position != nullptr && (p->position_count < 0 || p->position_count > 32))
+    return fail(-1, "position_count must be 0 or 1 (one position for all rows) or the batch size, at most 32 (got %d)", p->position_count);
   if (p->position != nullptr && p->position_limit < 1)
     return fail(-1, "position_limit must be the cache length of the position-following ops (got %d)", p->position_limit);
   for (int i = 0; i < p->n_waits; ++i)
@@ -696,6 +698,7 @@ static int create_program(const mk_program_t* prog, mk_handle_t* out, bool strea
   h->pv.trace_cap = 0;
   h->pv.dyn_pos = prog->position;
   h->pv.pos_limit = prog->position_limit;
+  h->pv.pos_count = prog->position_count > 0 ? prog->position_count : 1;
   h->n_ctas = prog->n_ctas;
   h->smem_bytes = smem_bytes;
   h->smem_optin = smem_optin;

@@ -267,7 +267,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
   const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV];
   // the window: the scheduled length, or (device-resident position) every token up to this step's
   const bool dyn = op->i[MK_AT_DYNPOS] != 0;
-  const int N = dyn ? min(op->i[MK_AT_N], c.ctrl->pos + M) : op->i[MK_AT_N];
+  const int N = dyn ? min(op->i[MK_AT_N], c.ctrl->pos[u.b & 31] + M) : op->i[MK_AT_N];
   u.t_begin = min(u.t_begin, N);
   u.t_end = min(u.t_end, N);
   const int G = H / HKV;
@@ -379,7 +379,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
     const uint32_t kpage = page, vpage = page + tile_bytes;
     const int tp0 = u.t_begin + p * tn;
     if (qknorm) {
-      const int nt = dyn ? c.ctrl->pos : op->i[MK_AT_NEW_TOK];
+      const int nt = dyn ? c.ctrl->pos[u.b & 31] : op->i[MK_AT_NEW_TOK];
       if (nt >= tp0 && nt < tp0 + tn && nt < u.t_end) at_fix_k_row<D>(c, op, u, kpage, tn, nt - tp0, nt);
     }
     for (int blk = 0; blk * TN < tn; ++blk) {

@@ -184,10 +184,8 @@ __device__ __forceinline__ void ew_top1_final(Ctx& c, const mk_op_t* op, int uni
       uint4* dst = reinterpret_cast<uint4*>(xin + (int64_t)m * op->s[MK_EW_S_RO]);
       for (int ch = c.lane; ch < D / 8; ch += 32) dst[ch] = src[ch];
     }
-    if (c.lane == 0) {
-      int32_t* pos = reinterpret_cast<int32_t*>(op->p[MK_EW_P_GATE]);
-      if (pos != nullptr) *pos = *pos + op->i[MK_EW_S];
-    }
+    int32_t* pos = reinterpret_cast<int32_t*>(op->p[MK_EW_P_GATE]);
+    if (pos != nullptr && c.lane < c.pv->pos_count) pos[c.lane] += op->i[MK_EW_S];   // every sequence moves on
   }
 }
 

@@ -155,10 +155,12 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   const bool add = (pro == MK_PRO_ADD_RMS) && ri != nullptr;
   write_res = write_res && add && ro != nullptr;
   if (!stage && !write_res) return;
-  if (stage && op->i[MK_MV_TR] == MK_TR_ROPE && tid < 2 * S) {
+  const bool dyn_tab = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) != 0;
+  if (stage && op->i[MK_MV_TR] == MK_TR_ROPE && tid < 2 * (dyn_tab ? M : S)) {
     // the epilogue's cos / sin rows: pull them into L1 while the activations are on their way
+    // (with device-resident positions: the row of every batch row's own position)
     const uint8_t* tab = reinterpret_cast<const uint8_t*>(op->p[(tid & 1) ? MK_MV_P_SIN : MK_MV_P_COS]);
-    const int row = (tid >> 1) + ((op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) ? c.ctrl->pos : 0);
+    const int row = dyn_tab ? c.ctrl->pos[(tid >> 1) & 31] : (tid >> 1);
     asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + (size_t)row * (size_t)op->s[MK_MV_S_COS] * 2u));
   }
   auto row_off = [&](int m, int sb, int ss) -> int64_t {
@@ -337,8 +339,7 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
   const bool va = g < nA, vb = g < nB;
   const bool two = tr != MK_TR_SILU_MUL;
   // device-resident cache position: which of the table row and the output row follow it
-  const int tpos = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) ? c.ctrl->pos : 0;
-  const int dpos = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_OUT) ? c.ctrl->pos : 0;
+  const bool dyn_t = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_TABLES) != 0, dyn_o = (op->i[MK_MV_DYNPOS] & MK_MV_DYN_OUT) != 0;
 #pragma unroll 1
   for (int q = 0; q < 2 * NT; ++q) {
     const int m0 = (q >> 1) * 8 + (q & 1);   // the smallest activation row any lane has in this pass
@@ -370,6 +371,9 @@ __device__ __forceinline__ void mv_epilogue(Ctx& c, const mk_op_t* op, const MvO
       bb = m / S;
       ss = m - bb * S;
     }
+    // the batch row's own cache position (a dynamic position means one token per sequence: bb = m)
+    const int prow = (dyn_t || dyn_o) ? c.ctrl->pos[(vm ? bb : 0) & 31] : 0;
+    const int tpos = dyn_t ? prow : 0, dpos = dyn_o ? prow : 0;
     if (tr == MK_TR_ROPE) {
       if (vm) {
         const int d = r.chunk * 8 + g;

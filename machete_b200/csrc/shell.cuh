@@ -80,6 +80,7 @@ struct ProgramView {
   int32_t mv_sets;  // split-K slot sets in use: 4 (every matvec has M <= 8), 2 (M <= 16) or 1
   const int32_t* dyn_pos;  // device-resident cache position, or null
   int32_t pos_limit;       // positions >= this end the launch with MK_ST_BAD_POSITION before any op runs
+  int32_t pos_count;       // entries behind dyn_pos: 1 (one position for every batch row) or one per row (<= 32)
 };
 
 // One trace event: a globaltimer stamp, an event code and an argument.
@@ -123,8 +124,11 @@ struct Ctrl {
   uint32_t bulk_done[2];
   uint32_t ticket;     // next consumer slot of the CTA (see consumer_loop)
   uint32_t ev_arrive;  // consumer warps that have reached an op-entry event (kConsumerWarps per event)
-  int32_t pos;         // the device-resident cache position as read when the launch started (0 without one)
+  int32_t pos_bad;     // a device-resident cache position was outside [0, pos_limit) when the launch started
   int32_t pad[1];
+  // the device-resident cache position of every batch row as read when the launch started (all rows
+  // share one value when the program has a single position; 0 without one)
+  int32_t pos[32];
   // released[slot] = number of fills of the slot that consumers have handed back
   uint32_t released[kMaxPages];
   // per activation row and consumer warp: sum of squares of the staged row (RMSNorm)

@@ -109,6 +109,10 @@ def schedule_decode_model_sm100(
         # into ``x_in`` and advances the position, so every further launch decodes the next token.
         if x_in is None or top_indices is None or logits is not None or seq_len != 1:
             raise ValueError("position= needs x_in, the top-1 head and one token per step")
+        # one element: every sequence of the batch sits at the same position; ``batch`` elements: each
+        # sequence has its own (sequences of different lengths decode side by side)
+        if position.numel() not in (1, batch):
+            raise ValueError(f"position must hold 1 or {batch} (= batch) elements, got {position.numel()}")
         if tp_peers is not None and embedding is None:
             raise ValueError("position= under tensor parallelism needs the full embedding table (embedding=)")
     if tp_peers is not None and logits is not None:

@@ -248,9 +248,11 @@ class Megakernel:
         prog.waits = arrays["waits"].ctypes.data
         pos = self.config.position
         if pos is not None:
-            if pos.dtype != torch.int32 or pos.numel() != 1 or not pos.is_cuda:
-                raise ValueError("MegakernelConfig.position must be a one-element int32 CUDA tensor")
+            if pos.dtype != torch.int32 or not 1 <= pos.numel() <= 32 or not pos.is_cuda or not pos.is_contiguous():
+                raise ValueError("MegakernelConfig.position must be a contiguous int32 CUDA tensor with one element, "
+                                 "or one per batch row (at most 32)")
             prog.position = pos.data_ptr()
+            prog.position_count = int(pos.numel())
             limits = [op.pos_limit for op in self.native_ops if op.pos_limit is not None]
             if self.config.position_limit is not None:
                 limits.append(int(self.config.position_limit))

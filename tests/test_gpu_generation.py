@@ -160,3 +160,65 @@ def test_position_past_the_cache_runs_nothing_and_reports_it():
     mk.run()
     assert mk.status()[0] == 0 and int(position.item()) == T and 0 <= int(ti.item()) < vocab
     assert not torch.equal(kd[0][:, T - 1], k_before[:, T - 1]) and torch.equal(kd[0][:, :T - 1], k_before[:, :T - 1])
+
+
+def test_sequences_of_different_lengths_decode_side_by_side():
+    """One position per batch row: each sequence appends, rotates and attends at its own position,
+    and every launch moves all of them on.  The oracle decodes each sequence on its own."""
+    B, L, T, hidden, nq, nkv, hd, inter, vocab = 3, 2, 256, 512, 8, 2, 64, 1024, 1024
+    starts, steps = [60, 125, 10], 6
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=37, device="cuda")
+    g = torch.Generator().manual_seed(38)
+    kcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    vcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF)
+    emb = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF)
+    x0 = emb[torch.tensor([3, 400, 77])].view(B, 1, hidden).clone()
+    r0 = torch.zeros(B, 1, hidden, dtype=BF)
+    dev = "cuda"
+    x_in, kd, vd = x0.to(dev), [t.to(dev) for t in kcs], [t.to(dev) for t in vcs]
+    position = torch.tensor(starts, dtype=torch.int32, device=dev)
+    tv, ti = torch.zeros(B, 1, device=dev), torch.zeros(B, 1, dtype=torch.int32, device=dev)
+    ops, _keep = schedule_decode_model_sm100(
+        batch=B, cache_pos=0, weights=w, k_cache=kd, v_cache=vd,
+        x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+        mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), final_norm=fn.to(dev), lm_head=emb.to(dev),
+        top_values=tv, top_indices=ti, num_layers=L, x_in=x_in, residual_in=r0.to(dev), position=position,
+        hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+    mk = Megakernel(ops, config=MegakernelConfig(position=position), scheduler=OverlapTileScheduler())
+    wc = to_cpu(w)
+    x = x0.clone()
+    for step in range(steps):
+        mk.run()
+        assert position.cpu().tolist() == [s0 + step + 1 for s0 in starts]
+        got = ti.cpu()
+        for b in range(B):
+            pos = starts[b] + step
+            kb, vb = [t[b:b + 1] for t in kcs], [t[b:b + 1] for t in vcs]      # views: the oracle appends in place
+            logits, _v, want_i = oracle.decode_model(weights=wc, x=x[b:b + 1], residual=r0[b:b + 1], k_caches=kb, v_caches=vb,
+                                                     cache_pos=pos, final_norm=fn, lm_head=emb, num_layers=L,
+                                                     num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+            bar = parity_bar(logits, roundings=2 * L)
+            top2 = logits.topk(2, dim=-1).values
+            assert float(top2[0, 0, 0] - top2[0, 0, 1]) > bar, "test input has a near-tie: pick another seed"
+            assert int(got[b, 0]) == int(want_i[0, 0]), f"step {step}, sequence {b}: token differs"
+            for l in range(L):
+                assert float((kd[l][b, pos].cpu().float() - kcs[l][b, pos].float()).abs().max()) <= 2 * bar
+        x = emb[got[:, 0].long()].view(B, 1, hidden).clone()
+        assert torch.equal(x_in.cpu(), x)
+    # one sequence past its cache: nothing runs, the status names that row's position
+    position[1] = T
+    with pytest.raises(RuntimeError, match="position is outside"):
+        mk.run()
+    with pytest.raises(ValueError):
+        schedule_decode_model_sm100(
+            batch=B, cache_pos=0, weights=w, k_cache=kd, v_cache=vd,
+            x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+            residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+            q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+            mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), final_norm=fn.to(dev), lm_head=emb.to(dev),
+            top_values=tv, top_indices=ti, num_layers=L, x_in=x_in, residual_in=r0.to(dev),
+            position=torch.zeros(2, dtype=torch.int32, device=dev),
+            hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
