@@ -297,19 +297,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      // pass 1: the row's maximum over this tile
+      // pass 1: the row's maximum over this tile.  Only the tiles on the causal diagonal and the last one
+      // of a ragged cache need the per-score mask: `open` is true (for the whole warp) everywhere else.
+      const bool open = __all_sync(0xffffffffu, (j * kBN + kBN - 1 <= lim) && (j * kBN + kBN <= p.N));
       float tmax = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < kBN; c += 32) {
         uint32_t r[32];
         tmem_ld32(lane_addr + (uint32_t)(j & 1) * kSBuf + (uint32_t)c, r);
+        if (open) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int tok = j * kBN + c + i;
-          const float s = (tok <= lim && tok < p.N) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
-          tmax = fmaxf(tmax, s);
+          for (int i = 0; i < 32; ++i) tmax = fmaxf(tmax, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int tok = j * kBN + c + i;
+            tmax = fmaxf(tmax, (tok <= lim && tok < p.N) ? __uint_as_float(r[i]) : -INFINITY);
+          }
         }
       }
+      tmax *= p.scale_log2;                          // the scale is positive: maximum and scale commute
       // mx is the exponent reference in use, not always the running maximum: it moves only when the
       // maximum has grown by more than 2^8 since it was set, so O is rescaled rarely (P stays <= 256)
       float alpha = 1.f;
@@ -348,14 +355,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           float e[2];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int tok = j * kBN + c + i + u;
-            const bool vis = tok <= lim && tok < p.N;
-            e[u] = vis ? exp2f(__uint_as_float(r[i + u]) * p.scale_log2 - muse) : 0.f;
+          for (int u = 0; u < 2; ++u) e[u] = exp2f(fmaf(__uint_as_float(r[i + u]), p.scale_log2, -muse));
+          if (!open) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int tok = j * kBN + c + i + u;
+              if (!(tok <= lim && tok < p.N)) e[u] = 0.f;
+            }
           }
           const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
-          // the sum uses the values the tensor cores will see
-          tsum += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+          // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
+          tsum += e[0] + e[1];
           w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
         }
         // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
