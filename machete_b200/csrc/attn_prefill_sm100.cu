@@ -297,42 +297,46 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      // pass 1: the row's maximum over this tile.  Only the tiles on the causal diagonal and the last one
-      // of a ragged cache need the per-score mask: `open` is true (for the whole warp) everywhere else.
+      // Only the tiles on the causal diagonal and the last one of a ragged cache need the per-score
+      // mask: `open` is true (for the whole warp) everywhere else.
       const bool open = __all_sync(0xffffffffu, (j * kBN + kBN - 1 <= lim) && (j * kBN + kBN <= p.N));
-      float tmax = -INFINITY;
+      const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * kSBuf;
+      // mx is the exponent reference in use, not always the running maximum: it moves only when the
+      // maximum has grown by more than 2^8 since it was set, so O is rescaled rarely (P stays <= 256).
+      // While some row of the warp has no reference yet, the tile's maximum is taken in a pass of its own;
+      // afterwards ONE pass computes P against the reference in use and the maximum beside it, and is
+      // repeated only if a maximum outgrew the reference (rare after the first tiles).
+      const bool first = __any_sync(0xffffffffu, mx == -INFINITY);
+      float alpha = 1.f;
+      if (first) {
+        float tmax = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_addr + (uint32_t)(j & 1) * kSBuf + (uint32_t)c, r);
-        if (open) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tmax = fmaxf(tmax, __uint_as_float(r[i]));
-        } else {
+        for (int c = 0; c < kBN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + (uint32_t)c, r);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int tok = j * kBN + c + i;
-            tmax = fmaxf(tmax, (tok <= lim && tok < p.N) ? __uint_as_float(r[i]) : -INFINITY);
+            tmax = fmaxf(tmax, (open || (tok <= lim && tok < p.N)) ? __uint_as_float(r[i]) : -INFINITY);
           }
         }
+        tmax *= p.scale_log2;                        // the scale is positive: maximum and scale commute
+        if (tmax > mx + 8.f) {                       // also the first visible tile (mx = -inf)
+          alpha = exp2f(mx - tmax);                  // 0 when mx = -inf
+          mx = tmax;
+        }
       }
-      tmax *= p.scale_log2;                          // the scale is positive: maximum and scale commute
-      // mx is the exponent reference in use, not always the running maximum: it moves only when the
-      // maximum has grown by more than 2^8 since it was set, so O is rescaled rarely (P stays <= 256)
-      float alpha = 1.f;
-      float mnew = mx;
-      if (tmax > mx + 8.f) {                         // also the first visible tile (mx = -inf)
-        alpha = exp2f(mx - tmax);                    // 0 when mx = -inf
-        mnew = tmax;
-      }
-      const float muse = mnew == -INFINITY ? 0.f : mnew;
-      // O may be rescaled only after the previous P V has finished with it
+      // P's buffer and O are free only after the previous P V has finished with them
       if (j > 0) {
         ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+      }
+      float tsum = 0.f;
+#pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t r[32];
@@ -343,44 +347,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           tmem_wait_st();
         }
-      }
-      // pass 2: P = exp2(s - max) as bf16 into the K-major operand tile (this thread's row)
-      float tsum = 0.f;
+        sum *= alpha;
+        alpha = 1.f;
+        const float muse = mx == -INFINITY ? 0.f : mx;
+        // P = exp2(s * scale - reference) as bf16 into the K-major operand tile (this thread's row)
+        float pmax = -INFINITY;
+        tsum = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_addr + (uint32_t)(j & 1) * kSBuf + (uint32_t)c, r);
-        uint32_t w[16];
+        for (int c = 0; c < kBN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + (uint32_t)c, r);
+          uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e[2];
+          for (int i = 0; i < 32; i += 2) {
+            float sc[2], e[2];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) e[u] = exp2f(fmaf(__uint_as_float(r[i + u]), p.scale_log2, -muse));
-          if (!open) {
+            for (int u = 0; u < 2; ++u) sc[u] = __uint_as_float(r[i + u]);
+            if (!open) {
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int tok = j * kBN + c + i + u;
-              if (!(tok <= lim && tok < p.N)) e[u] = 0.f;
+              for (int u = 0; u < 2; ++u) {
+                const int tok = j * kBN + c + i + u;
+                if (!(tok <= lim && tok < p.N)) sc[u] = -INFINITY;     // exp2(-inf) = 0
+              }
             }
-          }
-          const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
-          // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
-          tsum += e[0] + e[1];
-          w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-        }
-        // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
+            pmax = fmaxf(pmax, fmaxf(sc[0], sc[1]));
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c >> 3) + q4;            // 0..15 over the 128 tokens
-          const uint32_t addr = p_s + (uint32_t)(chunk >> 3) * kBox + (uint32_t)row * 128u +
-                                (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * q4]), "r"(w[4 * q4 + 1]),
-                       "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3])
-                       : "memory");
+            for (int u = 0; u < 2; ++u) e[u] = exp2f(fmaf(sc[u], p.scale_log2, -muse));
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
+            // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
+            tsum += e[0] + e[1];
+            w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
+          // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c >> 3) + q4;            // 0..15 over the 128 tokens
+            const uint32_t addr = p_s + (uint32_t)(chunk >> 3) * kBox + (uint32_t)row * 128u +
+                                  (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * q4]), "r"(w[4 * q4 + 1]),
+                         "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3])
+                         : "memory");
+          }
+        }
+        // did a maximum outgrow the reference in this tile?  (never on the pass that followed pass 1)
+        pmax *= p.scale_log2;
+        const bool grow = !first && attempt == 0 && pmax > mx + 8.f;
+        if (!__any_sync(0xffffffffu, grow)) break;
+        if (grow) {
+          alpha = exp2f(mx - pmax);
+          mx = pmax;
         }
       }
-      sum = sum * alpha + tsum;
-      mx = mnew;
+      sum += tsum;
       // P (generic-proxy stores) must be visible to the tensor cores (async proxy); O's rescale is done
       mk::fence_proxy_async();
       tc_fence_before();
