@@ -114,6 +114,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Two fp32 operations per instruction (the packed f32x2 forms of sm_100): the softmax of one score costs the
+// issue slots of half a multiply-add, one exp2, half an add and half a conversion.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // K-major bf16 tile of 128-byte swizzled rows (8-row groups 1024 bytes apart): Q, K and P.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
@@ -173,7 +192,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kKVTile, p_s = v_s + kKVTile;
   Shared* sh = reinterpret_cast<Shared*>(smem + kTile + 3 * kKVTile + (BN / 64) * kBox);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // Blocks are handed out in the order x, y, z: the query tile is the slowest index and runs from the LAST tile
+  // down, so that under a causal mask the tiles with the most KV tiles start first and the short ones fill the
+  // tail (longest job first; 256 -> 175 us at 32 heads x 4096 x 4096, head dim 128).
+  const int mt = (int)(gridDim.z - 1 - blockIdx.z), h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.H / p.Hkv);
   const int m0 = mt * kBM;
   // tokens this query tile can see: all N, or (causal) up to the diagonal of its last row
@@ -301,41 +323,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // mask: `open` is true (for the whole warp) everywhere else.
       const bool open = __all_sync(0xffffffffu, (j * kBN + kBN - 1 <= lim) && (j * kBN + kBN <= p.N));
       const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * kSBuf;
-      // mx is the exponent reference in use, not always the running maximum: it moves only when the
-      // maximum has grown by more than 2^8 since it was set, so O is rescaled rarely (P stays <= 256).
-      // While some row of the warp has no reference yet, the tile's maximum is taken in a pass of its own;
-      // afterwards ONE pass computes P against the reference in use and the maximum beside it, and is
-      // repeated only if a maximum outgrew the reference (rare after the first tiles).
-      const bool first = __any_sync(0xffffffffu, mx == -INFINITY);
-      float alpha = 1.f;
-      if (first) {
-        float tmax = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < kBN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + (uint32_t)c, r);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int tok = j * kBN + c + i;
-            tmax = fmaxf(tmax, (open || (tok <= lim && tok < p.N)) ? __uint_as_float(r[i]) : -INFINITY);
-          }
-        }
-        tmax *= p.scale_log2;                        // the scale is positive: maximum and scale commute
-        if (tmax > mx + 8.f) {                       // also the first visible tile (mx = -inf)
-          alpha = exp2f(mx - tmax);                  // 0 when mx = -inf
-          mx = tmax;
-        }
-      }
-      // P's buffer and O are free only after the previous P V has finished with them
-      if (j > 0) {
-        ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      float tsum = 0.f;
+      // mx is the exponent reference in use, not the running maximum: it moves only when a maximum has grown
+      // by more than 2^8 since it was set, so O is rescaled rarely.
+      // A tile's maximum is taken (in a pass of its own) only while some row of the warp has no reference
+      // yet, or after the P pass found a row sum above 2^14: no single P is larger than the sum, so below
+      // that nothing can overflow, and the pass needs no maximum at all.
+      bool need_max = __any_sync(0xffffffffu, mx == -INFINITY);
+      bool waited = j == 0;
+      float alpha = 1.f, tsum = 0.f;
 #pragma unroll 1
       for (int attempt = 0; attempt < 2; ++attempt) {
+        if (need_max) {
+          float tmax = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < kBN; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(s_addr + (uint32_t)c, r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int tok = j * kBN + c + i;
+              tmax = fmaxf(tmax, (open || (tok <= lim && tok < p.N)) ? __uint_as_float(r[i]) : -INFINITY);
+            }
+          }
+          tmax *= p.scale_log2;                      // the scale is positive: maximum and scale commute
+          if (tmax > mx + 8.f) {                     // also the first visible tile (mx = -inf)
+            alpha = exp2f(mx - tmax);                // 0 when mx = -inf
+            mx = tmax;
+          }
+        }
+        // P's buffer and O are free only after the previous P V has finished with them
+        if (!waited) {
+          ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          waited = true;
+        }
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -350,9 +373,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         sum *= alpha;
         alpha = 1.f;
         const float muse = mx == -INFINITY ? 0.f : mx;
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), ref2 = pack2(-muse, -muse);
         // P = exp2(s * scale - reference) as bf16 into the K-major operand tile (this thread's row)
-        float pmax = -INFINITY;
-        tsum = 0.f;
+        uint64_t tsum2 = pack2(0.f, 0.f);
 #pragma unroll 1
         for (int c = 0; c < kBN; c += 32) {
           uint32_t r[32];
@@ -370,12 +393,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (!(tok <= lim && tok < p.N)) sc[u] = -INFINITY;     // exp2(-inf) = 0
               }
             }
-            pmax = fmaxf(pmax, fmaxf(sc[0], sc[1]));
-#pragma unroll
-            for (int u = 0; u < 2; ++u) e[u] = exp2f(fmaf(sc[u], p.scale_log2, -muse));
+            float x0, x1;
+            unpack2(fma2(pack2(sc[0], sc[1]), scale2, ref2), x0, x1);
+            e[0] = exp2f(x0);
+            e[1] = exp2f(x1);
             const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
             // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
-            tsum += e[0] + e[1];
+            tsum2 = add2(tsum2, pack2(e[0], e[1]));
             w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
           }
           // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
@@ -389,15 +413,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                          : "memory");
           }
         }
-        // did a maximum outgrow the reference in this tile?  (never on the pass that followed pass 1)
-        pmax *= p.scale_log2;
-        const bool grow = !first && attempt == 0 && pmax > mx + 8.f;
+        float t0, t1;
+        unpack2(tsum2, t0, t1);
+        tsum = t0 + t1;
+        // a sum this large (or not finite) means the reference is stale: take the maximum and do the tile again
+        const bool grow = attempt == 0 && !need_max && !(tsum <= 16384.f);
         if (!__any_sync(0xffffffffu, grow)) break;
-        if (grow) {
-          alpha = exp2f(mx - pmax);
-          mx = pmax;
-        }
+        need_max = true;
       }
+      if (!ok) break;
       sum += tsum;
       // P (generic-proxy stores) must be visible to the tensor cores (async proxy); O's rescale is done
       mk::fence_proxy_async();
@@ -507,6 +531,7 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   if (B < 1 || H < 1 || Hkv < 1 || M < 1 || N < 1 || H % Hkv)
     return fail(-2, "mk_flash_prefill_bf16: B, H, Hkv, M, N must be positive and H a multiple of Hkv");
   if (D != 64 && D != 128) return fail(-2, "mk_flash_prefill_bf16: head dim must be 64 or 128, got %d", D);
+  if (B > 65535 || (M + 127) / 128 > 65535) return fail(-2, "mk_flash_prefill_bf16: at most 65535 batch entries and 65535 query tiles of 128 rows");
   if (causal && M > N) return fail(-2, "mk_flash_prefill_bf16: causal attention needs M <= N (the queries are the last M tokens)");
   if (workspace_bytes < 256 || ((uint64_t)workspace & 255)) return fail(-2, "mk_flash_prefill_bf16: workspace of 256 aligned bytes");
   if (((uint64_t)o & 15) || o_strides[2] % 8 || o_strides[1] % 8 || o_strides[0] % 8)
@@ -536,7 +561,7 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   p.causal = causal ? 1 : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.timeout_ns = (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
-  const dim3 grid((M + kBM - 1) / kBM, H, B);
+  const dim3 grid(H, B, (M + kBM - 1) / kBM);
   static bool attr64[64] = {}, attr128[64] = {};
   cudaError_t e = cudaSuccess;
   if (D == 64) {
