@@ -7,20 +7,24 @@
 // sm_100.py:88-…, dispatch attention/__init__.py:16-130) as a launch of its own, so that a prompt can
 // fill the KV cache the decode kernel then reads.
 //
-// One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 128 tokens (head dim 64) or 64
-// tokens (head dim 128); two CTAs share an SM:
+// One CTA = one (batch, query head, tile of 128 query rows); KV tiles of 64 tokens; two CTAs share an SM
+// (<= 97 KB of shared memory and 256 tensor-memory columns each):
 //
-//   warp 0     TMA: Q once, then K tiles (double-buffered, one tile ahead of V) and V tiles as
-//              128-row x 64-column boxes, 128-byte swizzle;
-//   warp 1     tcgen05.mma issuer: S(j) = Q K(j)ᵀ into one of two tensor-memory accumulators (columns
-//              [0, 128) / [128, 256)), one tile ahead of the softmax for head dim 128, and O += P V
-//              (columns [256, 256 + D)); V is the N operand in MN-major form (its head dimension is
-//              contiguous in shared memory exactly as the cache stores it);
-//   warps 2-5  one thread per query row (= tensor-memory lane): tcgen05.ld of the row of S, scale,
-//              mask, running maximum and sum kept in registers (no shuffles: a thread owns its row),
-//              P written to shared memory as bf16 in the K-major operand layout, O rescaled in
-//              tensor memory only when a row maximum outgrew the exponent reference by 2^8
-//              (tcgen05.ld / st), normalised bf16 store at the end.
+//   warp 0     TMA: Q once, then K and V tiles (both double-buffered, K one tile ahead of V) as
+//              64-column boxes, 128-byte swizzle;
+//   warp 1     tcgen05.mma issuer: S(j) = Q K(j)^T into one of two tensor-memory accumulators, one tile
+//              ahead of the softmax, and O += P(j) V(j) with P read FROM TENSOR MEMORY (the M x K
+//              operand) and V as the N operand in MN-major form (its head dimension is contiguous in
+//              shared memory exactly as the cache stores it);
+//   warps 2-5  one thread per query row (= tensor-memory lane): one tcgen05.ld of the row of S(j), mask,
+//              maximum, P = exp2(scale * s - reference) with packed f32x2 arithmetic, running sum in
+//              registers (no shuffles: a thread owns its row), P stored as bf16 pairs over the first half
+//              of the accumulator it came from (tcgen05.st), O rescaled in tensor memory only when a row
+//              maximum outgrew the exponent reference by 2^8; normalised bf16 store at the end.
+//
+// The row threads never wait for P V: while the tensor cores run P(j) V(j) and S(j + 2) they are already
+// on tile j + 1, so the exponentials (the scarce unit: 16 per clock and SM) and the products overlap inside
+// one CTA, and the second CTA of the SM fills what is left.
 //
 // Every wait is bounded; on expiry the CTA records a status, raises its abort flag, all roles fall
 // through to the common exit and tensor memory is freed.
@@ -41,7 +45,7 @@ namespace mkp {
 
 constexpr int kThreads = 192;
 constexpr int kBM = 128;   // query rows per CTA
-// tokens per KV tile: 128 for head dim 64, 64 for head dim 128 (template parameter BN below)
+constexpr int kBN = 64;    // tokens per KV tile
 constexpr uint32_t kBox = 128 * 64 * 2;   // one 128-row x 64-column bf16 box
 
 struct Params {
@@ -58,7 +62,7 @@ struct Params {
 enum { PF_ST_TIMEOUT_EMPTY = 1, PF_ST_TIMEOUT_FULL = 2, PF_ST_TIMEOUT_S = 3, PF_ST_TIMEOUT_P = 4, PF_ST_TIMEOUT_O = 5 };
 
 struct Shared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_ready[2], p_ready, pv_done;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_ready[2], p_ready[2], pv_done[2];
   uint32_t tmem_base;
   int32_t abort_flag;
 };
@@ -88,6 +92,19 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  // the M x K operand comes from tensor memory (lane = row, one 32-bit column = two bf16 along K)
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -100,6 +117,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// one row of a 64-column accumulator; the wait is part of the statement so that nothing reads r before it
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {"
+      "%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+        "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+        "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -175,39 +212,35 @@ __device__ __forceinline__ bool wait_bar(const Params& p, Shared* sh, uint32_t b
   }
 }
 
-template <int D, int BN>
+template <int D>
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const Params p) {
   constexpr int NB = D / 64;                       // 64-column boxes per row tile
   constexpr uint32_t kTile = NB * kBox;            // the 128 x D query tile
-  constexpr uint32_t kKVBox = BN * 64 * 2;         // one BN-token x 64-column box of K or V
+  constexpr uint32_t kKVBox = kBN * 64 * 2;        // one 64-token x 64-column box of K or V
   constexpr uint32_t kKVTile = NB * kKVBox;
-  constexpr int kBN = BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = mk::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  // layout: Q | K0 | K1 | V | P (two 128 x 64 boxes) | control
-  const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kKVTile, p_s = v_s + kKVTile;
-  Shared* sh = reinterpret_cast<Shared*>(smem + kTile + 3 * kKVTile + (BN / 64) * kBox);
+  // layout: Q | K0 | K1 | V0 | V1 | control
+  const uint32_t q_s = base, k_s = q_s + kTile, v_s = k_s + 2 * kKVTile;
+  Shared* sh = reinterpret_cast<Shared*>(smem + kTile + 4 * kKVTile);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Blocks are handed out in the order x, y, z: the query tile is the slowest index and runs from the LAST tile
   // down, so that under a causal mask the tiles with the most KV tiles start first and the short ones fill the
-  // tail (longest job first; 256 -> 175 us at 32 heads x 4096 x 4096, head dim 128).
+  // tail (longest job first).
   const int mt = (int)(gridDim.z - 1 - blockIdx.z), h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.H / p.Hkv);
   const int m0 = mt * kBM;
   // tokens this query tile can see: all N, or (causal) up to the diagonal of its last row
   const int n_vis = p.causal ? min(p.N, p.N - p.M + m0 + kBM) : p.N;
   const int n_tiles = n_vis > 0 ? (n_vis + kBN - 1) / kBN : 0;
-  // 256 tensor-memory columns and at most ~100 KB of shared memory per CTA, so that TWO CTAs share an SM and
-  // one's softmax runs beside the other's tensor work (with 512 columns each the second CTA waits in its
-  // allocation: 323 -> 460 us at head dim 64).  Head dim 64: KV tiles of 128 tokens, S at columns [0, 128),
-  // O at [128, 192).  Head dim 128: KV tiles of 64 tokens, two S accumulators [0, 64) / [64, 128), O at
-  // [128, 256).
-  constexpr bool kAhead = D == 128;
-  constexpr uint32_t kSBuf = kAhead ? BN : 0, kOCol = kAhead ? 2 * BN : BN, kCols = 256;
+  // 256 tensor-memory columns and at most ~100 KB of shared memory per CTA, so that TWO CTAs share an SM.
+  // Two S accumulators at columns [0, 64) / [64, 128) (P, as bf16 pairs, overwrites the first 32 columns of
+  // the accumulator it was computed from), O at [128, 128 + D).
+  constexpr uint32_t kOCol = 2 * kBN, kCols = 256;
   static_assert(kOCol + D <= kCols, "accumulators must fit the allocation");
 
   if (threadIdx.x == 0) {
@@ -215,13 +248,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mk::mbar_init(mk::smem_u32(&sh->k_full[s]), 1);
       mk::mbar_init(mk::smem_u32(&sh->k_empty[s]), 1);
+      mk::mbar_init(mk::smem_u32(&sh->v_full[s]), 1);
+      mk::mbar_init(mk::smem_u32(&sh->v_empty[s]), 1);
+      mk::mbar_init(mk::smem_u32(&sh->s_ready[s]), 1);
+      mk::mbar_init(mk::smem_u32(&sh->p_ready[s]), 128);
+      mk::mbar_init(mk::smem_u32(&sh->pv_done[s]), 1);
     }
-    mk::mbar_init(mk::smem_u32(&sh->v_full), 1);
-    mk::mbar_init(mk::smem_u32(&sh->v_empty), 1);
-    mk::mbar_init(mk::smem_u32(&sh->s_ready[0]), 1);
-    mk::mbar_init(mk::smem_u32(&sh->s_ready[1]), 1);
-    mk::mbar_init(mk::smem_u32(&sh->p_ready), 128);
-    mk::mbar_init(mk::smem_u32(&sh->pv_done), 1);
     sh->abort_flag = 0;
     mk::fence_mbar_init();
   }
@@ -231,27 +263,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
 
+  // Tile j uses slot j & 1 of every double-buffered resource; its barrier phase is (j >> 1) & 1.
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t qb = mk::smem_u32(&sh->q_full);
       mk::mbar_arrive_expect_tx(qb, kTile);
       for (int x = 0; x < NB; ++x) tma_load_4d(q_s + x * kBox, &map_q, x * 64, m0, h, b, qb);
-      auto load_k = [&](int j) -> bool {
+      auto load_kv = [&](int j, bool is_v) -> bool {
         const int s = j & 1;
-        const uint32_t it = (uint32_t)(j >> 1);
-        if (!wait_bar(p, sh, mk::smem_u32(&sh->k_empty[s]), (it & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) return false;
-        const uint32_t kb = mk::smem_u32(&sh->k_full[s]);
-        mk::mbar_arrive_expect_tx(kb, kKVTile);
-        for (int x = 0; x < NB; ++x) tma_load_4d(k_s + s * kKVTile + x * kKVBox, &map_k, x * 64, j * kBN, kvh, b, kb);
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        uint64_t* empty = is_v ? &sh->v_empty[s] : &sh->k_empty[s];
+        uint64_t* full = is_v ? &sh->v_full[s] : &sh->k_full[s];
+        if (!wait_bar(p, sh, mk::smem_u32(empty), ph ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) return false;
+        const uint32_t fb = mk::smem_u32(full);
+        mk::mbar_arrive_expect_tx(fb, kKVTile);
+        const uint32_t dst = (is_v ? v_s : k_s) + (uint32_t)s * kKVTile;
+        for (int x = 0; x < NB; ++x) tma_load_4d(dst + x * kKVBox, is_v ? &map_v : &map_k, x * 64, j * kBN, kvh, b, fb);
         return true;
       };
-      bool pok = n_tiles > 0 ? load_k(0) : true;
+      // K runs one tile ahead of V: S(j + 1) is issued before P(j) V(j)
+      bool pok = n_tiles > 0 ? load_kv(0, false) : true;
       for (int j = 0; j < n_tiles && pok; ++j) {
-        if (j + 1 < n_tiles && !load_k(j + 1)) break;
-        if (!wait_bar(p, sh, mk::smem_u32(&sh->v_empty), ((uint32_t)j & 1u) ^ 1u, PF_ST_TIMEOUT_EMPTY, j)) break;
-        const uint32_t vb = mk::smem_u32(&sh->v_full);
-        mk::mbar_arrive_expect_tx(vb, kKVTile);
-        for (int x = 0; x < NB; ++x) tma_load_4d(v_s + x * kKVBox, &map_v, x * 64, j * kBN, kvh, b, vb);
+        if (j + 1 < n_tiles && !load_kv(j + 1, false)) break;
+        if (!load_kv(j, true)) break;
       }
       if (*reinterpret_cast<volatile int32_t*>(&sh->abort_flag)) {
         // shared memory must outlive the copies in flight: a bounded wait for whatever was issued last
@@ -271,38 +305,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t in_box = (uint32_t)(k & 3) * 32u;
-          tc_mma(tmem + (uint32_t)s * kSBuf, desc_kmajor(q_s + (uint32_t)(k >> 2) * kBox + in_box),
+          tc_mma(tmem + (uint32_t)s * kBN, desc_kmajor(q_s + (uint32_t)(k >> 2) * kBox + in_box),
                  desc_kmajor(k_s + s * kKVTile + (uint32_t)(k >> 2) * kKVBox + in_box), id_s, k > 0 ? 1u : 0u);
         }
         tc_commit(mk::smem_u32(&sh->s_ready[s]));
         tc_commit(mk::smem_u32(&sh->k_empty[s]));
         return true;
       };
-      // With head dim 128 S(j + 1) is issued BEFORE P(j) is awaited, into the other accumulator, so the
-      // tensor cores work on it while the row threads run the softmax of tile j (461 -> 372 us at
-      // 32 heads x 4096 x 4096).  With head dim 64 the same order measured slower (323 -> 383 us).
-      if (kAhead && ok && n_tiles > 0) ok = issue_s(0);
+      // Issue order S(0), S(1), P V(0), S(2), P V(1), S(3), ...  The tensor cores run the products in this
+      // order, so S(j + 2) overwrites accumulator j & 1 only after P V(j) has read P(j) from it, and the
+      // row threads find S(j + 1) finished while P V(j) is still running.
+      if (ok && n_tiles > 0) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (kAhead) {
-          if (j + 1 < n_tiles) ok = issue_s(j + 1);
-        } else {
-          ok = issue_s(j);
-        }
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         // O += P V once the row threads have written P (and rescaled O)
-        ok = wait_bar(p, sh, mk::smem_u32(&sh->p_ready), (uint32_t)j & 1u, PF_ST_TIMEOUT_P, j) &&
-             wait_bar(p, sh, mk::smem_u32(&sh->v_full), (uint32_t)j & 1u, PF_ST_TIMEOUT_FULL, j);
+        ok = wait_bar(p, sh, mk::smem_u32(&sh->p_ready[s]), ph, PF_ST_TIMEOUT_P, j) &&
+             wait_bar(p, sh, mk::smem_u32(&sh->v_full[s]), ph, PF_ST_TIMEOUT_FULL, j);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kBN / 16; ++k) {
-          // P: K-major, token step k in box k / 4; V: MN-major, 16 tokens = 16 rows of 128 bytes
-          const uint64_t dp = desc_kmajor(p_s + (uint32_t)(k >> 2) * kBox + (uint32_t)(k & 3) * 32u);
-          const uint64_t dv = desc_mnmajor(v_s + (uint32_t)k * 2048u, kKVBox);
-          tc_mma(tmem + kOCol, dp, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
+          // P: 16 tokens = 8 tensor-memory columns of bf16 pairs; V: MN-major, 16 tokens = 16 rows of 128 bytes
+          const uint64_t dv = desc_mnmajor(v_s + (uint32_t)s * kKVTile + (uint32_t)k * 2048u, kKVBox);
+          tc_mma_ts(tmem + kOCol, tmem + (uint32_t)s * kBN + (uint32_t)k * 8u, dv, id_o, (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(mk::smem_u32(&sh->pv_done));
-        tc_commit(mk::smem_u32(&sh->v_empty));
+        tc_commit(mk::smem_u32(&sh->pv_done[s]));
+        tc_commit(mk::smem_u32(&sh->v_empty[s]));
       }
     }
   } else {
@@ -312,6 +343,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int m = m0 + row;
     const int lim = p.causal ? (p.N - p.M + m) : (p.N - 1);   // last visible token of this row
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
     float mx = -INFINITY, sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -322,115 +354,74 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // Only the tiles on the causal diagonal and the last one of a ragged cache need the per-score
       // mask: `open` is true (for the whole warp) everywhere else.
       const bool open = __all_sync(0xffffffffu, (j * kBN + kBN - 1 <= lim) && (j * kBN + kBN <= p.N));
-      const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * kSBuf;
-      // mx is the exponent reference in use, not the running maximum: it moves only when a maximum has grown
-      // by more than 2^8 since it was set, so O is rescaled rarely.
-      // A tile's maximum is taken (in a pass of its own) only while some row of the warp has no reference
-      // yet, or after the P pass found a row sum above 2^14: no single P is larger than the sum, so below
-      // that nothing can overflow, and the pass needs no maximum at all.
-      bool need_max = __any_sync(0xffffffffu, mx == -INFINITY);
-      bool waited = j == 0;
-      float alpha = 1.f, tsum = 0.f;
-#pragma unroll 1
-      for (int attempt = 0; attempt < 2; ++attempt) {
-        if (need_max) {
-          float tmax = -INFINITY;
-#pragma unroll 1
-          for (int c = 0; c < kBN; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(s_addr + (uint32_t)c, r);
+      const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * kBN;
+      uint32_t r[kBN];                               // this row of S, then of P (bf16 pairs in r[0 .. 32))
+      tmem_ld64(s_addr, r);
+      if (!open) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int tok = j * kBN + c + i;
-              tmax = fmaxf(tmax, (open || (tok <= lim && tok < p.N)) ? __uint_as_float(r[i]) : -INFINITY);
-            }
-          }
-          tmax *= p.scale_log2;                      // the scale is positive: maximum and scale commute
-          if (tmax > mx + 8.f) {                     // also the first visible tile (mx = -inf)
-            alpha = exp2f(mx - tmax);                // 0 when mx = -inf
-            mx = tmax;
-          }
+        for (int i = 0; i < kBN; ++i) {
+          const int tok = j * kBN + i;
+          if (!(tok <= lim && tok < p.N)) r[i] = 0xff800000u;          // -inf: exp2 gives 0
         }
-        // P's buffer and O are free only after the previous P V has finished with them
-        if (!waited) {
-          ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(j - 1) & 1u, PF_ST_TIMEOUT_O, j);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          waited = true;
-        }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + kOCol + (uint32_t)c, r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(lane_addr + kOCol + (uint32_t)c, r);
-          }
-          tmem_wait_st();
-        }
-        sum *= alpha;
-        alpha = 1.f;
-        const float muse = mx == -INFINITY ? 0.f : mx;
-        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), ref2 = pack2(-muse, -muse);
-        // P = exp2(s * scale - reference) as bf16 into the K-major operand tile (this thread's row)
-        uint64_t tsum2 = pack2(0.f, 0.f);
-#pragma unroll 1
-        for (int c = 0; c < kBN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + (uint32_t)c, r);
-          uint32_t w[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float sc[2], e[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) sc[u] = __uint_as_float(r[i + u]);
-            if (!open) {
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int tok = j * kBN + c + i + u;
-                if (!(tok <= lim && tok < p.N)) sc[u] = -INFINITY;     // exp2(-inf) = 0
-              }
-            }
-            float x0, x1;
-            unpack2(fma2(pack2(sc[0], sc[1]), scale2, ref2), x0, x1);
-            e[0] = exp2f(x0);
-            e[1] = exp2f(x1);
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(e[0], e[1]);
-            // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
-            tsum2 = add2(tsum2, pack2(e[0], e[1]));
-            w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-          }
-          // 32 tokens = 4 chunks of 16 bytes; chunk index inside the 64-token box, swizzled by the row
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = (c >> 3) + q4;            // 0..15 over the 128 tokens
-            const uint32_t addr = p_s + (uint32_t)(chunk >> 3) * kBox + (uint32_t)row * 128u +
-                                  (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * q4]), "r"(w[4 * q4 + 1]),
-                         "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3])
-                         : "memory");
-          }
-        }
-        float t0, t1;
-        unpack2(tsum2, t0, t1);
-        tsum = t0 + t1;
-        // a sum this large (or not finite) means the reference is stale: take the maximum and do the tile again
-        const bool grow = attempt == 0 && !need_max && !(tsum <= 16384.f);
-        if (!__any_sync(0xffffffffu, grow)) break;
-        need_max = true;
       }
-      if (!ok) break;
-      sum += tsum;
-      // P (generic-proxy stores) must be visible to the tensor cores (async proxy); O's rescale is done
-      mk::fence_proxy_async();
+      float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < kBN; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) t4[u] = max3(t4[u], __uint_as_float(r[i + 2 * u]), __uint_as_float(r[i + 2 * u + 1]));
+      }
+      const float tmax = max3(fmaxf(t4[0], t4[1]), t4[2], t4[3]) * p.scale_log2;   // the scale is positive
+      // mx is the exponent reference in use, not the running maximum: it moves only when a maximum has grown
+      // by more than 2^8 since it was set, so O is rescaled rarely (and no P exceeds 2^8).
+      float alpha = 1.f;
+      if (tmax > mx + 8.f) {                         // also the first visible tile (mx = -inf)
+        alpha = exp2f(mx - tmax);                    // 0 when mx = -inf
+        mx = tmax;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // O is free only after the previous P V has finished with it.  S(j) was issued after P V(j - 2), so
+        // that phase of this barrier is behind us and the parity is unambiguous.
+        ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u, PF_ST_TIMEOUT_O, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(lane_addr + kOCol + (uint32_t)c, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(lane_addr + kOCol + (uint32_t)c, o);
+        }
+      }
+      sum *= alpha;
+      const float muse = mx == -INFINITY ? 0.f : mx;
+      const uint64_t ref2 = pack2(-muse, -muse);
+      // P = exp2(s * scale - reference), two scores per multiply-add, add and conversion
+      uint64_t tsum2 = pack2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < kBN; i += 2) {
+        float x0, x1;
+        unpack2(fma2(pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, ref2), x0, x1);
+        const float e0 = exp2f(x0), e1 = exp2f(x1);
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+        // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
+        tsum2 = add2(tsum2, pack2(e0, e1));
+        r[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      float t0, t1;
+      unpack2(tsum2, t0, t1);
+      sum += t0 + t1;
+      // P goes where its S came from: 64 bf16 = the first 32 columns of the accumulator
+      tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_wait_st();
       tc_fence_before();
-      mk::mbar_arrive(mk::smem_u32(&sh->p_ready));
+      mk::mbar_arrive(mk::smem_u32(&sh->p_ready[j & 1]));
     }
     // epilogue: O / sum -> bf16
     if (ok && n_tiles > 0) {
-      ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done), (uint32_t)(n_tiles - 1) & 1u, PF_ST_TIMEOUT_O, n_tiles);
+      ok = wait_bar(p, sh, mk::smem_u32(&sh->pv_done[(n_tiles - 1) & 1]), (uint32_t)((n_tiles - 1) >> 1) & 1u,
+                    PF_ST_TIMEOUT_O, n_tiles);
       ok = __all_sync(0xffffffffu, ok);
     }
     tc_fence_after();
@@ -439,12 +430,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)m * p.o_sm;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
-        uint32_t r[32];
+        uint32_t o[32];
         if (n_tiles > 0) {
-          tmem_ld32(lane_addr + kOCol + (uint32_t)c, r);
+          tmem_ld32(lane_addr + kOCol + (uint32_t)c, o);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
         if (m < p.M) {
 #pragma unroll
@@ -452,8 +443,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             uint32_t w[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * u]) * inv,
-                                                              __uint_as_float(r[i + 2 * u + 1]) * inv);
+              const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv,
+                                                              __uint_as_float(o[i + 2 * u + 1]) * inv);
               w[u] = *reinterpret_cast<const uint32_t*>(&pk);
             }
             *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -541,7 +532,7 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev);
   if (cc != 10) return fail(-6, "mk_flash_prefill_bf16 needs an sm_100 device (compute capability %d.x found)", cc);
-  const int bn = D == 128 ? 64 : 128;              // tokens per KV tile
+  const int bn = kBN;                              // tokens per KV tile
   CUtensorMap mq, mkk, mv;
   int rc = encode_rows_map(&mq, q, D, M, H, B, q_strides[2], q_strides[1], q_strides[0], kBM, "q");
   if (rc) return rc;
@@ -550,7 +541,7 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   rc = encode_rows_map(&mv, v, D, N, Hkv, B, v_strides[2], v_strides[1], v_strides[0], bn, "v");
   if (rc) return rc;
   const size_t tile = (size_t)(D / 64) * kBox, kv_tile = (size_t)(D / 64) * bn * 128;
-  const size_t smem = 1024 + tile + 3 * kv_tile + (size_t)(bn / 64) * kBox + sizeof(Shared);
+  const size_t smem = 1024 + tile + 4 * kv_tile + sizeof(Shared);
   if ((int)smem > smem_optin) return fail(-4, "mk_flash_prefill_bf16: %zu bytes of shared memory needed, %d available", smem, smem_optin);
   Params p;
   p.o = reinterpret_cast<__nv_bfloat16*>(o);
@@ -566,16 +557,16 @@ int mk_flash_prefill_bf16(const void* q, const void* k, const void* v, void* o, 
   cudaError_t e = cudaSuccess;
   if (D == 64) {
     if (dev < 64 && !attr64[dev]) {
-      e = cudaFuncSetAttribute(prefill_kernel<64, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      e = cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
       attr64[dev] = e == cudaSuccess;
     }
-    if (e == cudaSuccess) prefill_kernel<64, 128><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+    if (e == cudaSuccess) prefill_kernel<64><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
   } else {
     if (dev < 64 && !attr128[dev]) {
-      e = cudaFuncSetAttribute(prefill_kernel<128, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
+      e = cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin);
       attr128[dev] = e == cudaSuccess;
     }
-    if (e == cudaSuccess) prefill_kernel<128, 64><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
+    if (e == cudaSuccess) prefill_kernel<128><<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(mq, mkk, mv, p);
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(-(int)e - 1000, "mk_flash_prefill_bf16 launch: %s", cudaGetErrorString(e));
