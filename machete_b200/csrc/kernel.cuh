@@ -179,7 +179,9 @@ static __device__ void loader_loop(Ctx& c, int ibeg, int iend) {
 template <int NTC, int WFC, int FEAT>
 __device__ __forceinline__ bool run_unit(Ctx& c, const mk_op_t* op, const UnitArgs& u) {
   const int opcode = op->opcode;
-  if (opcode == MK_OP_MATVEC) return mv_dispatch<NTC, WFC, FEAT>(c, op, u);
+  if constexpr (NTC >= 0) {   // NTC < 0: a kernel for programs without a matvec op
+    if (opcode == MK_OP_MATVEC) return mv_dispatch<NTC, WFC, FEAT>(c, op, u);
+  }
   if constexpr ((FEAT & (MK_F_AT64 | MK_F_AT128)) != 0) {
     if (opcode == MK_OP_ATTN_SPLIT) return at_dispatch<FEAT>(c, op, u);
   }
@@ -300,10 +302,12 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     bulk_done = &c.ctrl->bulk_done[k & 1];
     cached_op = e_op;
     cached_rec = op;
-    if (op->opcode == MK_OP_MATVEC) {
-      const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-      mv_stage<!(NTC == 1 && WFC == 0), WFC>(c, op, need, (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
-      staged_key = op->act_key;
+    if constexpr (NTC >= 0) {
+      if (op->opcode == MK_OP_MATVEC) {
+        const bool need = (op->act_key == 0) || (op->act_key != staged_key);
+        mv_stage<!(NTC == 1 && WFC == 0), WFC>(c, op, need, (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
+        staged_key = op->act_key;
+      }
     }
     if (w == 1 && have_next) {
       // units of the op two events back (the slot's last user) are complete since the barrier above

@@ -469,13 +469,15 @@ extern "C" const mk_variant* mk_variants_bf16_wide(int* n);
 extern "C" const mk_variant* mk_variants_fp4(int* n);
 extern "C" const mk_variant* mk_variants_fp4_wide(int* n);
 extern "C" const mk_variant* mk_variants_fp4_tp(int* n);
+extern "C" const mk_variant* mk_variants_attn(int* n);
 
 static const std::vector<mk_variant>& all_variants() {
   static const std::vector<mk_variant> v = [] {
     std::vector<mk_variant> out;
     typedef const mk_variant* (*group_fn)(int*);
     const group_fn groups[] = {mk_variants_generic, mk_variants_bf16,     mk_variants_bf16_wide,
-                               mk_variants_fp4,     mk_variants_fp4_wide, mk_variants_fp4_tp};
+                               mk_variants_fp4,     mk_variants_fp4_wide, mk_variants_fp4_tp,
+                               mk_variants_attn};
     for (group_fn g : groups) {
       int n = 0;
       const mk_variant* t = g(&n);
@@ -543,7 +545,9 @@ static int select_kernel(mk_handle_s* h) {
       mixed = true;
     }
   }
-  if (mixed || ntc <= 0 || wfc == 1) {   // fp16 weights run the generic matvec code
+  if (ntc == -1) {   // no matvec op at all: the variants built without matvec code
+    wfc = 0;
+  } else if (mixed || ntc <= 0 || wfc == 1) {   // fp16 weights run the generic matvec code
     ntc = 0;
     wfc = -1;
   }
