@@ -141,11 +141,22 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
         }
       }
       if (s0 == 0) {
+        if (M == 1) {
+          // one query token: the group's lse values are contiguous, (row, split) -> row * S + split
+          const float* l0 = lpart + ((int64_t)u.b * H + (int64_t)u.kvh * G + u.mt * 16 + r0) * S;
+          float lv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) lv[q] = (c.lane + 32 * q < nr * S) ? ldcg_f(l0 + c.lane + 32 * q) : 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (c.lane + 32 * q < nr * S) scratch[c.lane + 32 * q] = lv[q];
+        } else {
 #pragma unroll 1
         for (int i = c.lane; i < nr * S; i += 32) {
           const int rr = i / S, s = i - rr * S, r2 = u.mt * 16 + r0 + rr;
           const int m2 = r2 / G, h2 = u.kvh * G + r2 % G;
           scratch[i] = ldcg_f(lpart + (((int64_t)u.b * H + h2) * S + s) * M + m2);
+        }
         }
         __syncwarp();
 #pragma unroll 1
