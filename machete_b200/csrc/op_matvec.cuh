@@ -128,14 +128,15 @@ __device__ __forceinline__ bool mv_rstd_in_epilogue(const mk_op_t* op) {
 // cold instruction cache.
 //   * no prologue, same type: the rows are copied global -> shared with
 //     16-byte asynchronous copies, all in flight at once;
-//   * RMSNorm prologue: R rows x 2 chunks per thread are requested together
-//     (one trip to L2), then reduced; R = 1 for the batch-1 kernel, 4 otherwise.
+//   * RMSNorm prologue: R rows x H chunks per thread are requested together
+//     (one trip to L2), then reduced; R x H = 1 x 2 for the bf16 kernel of up to 8
+//     rows, 2 x 4 for its NVFP4 counterpart (K = 4096 in one trip), 4 x 2 otherwise.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <bool GROUPED, int WFC>
+template <int R, int H, int WFC>
 __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, bool write_res) {
   const int tid = (c.warp - 1) * 32 + c.lane;
   constexpr int T = kConsumerWarps * 32;
@@ -185,8 +186,30 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
     return;
   }
 
-  constexpr int R = GROUPED ? 4 : 1;
   const uint4 z = make_uint4(0, 0, 0, 0);
+  if (WFC != 0 && pro == MK_PRO_NONE) {
+    // no prologue, the mma's type differs from the input's: a converting copy, eight chunks per
+    // thread in flight (K = 12288 in one trip per row)
+#pragma unroll 1
+    for (int m = 0; m < M; ++m) {
+      const uint16_t* xr = x + row_off(m, MK_MV_S_X_B, MK_MV_S_X_S);
+      const uint32_t dst = c.act_u32 + (uint32_t)m * xs;
+#pragma unroll 1
+      for (int ch0 = tid; ch0 < chunks; ch0 += 8 * T) {
+        uint4 v[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) v[h] = (ch0 + h * T < chunks) ? *reinterpret_cast<const uint4*>(xr + (ch0 + h * T) * 8) : z;
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          if (ch0 + h * T >= chunks) break;
+          float f[8];
+          unpack8(v[h], xt, f);
+          sts128(dst + (uint32_t)(ch0 + h * T) * 16u, pack8(f, at));
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll 1
   for (int m0 = 0; m0 < M; m0 += R) {
     const uint16_t *xr[R], *rr[R];
@@ -201,21 +224,24 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
       sum[j] = 0.f;
     }
 #pragma unroll 1
-    for (int ch0 = tid; ch0 < chunks; ch0 += 2 * T) {
-      uint4 v[R][2], r[R][2], wv[2];
+    for (int ch0 = tid; ch0 < chunks; ch0 += H * T) {
+      uint4 v[R][H], r[R][H], wv[H];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < H; ++h) {
         const int ch = ch0 + h * T;
         const bool ok = ch < chunks;
         wv[h] = (ok && fused) ? *reinterpret_cast<const uint4*>(nw + ch * 8) : z;
+        // two-pass form: the second pass reads this thread's norm weights; have them in L1 by then
+        if (WFC != 0 && ok && !fused && pro != MK_PRO_NONE) asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + ch * 8));
 #pragma unroll
         for (int j = 0; j < R; ++j) {
-          v[j][h] = ok ? *reinterpret_cast<const uint4*>(xr[j] + ch * 8) : z;
-          r[j][h] = (ok && add) ? *reinterpret_cast<const uint4*>(rr[j] + ch * 8) : z;
+          const bool rok = ok && (R == 1 || m0 + j < M);   // rows past M are not fetched a second time
+          v[j][h] = rok ? *reinterpret_cast<const uint4*>(xr[j] + ch * 8) : z;
+          r[j][h] = (rok && add) ? *reinterpret_cast<const uint4*>(rr[j] + ch * 8) : z;
         }
       }
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < H; ++h) {
         const int ch = ch0 + h * T;
         if (ch >= chunks) break;
         float w[8];
@@ -261,29 +287,25 @@ __device__ __forceinline__ void mv_stage(Ctx& c, const mk_op_t* op, bool stage, 
   if constexpr (WFC == 0) return;
   // second pass: normalise and convert to the mma's activation type
   named_bar_sync(kConsumerBarrier, T);
-  if (pro != MK_PRO_NONE) {
-    if (tid < M) {
-      float tot = 0.f;
+  if (tid < M) {
+    float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) tot += c.ctrl->red[tid * kConsumerWarps + w];
-      c.ctrl->rstd[tid] = rsqrtf(tot / (float)K + op->f[MK_MV_F_EPS]);
-    }
-    named_bar_sync(kConsumerBarrier, T);
+    for (int w = 0; w < kConsumerWarps; ++w) tot += c.ctrl->red[tid * kConsumerWarps + w];
+    c.ctrl->rstd[tid] = rsqrtf(tot / (float)K + op->f[MK_MV_F_EPS]);
   }
+  named_bar_sync(kConsumerBarrier, T);
 #pragma unroll 1
   for (int ch = tid; ch < chunks; ch += T) {
     float w[8];
-    unpack8(pro != MK_PRO_NONE ? *reinterpret_cast<const uint4*>(nw + ch * 8) : z, xt, w);
+    unpack8(*reinterpret_cast<const uint4*>(nw + ch * 8), xt, w);
 #pragma unroll 1
     for (int m = 0; m < M; ++m) {
       const uint32_t a = c.act_u32 + (uint32_t)m * xs + (uint32_t)ch * 16u;
       float f[8];
       unpack8(lds128(a), xt, f);
-      if (pro != MK_PRO_NONE) {
-        const float rstd = c.ctrl->rstd[m];
+      const float rstd = c.ctrl->rstd[m];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
-      }
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
       sts128(a, pack8(f, at));
     }
   }
