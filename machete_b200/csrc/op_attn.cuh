@@ -159,12 +159,21 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
         }
         }
         __syncwarp();
+        // The row's LPR lanes take the splits in turn: the maximum by shuffle (exact in any order), each
+        // e^{lse_s - max} once, written over its lse value; the sum then adds them in split order.  (One
+        // lane walking all S values waits for a shared-memory load and an exponential per step.)
+        const int li = c.lane % LPR;
 #pragma unroll 1
-        for (int s = 0; s < S; ++s) mx = fmaxf(mx, ls[s]);
-        if (mx != -INFINITY) {
+        for (int s = li; s < S; s += LPR) mx = fmaxf(mx, ls[s]);
+#pragma unroll
+        for (int o = 1; o < LPR; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (rv) {
 #pragma unroll 1
-          for (int s = 0; s < S; ++s) sum += __expf(ls[s] - mx);
+          for (int s = li; s < S; s += LPR) scratch[row * S + s] = mx != -INFINITY ? __expf(ls[s] - mx) : 0.f;
         }
+        __syncwarp();
+#pragma unroll 1
+        for (int s = 0; s < S; ++s) sum += ls[s];
         inv = sum > 0.f ? 1.f / sum : 0.f;
       } else {
         trace(c, TRC_AT_FETCHED, (uint32_t)r0);
@@ -172,7 +181,7 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
 #pragma unroll
       for (int k = 0; k < UN; ++k) {
         if (s0 + k >= S) break;
-        const float w = sum > 0.f ? __expf(ls[s0 + k] - mx) * inv : 0.f;
+        const float w = ls[s0 + k] * inv;
         acc[0] += w * a[k].x; acc[1] += w * a[k].y; acc[2] += w * a[k].z; acc[3] += w * a[k].w;
         acc[4] += w * b2[k].x; acc[5] += w * b2[k].y; acc[6] += w * b2[k].z; acc[7] += w * b2[k].w;
       }
