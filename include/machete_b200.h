@@ -152,7 +152,9 @@ enum {
    * attends to tokens [0, p + M); MK_AT_N is then the cache CAPACITY (tensor
    * maps, split bounds and the per-unit page limits derive from it; loader
    * and consumers compute the pages in use from p), and the new-token row of
-   * the fused q/k norm is p. */
+   * the fused q/k norm is p: MK_AT_P_COS / MK_AT_P_SIN then point at the whole
+   * tables and MK_AT_NEW_TOK holds their row stride in elements (row p is
+   * used). */
   MK_AT_DYNPOS
 };
 enum { MK_AT_F_SCALE = 0, MK_AT_F_EPS };

@@ -347,7 +347,12 @@ static int validate_op(const mk_op_t& op, int idx, int page_bytes, int act_bytes
         return fail(-2, "op %d: a KV window that follows the cache position needs one token per sequence, non-causal", idx);
       if (op.i[MK_AT_QKNORM]) {
         if (M != 1 || op.i[MK_AT_MT] != 1) return fail(-2, "op %d: fused q/k norm needs one token per sequence and H/Hkv <= 16", idx);
-        if (op.i[MK_AT_NEW_TOK] < 0 || op.i[MK_AT_NEW_TOK] >= op.i[MK_AT_N]) return fail(-2, "op %d: new-token row outside the cache window", idx);
+        if (op.i[MK_AT_DYNPOS]) {
+          if (op.i[MK_AT_NEW_TOK] < D / 2 || (op.i[MK_AT_NEW_TOK] & 7))
+            return fail(-2, "op %d: with a device-resident position MK_AT_NEW_TOK is the cos / sin row stride (>= D/2, a multiple of 8)", idx);
+        } else if (op.i[MK_AT_NEW_TOK] < 0 || op.i[MK_AT_NEW_TOK] >= op.i[MK_AT_N]) {
+          return fail(-2, "op %d: new-token row outside the cache window", idx);
+        }
         for (int k = MK_AT_P_QNW; k <= MK_AT_P_SIN; ++k)
           if (!op.p[k] || !aligned16(op.p[k])) return fail(-2, "op %d: fused q/k norm tables missing or unaligned", idx);
       }

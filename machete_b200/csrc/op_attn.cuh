@@ -224,7 +224,7 @@ __device__ __forceinline__ uint4 at_pack8(const float (&f)[8]) {
 }
 template <int D>
 __device__ __forceinline__ void at_fix_k_row(Ctx& c, const mk_op_t* op, const AtUnit& u, uint32_t kpage, int tn, int row,
-                                             int tok) {
+                                             int tok, int64_t tab_off) {
   constexpr int HALF = D / 16;
   const bool act = c.lane < HALF;
   const int l = act ? c.lane : 0;
@@ -241,8 +241,8 @@ __device__ __forceinline__ void at_fix_k_row(Ctx& c, const mk_op_t* op, const At
   float wa[8], wb[8], cv[8], sv[8];
   at_unpack8(*reinterpret_cast<const uint4*>(nw + 8 * l), wa);
   at_unpack8(*reinterpret_cast<const uint4*>(nw + 8 * l + D / 2), wb);
-  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]) + 8 * l), cv);
-  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]) + 8 * l), sv);
+  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]) + tab_off + 8 * l), cv);
+  at_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]) + tab_off + 8 * l), sv);
   float o0[8], o1[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -330,8 +330,10 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
     // rotation.  A row's D values sit in the four lanes of a quad; value d and its
     // partner d + D/2 are k-steps ks and ks + KS/2 of the same lane.
     const uint16_t* nw = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_QNW]);
-    const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]);
-    const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]);
+    // a device-resident position picks the table row (MK_AT_NEW_TOK then holds the row stride)
+    const int64_t tab_off = dyn ? (int64_t)c.ctrl->pos[u.b & 31] * op->i[MK_AT_NEW_TOK] : 0;
+    const uint16_t* cs = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_COS]) + tab_off;
+    const uint16_t* sn = reinterpret_cast<const uint16_t*>(op->p[MK_AT_P_SIN]) + tab_off;
     // the tables do not depend on q: request them first, so that they share q's round trip
     uint32_t tw0[KS / 2][2], tw1[KS / 2][2], tcs[KS / 2][2], tsn[KS / 2][2];
 #pragma unroll
@@ -400,7 +402,8 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
     const int tp0 = u.t_begin + p * tn;
     if (qknorm) {
       const int nt = dyn ? c.ctrl->pos[u.b & 31] : op->i[MK_AT_NEW_TOK];
-      if (nt >= tp0 && nt < tp0 + tn && nt < u.t_end) at_fix_k_row<D>(c, op, u, kpage, tn, nt - tp0, nt);
+      if (nt >= tp0 && nt < tp0 + tn && nt < u.t_end)
+        at_fix_k_row<D>(c, op, u, kpage, tn, nt - tp0, nt, dyn ? (int64_t)nt * op->i[MK_AT_NEW_TOK] : 0);
     }
     for (int blk = 0; blk * TN < tn; ++blk) {
       const int tb0 = tp0 + blk * TN;       // global token of column 0 of the block

@@ -70,7 +70,9 @@ class FlashDecodingSplitBSHDOp(Op):
     def schedule(cls, tile_sizes=None, causal=False, page_size=DEFAULT_PAGE_SIZE, kv_group_size=1,
                  num_splits=0, qk_norm=None, dynamic_len=False, **tensors):
         """``qk_norm`` (not in the reference's signature): ``dict(q_weight, k_weight, cos, sin, eps,
-        new_token)`` makes the op take UNROTATED q and an unrotated k row ``new_token`` and apply the
+        new_token)`` makes the op take UNROTATED q and an unrotated k row ``new_token`` (with
+        ``dynamic_len``: the row of the device-resident position; ``cos`` / ``sin`` are then the whole
+        ``(T, head_dim / 2)`` tables) and apply the
         per-head RMSNorm + split-half rotation itself (the reference schedules a separate
         ``QKNormRopeOp`` pass for that, src/machete/kernels/qwen_3_5/sm120.py:2986-2994); the finished
         k row is written back to the cache.  ``cos`` / ``sin`` are the ``(head_dim / 2,)`` table rows
@@ -124,11 +126,19 @@ class FlashDecodingSplitBSHDOp(Op):
                     raise ValueError(f"qk_norm[{name!r}] must be a contiguous, 16-byte aligned bf16 ({D},) tensor")
             for name in ("cos", "sin"):
                 r = qk_norm[name]
-                if r.dtype != torch.bfloat16 or r.numel() != D // 2 or r.stride(-1) != 1 or r.data_ptr() % 16:
+                if dynamic_len:
+                    # the token follows the device-resident position: the whole (T, head_dim / 2) table
+                    if r.dtype != torch.bfloat16 or r.ndim != 2 or r.shape[1] != D // 2 or r.stride(1) != 1 \
+                            or r.stride(0) % 8 or r.data_ptr() % 16 or r.shape[0] < N_kv:
+                        raise ValueError(f"qk_norm[{name!r}] must be the bf16 (>= {N_kv}, {D // 2}) table, 16-byte "
+                                         "aligned rows, when the window follows the cache position")
+                elif r.dtype != torch.bfloat16 or r.numel() != D // 2 or r.stride(-1) != 1 or r.data_ptr() % 16:
                     raise ValueError(f"qk_norm[{name!r}] must be the bf16 ({D // 2},) table row of the new token, "
                                      "16-byte aligned (full split-half rotation)")
-            if not 0 <= int(qk_norm["new_token"]) < N_kv:
+            if not dynamic_len and not 0 <= int(qk_norm["new_token"]) < N_kv:
                 raise ValueError("qk_norm['new_token'] must be a row of the cache window")
+            if dynamic_len and qk_norm["cos"].stride(0) != qk_norm["sin"].stride(0):
+                raise ValueError("qk_norm cos / sin tables must share their row stride")
             op.params["qk_norm"] = dict(qk_norm)
         return [op], o_partial, lse_partial
 
@@ -178,7 +188,9 @@ class FlashDecodingSplitBSHDOp(Op):
             op.pos_limit = int(k.shape[1])
         qkn = sop.params.get("qk_norm")
         if qkn is not None:
-            op.i[N.AT_QKNORM], op.i[N.AT_NEW_TOK] = 1, int(qkn["new_token"])
+            # with a device-resident position the slot carries the tables' row stride instead of the token
+            op.i[N.AT_QKNORM] = 1
+            op.i[N.AT_NEW_TOK] = int(qkn["cos"].stride(0)) if sop.static_dims.get("dynamic_len") else int(qkn["new_token"])
             op.f[N.AT_F_EPS] = float(qkn.get("eps", 1e-6))
             op.p.update({N.AT_P_QNW: qkn["q_weight"].data_ptr(), N.AT_P_KNW: qkn["k_weight"].data_ptr(),
                          N.AT_P_COS: qkn["cos"].data_ptr(), N.AT_P_SIN: qkn["sin"].data_ptr()})

@@ -84,12 +84,16 @@ class _RmsProjectionNvfp4Sm120Base(_Nvfp4Base):
 
     @classmethod
     def schedule(cls, tile_sizes=None, page_size=DEFAULT_PAGE_SIZE, eps=1e-5, cache_pos=0, group_size=32,
-                 head_dim=None, global_scale=1.0, **tensors):
+                 head_dim=None, global_scale=1.0, dynamic_pos=False, **tensors):
+        """``dynamic_pos`` (not in the reference): the cache row (and the RoPE table row) follow the
+        program's device-resident position; ``cos`` / ``sin`` are then the whole tables and
+        ``dst_cache`` the whole cache."""
         k = tensors["x"].shape[-1]
         _check_nvfp4(tensors["weight_packed"], tensors["weight_scales"], k, group_size)
         op = cls._schedule_single(tile_sizes=cls._tiles(tile_sizes, "O"), **tensors)
         op.static_dims["eps"] = eps
         op.static_dims["cache_pos"] = cache_pos
+        op.static_dims["dynamic_pos"] = int(bool(dynamic_pos))
         op.static_dims["head_dim"] = int(head_dim or tensors["cos"].shape[1] * 2)
         return _finalize(op, page_size=page_size, group_size=group_size, k_dim=k, global_scale=global_scale)
 
@@ -111,9 +115,15 @@ class _RmsProjectionNvfp4Sm120Base(_Nvfp4Base):
                 raise ValueError(f"{cls.__name__}: dst_cache must be (B, T > cache_pos, H, {hd})")
             kw.update(out=out, out_strides=(out.stride(0), out.stride(1), out.stride(2)), pos=pos)
         nop = lower_matvec(cls.__name__, ctx, kind="rms_proj", **kw)
+        dyn = bool(sop.static_dims.get("dynamic_pos", 0))
+        if dyn:
+            nop.i[N.MV_DYNPOS] = (N.MV_DYN_TABLES if cls.apply_rope else 0) | (N.MV_DYN_OUT if cls.write_cache else 0)
+            if cls.write_cache:
+                nop.pos_limit = int(t["dst_cache"].shape[1])
         if cls.write_cache:
             pos = int(sop.static_dims.get("cache_pos", 0))
-            nop.writes[-1].axis, nop.writes[-1].lo, nop.writes[-1].hi = 1, pos, pos + int(t["x"].shape[1])
+            hi = int(t["dst_cache"].shape[1]) if dyn else pos + int(t["x"].shape[1])
+            nop.writes[-1].axis, nop.writes[-1].lo, nop.writes[-1].hi = 1, pos, hi
             nop.kind = "cache_append"
         return [nop]
 

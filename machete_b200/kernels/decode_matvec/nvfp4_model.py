@@ -51,19 +51,32 @@ def _w(weights, key):
 def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, weights, k_cache, v_cache, x_in,
                                       residual_in, x_out, residual_out, q_buf, attn_out_buf, mlp_h_buf,
                                       page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0, num_q_heads=32,
-                                      num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True):
+                                      num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True,
+                                      dynamic_position=False):
     """One decoder layer with packed weights: ``DecodeLayerSchedule`` like the bf16 layer.
 
     ``fuse_qk_norm``: with q/k norm weights present, let the attention op apply the norm and the
-    rotation itself (one dependency stage less per layer) instead of scheduling ``QKNormRopeOp``."""
+    rotation itself (one dependency stage less per layer) instead of scheduling ``QKNormRopeOp``.
+    ``dynamic_position`` (not in the reference): the step follows the program's device-resident cache
+    position instead of ``cache_pos`` (see ``schedule_decode_layer_sm100``); a q/k-norm layer then needs
+    the fused form."""
     from ..attention.flash_decoding import flash_decoding_schedule
 
     pfx = f"layer.{layer_idx}"
-    cos = weights["cos"][cache_pos: cache_pos + seq_len]
-    sin = weights["sin"][cache_pos: cache_pos + seq_len]
+    if dynamic_position:
+        if seq_len != 1:
+            raise ValueError("a device-resident position decodes one token per sequence and step")
+        if weights["cos"].shape[0] < k_cache.shape[1]:
+            raise ValueError(f"RoPE tables hold {weights['cos'].shape[0]} positions, the cache {k_cache.shape[1]}")
+        cache_pos = 0
+        cos, sin = weights["cos"][:seq_len], weights["sin"][:seq_len]   # row 0: the kernel adds the position
+        k_window, v_window = k_cache, v_cache
+    else:
+        cos = weights["cos"][cache_pos: cache_pos + seq_len]
+        sin = weights["sin"][cache_pos: cache_pos + seq_len]
+        k_window = k_cache[:, : cache_pos + seq_len]
+        v_window = v_cache[:, : cache_pos + seq_len]
     q_4d = q_buf.view(batch, seq_len, num_q_heads, head_dim)
-    k_window = k_cache[:, : cache_pos + seq_len]
-    v_window = v_cache[:, : cache_pos + seq_len]
     o_4d = attn_out_buf.view(batch, seq_len, num_q_heads, head_dim)
 
     def proj(cls, key, **extra):
@@ -71,7 +84,7 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
         return cls.schedule(x=x_in, residual_in=residual_in, norm_weight=weights[f"{pfx}.attn_norm"], cos=cos, sin=sin,
                             weight_packed=w["packed"], weight_scales=w["scales"], group_size=w["group_size"],
                             global_scale=w["global_scale"], tile_sizes={"S": seq_len, "O": 16}, page_size=page_size,
-                            eps=eps, head_dim=head_dim, **extra)
+                            eps=eps, head_dim=head_dim, dynamic_pos=dynamic_position, **extra)
 
     ops, extra_keep, qk_norm = [], [], None
     if f"{pfx}.q_norm" in weights:
@@ -87,8 +100,13 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
         ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
         if fuse_qk_norm and seq_len == 1 and num_q_heads // num_kv_heads <= 16 and cos.shape[1] * 2 == head_dim:
             # the attention op normalises and rotates q and the new k row itself: no extra stage
-            qk_norm = dict(q_weight=weights[f"{pfx}.q_norm"], k_weight=weights[f"{pfx}.k_norm"], cos=cos[0], sin=sin[0],
-                           eps=eps, new_token=cache_pos)
+            qk_norm = dict(q_weight=weights[f"{pfx}.q_norm"], k_weight=weights[f"{pfx}.k_norm"], eps=eps,
+                           new_token=cache_pos,
+                           cos=weights["cos"] if dynamic_position else cos[0],
+                           sin=weights["sin"] if dynamic_position else sin[0])
+        elif dynamic_position:
+            raise ValueError("a device-resident position needs the fused q/k norm (one token per sequence, "
+                             "at most 16 query heads per KV head, full split-half rotation)")
         else:
             # row m = (b, s) of the (M, H, D) views takes the table row of token s
             cos_m, sin_m = cos.repeat(batch, 1), sin.repeat(batch, 1)
@@ -105,7 +123,8 @@ def schedule_decode_layer_nvfp4_sm100(*, layer_idx, batch, seq_len, cache_pos, w
         ops += proj(RmsVMatvecCacheNvfp4Sm120Op, "W_v", dst_cache=v_window, cache_pos=cache_pos)
     fa_ops, fa_config = flash_decoding_schedule(q=q_4d, k=k_window, v=v_window, o=o_4d,
                                                 kv_group_size=num_q_heads // num_kv_heads, page_size=page_size,
-                                                num_splits=fa_num_splits, qk_norm=qk_norm)
+                                                num_splits=fa_num_splits, qk_norm=qk_norm,
+                                                dynamic_len=dynamic_position)
     ops += fa_ops
     wo = _w(weights, f"{pfx}.W_o")
     if tp_peers is not None:
@@ -180,7 +199,7 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
                                       q_buf, attn_out_buf, mlp_h_buf, top_values, top_indices, num_layers, x_in,
                                       residual_in, seq_len=1, page_size=DEFAULT_PAGE_SIZE, eps=1e-6, fa_num_splits=0,
                                       num_q_heads=32, num_kv_heads=8, head_dim=128, tp_peers=None, fuse_qk_norm=True,
-                                      batch_chunk=None):
+                                      batch_chunk=None, position=None, embedding=None):
     """A full greedy decode step with packed weights: ``(ops, keep_alive)``.
 
     Layer ``i`` reads the pair (``x``, residual) it is given and writes the
@@ -188,12 +207,18 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
     reads ``x_in`` / ``residual_in`` so that the step can be re-launched.  The
     LM head is ``weights['lm_head.packed']`` / ``['lm_head.scales']``.  Under ``tp_peers`` the
     LM head is this rank's vocabulary shard and the ranks exchange their top-1 keys.
+
+    ``position`` (not in the reference; see ``schedule_decode_model_sm100``): a 1- or ``batch``-element
+    int32 CUDA tensor with the cache position of the token being decoded.  The program reads it at the
+    start of every launch (pass it as ``MegakernelConfig(position=...)`` too), copies the greedy token's
+    row of ``embedding`` (a ``(vocab, hidden)`` table of ``x_in``'s dtype: the packed LM head cannot
+    serve as one) into ``x_in`` and advances the position: one handle decodes consecutive tokens.
     """
     # ``batch_chunk`` (None = as many rows as one op can stage, 0 = never chunk): a batch whose
     # activations do not fit shared memory runs as interleaved chunks (kernels/_batching.py)
     if batch_chunk is None:
         batch_chunk = 0
-        if tp_peers is None:
+        if tp_peers is None and position is None:
             c = pick_batch_chunk(batch, seq_len, max(int(x_in.shape[-1]), num_q_heads * head_dim))
             batch_chunk = c if c < batch else 0
     if batch_chunk and batch_chunk < batch:
@@ -202,6 +227,12 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
         kw.pop("c", None)
         return schedule_in_batch_chunks(lambda **sub: schedule_decode_model_nvfp4_sm100(batch_chunk=0, **sub),
                                         batch_chunk, **kw)
+    dynamic = position is not None
+    if dynamic:
+        if seq_len != 1 or embedding is None:
+            raise ValueError("position= needs one token per step and the embedding table (embedding=)")
+        if position.numel() not in (1, batch):
+            raise ValueError(f"position must hold 1 or {batch} (= batch) elements, got {position.numel()}")
     ops, keep = [], []
     cur, cur_x, cur_r = 1, x_in, residual_in
     for layer_idx in range(num_layers):
@@ -211,7 +242,8 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
             k_cache=k_cache[layer_idx], v_cache=v_cache[layer_idx], x_in=cur_x, residual_in=cur_r,
             x_out=x_buffers[nxt], residual_out=residual_buffers[nxt], q_buf=q_buf, attn_out_buf=attn_out_buf,
             mlp_h_buf=mlp_h_buf, page_size=page_size, eps=eps, fa_num_splits=fa_num_splits, num_q_heads=num_q_heads,
-            num_kv_heads=num_kv_heads, head_dim=head_dim, tp_peers=tp_peers, fuse_qk_norm=fuse_qk_norm)
+            num_kv_heads=num_kv_heads, head_dim=head_dim, tp_peers=tp_peers, fuse_qk_norm=fuse_qk_norm,
+            dynamic_position=dynamic)
         ops += layer.ops
         keep += layer.keep_alive
         cur = nxt
@@ -220,7 +252,8 @@ def schedule_decode_model_nvfp4_sm100(*, batch, cache_pos, weights, k_cache, v_c
     ops += schedule_final_top1_sm100(x=cur_x, residual_in=cur_r, final_norm=weights["final_norm"], lm_head=lm["packed"],
                                      lm_head_scales=lm["scales"], group_size=lm["group_size"],
                                      global_scale=lm["global_scale"], top_values=top_values, top_indices=top_indices,
-                                     seq_len=seq_len, page_size=page_size, eps=eps, tp_peers=tp_peers)
+                                     seq_len=seq_len, page_size=page_size, eps=eps, tp_peers=tp_peers,
+                                     feedback=dict(embedding=embedding, x_in=x_in, position=position) if dynamic else None)
     return ops, keep
 
 

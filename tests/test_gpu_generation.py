@@ -222,3 +222,75 @@ def test_sequences_of_different_lengths_decode_side_by_side():
             top_values=tv, top_indices=ti, num_layers=L, x_in=x_in, residual_in=r0.to(dev),
             position=torch.zeros(2, dtype=torch.int32, device=dev),
             hidden_size=hidden, intermediate_size=inter, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+
+
+@pytest.mark.parametrize("qk_norm,B,seed", [(True, 1, 46), (True, 2, 52), (False, 1, 48)])
+def test_nvfp4_model_decodes_consecutive_tokens_from_one_handle(qk_norm, B, seed):
+    """The packed-weight model with a device-resident position (Qwen3 head geometry: head dim 128, q/k
+    RMSNorm + rotation inside the attention op, whose table row follows the position too): six tokens
+    from one handle against the oracle on the dequantised weights, step by step.  (The seeds are picked
+    so that no step has a near-tie between its two best logits.)"""
+    from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+    from machete_b200.quantization import dequantize_nvfp4_weight, quantize_nvfp4_weight
+
+    L, T, hidden, nq, nkv, hd, inter, vocab, start, steps = 2, 128, 1024, 8, 2, 128, 2048, 256, 29, 6
+    mats = ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=41, theta=1000000.0)
+    g = torch.Generator().manual_seed(seed)
+    emb = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF)
+    lm = (torch.randn(vocab, hidden, generator=g) * 0.05).to(BF)
+    fn = (1 + torch.randn(hidden, generator=g) * 0.02).to(BF)
+    dev = "cuda"
+    packed, deq = {"cos": w["cos"].to(dev), "sin": w["sin"].to(dev), "final_norm": fn.to(dev)}, dict(w)
+    for name, mat in [(f"layer.{l}.{m}", w[f"layer.{l}.{m}"]) for l in range(L) for m in mats] + [("lm_head", lm)]:
+        q = quantize_nvfp4_weight(mat, group_size=16)
+        packed[f"{name}.packed"], packed[f"{name}.scales"] = q.packed.to(dev), q.scales.to(dev)
+        packed[f"{name}.global_scale"] = float(q.global_scale)
+        deq[name] = dequantize_nvfp4_weight(q)
+    for l in range(L):
+        packed[f"layer.{l}.attn_norm"] = w[f"layer.{l}.attn_norm"].to(dev)
+        packed[f"layer.{l}.mlp_norm"] = w[f"layer.{l}.mlp_norm"].to(dev)
+        if qk_norm:
+            for nm in ("q_norm", "k_norm"):
+                deq[f"layer.{l}.{nm}"] = (1 + torch.randn(hd, generator=g) * 0.1).to(BF)
+                packed[f"layer.{l}.{nm}"] = deq[f"layer.{l}.{nm}"].to(dev)
+    kcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    vcs = [torch.randn(B, T, nkv, hd, generator=g).to(BF) for _ in range(L)]
+    kd, vd = [t.to(dev) for t in kcs], [t.to(dev) for t in vcs]
+    x0 = emb[torch.arange(B) + 7].view(B, 1, hidden).clone()
+    r0 = torch.zeros(B, 1, hidden, dtype=BF)
+    x_in = x0.to(dev)
+    # one position per sequence when there are two: they start two tokens apart
+    pos0 = [start + 2 * b for b in range(B)]
+    position = torch.tensor(pos0, dtype=torch.int32, device=dev)
+    tv, ti = torch.zeros(B, 1, device=dev), torch.zeros(B, 1, dtype=torch.int32, device=dev)
+    ops, _keep = schedule_decode_model_nvfp4_sm100(
+        batch=B, cache_pos=0, weights=packed, k_cache=kd, v_cache=vd,
+        x_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        residual_buffers=[torch.zeros(B, 1, hidden, dtype=BF, device=dev) for _ in range(2)],
+        q_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev), attn_out_buf=torch.zeros(B, 1, nq * hd, dtype=BF, device=dev),
+        mlp_h_buf=torch.zeros(B, 1, inter, dtype=BF, device=dev), top_values=tv, top_indices=ti, num_layers=L,
+        x_in=x_in, residual_in=r0.to(dev), num_q_heads=nq, num_kv_heads=nkv, head_dim=hd, eps=1e-6,
+        position=position, embedding=emb.to(dev))
+    mk = Megakernel(ops, config=MegakernelConfig(position=position), scheduler=OverlapTileScheduler())
+    x = x0.clone()
+    for step in range(steps):
+        mk.run()
+        assert position.cpu().tolist() == [p + step + 1 for p in pos0]
+        got = ti.cpu()
+        for b in range(B):      # the oracle takes one position: row by row
+            pos = pos0[b] + step
+            logits, _v, want_i = oracle.decode_model(
+                weights=deq, x=x[b:b + 1], residual=r0[b:b + 1], k_caches=[k[b:b + 1] for k in kcs],
+                v_caches=[v[b:b + 1] for v in vcs], cache_pos=pos, final_norm=fn, lm_head=deq["lm_head"], num_layers=L,
+                eps=1e-6, num_q_heads=nq, num_kv_heads=nkv, head_dim=hd)
+            bar = parity_bar(logits, roundings=2 * L)
+            top2 = logits.topk(2, dim=-1).values
+            assert float(top2[0, 0, 0] - top2[0, 0, 1]) > bar, "test input has a near-tie: pick another seed"
+            assert int(got[b, 0]) == int(want_i[0, 0]), f"step {step}, row {b}: token differs"
+            assert abs(float(tv[b, 0]) - float(logits[0, 0, int(got[b, 0])])) <= bar
+            for l in range(L):   # this position's K/V rows were appended (the oracle appended to its views)
+                assert float((kd[l][b, pos].cpu().float() - kcs[l][b, pos].float()).abs().max()) <= 2 * bar
+        x = emb[got[:, 0].long()].view(B, 1, hidden).clone()
+        assert torch.equal(x_in.cpu(), x)
+        assert mk.status()[0] == 0 and (mk.read_counters() == 0).all()
