@@ -305,7 +305,7 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     if constexpr (NTC >= 0) {
       if (op->opcode == MK_OP_MATVEC) {
         const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-        mv_stage<(NTC == 1 ? (WFC == 0 ? 1 : 2) : 4), (NTC == 1 && WFC != 0 ? 4 : 2), WFC>(c, op, need,
+        mv_stage<(NTC == 1 ? (WFC == 0 ? 1 : 2) : 4), (NTC == 1 ? 4 : 2), WFC>(c, op, need,
                                                                                                   (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
         staged_key = op->act_key;
       }
