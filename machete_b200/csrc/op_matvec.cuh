@@ -129,7 +129,7 @@ __device__ __forceinline__ bool mv_rstd_in_epilogue(const mk_op_t* op) {
 //   * no prologue, same type: the rows are copied global -> shared with
 //     16-byte asynchronous copies, all in flight at once;
 //   * RMSNorm prologue: R rows x H chunks per thread are requested together
-//     (one trip to L2), then reduced; R x H = 1 x 2 for the bf16 kernel of up to 8
+//     (one trip to L2), then reduced; R x H = 1 x 4 for the bf16 kernel of up to 8
 //     rows, 2 x 4 for its NVFP4 counterpart (K = 4096 in one trip), 4 x 2 otherwise.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
