@@ -500,6 +500,31 @@ def record_cfg4(args, dev, rank, world, use_dist, peak):
     return out
 
 
+def time_graph(fn, iters, dev, replays=5):
+    """``fn(i)`` for i in range(iters) captured into ONE CUDA graph (a single-op launch runs for a few
+    microseconds, less than the host side of the call takes), replayed ``replays`` times between CUDA
+    events: microseconds per launch."""
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize(dev)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(iters):
+            fn(i)
+    torch.cuda.synchronize(dev)
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / (replays * iters) * 1e3
+
+
 def rotating(make, nbytes, floor=3):
     """Enough independent copies of a small workload that consecutive launches miss in L2."""
     return [make(i) for i in range(max(floor, -(-2 * L2_BYTES // max(1, nbytes)) + 1))]
@@ -515,7 +540,8 @@ def record_cfg1(args, dev, peak):
 
     bf = torch.bfloat16
     shapes = [(M, N_, 4096) for M in (1, 4, 16) for N_ in (4096, 14336)] + [(16, 1024, 1024)]
-    out = {"l2": "launches rotate over weight copies totalling more than twice L2", "bf16": {}, "nvfp4": {}}
+    out = {"l2": "launches rotate over weight copies totalling more than twice L2; one CUDA graph of all launches",
+           "bf16": {}, "nvfp4": {}}
     for fmt in ("bf16", "nvfp4"):
         for (M, Nout, K) in shapes:
             g = torch.Generator(device=dev).manual_seed(7)
@@ -532,13 +558,12 @@ def record_cfg1(args, dev, peak):
                                                               group_size=16, global_scale=q.global_scale)).compile()
 
             mks = rotating(make, int(wbytes))
-            it = [0]
-
-            def launch():
-                mks[it[0] % len(mks)].run(sync=False, validate=False)
-                it[0] += 1
-
-            ms, blocks, _ = time_launches(launch, args.sub_steps, 5, dev, False, min_seconds=0.05)
+            # every replay walks all copies (more than twice L2) at least once
+            iters = len(mks) * -(-40 // len(mks))
+            us = time_graph(lambda i: mks[i % len(mks)].run(sync=False, validate=False), iters, dev)
+            for m_ in mks:
+                m_.wait()
+            ms = us * 1e-3
             alg = wbytes + M * K * 2 + M * Nout * 2
             out[fmt][f"{M}x{K}x{Nout}"] = {"us": ms * 1e3, "algorithmic_bytes": int(alg),
                                            "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak}
@@ -566,25 +591,7 @@ def record_gemm_sm100(args, dev, peak):
     iters = 40
 
     def timed(fn):
-        for i in range(3):
-            fn(i)
-        torch.cuda.synchronize(dev)
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(iters):
-                fn(i)
-        torch.cuda.synchronize(dev)
-        graph.replay()
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(5):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize(dev)
-        return e0.elapsed_time(e1) / (5 * iters) * 1e3
+        return time_graph(fn, iters, dev)
 
     for (Nout, K) in ((4096, 4096), (14336, 4096), (4096, 14336)):
         g = torch.Generator(device=dev).manual_seed(9)
