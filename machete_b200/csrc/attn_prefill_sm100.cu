@@ -37,6 +37,7 @@
 #include <stdio.h>
 
 #include <string>
+#include <type_traits>
 
 #include "../../include/machete_b200.h"
 #include "prims.cuh"
@@ -163,6 +164,38 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
   asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
+}
+// 2^x for two values on the FMA and integer pipes instead of the exp2 unit (16 results per clock and SM,
+// the scarce unit at head dim 64): x = n + f with n = round(x) by the 1.5 * 2^23 addition, f in [-0.5, 0.5];
+// 2^f by a cubic fitted here for the smallest maximal relative error (7.5e-5, far inside bf16's 2^-9), and
+// n added to the exponent field.  x <= 8 by construction; below -126 it is clamped (the result, ~1e-38,
+// rounds into nothing next to the row's maximum of at least 2^-8).
+// Measured at 32 heads x 4096 x 4096: head dim 64, every third pair of scores on this path, 113 -> 109 us
+// (every second: 114); head dim 128, where the tensor pipe is the bound, 131 -> 135 us: used at 64 only.
+#ifndef MK_PF_POLY
+#define MK_PF_POLY 3      /* head dim 64: every MK_PF_POLY-th pair of scores takes this path on unmasked tiles (0 = none) */
+#endif
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& e0, float& e1) {
+  float x0, x1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(x2));
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  uint64_t xc, r, t, f, pl;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(xc) : "f"(x0), "f"(x1));
+  const uint64_t magic = 0x4B4000004B400000ull, nmagic = 0xCB400000CB400000ull, neg1 = 0xBF800000BF800000ull;
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(xc), "l"(magic));
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(t) : "l"(r), "l"(nmagic));
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(f) : "l"(t), "l"(neg1), "l"(xc));
+  // Horner: ((c3 f + c2) f + c1) f + c0
+  const uint64_t c3 = 0x3D61FBB03D61FBB0ull, c2 = 0x3E786F0D3E786F0Dull, c1 = 0x3F31798D3F31798Dull, c0 = 0x3F7FFB493F7FFB49ull;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(pl) : "l"(c3), "l"(f), "l"(c2));
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(pl) : "l"(pl), "l"(f), "l"(c1));
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(pl) : "l"(pl), "l"(f), "l"(c0));
+  uint32_t p0, p1, r0, r1;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(p0), "=r"(p1) : "l"(pl));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(r0), "=r"(r1) : "l"(r));
+  e0 = __uint_as_float(p0 + (r0 << 23));
+  e1 = __uint_as_float(p1 + (r1 << 23));
 }
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t r;
@@ -399,16 +432,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const uint64_t ref2 = pack2(-muse, -muse);
       // P = exp2(s * scale - reference), two scores per multiply-add, add and conversion
       uint64_t tsum2 = pack2(0.f, 0.f);
+      auto p_pass = [&](auto mixed) {
 #pragma unroll
-      for (int i = 0; i < kBN; i += 2) {
-        float x0, x1;
-        unpack2(fma2(pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, ref2), x0, x1);
-        const float e0 = exp2f(x0), e1 = exp2f(x1);
-        const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
-        // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
-        tsum2 = add2(tsum2, pack2(e0, e1));
-        r[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-      }
+        for (int i = 0; i < kBN; i += 2) {
+          const uint64_t x2 = fma2(pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, ref2);
+          float e0, e1;
+          if (decltype(mixed)::value && ((i >> 1) % (MK_PF_POLY > 0 ? MK_PF_POLY : 1)) == 0) {   // compile-time pattern
+            exp2_poly2(x2, e0, e1);
+          } else {
+            float x0, x1;
+            unpack2(x2, x0, x1);
+            e0 = exp2f(x0);
+            e1 = exp2f(x1);
+          }
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+          // the row sum is taken before the rounding to bf16 (an unbiased 2^-9 relative error per term)
+          tsum2 = add2(tsum2, pack2(e0, e1));
+          r[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+      };
+      // masked tiles keep the exp2 unit for every score: exp2(-inf) is exactly 0 there
+      if (MK_PF_POLY > 0 && D == 64 && open)
+        p_pass(std::true_type{});
+      else
+        p_pass(std::false_type{});
       float t0, t1;
       unpack2(tsum2, t0, t1);
       sum += t0 + t1;
