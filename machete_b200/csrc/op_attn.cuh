@@ -524,9 +524,11 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
       for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     mrow[0] = mrow[1] = -INFINITY;
     lrow[0] = lrow[1] = 0.f;
+    // last page of participant j: the largest p = j (mod parts) below np — one division for all of them
+    const int lq = (np - 1) / parts, lr = (np - 1) - lq * parts;
 #pragma unroll 1
     for (int j = 0; j < parts; ++j) {
-      const int pl = j + ((np - 1 - j) / parts) * parts;   // last page of participant j
+      const int pl = j + (j <= lr ? lq : lq - 1) * parts;
       RingPos rj = ua.rp0;
       ring_advance(rj, pl, NPG);
       const uint32_t src = c.pages_u32 + rj.slot * (uint32_t)c.pv->page_bytes;
@@ -560,7 +562,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
     if (c.lane == 0) {
       fence_proxy_async();
       for (int j = 0; j < parts; ++j) {
-        const int pl = j + ((np - 1 - j) / parts) * parts;
+        const int pl = j + (j <= lr ? lq : lq - 1) * parts;
         RingPos rj = ua.rp0;
         ring_advance(rj, pl, NPG);
         mbar_arrive(empty_bar(c, rj.slot));
