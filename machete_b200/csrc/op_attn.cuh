@@ -117,7 +117,7 @@ __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, cons
     const int nr = min(RPP, rows - r0);
     const bool rv = row < nr;
     const int r = u.mt * 16 + r0 + (rv ? row : 0);
-    const int m = r / G, h = u.kvh * G + r % G;
+    const int m = M != 1 ? r / G : 0, h = u.kvh * G + (M != 1 ? r % G : r);
     const float* base = opart + ((((int64_t)u.b * H + h) * S) * M + m) * D + dch;
     const int64_t sstride = (int64_t)M * D;
     const float* ls = scratch + (rv ? row : 0) * S;
@@ -306,8 +306,9 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
   for (int e = 0; e < 2; ++e) {
     const int r = u.mt * 16 + g + 8 * e;
     rv[e] = r < M * G;
-    rm[e] = rv[e] ? r / G : 0;
-    rh[e] = u.kvh * G + (rv[e] ? r % G : 0);
+    // one token per sequence (decode): row r is head r of the group, no division
+    rm[e] = (rv[e] && M != 1) ? r / G : 0;
+    rh[e] = u.kvh * G + (rv[e] ? (M != 1 ? r % G : r) : 0);
   }
   // Q fragments (A operand), loaded straight from global.
   uint32_t qf[KS][4];
@@ -496,7 +497,8 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
 
   if (parts > 1) {
     // park (o, m, l) in the kept page: 16-byte record (i*32 + lane) holds o[i][0..3], the last one (m, m, l, l)
-    const uint32_t set = ord % (uint32_t)c.pv->mv_sets, gen = ord / (uint32_t)c.pv->mv_sets;
+    const int sets_log2 = __ffs(c.pv->mv_sets) - 1;                      // 1, 2 or 4 slot sets
+    const uint32_t set = ord & (uint32_t)(c.pv->mv_sets - 1), gen = ord >> sets_log2;
     if (!wait_smem_ge(c, &c.ctrl->mv_done[set], gen, (int)ord)) return false;
     __syncwarp();
 #pragma unroll
