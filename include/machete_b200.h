@@ -155,7 +155,10 @@ enum {
    * the fused q/k norm is p: MK_AT_P_COS / MK_AT_P_SIN then point at the whole
    * tables and MK_AT_NEW_TOK holds their row stride in elements (row p is
    * used). */
-  MK_AT_DYNPOS
+  MK_AT_DYNPOS,
+  /* query heads per KV head (H / Hkv): filled in by mk_create / mk_update_op, whatever the caller
+   * leaves here, so that the kernel does not divide */
+  MK_AT_GROUP
 };
 enum { MK_AT_F_SCALE = 0, MK_AT_F_EPS };
 enum {

@@ -154,6 +154,8 @@ static int encode_kv_map(CUtensorMap* out, uint64_t base, int D, int HKV, int N,
 }
 
 static int build_op_maps(mk_op_t& op, CUtensorMap* maps, uint64_t dev_maps, int page_bytes) {
+  if (op.opcode == MK_OP_ATTN_SPLIT || op.opcode == MK_OP_ATTN_COMBINE)
+    op.i[MK_AT_GROUP] = op.i[MK_AT_H] / op.i[MK_AT_HKV];   // validated: H a positive multiple of HKV
   if (op.opcode == MK_OP_ATTN_SPLIT) {
     const int D = op.i[MK_AT_D];
     const uint32_t tn = (uint32_t)at_page_tokens(D, page_bytes);

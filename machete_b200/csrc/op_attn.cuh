@@ -103,7 +103,7 @@ template <int D>
 __device__ __forceinline__ void at_combine_group(Ctx& c, const mk_op_t* op, const AtUnit& u) {
   constexpr int LPR = D / 8, RPP = 32 / LPR, UN = 9;
   const int M = op->i[MK_AT_M], H = op->i[MK_AT_H], HKV = op->i[MK_AT_HKV], S = op->i[MK_AT_SPLITS];
-  const int G = H / HKV;
+  const int G = op->i[MK_AT_GROUP];
   const float* opart = reinterpret_cast<const float*>(op->p[MK_AT_P_OPART]);
   const float* lpart = reinterpret_cast<const float*>(op->p[MK_AT_P_LSEPART]);
   float* lse_out = reinterpret_cast<float*>(op->p[MK_AT_P_LSE]);
@@ -290,7 +290,7 @@ __device__ __forceinline__ bool at_unit(Ctx& c, const mk_op_t* op, const UnitArg
   const int N = dyn ? min(op->i[MK_AT_N], c.ctrl->pos[u.b & 31] + M) : op->i[MK_AT_N];
   u.t_begin = min(u.t_begin, N);
   u.t_end = min(u.t_end, N);
-  const int G = H / HKV;
+  const int G = op->i[MK_AT_GROUP];
   const int S = op->i[MK_AT_SPLITS];
   const bool causal = op->i[MK_AT_CAUSAL] != 0;
   const float sc = op->f[MK_AT_F_SCALE];

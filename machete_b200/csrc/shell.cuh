@@ -420,7 +420,7 @@ __device__ __forceinline__ void ring_next(RingPos& r, int np) {
 __device__ __forceinline__ int at_dyn_pages(int t_begin, int limit, int tn, int n_tokens) {
   const int left = n_tokens - t_begin;
   if (left <= 0) return 0;
-  const int need = (left + tn - 1) / tn;
+  const int need = (left + tn - 1) >> (__ffs(tn) - 1);   // tn is 32 or 64 (at_page_tokens)
   return need < limit ? need : limit;
 }
 
