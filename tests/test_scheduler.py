@@ -291,3 +291,62 @@ def test_batch_chunks_interleave_groups_and_keep_chunks_independent():
         schedule_in_batch_chunks(schedule_decode_model_sm100, 5, **kw)
     with pytest.raises(ValueError):
         schedule_decode_model_sm100(**{**kw, "batch_chunk": 8, "position": torch.zeros(1, dtype=torch.int32)})
+
+
+def test_nvfp4_model_with_device_resident_position_lowers_and_simulates():
+    """`position=` on the packed-weight model: the cache-append ops and the attention op follow the
+    position (the fused q/k norm gets the whole rotation tables and their row stride), the final op
+    feeds the token back, the program still simulates to completion; the unfused q/k-norm pass and a
+    missing embedding table are refused."""
+    from machete_b200 import _native as N
+    from machete_b200.kernels.decode_matvec.nvfp4_model import schedule_decode_model_nvfp4_sm100
+    from machete_b200.quantization import quantize_nvfp4_weight
+
+    L, T, hidden, nq, nkv, hd, inter, vocab, B = 2, 96, 512, 4, 2, 128, 1024, 256, 2
+    w = llama_weights(L, hidden, inter, nq * hd, nkv * hd, hd // 2, T, seed=3)
+    packed = {"cos": w["cos"], "sin": w["sin"], "final_norm": torch.ones(hidden, dtype=BF)}
+    w["lm_head"] = (torch.randn(vocab, hidden) * 0.02).to(BF)
+    for name in [f"layer.{l}.{m}" for l in range(L) for m in ("W_q", "W_k", "W_v", "W_o", "W_gate", "W_up", "W_down")] \
+            + ["lm_head"]:
+        q = quantize_nvfp4_weight(w[name], group_size=16)
+        packed[f"{name}.packed"], packed[f"{name}.scales"], packed[f"{name}.global_scale"] = (
+            q.packed, q.scales, float(q.global_scale))
+    for l in range(L):
+        for nm in ("attn_norm", "mlp_norm"):
+            packed[f"layer.{l}.{nm}"] = w[f"layer.{l}.{nm}"]
+        packed[f"layer.{l}.q_norm"] = torch.ones(hd, dtype=BF)
+        packed[f"layer.{l}.k_norm"] = torch.ones(hd, dtype=BF)
+    z = lambda *s: torch.zeros(*s, dtype=BF)   # noqa: E731
+    position = torch.zeros(B, dtype=torch.int32)
+    emb = z(vocab, hidden)
+
+    def schedule(**kw):
+        return schedule_decode_model_nvfp4_sm100(
+            batch=B, cache_pos=0, weights=packed, k_cache=[z(B, T, nkv, hd) for _ in range(L)],
+            v_cache=[z(B, T, nkv, hd) for _ in range(L)], x_buffers=[z(B, 1, hidden), z(B, 1, hidden)],
+            residual_buffers=[z(B, 1, hidden), z(B, 1, hidden)], q_buf=z(B, 1, nq * hd), attn_out_buf=z(B, 1, nq * hd),
+            mlp_h_buf=z(B, 1, inter), top_values=torch.zeros(B, 1), top_indices=torch.zeros(B, 1, dtype=torch.int32),
+            num_layers=L, x_in=z(B, 1, hidden), residual_in=z(B, 1, hidden), num_q_heads=nq, num_kv_heads=nkv,
+            head_dim=hd, **kw)
+
+    ops, _keep = schedule(position=position, embedding=emb)
+    mk = Megakernel(ops, config=MegakernelConfig(num_sms=8, position=position), scheduler=OverlapTileScheduler())
+    attn = [o for o in mk.native_ops if o.name == "FlashDecodingFused"]
+    assert len(attn) == L
+    for o in attn:
+        assert o.i[N.AT_DYNPOS] == 1 and o.i[N.AT_QKNORM] == 1 and o.pos_limit == T
+        assert o.i[N.AT_NEW_TOK] == w["cos"].stride(0)                     # the tables' row stride, not a token
+        assert o.p[N.AT_P_COS] == w["cos"].data_ptr() and o.p[N.AT_P_SIN] == w["sin"].data_ptr()
+    appends = [o for o in mk.native_ops if o.kind == "cache_append"]
+    assert len(appends) == 2 * L
+    for o in appends:
+        assert o.i[N.MV_DYNPOS] == N.MV_DYN_OUT and o.pos_limit == T         # K and V stay unrotated here
+        assert (o.writes[-1].lo, o.writes[-1].hi) == (0, T)                  # any row may be the one written
+    final = simulate(mk.program)
+    assert (final == mk.program.counter_expected[:len(final)]).all()
+    with pytest.raises(ValueError, match="embedding"):
+        schedule(position=position)
+    with pytest.raises(ValueError, match="fused q/k norm"):
+        schedule(position=position, embedding=emb, fuse_qk_norm=False)
+    with pytest.raises(ValueError, match="position must hold"):
+        schedule(position=torch.zeros(B + 1, dtype=torch.int32), embedding=emb)
