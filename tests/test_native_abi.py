@@ -50,3 +50,29 @@ def test_host_errors_without_a_gpu():
     rc = lib.mk_create(None, ctypes.byref(handle))
     assert rc != 0 and b"null program" in lib.mk_last_error()
     assert lib.mk_run(None, None) != 0
+
+
+def test_public_calls_refuse_cpu_tensors():
+    """There is no CPU path behind the operator API: CPU tensors are refused with a message, and the
+    C entry points of the tensor-core kernels refuse bad arguments before touching a device."""
+    import pytest
+    import torch
+
+    from machete_b200.kernels.attention import flash_prefill
+    from machete_b200.kernels.gemm.gemm_sm100 import gemm_sm100
+
+    bf = torch.bfloat16
+    q = torch.zeros(1, 2, 128, 64, dtype=bf)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flash_prefill(q, q, q, torch.zeros_like(q))
+    with pytest.raises(ValueError, match="layout"):
+        flash_prefill(q, q, q, torch.zeros_like(q), layout="hbmd")
+    a, w, c = torch.zeros(1, 64, 256, dtype=bf), torch.zeros(128, 256, dtype=bf), torch.zeros(1, 64, 128, dtype=bf)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        gemm_sm100(a, w, c)
+    lib = N.lib()
+    strides = (ctypes.c_int64 * 3)(1, 1, 1)
+    rc = lib.mk_flash_prefill_bf16(None, None, None, None, None, 1, 1, 1, 1, 1, 64, strides, strides, strides, strides,
+                                   ctypes.c_float(1.0), 0, None, 0, 0, None)
+    assert rc != 0 and b"null pointer" in lib.mk_flash_prefill_last_error()
+    assert lib.mk_gemm_bf16_workspace_bytes(64, 4096, 4096, 4) > 0
