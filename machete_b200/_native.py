@@ -38,7 +38,7 @@ MV_F_EPS, MV_F_GSCALE, MV_F_GSCALE1 = range(3)
  MV_S_ER_B, MV_S_ER_S, MV_S_COS, MV_S_SCROW) = range(14)
 
 (AT_B, AT_M, AT_H, AT_HKV, AT_D, AT_N, AT_SPLITS, AT_CAUSAL, AT_MT, AT_TS, AT_O_T, AT_FUSE_COMBINE, AT_QKNORM,
- AT_NEW_TOK, AT_DYNPOS) = range(15)
+ AT_NEW_TOK, AT_DYNPOS, AT_GROUP) = range(16)      # AT_GROUP (H / Hkv) is filled in by the library
 AT_F_SCALE, AT_F_EPS = 0, 1
 (AT_P_Q, AT_P_K, AT_P_V, AT_P_OPART, AT_P_LSEPART, AT_P_O, AT_P_LSE, AT_P_ARRIVE, AT_P_QNW, AT_P_KNW, AT_P_COS,
  AT_P_SIN) = range(12)

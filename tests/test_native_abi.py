@@ -40,6 +40,10 @@ def test_enum_values_match_header():
                         ("MK_OP_TOP1_FINAL", N.OP_TOP1_FINAL)):
         assert re.search(rf"{name} = {value}\b", text), name
     assert f"#define MK_ABI_VERSION {N.ABI_VERSION}" in text
+    # the attention op's integer slots, in header order (the last one is filled in by the library)
+    slots = re.search(r"MK_AT_B = 0,(.*?)\};", text, re.S).group(1)
+    names = ["MK_AT_B"] + re.findall(r"\b(MK_AT_[A-Z0-9_]+)\b(?=\s*[,/\n}])", re.sub(r"/\*.*?\*/", "", slots, flags=re.S))
+    assert names[-2:] == ["MK_AT_DYNPOS", "MK_AT_GROUP"] and len(names) == N.AT_GROUP + 1 <= 24
 
 
 def test_host_errors_without_a_gpu():
