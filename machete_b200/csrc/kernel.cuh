@@ -305,8 +305,9 @@ __device__ void consumer_loop(Ctx& c, int ibeg, int iend, int ebeg, int eend) {
     if constexpr (NTC >= 0) {
       if (op->opcode == MK_OP_MATVEC) {
         const bool need = (op->act_key == 0) || (op->act_key != staged_key);
-        mv_stage<(NTC == 1 ? (WFC == 0 ? 1 : 2) : 4), (NTC == 1 ? 4 : 2), WFC>(c, op, need,
-                                                                                                  (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
+        // rows x chunks requested per thread and trip to L2 (see mv_stage)
+        constexpr int kStageRows = NTC == 1 ? (WFC == 0 ? 1 : 2) : 4, kStageChunks = NTC == 1 ? 4 : 2;
+        mv_stage<kStageRows, kStageChunks, WFC>(c, op, need, (e_flags & MK_EVF_WRITE_RES_OUT) != 0);
         staged_key = op->act_key;
       }
     }
