@@ -80,3 +80,17 @@ def test_public_calls_refuse_cpu_tensors():
                                    ctypes.c_float(1.0), 0, None, 0, 0, None)
     assert rc != 0 and b"null pointer" in lib.mk_flash_prefill_last_error()
     assert lib.mk_gemm_bf16_workspace_bytes(64, 4096, 4096, 4) > 0
+
+
+def test_a_missing_library_is_an_error_not_a_fallback(tmp_path):
+    """With no loadable native library the package refuses to work: there is no CPU path to fall back to."""
+    import os
+    import subprocess
+    import sys
+
+    code = ("import machete_b200._native as N\n"
+            "try:\n    N.lib()\nexcept RuntimeError as e:\n    print('refused:', str(e)[:60])\nelse:\n    print('loaded')\n")
+    env = dict(os.environ, MACHETE_B200_LIB=str(tmp_path / "no_such_library.so"))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         cwd=str(HEADER.parent.parent), timeout=300)
+    assert "refused: machete_b200: cannot load" in out.stdout, out.stdout + out.stderr
